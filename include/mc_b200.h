@@ -1,0 +1,143 @@
+/*
+ * mc_b200.h - C ABI of the sm_100a mapped-convolution kernels.
+ *
+ * Every entry point replaces one device-side driver of the reference project
+ * (meder411/MappedConvolutions); the reference file:line each one stands in for is cited
+ * beside its declaration (paths relative to package/ext_modules/).
+ *
+ * Conventions
+ *  - plain pointers and sizes only; all pointers are device pointers on the current CUDA device;
+ *  - every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL = legacy
+ *    default stream) and allocates nothing: outputs and scratch are provided by the caller;
+ *  - return value: MC_OK (0) or a negative MC_ERR_* code; mc_strerror() gives the text;
+ *    nothing throws, prints or exits;
+ *  - activations are (B, C, H, W) tensors; `layout` says how they lie in memory:
+ *    MC_NCHW (the reference's contiguous layout) or MC_NHWC (channels innermost);
+ *  - sample maps / interpolation weights keep the reference's layout:
+ *    map (OH, OW, K, [P,] 2) with (x, y) pairs, weights (OH, OW, K, P); their scalar type is
+ *    double when dtype == MC_F64 and float otherwise (also for MC_BF16 activations);
+ *  - interp: 0 nearest, 1 bilinear, 2 bispherical (x wraps), any other value = nearest
+ *    (include/core/resample.h:45-58).
+ */
+#ifndef MC_B200_H_
+#define MC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { MC_F32 = 0, MC_F64 = 1, MC_BF16 = 2 };
+enum { MC_NCHW = 0, MC_NHWC = 1 };
+
+enum {
+  MC_OK = 0,
+  MC_ERR_BAD_ARG = -1,      /* null pointer, non-positive size, unknown enum */
+  MC_ERR_UNSUPPORTED = -2,  /* valid request this build has no kernel for */
+  MC_ERR_WORKSPACE = -3,    /* scratch buffer missing or too small */
+  MC_ERR_LAUNCH = -4,       /* CUDA reported a launch / runtime error */
+  MC_ERR_DEVICE = -5,       /* kernel raised its device status word (bounded wait ran out) */
+  MC_ERR_TOO_LARGE = -6     /* size beyond a documented fixed limit */
+};
+
+/* Problem description shared by the conv / pool / resample entry points.
+ * B batch; C_in/C_out channels (pool and resample use C_in only);
+ * (IH, IW) size of the image that is *sampled*; (OH, OW) size of the map grid;
+ * K taps per map location (1 for resample); P interpolation points per tap, 0 = unweighted map. */
+typedef struct mc_desc {
+  int32_t B, C_in, C_out;
+  int32_t IH, IW, OH, OW;
+  int32_t K, P;
+  int32_t interp;
+  int32_t dtype;  /* MC_F32 / MC_F64 / MC_BF16 */
+  int32_t layout; /* MC_NCHW / MC_NHWC, applies to every activation tensor of the call */
+} mc_desc;
+
+const char* mc_strerror(int code);
+/* ABI version, bumped on any signature change. */
+int mc_abi_version(void);
+
+/* ---- mapped convolution ---------------------------------------------------------------
+ * weight (C_out, C_in, K) and bias (C_out) in `dtype`, contiguous. */
+
+/* y(B,C_out,OH,OW) = W . im2col_map(x) + bias.
+ * Replaces cuda::MappedConvForward, src/nn/cuda/mapped_convolution_layer.cu:16-73
+ * (weighted form: src/nn/cuda/weighted_mapped_convolution_layer.cu:16-75). bias may be NULL. */
+int mc_conv_fwd(const mc_desc* d, const void* x, const void* map, const void* iw, const void* w,
+                const void* bias, void* y, void* ws, size_t ws_bytes, void* stream);
+size_t mc_conv_fwd_workspace_bytes(const mc_desc* d);
+
+/* gx(B,C_in,IH,IW) = col2im_map(W^T . gy) [+ bias_out per channel of gx when bias_out != NULL,
+ * which is how the transposed convolution forward uses it].
+ * Replaces cuda::MappedConvBackwardInput, src/nn/cuda/mapped_convolution_layer.cu:75-132.
+ * gx is fully written (no need to pre-zero). */
+int mc_conv_dgrad(const mc_desc* d, const void* gy, const void* map, const void* iw, const void* w,
+                  const void* bias_out, void* gx, void* ws, size_t ws_bytes, void* stream);
+size_t mc_conv_dgrad_workspace_bytes(const mc_desc* d);
+
+/* gw(C_out,C_in,K) = sum_b gy_b . im2col_map(x_b)^T and gb(C_out) = sum_{b,h,w} gy.
+ * gw and gb are written in the accumulation type: double for MC_F64, float otherwise
+ * (also for MC_BF16), fully overwritten.  gb may be NULL.
+ * Replaces cuda::MappedConvBackwardWeight, src/nn/cuda/mapped_convolution_layer.cu:134-193 and
+ * grad_output.sum({0,2,3}), include/nn/layers/mapped_convolution_layer.h:113. */
+int mc_conv_wgrad(const mc_desc* d, const void* gy, const void* x, const void* map, const void* iw,
+                  void* gw, void* gb, void* ws, size_t ws_bytes, void* stream);
+size_t mc_conv_wgrad_workspace_bytes(const mc_desc* d);
+
+/* ---- mapped transposed convolution ----------------------------------------------------
+ * Here d->C_in / d->C_out are the transposed layer's own in/out channels, weight is
+ * (C_in, C_out, K), the map has the size of the layer *input* (d->OH, d->OW = input size) and
+ * points into the layer *output* (d->IH, d->IW = output size).
+ * Replace cuda::MappedTransposedConv{Forward,BackwardInput,BackwardWeight},
+ * src/nn/cuda/mapped_transposed_convolution_layer.cu:53-108, :110-160, :162-220. */
+int mc_tconv_fwd(const mc_desc* d, const void* x, const void* map, const void* iw, const void* w,
+                 const void* bias, void* y, void* ws, size_t ws_bytes, void* stream);
+int mc_tconv_dgrad(const mc_desc* d, const void* gy, const void* map, const void* iw,
+                   const void* w, void* gx, void* ws, size_t ws_bytes, void* stream);
+int mc_tconv_wgrad(const mc_desc* d, const void* gy, const void* x, const void* map,
+                   const void* iw, void* gw, void* gb, void* ws, size_t ws_bytes, void* stream);
+size_t mc_tconv_workspace_bytes(const mc_desc* d);
+
+/* ---- mapped pooling ---------------------------------------------------------------------
+ * x (B,C_in,IH,IW) -> y (B,C_in,OH,OW).  idx is int64, same shape/layout as y, and holds the
+ * element offset of the winning tap inside the sample map (first maximum wins, -1 if no tap
+ * compared greater than -FLT_MAX).
+ * Replace MappedMaxPool2DLauncher / MappedMaxUnpool2DLauncher, include/nn/cuda/mapped_max_pool.cuh:15-183
+ * and MappedAvgPool2DLauncher / MappedAvgUnpool2DLauncher, include/nn/cuda/mapped_avg_pool.cuh:15-169. */
+int mc_pool_max_fwd(const mc_desc* d, const void* x, const void* map, const void* iw, void* y,
+                    int64_t* idx, void* stream);
+/* gx (B,C_in,IH,IW) is fully written.  bf16 needs scratch (see the workspace query). */
+int mc_pool_max_bwd(const mc_desc* d, const void* gy, const int64_t* idx, const void* map,
+                    const void* iw, void* gx, void* ws, size_t ws_bytes, void* stream);
+int mc_pool_avg_fwd(const mc_desc* d, const void* x, const void* map, const void* iw, void* y,
+                    void* stream);
+int mc_pool_avg_bwd(const mc_desc* d, const void* gy, const void* map, const void* iw, void* gx,
+                    void* ws, size_t ws_bytes, void* stream);
+/* Scratch needed by the scatter-type kernels (pool backward, resample scatter). */
+size_t mc_scatter_workspace_bytes(const mc_desc* d);
+
+/* ---- resample ---------------------------------------------------------------------------
+ * gather  ("Unresample"): y(B,C,OH,OW)[p] = interp(x(B,C,IH,IW), map(OH,OW,[P,]2)[p]);
+ *   replaces ResampleFromMap2DLauncher, include/nn/cuda/resample.cuh:54-92 (+weighted :128-160).
+ * scatter ("Resample"):   y(B,C,IH,IW) += extrapolate(x(B,C,OH,OW)[q], map(OH,OW,[P,]2)[q]);
+ *   y is fully written (zero-filled first); replaces ResampleToMap2DLauncher, resample.cuh:14-52.
+ * In both calls (OH,OW) is the map grid and (IH,IW) the image the map points into; d->K must be 1. */
+int mc_resample_gather(const mc_desc* d, const void* x, const void* map, const void* iw, void* y,
+                       void* stream);
+int mc_resample_scatter(const mc_desc* d, const void* x, const void* map, const void* iw, void* y,
+                        void* ws, size_t ws_bytes, void* stream);
+
+/* ---- k nearest neighbours -----------------------------------------------------------------
+ * ref (B, D, M), query (B, D, N) float, contiguous.  idx (B, k, N) int64 holds 1-BASED reference
+ * indices, ordered by (distance, index); dist (B, k, N) the Euclidean distances.
+ * Replaces KNNLauncher, include/util/cuda/knn.cuh:232-275 and KNNForward,
+ * src/util/cuda/knn_layer.cu:13-32.  Limits: 1 <= k <= 32, k <= M, D <= 16. */
+int mc_knn(const float* ref, const float* query, int32_t B, int32_t D, int32_t M, int32_t N,
+           int32_t k, int64_t* idx, float* dist, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MC_B200_H_ */

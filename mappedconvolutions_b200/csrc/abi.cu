@@ -1,0 +1,147 @@
+// C-ABI entry points of the convolution family: argument checks and the choice between the
+// tensor-core (tcgen05) kernels and the generic CUDA-core kernels.
+#include "common.cuh"
+
+namespace mc {
+int check_conv_desc_public(const mc_desc* d);
+int conv_fwd_simt_launch(const mc_desc*, const void*, const void*, const void*, const void*,
+                         const void*, void*, cudaStream_t);
+size_t conv_dgrad_simt_ws(const mc_desc*);
+int conv_dgrad_simt_launch(const mc_desc*, const void*, const void*, const void*, const void*,
+                           const void*, void*, void*, size_t, cudaStream_t);
+int conv_wgrad_simt_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
+                           cudaStream_t);
+int bias_grad_launch(const mc_desc*, const void*, void*, cudaStream_t);
+
+// Tensor-core path (conv_tc.cu).  Each returns MC_ERR_UNSUPPORTED when the shape is not one it
+// takes, in which case the generic kernel runs instead.
+bool conv_tc_fwd_supported(const mc_desc*);
+int conv_tc_fwd_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
+                       cudaStream_t);
+bool conv_tc_dgrad_supported(const mc_desc*);
+size_t conv_tc_dgrad_ws(const mc_desc*);
+int conv_tc_dgrad_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
+                         void*, size_t, cudaStream_t);
+bool conv_tc_wgrad_supported(const mc_desc*);
+size_t conv_tc_wgrad_ws(const mc_desc*);
+int conv_tc_wgrad_launch(const mc_desc*, const void*, const void*, const void*, void*, void*, void*,
+                         size_t, cudaStream_t);
+}  // namespace mc
+
+using namespace mc;
+
+extern "C" {
+
+int mc_abi_version(void) { return 1; }
+
+const char* mc_strerror(int code) {
+  switch (code) {
+    case MC_OK: return "ok";
+    case MC_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size or unknown enum)";
+    case MC_ERR_UNSUPPORTED: return "unsupported configuration";
+    case MC_ERR_WORKSPACE: return "workspace missing or too small";
+    case MC_ERR_LAUNCH: return "CUDA launch or runtime error";
+    case MC_ERR_DEVICE: return "device-side status word raised (bounded wait ran out)";
+    case MC_ERR_TOO_LARGE: return "size beyond a fixed limit of this entry point";
+    default: return "unknown error code";
+  }
+}
+
+// ---- conv ----------------------------------------------------------------------------------
+
+size_t mc_conv_fwd_workspace_bytes(const mc_desc* d) { (void)d; return 0; }
+
+int mc_conv_fwd(const mc_desc* d, const void* x, const void* map, const void* iw, const void* w,
+                const void* bias, void* y, void* ws, size_t ws_bytes, void* stream) {
+  (void)ws; (void)ws_bytes;
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!x || !map || !w || !y || (d->P > 0 && !iw)) return MC_ERR_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (conv_tc_fwd_supported(d)) return conv_tc_fwd_launch(d, x, map, w, bias, y, st);
+  return conv_fwd_simt_launch(d, x, map, iw, w, bias, y, st);
+}
+
+size_t mc_conv_dgrad_workspace_bytes(const mc_desc* d) {
+  if (!d) return 0;
+  if (conv_tc_dgrad_supported(d)) return conv_tc_dgrad_ws(d);
+  return conv_dgrad_simt_ws(d);
+}
+
+int mc_conv_dgrad(const mc_desc* d, const void* gy, const void* map, const void* iw, const void* w,
+                  const void* bias_out, void* gx, void* ws, size_t ws_bytes, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!gy || !map || !w || !gx || (d->P > 0 && !iw)) return MC_ERR_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (conv_tc_dgrad_supported(d))
+    return conv_tc_dgrad_launch(d, gy, map, w, bias_out, gx, ws, ws_bytes, st);
+  return conv_dgrad_simt_launch(d, gy, map, iw, w, bias_out, gx, ws, ws_bytes, st);
+}
+
+size_t mc_conv_wgrad_workspace_bytes(const mc_desc* d) {
+  if (!d) return 0;
+  if (conv_tc_wgrad_supported(d)) return conv_tc_wgrad_ws(d);
+  return 0;
+}
+
+int mc_conv_wgrad(const mc_desc* d, const void* gy, const void* x, const void* map, const void* iw,
+                  void* gw, void* gb, void* ws, size_t ws_bytes, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!gy || !x || !map || !gw || (d->P > 0 && !iw)) return MC_ERR_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (conv_tc_wgrad_supported(d)) return conv_tc_wgrad_launch(d, gy, x, map, gw, gb, ws, ws_bytes, st);
+  rc = conv_wgrad_simt_launch(d, gy, x, map, iw, gw, st);
+  if (rc) return rc;
+  if (gb) rc = bias_grad_launch(d, gy, gb, st);
+  return rc;
+}
+
+// ---- transposed conv: the same three primitives with the roles of the tensors swapped --------
+// (design note of the reference: src/nn/cuda/mapped_transposed_convolution_layer.cu:17-51)
+
+static mc_desc swap_roles(const mc_desc* d) {
+  mc_desc s = *d;
+  s.C_in = d->C_out;  // the image that is sampled / scattered into has the layer's output channels
+  s.C_out = d->C_in;  // the tensor living on the map grid has the layer's input channels
+  return s;
+}
+
+size_t mc_tconv_workspace_bytes(const mc_desc* d) {
+  if (!d) return 0;
+  mc_desc s = swap_roles(d);
+  size_t a = mc_conv_dgrad_workspace_bytes(&s), b = mc_conv_wgrad_workspace_bytes(&s);
+  return a > b ? a : b;
+}
+
+int mc_tconv_fwd(const mc_desc* d, const void* x, const void* map, const void* iw, const void* w,
+                 const void* bias, void* y, void* ws, size_t ws_bytes, void* stream) {
+  if (!d) return MC_ERR_BAD_ARG;
+  mc_desc s = swap_roles(d);
+  // y = col2im(W.view(C_in, C_out*K)^T . x) + bias  == dgrad of a conv whose weight is W
+  return mc_conv_dgrad(&s, x, map, iw, w, bias, y, ws, ws_bytes, stream);
+}
+
+int mc_tconv_dgrad(const mc_desc* d, const void* gy, const void* map, const void* iw,
+                   const void* w, void* gx, void* ws, size_t ws_bytes, void* stream) {
+  if (!d) return MC_ERR_BAD_ARG;
+  mc_desc s = swap_roles(d);
+  // gx = W.view(C_in, C_out*K) . im2col(gy)  == forward of that conv applied to gy, no bias
+  return mc_conv_fwd(&s, gy, map, iw, w, nullptr, gx, ws, ws_bytes, stream);
+}
+
+int mc_tconv_wgrad(const mc_desc* d, const void* gy, const void* x, const void* map,
+                   const void* iw, void* gw, void* gb, void* ws, size_t ws_bytes, void* stream) {
+  if (!d) return MC_ERR_BAD_ARG;
+  mc_desc s = swap_roles(d);
+  // gw(C_in, C_out, K) = sum_b x_b . im2col(gy_b)^T : wgrad with x on the grid and gy sampled
+  int rc = mc_conv_wgrad(&s, x, gy, map, iw, gw, nullptr, ws, ws_bytes, stream);
+  if (rc || !gb) return rc;
+  // bias gradient = gy summed over batch and pixels; gy lives on the (IH, IW) image here
+  mc_desc b = *d;
+  b.OH = d->IH; b.OW = d->IW;
+  return bias_grad_launch(&b, gy, gb, (cudaStream_t)stream);
+}
+
+}  // extern "C"

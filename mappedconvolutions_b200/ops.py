@@ -1,0 +1,450 @@
+"""Operator surface of the reference's pybind modules, bound to the sm_100a C-ABI library.
+
+Function names, argument order and return values follow the reference's
+`_mapped_convolution_ext.<module>` functions (include/nn/layers/*.h, include/util/layers/knn_layer.h
+of the reference's package/ext_modules); each docstring cites the one it mirrors.  As in the
+reference, outputs are freshly allocated and returned, and inputs must be contiguous and on one
+device.  Differences: tensors must be CUDA tensors (there is no CPU path), bf16 activations are
+accepted (with a float32 sample map), and a 4-D activation may be channels_last, in which case
+the outputs are channels_last too.
+"""
+import torch
+
+from . import _lib
+from ._lib import McDesc, check, lib
+
+_DT = {torch.float32: _lib.MC_F32, torch.float64: _lib.MC_F64, torch.bfloat16: _lib.MC_BF16}
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts):
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("mapped convolution ops are CUDA only: got a CPU tensor "
+                               "(this build has no CPU path)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+    return dev
+
+
+def _layout(x):
+    if x.is_contiguous():
+        return _lib.MC_NCHW
+    if x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last):
+        return _lib.MC_NHWC
+    raise RuntimeError("input must be contiguous")
+
+
+def _as_layout(t, layout):
+    if layout == _lib.MC_NHWC:
+        return t.contiguous(memory_format=torch.channels_last)
+    return t.contiguous()
+
+
+def _empty(shape, like, layout, dtype=None):
+    fmt = torch.channels_last if layout == _lib.MC_NHWC else torch.contiguous_format
+    return torch.empty(shape, dtype=dtype or like.dtype, device=like.device, memory_format=fmt)
+
+
+def _map_args(x, sample_map, interp_weights):
+    """Checks the map / weights tensors; returns (map, weights-or-None)."""
+    want = torch.float64 if x.dtype == torch.float64 else torch.float32
+    if sample_map.dtype != want:
+        if x.dtype == torch.bfloat16 and sample_map.dtype == torch.bfloat16:
+            raise RuntimeError("sample map of a bfloat16 input must be float32")
+        raise RuntimeError("sample map dtype %s does not match input dtype %s"
+                           % (sample_map.dtype, x.dtype))
+    if not sample_map.is_contiguous():
+        raise RuntimeError("sample_map must be contiguous")
+    if interp_weights is not None:
+        if interp_weights.dtype != want:
+            raise RuntimeError("interp_weights dtype must match the sample map")
+        if not interp_weights.is_contiguous():
+            raise RuntimeError("interp_weights must be contiguous")
+    return sample_map, interp_weights
+
+
+def _desc(x_dtype, layout, B, C_in, C_out, IH, IW, OH, OW, K, P, interp):
+    if x_dtype not in _DT:
+        raise RuntimeError("unsupported dtype %s (float32, float64, bfloat16)" % x_dtype)
+    return McDesc(int(B), int(C_in), int(C_out), int(IH), int(IW), int(OH), int(OW), int(K), int(P),
+                  int(interp), _DT[x_dtype], layout)
+
+
+def _ws(nbytes, device):
+    if nbytes == 0:
+        return None, 0, None
+    t = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+    return t, int(nbytes), t.data_ptr()
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _P(interp_weights):
+    return 0 if interp_weights is None else int(interp_weights.shape[-1])
+
+
+# ------------------------------------------------------------------------------------------
+# convolution
+# ------------------------------------------------------------------------------------------
+
+def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, interpolation):
+    dev = _need_cuda(input, sample_map, interp_weights, weight, bias)
+    layout = _layout(input)
+    sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
+    if not weight.is_contiguous() or not bias.is_contiguous():
+        raise RuntimeError("weight and bias must be contiguous")
+    B, Cin, IH, IW = input.shape
+    Cout = weight.shape[0]
+    OH, OW = sample_map.shape[0], sample_map.shape[1]
+    d = _desc(input.dtype, layout, B, Cin, Cout, IH, IW, OH, OW, kernel_size, _P(interp_weights),
+              interpolation)
+    y = _empty((B, Cout, OH, OW), input, layout)
+    with torch.cuda.device(dev):
+        wst, wsn, wsp = _ws(lib().mc_conv_fwd_workspace_bytes(d), dev)
+        check(lib().mc_conv_fwd(d, input.data_ptr(), sample_map.data_ptr(), _ptr(interp_weights),
+                                weight.data_ptr(), bias.data_ptr(), y.data_ptr(), wsp, wsn,
+                                _stream()))
+    return y
+
+
+def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
+                   interpolation):
+    dev = _need_cuda(grad_output, sample_map, interp_weights, input, weight, bias)
+    layout = _layout(input)
+    grad_output = _as_layout(grad_output, layout)
+    sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
+    B, Cin, IH, IW = input.shape
+    Cout = weight.shape[0]
+    OH, OW = sample_map.shape[0], sample_map.shape[1]
+    d = _desc(input.dtype, layout, B, Cin, Cout, IH, IW, OH, OW, kernel_size, _P(interp_weights),
+              interpolation)
+    acc = torch.float64 if input.dtype == torch.float64 else torch.float32
+    gx = _empty(input.shape, input, layout)
+    gw = torch.empty(weight.shape, dtype=acc, device=dev)
+    gb = torch.empty((Cout,), dtype=acc, device=dev)
+    L = lib()
+    with torch.cuda.device(dev):
+        wst, wsn, wsp = _ws(max(L.mc_conv_dgrad_workspace_bytes(d),
+                                L.mc_conv_wgrad_workspace_bytes(d)), dev)
+        check(L.mc_conv_dgrad(d, grad_output.data_ptr(), sample_map.data_ptr(),
+                              _ptr(interp_weights), weight.data_ptr(), None, gx.data_ptr(), wsp, wsn,
+                              _stream()))
+        check(L.mc_conv_wgrad(d, grad_output.data_ptr(), input.data_ptr(), sample_map.data_ptr(),
+                              _ptr(interp_weights), gw.data_ptr(), gb.data_ptr(), wsp, wsn,
+                              _stream()))
+    return [gx, gw.to(weight.dtype), gb.to(bias.dtype)]
+
+
+def mapped_conv_forward(input, sample_map, weight, bias, kernel_size, interpolation):
+    """MappedConvForward, include/nn/layers/mapped_convolution_layer.h:64-88."""
+    return _conv_forward(input, sample_map, None, weight, bias, kernel_size, interpolation)
+
+
+def mapped_conv_backward(grad_output, sample_map, input, weight, bias, kernel_size, interpolation):
+    """MappedConvBackward, include/nn/layers/mapped_convolution_layer.h:90-135.
+    Returns [grad_input, grad_weight, grad_bias]."""
+    return _conv_backward(grad_output, sample_map, None, input, weight, bias, kernel_size,
+                          interpolation)
+
+
+def weighted_mapped_conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size,
+                                 interpolation):
+    """WeightedMappedConvForward, include/nn/layers/weighted_mapped_convolution_layer.h:65-93."""
+    return _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size,
+                         interpolation)
+
+
+def weighted_mapped_conv_backward(grad_output, sample_map, interp_weights, input, weight, bias,
+                                  kernel_size, interpolation):
+    """WeightedMappedConvBackward, include/nn/layers/weighted_mapped_convolution_layer.h:95-149."""
+    return _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias,
+                          kernel_size, interpolation)
+
+
+# ------------------------------------------------------------------------------------------
+# transposed convolution
+# ------------------------------------------------------------------------------------------
+
+def _tconv_forward(input, sample_map, interp_weights, weight, bias, output_height, output_width,
+                   kernel_size, interpolation):
+    dev = _need_cuda(input, sample_map, interp_weights, weight, bias)
+    layout = _layout(input)
+    sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
+    if not weight.is_contiguous() or not bias.is_contiguous():
+        raise RuntimeError("weight and bias must be contiguous")
+    B, Cin, H, W = input.shape
+    Cout = weight.shape[1]
+    d = _desc(input.dtype, layout, B, Cin, Cout, output_height, output_width, H, W, kernel_size,
+              _P(interp_weights), interpolation)
+    y = _empty((B, Cout, int(output_height), int(output_width)), input, layout)
+    L = lib()
+    with torch.cuda.device(dev):
+        wst, wsn, wsp = _ws(L.mc_tconv_workspace_bytes(d), dev)
+        check(L.mc_tconv_fwd(d, input.data_ptr(), sample_map.data_ptr(), _ptr(interp_weights),
+                             weight.data_ptr(), bias.data_ptr(), y.data_ptr(), wsp, wsn, _stream()))
+    return y
+
+
+def _tconv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
+                    interpolation):
+    dev = _need_cuda(grad_output, sample_map, interp_weights, input, weight, bias)
+    layout = _layout(input)
+    grad_output = _as_layout(grad_output, layout)
+    sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
+    B, Cin, H, W = input.shape
+    Cout = weight.shape[1]
+    OHt, OWt = grad_output.shape[2], grad_output.shape[3]
+    d = _desc(input.dtype, layout, B, Cin, Cout, OHt, OWt, H, W, kernel_size, _P(interp_weights),
+              interpolation)
+    acc = torch.float64 if input.dtype == torch.float64 else torch.float32
+    gx = _empty(input.shape, input, layout)
+    gw = torch.empty(weight.shape, dtype=acc, device=dev)
+    gb = torch.empty((Cout,), dtype=acc, device=dev)
+    L = lib()
+    with torch.cuda.device(dev):
+        wst, wsn, wsp = _ws(L.mc_tconv_workspace_bytes(d), dev)
+        check(L.mc_tconv_dgrad(d, grad_output.data_ptr(), sample_map.data_ptr(),
+                               _ptr(interp_weights), weight.data_ptr(), gx.data_ptr(), wsp, wsn,
+                               _stream()))
+        check(L.mc_tconv_wgrad(d, grad_output.data_ptr(), input.data_ptr(), sample_map.data_ptr(),
+                               _ptr(interp_weights), gw.data_ptr(), gb.data_ptr(), wsp, wsn,
+                               _stream()))
+    return [gx, gw.to(weight.dtype), gb.to(bias.dtype)]
+
+
+def mapped_transposed_conv_forward(input, sample_map, weight, bias, output_height, output_width,
+                                   kernel_size, interpolation):
+    """MappedTransposedConvForward, include/nn/layers/mapped_transposed_convolution_layer.h:64-92."""
+    return _tconv_forward(input, sample_map, None, weight, bias, output_height, output_width,
+                          kernel_size, interpolation)
+
+
+def mapped_transposed_conv_backward(grad_output, sample_map, input, weight, bias, kernel_size,
+                                    interpolation):
+    """MappedTransposedConvBackward, include/nn/layers/mapped_transposed_convolution_layer.h:94-143."""
+    return _tconv_backward(grad_output, sample_map, None, input, weight, bias, kernel_size,
+                           interpolation)
+
+
+def weighted_mapped_transposed_conv_forward(input, sample_map, interp_weights, weight, bias,
+                                            output_height, output_width, kernel_size,
+                                            interpolation):
+    """include/nn/layers/weighted_mapped_transposed_convolution_layer.h:66-98."""
+    return _tconv_forward(input, sample_map, interp_weights, weight, bias, output_height,
+                          output_width, kernel_size, interpolation)
+
+
+def weighted_mapped_transposed_conv_backward(grad_output, sample_map, interp_weights, input,
+                                             weight, bias, kernel_size, interpolation):
+    """include/nn/layers/weighted_mapped_transposed_convolution_layer.h:100-155."""
+    return _tconv_backward(grad_output, sample_map, interp_weights, input, weight, bias,
+                           kernel_size, interpolation)
+
+
+# ------------------------------------------------------------------------------------------
+# pooling
+# ------------------------------------------------------------------------------------------
+
+def _pool_desc(x, sample_map, interp_weights, kernel_size, interpolation, img_hw=None):
+    """Descriptor for pooling: x lives on the image for forward, on the map grid for backward."""
+    layout = _layout(x)
+    B, C = x.shape[0], x.shape[1]
+    OH, OW = sample_map.shape[0], sample_map.shape[1]
+    IH, IW = (x.shape[2], x.shape[3]) if img_hw is None else img_hw
+    return layout, _desc(x.dtype, layout, B, C, C, IH, IW, OH, OW, kernel_size, _P(interp_weights),
+                         interpolation)
+
+
+def _max_pool(input, sample_map, interp_weights, kernel_size, interpolation):
+    dev = _need_cuda(input, sample_map, interp_weights)
+    sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
+    layout, d = _pool_desc(input, sample_map, interp_weights, kernel_size, interpolation)
+    shape = (d.B, d.C_in, d.OH, d.OW)
+    y = _empty(shape, input, layout)
+    idx = _empty(shape, input, layout, dtype=torch.int64)
+    with torch.cuda.device(dev):
+        check(lib().mc_pool_max_fwd(d, input.data_ptr(), sample_map.data_ptr(),
+                                    _ptr(interp_weights), y.data_ptr(), idx.data_ptr(), _stream()))
+    return [y, idx]
+
+
+def _max_unpool(grad_output, idx_mask, sample_map, interp_weights, input_height, input_width,
+                kernel_size, interpolation):
+    dev = _need_cuda(grad_output, idx_mask, sample_map, interp_weights)
+    layout = _layout(idx_mask) if idx_mask.dim() == 4 else _lib.MC_NCHW
+    grad_output = _as_layout(grad_output, layout)
+    sample_map, interp_weights = _map_args(grad_output, sample_map, interp_weights)
+    IH, IW = int(input_height), int(input_width)
+    _, d = _pool_desc(grad_output, sample_map, interp_weights, kernel_size, interpolation, (IH, IW))
+    gx = _empty((d.B, d.C_in, IH, IW), grad_output, layout)
+    L = lib()
+    with torch.cuda.device(dev):
+        wst, wsn, wsp = _ws(L.mc_scatter_workspace_bytes(d), dev)
+        check(L.mc_pool_max_bwd(d, grad_output.data_ptr(), idx_mask.data_ptr(),
+                                sample_map.data_ptr(), _ptr(interp_weights), gx.data_ptr(), wsp,
+                                wsn, _stream()))
+    return gx
+
+
+def _avg_pool(input, sample_map, interp_weights, kernel_size, interpolation):
+    dev = _need_cuda(input, sample_map, interp_weights)
+    sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
+    layout, d = _pool_desc(input, sample_map, interp_weights, kernel_size, interpolation)
+    y = _empty((d.B, d.C_in, d.OH, d.OW), input, layout)
+    with torch.cuda.device(dev):
+        check(lib().mc_pool_avg_fwd(d, input.data_ptr(), sample_map.data_ptr(),
+                                    _ptr(interp_weights), y.data_ptr(), _stream()))
+    return y
+
+
+def _avg_unpool(grad_output, sample_map, interp_weights, input_height, input_width, kernel_size,
+                interpolation):
+    dev = _need_cuda(grad_output, sample_map, interp_weights)
+    layout = _layout(grad_output)
+    sample_map, interp_weights = _map_args(grad_output, sample_map, interp_weights)
+    IH, IW = int(input_height), int(input_width)
+    _, d = _pool_desc(grad_output, sample_map, interp_weights, kernel_size, interpolation, (IH, IW))
+    gx = _empty((d.B, d.C_in, IH, IW), grad_output, layout)
+    L = lib()
+    with torch.cuda.device(dev):
+        wst, wsn, wsp = _ws(L.mc_scatter_workspace_bytes(d), dev)
+        check(L.mc_pool_avg_bwd(d, grad_output.data_ptr(), sample_map.data_ptr(),
+                                _ptr(interp_weights), gx.data_ptr(), wsp, wsn, _stream()))
+    return gx
+
+
+def mapped_max_pool(input, sample_map, kernel_size, interpolation):
+    """MappedMaxPoolForward, include/nn/layers/mapped_max_pooling_layer.h:46-71 -> [out, idx]."""
+    return _max_pool(input, sample_map, None, kernel_size, interpolation)
+
+
+def mapped_max_unpool(grad_output, idx_mask, sample_map, input_height, input_width, kernel_size,
+                      interpolation):
+    """MappedMaxPoolBackward, include/nn/layers/mapped_max_pooling_layer.h:73-98."""
+    return _max_unpool(grad_output, idx_mask, sample_map, None, input_height, input_width,
+                       kernel_size, interpolation)
+
+
+def weighted_mapped_max_pool(input, sample_map, interp_weights, kernel_size, interpolation):
+    """include/nn/layers/weighted_mapped_max_pooling_layer.h:42-70."""
+    return _max_pool(input, sample_map, interp_weights, kernel_size, interpolation)
+
+
+def weighted_mapped_max_unpool(grad_output, idx_mask, sample_map, interp_weights, input_height,
+                               input_width, kernel_size, interpolation):
+    """include/nn/layers/weighted_mapped_max_pooling_layer.h:72-101."""
+    return _max_unpool(grad_output, idx_mask, sample_map, interp_weights, input_height,
+                       input_width, kernel_size, interpolation)
+
+
+def mapped_avg_pool(input, sample_map, kernel_size, interpolation):
+    """MappedAvgPoolForward, include/nn/layers/mapped_avg_pooling_layer.h:42-64."""
+    return _avg_pool(input, sample_map, None, kernel_size, interpolation)
+
+
+def mapped_avg_unpool(grad_output, sample_map, input_height, input_width, kernel_size,
+                      interpolation):
+    """MappedAvgPoolBackward, include/nn/layers/mapped_avg_pooling_layer.h:66-88."""
+    return _avg_unpool(grad_output, sample_map, None, input_height, input_width, kernel_size,
+                       interpolation)
+
+
+def weighted_mapped_avg_pool(input, sample_map, interp_weights, kernel_size, interpolation):
+    """include/nn/layers/weighted_mapped_avg_pooling_layer.h:45-72."""
+    return _avg_pool(input, sample_map, interp_weights, kernel_size, interpolation)
+
+
+def weighted_mapped_avg_unpool(grad_output, sample_map, interp_weights, input_height, input_width,
+                               kernel_size, interpolation):
+    """include/nn/layers/weighted_mapped_avg_pooling_layer.h:74-107."""
+    return _avg_unpool(grad_output, sample_map, interp_weights, input_height, input_width,
+                       kernel_size, interpolation)
+
+
+# ------------------------------------------------------------------------------------------
+# resample
+# ------------------------------------------------------------------------------------------
+
+def _resample_to_map(input, sample_map, interp_weights, output_height, output_width,
+                     interpolation):
+    dev = _need_cuda(input, sample_map, interp_weights)
+    layout = _layout(input)
+    sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
+    B, C, H, W = input.shape
+    OH, OW = int(output_height), int(output_width)
+    d = _desc(input.dtype, layout, B, C, C, OH, OW, H, W, 1, _P(interp_weights), interpolation)
+    y = _empty((B, C, OH, OW), input, layout)
+    L = lib()
+    with torch.cuda.device(dev):
+        wst, wsn, wsp = _ws(L.mc_scatter_workspace_bytes(d), dev)
+        check(L.mc_resample_scatter(d, input.data_ptr(), sample_map.data_ptr(),
+                                    _ptr(interp_weights), y.data_ptr(), wsp, wsn, _stream()))
+    return y
+
+
+def _resample_from_map(input, sample_map, interp_weights, interpolation):
+    dev = _need_cuda(input, sample_map, interp_weights)
+    layout = _layout(input)
+    sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
+    B, C, H, W = input.shape
+    OH, OW = sample_map.shape[0], sample_map.shape[1]
+    d = _desc(input.dtype, layout, B, C, C, H, W, OH, OW, 1, _P(interp_weights), interpolation)
+    y = _empty((B, C, OH, OW), input, layout)
+    with torch.cuda.device(dev):
+        check(lib().mc_resample_gather(d, input.data_ptr(), sample_map.data_ptr(),
+                                       _ptr(interp_weights), y.data_ptr(), _stream()))
+    return y
+
+
+def resample_to_map(input, sample_map, output_height, output_width, interpolation):
+    """ResampleToMap (scatter), include/nn/layers/resample_layer.h:38-60."""
+    return _resample_to_map(input, sample_map, None, output_height, output_width, interpolation)
+
+
+def resample_from_map(input, sample_map, interpolation):
+    """ResampleFromMap (gather), include/nn/layers/resample_layer.h:62-80."""
+    return _resample_from_map(input, sample_map, None, interpolation)
+
+
+def weighted_resample_to_map(input, sample_map, interp_weights, output_height, output_width,
+                             interpolation):
+    """include/nn/layers/weighted_resample_layer.h:49-77."""
+    return _resample_to_map(input, sample_map, interp_weights, output_height, output_width,
+                            interpolation)
+
+
+def weighted_resample_from_map(input, sample_map, interp_weights, interpolation):
+    """include/nn/layers/weighted_resample_layer.h:79-103."""
+    return _resample_from_map(input, sample_map, interp_weights, interpolation)
+
+
+# ------------------------------------------------------------------------------------------
+# knn
+# ------------------------------------------------------------------------------------------
+
+def knn_forward(ref, query, k):
+    """KNNForward, include/util/layers/knn_layer.h:25-35 -> [idx (B,k,N) int64 1-based, dist]."""
+    dev = _need_cuda(ref, query)
+    if not ref.is_contiguous() or not query.is_contiguous():
+        raise RuntimeError("ref and query must be contiguous")
+    if ref.dtype != torch.float32 or query.dtype != torch.float32:
+        raise RuntimeError("knn works on float32 points")
+    B, D, M = ref.shape
+    N = query.shape[2]
+    idx = torch.empty((B, k, N), dtype=torch.int64, device=dev)
+    dist = torch.empty((B, k, N), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().mc_knn(ref.data_ptr(), query.data_ptr(), B, D, M, N, int(k), idx.data_ptr(),
+                           dist.data_ptr(), _stream()))
+    return [idx, dist]
