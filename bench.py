@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Benchmark of the mapped-convolution hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (one "step"): spherical mapped convolution forward + backward (input gradient, weight
+gradient, bias gradient) on an equirectangular 512 x 1024 image, batch 8 per GPU, 64 -> 64
+channels, bf16 activations with fp32 accumulation, 3 x 3 gnomonic kernel (K = 9), bilinear
+interpolation, N(0,1) synthetic data, channels-last activations.
+
+Metric: algorithmic TFLOP/s = 3 GEMMs x 2 * B*OH*OW*Cout*Cin*K per step (interpolation flops not
+counted), whole job over all GPUs, device time (CUDA events, max over ranks).
+
+  value        inputs resident in HBM when the timed region starts
+  e2e          same step through the public layer API with HOST (pinned) buffers: x and the
+               upstream gradient are copied in and y, grad_x, grad_w, grad_b are copied out inside
+               the timed region
+  roofline     the slowest kernel family of the step, timed alone with CUDA events
+  cpu_baseline the reference's own CPU extension (or, if it is not built, the C port of it) on
+               one batch element of the same workload, on the host's cores
+
+With N > 1 (torchrun) every rank runs the same per-GPU batch (weak scaling) and the weight / bias
+gradients are all-reduced over NCCL, the only exchange the path has.
+
+--impl reference times the reference's CPU implementation alone (rank 0 only).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, W, KH, KW = 512, 1024, 3, 3
+CIN = COUT = 64
+K = KH * KW
+BATCH = 8  # per GPU
+
+
+def flops_per_step(batch):
+    return 3 * 2.0 * batch * H * W * COUT * CIN * K
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.th.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(batch, seed):
+    import torch
+    from mappedconvolutions_b200.util import get_projection_map
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    x = torch.randn(batch, CIN, H, W, generator=g).to(bf).contiguous(memory_format=torch.channels_last)
+    gy = torch.randn(batch, COUT, H, W, generator=g).to(bf).contiguous(memory_format=torch.channels_last)
+    w = torch.randn(COUT, CIN, K, generator=g).to(bf)
+    b = torch.randn(COUT, generator=g).to(bf)
+    m = get_projection_map((H, W), (KH, KW), "gnomonic")
+    return x, gy, w, b, m
+
+
+# ---------------------------------------------------------------------------------------------
+# reference / CPU arm
+# ---------------------------------------------------------------------------------------------
+def cpu_ops():
+    """-> (ops namespace, kind).  The reference's own CPU build if present, else the C port."""
+    from oracle import ref
+    if ref.available():
+        return ref.ops(), "reference"
+    from oracle import oracle
+    return oracle, "port"
+
+
+def cpu_step(O, x, gy, w, b, m):
+    y = O.mapped_conv_forward(x, m, w, b, K, 1)
+    g = O.mapped_conv_backward(gy, m, x, w, b, K, 1)
+    return y, g
+
+
+def cpu_baseline(reps=1, warm=0):
+    """fp32 forward + backward of ONE batch element of the workload on the host cores."""
+    import torch
+    O, kind = cpu_ops()
+    x, gy, w, b, m = make_inputs(1, 1)
+    x, gy, w, b = [t.float().contiguous() for t in (x, gy, w, b)]
+    for _ in range(warm):
+        cpu_step(O, x, gy, w, b, m)
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        cpu_step(O, x, gy, w, b, m)
+        ts.append(time.perf_counter() - t0)
+    t = statistics.median(ts)
+    return dict(value=flops_per_step(1) / t / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(),
+                kind=kind, sample="1 of 8 batch elements, fp32 on bf16-rounded inputs, fwd+bwd, "
+                "median of %d run(s), %.2f s per run" % (reps, t)), t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    O, kind = cpu_ops()
+    x, gy, w, b, m = make_inputs(1, 1)
+    x, gy, w, b = [t.float().contiguous() for t in (x, gy, w, b)]
+    for _ in range(args.warmup):
+        cpu_step(O, x, gy, w, b, m)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(O, x, gy, w, b, m)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = flops_per_step(1) / dt / 1e12
+    sample = "each step = 1 of the 8 batch elements of the workload, fp32 on bf16-rounded inputs"
+    print(json.dumps({
+        "impl": "reference", "metric": "mapped-conv fwd+bwd TFLOP/s", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "config2: spherical mapped conv fwd+bwd 512x1024, 64->64, K=9 gnomonic, "
+                               "bilinear; CPU sample of batch 1"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+# ---------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from mappedconvolutions_b200 import _lib, ops
+    from mapped_convolution.nn import MappedConvolution
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+
+    xh, gyh, w, b, m = make_inputs(BATCH, 1000 + rank)
+    x, gy, w, b, m = [t.to(dev) for t in (xh, gyh, w, b, m)]
+    x = x.contiguous(memory_format=torch.channels_last)
+    gy = gy.contiguous(memory_format=torch.channels_last)
+
+    def step():
+        y = ops.mapped_conv_forward(x, m, w, b, K, 1)
+        gx, gw, gb = ops.mapped_conv_backward(gy, m, x, w, b, K, 1)
+        if world > 1:
+            bucket = torch.cat([gw.float().view(-1), gb.float().view(-1)])
+            dist.all_reduce(bucket)
+        return y, gx, gw, gb
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    n0 = L.mc_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    launches = L.mc_kernel_launch_count() - n0
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    ms_step = ms / args.steps
+    value = world * flops_per_step(BATCH) / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the layer API with host buffers -------------------------------
+    layer = MappedConvolution(CIN, COUT, K, "bilinear").to(torch.bfloat16).to(dev)
+    with torch.no_grad():
+        layer.weight.copy_(w)
+        layer.bias.copy_(b)
+    xp, gyp = xh.pin_memory(), gyh.pin_memory()
+    outs = dict(y=torch.empty_like(gyh).pin_memory(), gx=torch.empty_like(xh).pin_memory(),
+                gw=torch.empty(COUT, CIN, K, dtype=torch.bfloat16).pin_memory(),
+                gb=torch.empty(COUT, dtype=torch.bfloat16).pin_memory())
+    h2d = xp.numel() * 2 + gyp.numel() * 2
+    d2h = sum(t.numel() * t.element_size() for t in outs.values())
+
+    def e2e_step():
+        xd = xp.to(dev, non_blocking=True).requires_grad_(True)
+        gd = gyp.to(dev, non_blocking=True)
+        layer.zero_grad(set_to_none=True)
+        y = layer(xd, m)
+        y.backward(gd)
+        if world > 1:
+            bucket = torch.cat([layer.weight.grad.float().view(-1), layer.bias.grad.float().view(-1)])
+            dist.all_reduce(bucket)
+        outs["y"].copy_(y.detach(), non_blocking=True)
+        outs["gx"].copy_(xd.grad, non_blocking=True)
+        outs["gw"].copy_(layer.weight.grad, non_blocking=True)
+        outs["gb"].copy_(layer.bias.grad, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e = t.item()
+    e2e_val = world * flops_per_step(BATCH) / (ms_e / e2e_steps * 1e-3) / 1e12
+
+    # ---- per-kernel timing for the roofline (rank 0, each family alone) ---------------------
+    roof = cpu = None
+    if rank == 0:
+        def timed(fn, n=5):
+            fn()
+            torch.cuda.synchronize()
+            a, c = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            c.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(c) / n
+
+        d = _lib.McDesc(BATCH, CIN, COUT, H, W, H, W, K, 0, 1, _lib.MC_BF16, _lib.MC_NHWC)
+        st = torch.cuda.current_stream().cuda_stream
+        y = torch.empty_like(gy)
+        gx = torch.empty_like(x)
+        gw = torch.empty(COUT, CIN, K, dtype=torch.float32, device=dev)
+        gb = torch.empty(COUT, dtype=torch.float32, device=dev)
+        nws = max(L.mc_conv_dgrad_workspace_bytes(d), L.mc_conv_wgrad_workspace_bytes(d), 16)
+        ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+        fam = {
+            "conv_fwd": lambda: _lib.check(L.mc_conv_fwd(d, x.data_ptr(), m.data_ptr(), None, w.data_ptr(), b.data_ptr(), y.data_ptr(), ws.data_ptr(), nws, st)),
+            "conv_dgrad": lambda: _lib.check(L.mc_conv_dgrad(d, gy.data_ptr(), m.data_ptr(), None, w.data_ptr(), None, gx.data_ptr(), ws.data_ptr(), nws, st)),
+            "conv_wgrad": lambda: _lib.check(L.mc_conv_wgrad(d, gy.data_ptr(), x.data_ptr(), m.data_ptr(), None, gw.data_ptr(), gb.data_ptr(), ws.data_ptr(), nws, st)),
+        }
+        times = {k: timed(f) for k, f in fam.items()}
+        top = max(times, key=times.get)
+        pk = peaks()
+        gemm_flops = flops_per_step(BATCH) / 3
+        ach = gemm_flops / (times[top] * 1e-3) / 1e12
+        traffic = None
+        tp = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tp):
+            traffic = json.load(open(tp)).get(top)
+        roof = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": pk["bf16"],
+                "unit": "TFLOP/s", "frac": ach / pk["bf16"], "traffic": traffic,
+                "peak_source": pk["source"] + " burst bf16 (kernel timed alone)",
+                "ms_per_launch": {k: round(v, 4) for k, v in times.items()},
+                "tflops": {k: round(gemm_flops / (v * 1e-3) / 1e12, 2) for k, v in times.items()}}
+        if not args.no_cpu:
+            cpu, _ = cpu_baseline()
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "mapped-conv fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "config2: spherical mapped conv fwd+bwd, equirect 512x1024, batch 8 "
+                                   "per GPU, 64->64 ch, K=9 gnomonic map, bilinear, channels-last",
+                       "l2": "inputs (537 MB per activation tensor) are larger than L2",
+                       "parallelism": "batch-sharded dp%d, NCCL allreduce of grad_w/grad_b" % world},
+            "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e / e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": roof, "cpu_baseline": cpu}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -58,6 +58,9 @@ typedef struct mc_desc {
 const char* mc_strerror(int code);
 /* ABI version, bumped on any signature change. */
 int mc_abi_version(void);
+/* Diagnostic: kernels launched by this library so far in this process (no counterpart in the
+ * reference; used by the benchmark to report its launch count). */
+uint64_t mc_kernel_launch_count(void);
 
 /* ---- mapped convolution ---------------------------------------------------------------
  * weight (C_out, C_in, K) and bias (C_out) in `dtype`, contiguous. */

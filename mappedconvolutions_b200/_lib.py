@@ -31,6 +31,7 @@ _dp = ctypes.POINTER(McDesc)
 SIGNATURES = {
     "mc_strerror": (ctypes.c_char_p, [ctypes.c_int]),
     "mc_abi_version": (ctypes.c_int, []),
+    "mc_kernel_launch_count": (ctypes.c_uint64, []),
     "mc_conv_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_fwd_workspace_bytes": (_sz, [_dp]),
     "mc_conv_dgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

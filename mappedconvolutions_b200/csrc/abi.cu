@@ -28,11 +28,16 @@ int conv_tc_wgrad_launch(const mc_desc*, const void*, const void*, const void*, 
                          size_t, cudaStream_t);
 }  // namespace mc
 
+namespace mc {
+unsigned long long g_launches = 0;
+}
 using namespace mc;
 
 extern "C" {
 
 int mc_abi_version(void) { return 1; }
+
+uint64_t mc_kernel_launch_count(void) { return g_launches; }
 
 const char* mc_strerror(int code) {
   switch (code) {

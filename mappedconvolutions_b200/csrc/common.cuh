@@ -159,6 +159,10 @@ inline int grid_for(long n, int block, int max_blocks = 148 * 32) {
   return (int)g;
 }
 
+// Number of kernels this library has launched in this process (diagnostic, not thread-safe).
+extern unsigned long long g_launches;
+#define MC_COUNT(n) (mc::g_launches += (n))
+
 #define MC_CHECK_LAUNCH()                                  \
   do {                                                     \
     if (cudaGetLastError() != cudaSuccess) return MC_ERR_LAUNCH; \

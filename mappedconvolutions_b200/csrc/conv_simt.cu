@@ -340,9 +340,9 @@ int conv_fwd_simt_launch(const mc_desc* d, const void* x, const void* map, const
   a.x = x; a.map = map; a.iw = d->P ? iw : nullptr; a.w = w; a.bias = bias; a.out = y;
   const long total_pix = (long)d->B * a.npix_grid;
   dim3 grid((unsigned)((total_pix + TP - 1) / TP), (unsigned)((d->C_out + TCO - 1) / TCO));
-  if (d->dtype == MC_F32) conv_fwd_simt<float><<<grid, 256, 0, st>>>(a);
-  else if (d->dtype == MC_F64) conv_fwd_simt<double><<<grid, 256, 0, st>>>(a);
-  else conv_fwd_simt<bf16><<<grid, 256, 0, st>>>(a);
+  if (d->dtype == MC_F32) conv_fwd_simt<float><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  else if (d->dtype == MC_F64) conv_fwd_simt<double><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  else conv_fwd_simt<bf16><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
@@ -362,18 +362,18 @@ int conv_dgrad_simt_launch(const mc_desc* d, const void* gy, const void* map, co
   const int fgrid = grid_for(nout, 256);
   if (d->dtype == MC_F32) {
     a.out = gx;
-    fill_bias_kernel<float, float><<<fgrid, 256, 0, st>>>((float*)gx, (const float*)bias_out, d->layout, d->C_in, a.npix_img, nout);
-    conv_dgrad_simt<float><<<grid, 256, 0, st>>>(a);
+    fill_bias_kernel<float, float><<<fgrid, 256, 0, st>>>((float*)gx, (const float*)bias_out, d->layout, d->C_in, a.npix_img, nout), MC_COUNT(1);
+    conv_dgrad_simt<float><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
   } else if (d->dtype == MC_F64) {
     a.out = gx;
-    fill_bias_kernel<double, double><<<fgrid, 256, 0, st>>>((double*)gx, (const double*)bias_out, d->layout, d->C_in, a.npix_img, nout);
-    conv_dgrad_simt<double><<<grid, 256, 0, st>>>(a);
+    fill_bias_kernel<double, double><<<fgrid, 256, 0, st>>>((double*)gx, (const double*)bias_out, d->layout, d->C_in, a.npix_img, nout), MC_COUNT(1);
+    conv_dgrad_simt<double><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
   } else {
     if (!ws || ws_bytes < (size_t)nout * sizeof(float)) return MC_ERR_WORKSPACE;
     a.out = ws;
-    fill_bias_kernel<bf16, float><<<fgrid, 256, 0, st>>>((float*)ws, (const bf16*)bias_out, d->layout, d->C_in, a.npix_img, nout);
-    conv_dgrad_simt<bf16><<<grid, 256, 0, st>>>(a);
-    f32_to_bf16_kernel<<<fgrid, 256, 0, st>>>((const float*)ws, (bf16*)gx, nout);
+    fill_bias_kernel<bf16, float><<<fgrid, 256, 0, st>>>((float*)ws, (const bf16*)bias_out, d->layout, d->C_in, a.npix_img, nout), MC_COUNT(1);
+    conv_dgrad_simt<bf16><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+    f32_to_bf16_kernel<<<fgrid, 256, 0, st>>>((const float*)ws, (bf16*)gx, nout), MC_COUNT(1);
   }
   MC_CHECK_LAUNCH();
   return MC_OK;
@@ -389,9 +389,9 @@ int bias_grad_launch(const mc_desc* d, const void* gy, void* gb, cudaStream_t st
   dim3 grid((unsigned)d->C_out, (unsigned)splits);
   const size_t esz = d->dtype == MC_F64 ? 8 : 4;
   if (cudaMemsetAsync(gb, 0, d->C_out * esz, st) != cudaSuccess) return MC_ERR_LAUNCH;
-  if (d->dtype == MC_F32) bias_grad_kernel<float, float><<<grid, 256, 0, st>>>((const float*)gy, (float*)gb, d->layout, d->B, d->C_out, npix, pps);
-  else if (d->dtype == MC_F64) bias_grad_kernel<double, double><<<grid, 256, 0, st>>>((const double*)gy, (double*)gb, d->layout, d->B, d->C_out, npix, pps);
-  else bias_grad_kernel<bf16, float><<<grid, 256, 0, st>>>((const bf16*)gy, (float*)gb, d->layout, d->B, d->C_out, npix, pps);
+  if (d->dtype == MC_F32) bias_grad_kernel<float, float><<<grid, 256, 0, st>>>((const float*)gy, (float*)gb, d->layout, d->B, d->C_out, npix, pps), MC_COUNT(1);
+  else if (d->dtype == MC_F64) bias_grad_kernel<double, double><<<grid, 256, 0, st>>>((const double*)gy, (double*)gb, d->layout, d->B, d->C_out, npix, pps), MC_COUNT(1);
+  else bias_grad_kernel<bf16, float><<<grid, 256, 0, st>>>((const bf16*)gy, (float*)gb, d->layout, d->B, d->C_out, npix, pps), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
@@ -410,9 +410,9 @@ int conv_wgrad_simt_launch(const mc_desc* d, const void* gy, const void* x, cons
   const size_t esz = d->dtype == MC_F64 ? 8 : 4;
   if (cudaMemsetAsync(gw, 0, (size_t)d->C_out * a.R * esz, st) != cudaSuccess) return MC_ERR_LAUNCH;
   dim3 grid((unsigned)tiles, (unsigned)splits);
-  if (d->dtype == MC_F32) conv_wgrad_simt<float><<<grid, 256, 0, st>>>(a);
-  else if (d->dtype == MC_F64) conv_wgrad_simt<double><<<grid, 256, 0, st>>>(a);
-  else conv_wgrad_simt<bf16><<<grid, 256, 0, st>>>(a);
+  if (d->dtype == MC_F32) conv_wgrad_simt<float><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  else if (d->dtype == MC_F64) conv_wgrad_simt<double><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  else conv_wgrad_simt<bf16><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }

@@ -94,9 +94,9 @@ template <int DT>
 static void knn_launch_k(const float* ref, const float* query, int B, int D, int M, int N, int k,
                          int64_t* idx, float* dist, cudaStream_t st) {
   dim3 grid((unsigned)((N + KNN_THREADS - 1) / KNN_THREADS), (unsigned)B);
-  if (k <= 8) knn_kernel<DT, 8><<<grid, KNN_THREADS, 0, st>>>(ref, query, D, M, N, k, idx, dist);
-  else if (k <= 16) knn_kernel<DT, 16><<<grid, KNN_THREADS, 0, st>>>(ref, query, D, M, N, k, idx, dist);
-  else knn_kernel<DT, 32><<<grid, KNN_THREADS, 0, st>>>(ref, query, D, M, N, k, idx, dist);
+  if (k <= 8) knn_kernel<DT, 8><<<grid, KNN_THREADS, 0, st>>>(ref, query, D, M, N, k, idx, dist), MC_COUNT(1);
+  else if (k <= 16) knn_kernel<DT, 16><<<grid, KNN_THREADS, 0, st>>>(ref, query, D, M, N, k, idx, dist), MC_COUNT(1);
+  else knn_kernel<DT, 32><<<grid, KNN_THREADS, 0, st>>>(ref, query, D, M, N, k, idx, dist), MC_COUNT(1);
 }
 
 }  // namespace mc

@@ -178,9 +178,9 @@ static int launch_fwd(const mc_desc* d, const void* x, const void* map, const vo
   a.npix_out = (long)d->OH * d->OW;
   const long total = (long)a.B * a.C * a.npix_out;
   const int grid = grid_for(total, 256);
-  if (d->dtype == MC_F32) sample_fwd_kernel<float, OP><<<grid, 256, 0, st>>>(a);
-  else if (d->dtype == MC_F64) sample_fwd_kernel<double, OP><<<grid, 256, 0, st>>>(a);
-  else sample_fwd_kernel<bf16, OP><<<grid, 256, 0, st>>>(a);
+  if (d->dtype == MC_F32) sample_fwd_kernel<float, OP><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  else if (d->dtype == MC_F64) sample_fwd_kernel<double, OP><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  else sample_fwd_kernel<bf16, OP><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
@@ -201,17 +201,17 @@ static int launch_bwd(const mc_desc* d, const void* g, const int64_t* idx, const
     if (!ws || ws_bytes < (size_t)nout * sizeof(float)) return MC_ERR_WORKSPACE;
     a.out = ws;
     if (cudaMemsetAsync(ws, 0, nout * sizeof(float), st) != cudaSuccess) return MC_ERR_LAUNCH;
-    sample_bwd_kernel<bf16, OP><<<grid, 256, 0, st>>>(a);
+    sample_bwd_kernel<bf16, OP><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
     MC_CHECK_LAUNCH();
-    convert_from_f32_kernel<bf16><<<grid_for(nout, 256), 256, 0, st>>>((const float*)ws, (bf16*)out, nout);
+    convert_from_f32_kernel<bf16><<<grid_for(nout, 256), 256, 0, st>>>((const float*)ws, (bf16*)out, nout), MC_COUNT(1);
   } else if (d->dtype == MC_F32) {
     a.out = out;
     if (cudaMemsetAsync(out, 0, nout * sizeof(float), st) != cudaSuccess) return MC_ERR_LAUNCH;
-    sample_bwd_kernel<float, OP><<<grid, 256, 0, st>>>(a);
+    sample_bwd_kernel<float, OP><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
   } else {
     a.out = out;
     if (cudaMemsetAsync(out, 0, nout * sizeof(double), st) != cudaSuccess) return MC_ERR_LAUNCH;
-    sample_bwd_kernel<double, OP><<<grid, 256, 0, st>>>(a);
+    sample_bwd_kernel<double, OP><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
   }
   MC_CHECK_LAUNCH();
   return MC_OK;

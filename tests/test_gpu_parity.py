@@ -1,0 +1,193 @@
+"""GPU parity tests proper: the CUDA path, called through the C-ABI, against the golden vectors of
+the reference's CPU code and against the oracle on seeded inputs.
+
+Bars: integer outputs (max-pool tap offsets, k-NN indices) bit-exact; gather-type float outputs
+bit-exact as well (their arithmetic has no reordering freedom); everything that goes through a
+contraction or an atomic accumulation within 1e-5 (float32), 1e-12 (float64), 2e-2 (bfloat16),
+relative to max(|ref|, rms(ref))."""
+import pytest
+import torch
+
+import helpers as H
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+RND = H.load_cases("random_small.npz")
+
+
+def _impl(layout):
+    from mappedconvolutions_b200 import ops
+    return H.Impl(ops, "cuda", layout)
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+@pytest.mark.parametrize("name", sorted(n for n in RND if n.startswith("conv_")))
+def test_conv_random(name, layout):
+    c = RND[name]
+    H.compare_case(H.run_conv(_impl(layout), c), c, H.TOL[c["input"].dtype], name)
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+@pytest.mark.parametrize("name", sorted(n for n in RND if n.startswith("tconv_")))
+def test_tconv_random(name, layout):
+    c = RND[name]
+    H.compare_case(H.run_conv(_impl(layout), c, transposed=True), c, H.TOL[c["input"].dtype], name)
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+@pytest.mark.parametrize("name", sorted(n for n in RND if n.startswith("pool_f")))
+def test_pool_random(name, layout):
+    c = RND[name]
+    H.compare_case(H.run_pool(_impl(layout), c), c, H.TOL[c["input"].dtype], name)
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+@pytest.mark.parametrize("name", sorted(n for n in RND if n.startswith("resample_")))
+def test_resample_random(name, layout):
+    c = RND[name]
+    H.compare_case(H.run_resample(_impl(layout), c), c, H.TOL[c["input"].dtype], name)
+
+
+def test_max_pool_uses_the_cuda_start_value():
+    """All-negative windows return their true maximum and tap offset (the reference's CUDA build,
+    include/nn/common/mapped_max_pool.h:29), not the CPU build's placeholder with index -1."""
+    from mappedconvolutions_b200 import ops
+    c = RND["pool_cpu_init_f32"]
+    y, idx = ops.mapped_max_pool(c["input"].cuda(), c["sample_map"].cuda(), c["K"], c["interp"])
+    y2, idx2 = oracle.mapped_max_pool(c["input"], c["sample_map"], c["K"], c["interp"], cuda_init=True)
+    assert torch.equal(y.cpu(), y2) and torch.equal(idx.cpu(), idx2)
+    ok = c["max_idx"] >= 0
+    assert torch.equal(y.cpu()[ok], c["max_output"][ok]) and torch.equal(idx.cpu()[ok], c["max_idx"][ok])
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+def test_config1_float32(layout):
+    c = H.load_cases("config1.npz")["config1"]
+    H.compare_case(H.run_conv(_impl(layout), c), c, 1e-5, "config1")
+
+
+# ---- seeded cases against the oracle -----------------------------------------------------------
+
+def _one_ring_like_map(n_out, n_in, K, gen):
+    """Nearest-mode map on an H = 1 image: tap 0 is the vertex itself, the others random vertices
+    (with one duplicated tap per row now and then, as at an icosphere's valence-5 vertices)."""
+    xs = torch.randint(0, n_in, (1, n_out, K), generator=gen).float()
+    xs[0, :, 0] = torch.arange(n_out).float()
+    dup = torch.rand(n_out, generator=gen) < 0.05
+    xs[0, dup, K - 1] = xs[0, dup, 1]
+    return torch.stack([xs, torch.zeros_like(xs)], -1).contiguous()
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+def test_pool_vertex_domain_bit_exact(layout):
+    g = torch.Generator().manual_seed(7)
+    B, C, Vin, Vout, K = 3, 16, 2562, 642, 7
+    x = torch.randn(B, C, 1, Vin, generator=g)
+    m = _one_ring_like_map(Vout, Vin, K, g)
+    impl = _impl(layout)
+    o = impl.ops
+    y, idx = o.mapped_max_pool(impl.act(x), m.cuda(), K, 0)
+    y2, idx2 = oracle.mapped_max_pool(x, m, K, 0, cuda_init=True)
+    assert torch.equal(idx.cpu(), idx2) and torch.equal(y.cpu().contiguous(), y2)
+    a = o.mapped_avg_pool(impl.act(x), m.cuda(), K, 0)
+    assert torch.equal(a.cpu().contiguous(), oracle.mapped_avg_pool(x, m, K, 0))
+    gy = torch.randn(B, C, 1, Vout, generator=g)
+    H.assert_close(o.mapped_max_unpool(impl.act(gy), idx, m.cuda(), 1, Vin, K, 0),
+                   oracle.mapped_max_unpool(gy, idx2, m, 1, Vin, K, 0), 1e-5, "max_unpool")
+    H.assert_close(o.mapped_avg_unpool(impl.act(gy), m.cuda(), 1, Vin, K, 0),
+                   oracle.mapped_avg_unpool(gy, m, 1, Vin, K, 0), 1e-5, "avg_unpool")
+
+
+@pytest.mark.parametrize("interp", [0, 1, 2])
+def test_bf16_conv_against_oracle_on_rounded_inputs(interp):
+    """bfloat16 has no counterpart in the reference: the oracle runs in float32 on the
+    bfloat16-rounded inputs; tolerance 2e-2."""
+    from mappedconvolutions_b200 import ops
+    g = torch.Generator().manual_seed(11)
+    B, Cin, Cout, IH, IW, OH, OW, K = 2, 16, 24, 12, 20, 10, 18, 5
+    bf = lambda t: t.to(torch.bfloat16)
+    x, w, b = bf(torch.randn(B, Cin, IH, IW, generator=g)), bf(torch.randn(Cout, Cin, K, generator=g)), \
+        bf(torch.randn(Cout, generator=g))
+    gy = bf(torch.randn(B, Cout, OH, OW, generator=g))
+    m = (torch.rand(OH, OW, K, 2, generator=g) * torch.tensor([IW + 1.0, IH + 1.0]) - 1.0).contiguous()
+    want_y = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, interp)
+    want_g = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, interp)
+    for layout in ("nchw", "nhwc"):
+        impl = H.Impl(ops, "cuda", layout)
+        y = ops.mapped_conv_forward(impl.act(x), m.cuda(), w.cuda(), b.cuda(), K, interp)
+        gx, gw, gb = ops.mapped_conv_backward(impl.act(gy), m.cuda(), impl.act(x), w.cuda(), b.cuda(),
+                                              K, interp)
+        assert y.dtype == torch.bfloat16 and gx.dtype == torch.bfloat16
+        H.assert_close(y.float(), want_y, 2e-2, "bf16 y")
+        H.assert_close(gx.float(), want_g[0], 2e-2, "bf16 gx")
+        H.assert_close(gw.float(), want_g[1], 2e-2, "bf16 gw")
+        H.assert_close(gb.float(), want_g[2], 2e-2, "bf16 gb")
+
+
+def test_bf16_pool_and_resample():
+    from mappedconvolutions_b200 import ops
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(2, 8, 9, 11, generator=g).to(torch.bfloat16)
+    m = (torch.rand(6, 7, 4, 2, generator=g) * torch.tensor([12.0, 10.0]) - 1.0).contiguous()
+    y, idx = ops.mapped_max_pool(x.cuda(), m.cuda(), 4, 0)
+    y2, idx2 = oracle.mapped_max_pool(x.float(), m, 4, 0, cuda_init=True)
+    assert torch.equal(idx.cpu(), idx2) and torch.equal(y.float().cpu(), y2)
+    a = ops.mapped_avg_pool(x.cuda(), m.cuda(), 4, 1)
+    H.assert_close(a.float(), oracle.mapped_avg_pool(x.float(), m, 4, 1), 2e-2, "bf16 avg")
+    gy = torch.randn(2, 8, 6, 7, generator=g).to(torch.bfloat16)
+    u = ops.mapped_avg_unpool(gy.cuda(), m.cuda(), 9, 11, 4, 1)
+    H.assert_close(u.float(), oracle.mapped_avg_unpool(gy.float(), m, 9, 11, 4, 1), 2e-2, "bf16 unpool")
+
+
+def test_empty_and_degenerate_shapes():
+    """Single pixel, single channel, K = 1, a map whose samples are all outside the image."""
+    from mappedconvolutions_b200 import ops
+    x = torch.randn(1, 1, 1, 1).cuda()
+    m = torch.zeros(1, 1, 1, 2).cuda()
+    w = torch.ones(1, 1, 1).cuda()
+    b = torch.zeros(1).cuda()
+    assert torch.equal(ops.mapped_conv_forward(x, m, w, b, 1, 1), x)
+    far = torch.full((3, 3, 2, 2), 1e9).cuda()
+    xx = torch.randn(2, 3, 4, 4).cuda()
+    assert torch.count_nonzero(ops.mapped_avg_pool(xx, far, 2, 1)) == 0
+    y, idx = ops.mapped_max_pool(xx, far, 2, 0)
+    assert torch.count_nonzero(y) == 0 and (idx == torch.arange(9, device="cuda").view(3, 3) * 4).all()
+    nan = torch.full((3, 3, 2, 2), float("nan")).cuda()
+    assert torch.count_nonzero(ops.mapped_avg_pool(xx, nan, 2, 1)[~torch.isnan(ops.mapped_avg_pool(xx, nan, 2, 0))]) == 0
+
+
+def test_non_contiguous_input_is_rejected():
+    from mappedconvolutions_b200 import ops
+    x = torch.randn(2, 3, 4, 8).cuda()[..., ::2]
+    with pytest.raises(RuntimeError):
+        ops.mapped_avg_pool(x, torch.zeros(2, 2, 1, 2).cuda(), 1, 0)
+
+
+# ---- k nearest neighbours ----------------------------------------------------------------------
+
+@pytest.mark.parametrize("D,M,N,k", [(3, 2562, 2562, 9), (3, 700, 333, 1), (2, 1000, 50, 16),
+                                     (5, 300, 257, 20), (3, 40, 40, 32), (16, 129, 65, 4)])
+def test_knn_bit_exact_against_oracle(D, M, N, k):
+    from mappedconvolutions_b200 import ops
+    g = torch.Generator().manual_seed(D * 1000 + k)
+    ref = torch.randn(2, D, M, generator=g)
+    if D == 3:
+        ref = ref / ref.norm(dim=1, keepdim=True)  # points on the unit sphere
+        ref[:, :, 5] = ref[:, :, 3]                # exact duplicates: ties broken by index
+    q = ref[:, :, :N].clone() if N <= M else torch.randn(2, D, N, generator=g)
+    idx, dist = ops.knn_forward(ref.cuda(), q.cuda(), k)
+    idx2, dist2 = oracle.knn_forward(ref, q, k)
+    assert idx.dtype == torch.int64 and torch.equal(idx.cpu(), idx2)
+    assert torch.equal(dist.cpu(), dist2)
+    assert idx.min() >= 1 and idx.max() <= M
+
+
+def test_knn_self_match_is_first_and_one_based():
+    from mapped_convolution.util import knn
+    g = torch.Generator().manual_seed(3)
+    p = torch.randn(1, 3, 500, generator=g).cuda()
+    idx, dist = knn(p, p, 4)
+    assert torch.equal(idx[0, 0], torch.arange(1, 501, device="cuda"))
+    assert torch.count_nonzero(dist[0, 0]) == 0
+    assert (dist[0, 1:] >= dist[0, :-1]).all()

@@ -1,0 +1,90 @@
+"""CPU: host-side behaviour of the layer API (argument checks, parameter shapes, the refusal to
+run on CPU tensors, the drop-in import names)."""
+import math
+
+import pytest
+import torch
+
+
+def test_drop_in_import_names():
+    import mapped_convolution.nn as a
+    import mapped_convolutions.nn as b
+    import mapped_convolution.util as u
+    for n in ("MappedConvolution", "MappedTransposedConvolution", "MappedMaxPool", "MappedAvgPool",
+              "MappedAvgUnpool", "Resample", "Unresample"):
+        assert getattr(a, n) is getattr(b, n)
+    assert callable(u.knn)
+    import _mapped_convolution_ext._mapped_convolution as m
+    assert callable(m.mapped_conv_forward) and callable(m.mapped_conv_backward)
+    import _mapped_convolution_ext._knn as k
+    assert callable(k.knn_forward)
+
+
+def test_parameter_shapes_and_init():
+    from mapped_convolution.nn import MappedConvolution, MappedTransposedConvolution
+    torch.manual_seed(0)
+    c = MappedConvolution(6, 10, kernel_size=7, interpolation='nearest')
+    assert c.weight.shape == (10, 6, 7) and c.bias.shape == (10,) and c.interp == 0
+    s = 1 / math.sqrt(6 * 7)
+    assert c.weight.abs().max() <= s and c.bias.abs().max() <= s
+    t = MappedTransposedConvolution(6, 10, kernel_size=7, interpolation='bispherical', bias=False)
+    assert t.weight.shape == (6, 10, 7) and t.interp == 2
+    assert torch.count_nonzero(t.bias) == 0 and t.bias.requires_grad
+    assert set(c.state_dict()) == {"weight", "bias"}
+    with pytest.raises(AssertionError):
+        MappedConvolution(1, 1, 1, interpolation='cubic')
+
+
+def test_argument_checks_raise_assertion_error():
+    from mapped_convolution.nn import MappedConvolution, MappedAvgUnpool, Resample
+    layer = MappedConvolution(2, 3, kernel_size=4)
+    x = torch.zeros(1, 2, 4, 5)
+    m = torch.zeros(4, 5, 4, 2)
+    with pytest.raises(AssertionError):
+        layer(x[0], m)                       # input not 4-D
+    with pytest.raises(AssertionError):
+        layer(x, m[..., :1])                 # last map dim != 2
+    with pytest.raises(AssertionError):
+        layer(x, m.double())                 # dtype mismatch
+    with pytest.raises(AssertionError):
+        layer(torch.zeros(1, 3, 4, 5), m)    # channel mismatch
+    with pytest.raises(AssertionError):
+        layer(x, torch.zeros(4, 5, 3, 2))    # kernel size mismatch
+    with pytest.raises(AssertionError):
+        layer(x, torch.zeros(4, 5, 4, 3, 2), torch.zeros(4, 5, 4, 2))  # P mismatch
+    with pytest.raises(AssertionError):
+        MappedAvgUnpool(4)(x, 8, 8, torch.zeros(3, 5, 4, 2))           # map grid != input size
+    with pytest.raises(AssertionError):
+        Resample()(x, torch.zeros(4, 4, 2), (8, 8))
+
+
+def test_bf16_input_takes_float32_map():
+    from mappedconvolutions_b200.nn.checks import check_args
+    check_args(torch.zeros(1, 2, 4, 5, dtype=torch.bfloat16), torch.zeros(4, 5, 4, 2), None, 2, 4)
+    with pytest.raises(AssertionError):
+        check_args(torch.zeros(1, 2, 4, 5, dtype=torch.bfloat16),
+                   torch.zeros(4, 5, 4, 2, dtype=torch.bfloat16), None, 2, 4)
+
+
+def test_cpu_tensors_are_refused_loudly():
+    from mapped_convolution.nn import MappedConvolution, Unresample
+    from mapped_convolution.util import knn
+    with pytest.raises(RuntimeError, match="CUDA only"):
+        MappedConvolution(2, 3, kernel_size=4)(torch.zeros(1, 2, 4, 5), torch.zeros(4, 5, 4, 2))
+    with pytest.raises(RuntimeError, match="CUDA only"):
+        Unresample()(torch.zeros(1, 2, 4, 5), torch.zeros(3, 3, 2))
+    with pytest.raises(RuntimeError, match="CUDA only"):
+        knn(torch.zeros(1, 3, 8), torch.zeros(1, 3, 8), 2)
+
+
+def test_product_does_not_import_the_oracle():
+    """No module of the product package may reach into oracle/."""
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for pkg in ("mappedconvolutions_b200", "mapped_convolution", "mapped_convolutions",
+                "_mapped_convolution_ext"):
+        for dp, _, fs in os.walk(os.path.join(root, pkg)):
+            for f in fs:
+                if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                    src = open(os.path.join(dp, f)).read()
+                    assert "oracle" not in src, os.path.join(dp, f)
