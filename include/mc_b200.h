@@ -62,6 +62,11 @@ int mc_abi_version(void);
  * reference; used by the benchmark to report its launch count). */
 uint64_t mc_kernel_launch_count(void);
 
+/* Synchronises `stream` and returns the device status word: 0, or the code of the first bounded
+ * device-side wait that ran out (the kernel then returned early and its output is invalid).
+ * reset != 0 clears the word.  No counterpart in the reference (its kernels have no waits). */
+int mc_device_status(void* stream, int reset);
+
 /* ---- mapped convolution ---------------------------------------------------------------
  * weight (C_out, C_in, K) and bias (C_out) in `dtype`, contiguous. */
 

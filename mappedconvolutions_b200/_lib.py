@@ -32,6 +32,7 @@ SIGNATURES = {
     "mc_strerror": (ctypes.c_char_p, [ctypes.c_int]),
     "mc_abi_version": (ctypes.c_int, []),
     "mc_kernel_launch_count": (ctypes.c_uint64, []),
+    "mc_device_status": (ctypes.c_int, [_vp, ctypes.c_int]),
     "mc_conv_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_fwd_workspace_bytes": (_sz, [_dp]),
     "mc_conv_dgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

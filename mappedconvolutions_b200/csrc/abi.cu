@@ -16,8 +16,10 @@ int bias_grad_launch(const mc_desc*, const void*, void*, cudaStream_t);
 // Tensor-core path (conv_tc.cu).  Each returns MC_ERR_UNSUPPORTED when the shape is not one it
 // takes, in which case the generic kernel runs instead.
 bool conv_tc_fwd_supported(const mc_desc*);
+size_t conv_tc_fwd_ws(const mc_desc*);
 int conv_tc_fwd_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
-                       cudaStream_t);
+                       void*, size_t, cudaStream_t);
+int device_status_read(cudaStream_t, int);
 bool conv_tc_dgrad_supported(const mc_desc*);
 size_t conv_tc_dgrad_ws(const mc_desc*);
 int conv_tc_dgrad_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
@@ -54,16 +56,22 @@ const char* mc_strerror(int code) {
 
 // ---- conv ----------------------------------------------------------------------------------
 
-size_t mc_conv_fwd_workspace_bytes(const mc_desc* d) { (void)d; return 0; }
+int mc_device_status(void* stream, int reset) {
+  return device_status_read((cudaStream_t)stream, reset);
+}
+
+size_t mc_conv_fwd_workspace_bytes(const mc_desc* d) {
+  if (!d || check_conv_desc_public(d)) return 0;
+  return conv_tc_fwd_supported(d) ? conv_tc_fwd_ws(d) : 0;
+}
 
 int mc_conv_fwd(const mc_desc* d, const void* x, const void* map, const void* iw, const void* w,
                 const void* bias, void* y, void* ws, size_t ws_bytes, void* stream) {
-  (void)ws; (void)ws_bytes;
   int rc = check_conv_desc_public(d);
   if (rc) return rc;
   if (!x || !map || !w || !y || (d->P > 0 && !iw)) return MC_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
-  if (conv_tc_fwd_supported(d)) return conv_tc_fwd_launch(d, x, map, w, bias, y, st);
+  if (conv_tc_fwd_supported(d)) return conv_tc_fwd_launch(d, x, map, w, bias, y, ws, ws_bytes, st);
   return conv_fwd_simt_launch(d, x, map, iw, w, bias, y, st);
 }
 
