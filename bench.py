@@ -308,11 +308,17 @@ def run_ours(args):
         gx = torch.empty_like(x)
         gw = torch.empty(COUT, CIN, K, dtype=torch.float32, device=dev)
         gb = torch.empty(COUT, dtype=torch.float32, device=dev)
-        nws = max(L.mc_conv_dgrad_workspace_bytes(d), L.mc_conv_wgrad_workspace_bytes(d), 16)
+        nws = max(L.mc_conv_dgrad_workspace_bytes(d), L.mc_conv_wgrad_workspace_bytes(d),
+                  L.mc_conv_fwd_workspace_bytes(d), L.mc_conv_dgrad_inv_workspace_bytes(d), 16)
         ws = torch.empty(nws, dtype=torch.uint8, device=dev)
+        if L.mc_conv_dgrad_inv_supported(d):
+            inv = ops._inverse_map(d, m)
+            dgrad = lambda: _lib.check(L.mc_conv_dgrad_inv(d, gy.data_ptr(), inv.data_ptr(), w.data_ptr(), None, gx.data_ptr(), ws.data_ptr(), nws, st))
+        else:
+            dgrad = lambda: _lib.check(L.mc_conv_dgrad(d, gy.data_ptr(), m.data_ptr(), None, w.data_ptr(), None, gx.data_ptr(), ws.data_ptr(), nws, st))
         fam = {
             "conv_fwd": lambda: _lib.check(L.mc_conv_fwd(d, x.data_ptr(), m.data_ptr(), None, w.data_ptr(), b.data_ptr(), y.data_ptr(), ws.data_ptr(), nws, st)),
-            "conv_dgrad": lambda: _lib.check(L.mc_conv_dgrad(d, gy.data_ptr(), m.data_ptr(), None, w.data_ptr(), None, gx.data_ptr(), ws.data_ptr(), nws, st)),
+            "conv_dgrad": dgrad,
             "conv_wgrad": lambda: _lib.check(L.mc_conv_wgrad(d, gy.data_ptr(), x.data_ptr(), m.data_ptr(), None, gw.data_ptr(), gb.data_ptr(), ws.data_ptr(), nws, st)),
         }
         times = {k: timed(f) for k, f in fam.items()}

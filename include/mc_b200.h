@@ -85,6 +85,25 @@ int mc_conv_dgrad(const mc_desc* d, const void* gy, const void* map, const void*
                   const void* bias_out, void* gx, void* ws, size_t ws_bytes, void* stream);
 size_t mc_conv_dgrad_workspace_bytes(const mc_desc* d);
 
+/* Inverse map: for every (input pixel, tap) the list of (grid pixel, weight) pairs whose forward
+ * sample reads that input pixel.  It depends only on the sample map and the two image sizes, so
+ * it is built once per map and reused by every backward pass.  With it the reference's atomic
+ * col2im scatter (MappedCol2Im2DLauncher, include/nn/cuda/mapped_im2col.cuh:51-89) becomes a gather:
+ * no atomics, and results that repeat bit for bit from run to run.
+ * Unweighted maps only (d->P == 0).  mc_invmap_bytes() gives the size of the `inv` buffer
+ * (0 = not supported for this descriptor). */
+size_t mc_invmap_bytes(const mc_desc* d);
+size_t mc_invmap_build_workspace_bytes(const mc_desc* d);
+int mc_invmap_build(const mc_desc* d, const void* map, void* inv, size_t inv_bytes, void* ws,
+                    size_t ws_bytes, void* stream);
+/* Same result as mc_conv_dgrad, computed on the tensor cores from a prebuilt inverse map.
+ * bf16, MC_NHWC, C_in == 64, C_out % 64 == 0 (mc_conv_dgrad_inv_supported() tells).
+ * Replaces cuda::MappedConvBackwardInput, src/nn/cuda/mapped_convolution_layer.cu:75-132. */
+int mc_conv_dgrad_inv_supported(const mc_desc* d);
+size_t mc_conv_dgrad_inv_workspace_bytes(const mc_desc* d);
+int mc_conv_dgrad_inv(const mc_desc* d, const void* gy, const void* inv, const void* w,
+                      const void* bias_out, void* gx, void* ws, size_t ws_bytes, void* stream);
+
 /* gw(C_out,C_in,K) = sum_b gy_b . im2col_map(x_b)^T and gb(C_out) = sum_{b,h,w} gy.
  * gw and gb are written in the accumulation type: double for MC_F64, float otherwise
  * (also for MC_BF16), fully overwritten.  gb may be NULL.

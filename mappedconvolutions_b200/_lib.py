@@ -37,6 +37,12 @@ SIGNATURES = {
     "mc_conv_fwd_workspace_bytes": (_sz, [_dp]),
     "mc_conv_dgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_dgrad_workspace_bytes": (_sz, [_dp]),
+    "mc_invmap_bytes": (_sz, [_dp]),
+    "mc_invmap_build_workspace_bytes": (_sz, [_dp]),
+    "mc_invmap_build": (ctypes.c_int, [_dp, _vp, _vp, _sz, _vp, _sz, _vp]),
+    "mc_conv_dgrad_inv_supported": (ctypes.c_int, [_dp]),
+    "mc_conv_dgrad_inv_workspace_bytes": (_sz, [_dp]),
+    "mc_conv_dgrad_inv": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_wgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_wgrad_workspace_bytes": (_sz, [_dp]),
     "mc_tconv_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

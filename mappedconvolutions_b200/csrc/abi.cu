@@ -24,6 +24,10 @@ bool conv_tc_dgrad_supported(const mc_desc*);
 size_t conv_tc_dgrad_ws(const mc_desc*);
 int conv_tc_dgrad_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
                          void*, size_t, cudaStream_t);
+bool invmap_supported(const mc_desc*);
+size_t invmap_bytes(const mc_desc*);
+size_t invmap_build_ws(const mc_desc*);
+int invmap_build_launch(const mc_desc*, const void*, void*, void*, size_t, cudaStream_t);
 bool conv_tc_wgrad_supported(const mc_desc*);
 size_t conv_tc_wgrad_ws(const mc_desc*);
 int conv_tc_wgrad_launch(const mc_desc*, const void*, const void*, const void*, void*, void*, void*,
@@ -76,9 +80,42 @@ int mc_conv_fwd(const mc_desc* d, const void* x, const void* map, const void* iw
 }
 
 size_t mc_conv_dgrad_workspace_bytes(const mc_desc* d) {
-  if (!d) return 0;
-  if (conv_tc_dgrad_supported(d)) return conv_tc_dgrad_ws(d);
+  if (!d || check_conv_desc_public(d)) return 0;
   return conv_dgrad_simt_ws(d);
+}
+
+// ---- inverse map and the gather-form dgrad ---------------------------------------------------
+
+size_t mc_invmap_bytes(const mc_desc* d) {
+  if (!d || check_conv_desc_public(d) || !invmap_supported(d)) return 0;
+  return invmap_bytes(d);
+}
+size_t mc_invmap_build_workspace_bytes(const mc_desc* d) {
+  if (!d || check_conv_desc_public(d) || !invmap_supported(d)) return 0;
+  return invmap_build_ws(d);
+}
+int mc_invmap_build(const mc_desc* d, const void* map, void* inv, size_t inv_bytes, void* ws,
+                    size_t ws_bytes, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!map || !inv) return MC_ERR_BAD_ARG;
+  if (!invmap_supported(d)) return MC_ERR_UNSUPPORTED;
+  if (inv_bytes < invmap_bytes(d)) return MC_ERR_WORKSPACE;
+  return invmap_build_launch(d, map, inv, ws, ws_bytes, (cudaStream_t)stream);
+}
+int mc_conv_dgrad_inv_supported(const mc_desc* d) {
+  return d && !check_conv_desc_public(d) && conv_tc_dgrad_supported(d) ? 1 : 0;
+}
+size_t mc_conv_dgrad_inv_workspace_bytes(const mc_desc* d) {
+  return mc_conv_dgrad_inv_supported(d) ? conv_tc_dgrad_ws(d) : 0;
+}
+int mc_conv_dgrad_inv(const mc_desc* d, const void* gy, const void* inv, const void* w,
+                      const void* bias_out, void* gx, void* ws, size_t ws_bytes, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!gy || !inv || !w || !gx) return MC_ERR_BAD_ARG;
+  if (!conv_tc_dgrad_supported(d)) return MC_ERR_UNSUPPORTED;
+  return conv_tc_dgrad_launch(d, gy, inv, w, bias_out, gx, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 int mc_conv_dgrad(const mc_desc* d, const void* gy, const void* map, const void* iw, const void* w,
@@ -87,8 +124,6 @@ int mc_conv_dgrad(const mc_desc* d, const void* gy, const void* map, const void*
   if (rc) return rc;
   if (!gy || !map || !w || !gx || (d->P > 0 && !iw)) return MC_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
-  if (conv_tc_dgrad_supported(d))
-    return conv_tc_dgrad_launch(d, gy, map, w, bias_out, gx, ws, ws_bytes, st);
   return conv_dgrad_simt_launch(d, gy, map, iw, w, bias_out, gx, ws, ws_bytes, st);
 }
 

@@ -1,21 +1,29 @@
-// Tensor-core mapped convolution for bf16 channels-last activations: an implicit GEMM whose A
-// operand never exists in global memory.
+// Tensor-core mapped convolution for bf16 channels-last activations: implicit GEMMs whose
+// interpolated operand never exists in global memory.
 //
-//   forward:  y[pixel, co] = sum_{tap, ci} A[pixel, (tap, ci)] * W[co, ci, tap] + bias[co]
-//             A[pixel, (tap, ci)] = interp(x[., ci], map[pixel, tap])
+//   forward: y[pix, co]  = sum_{tap, ci} A[pix, (tap, ci)] * W[co, ci, tap] + bias[co]
+//            A[pix, (tap, ci)] = interp(x[., ci], map[pix, tap])
+//   dgrad  : gx[q, ci]   = sum_{tap, co} G[q, (tap, co)] * W[co, ci, tap]
+//            G[q, (tap, co)] = sum over the (pix, corner) pairs of tap that land on input pixel q
+//                              of weight * gy[pix, co]        (gather through the inverse map;
+//                              no atomics, deterministic)
+//   wgrad  : gw[co, ci, tap] = sum_{pix} gy[pix, co] * A[pix, (tap, ci)]
 //
-// One persistent CTA per SM works on tiles of 128 output pixels:
-//   * producer warps read the sample map, gather the (up to four) source pixels of every
-//     (pixel, tap) as 16-byte channel vectors, blend them in fp32 and write the bf16 row straight
-//     into a 128-byte-swizzled shared-memory stage (one stage = one tap = a 128 x 64 K-slice);
-//   * one thread issues tcgen05.mma (M = 128, N = C_out, K = 16) from those stages against the
-//     weight slices, which stay resident in shared memory, accumulating fp32 in tensor memory;
-//   * four epilogue warps read the accumulators back with tcgen05.ld, add the bias and store bf16.
-// Stages and the two accumulator buffers are handed over through mbarriers; every wait is bounded
-// and raises a status word instead of spinning forever.
+// One persistent CTA per SM works on tiles of 128 pixels:
+//   * producer warps build A (or G) rows: they read the sample map (or the inverse-map lists),
+//     gather the source pixels as 16-byte channel vectors, blend them in fp32 and write the bf16
+//     row into a 128-byte-swizzled shared-memory stage (one stage = 128 pixels x 64 channels of
+//     one tap);
+//   * one thread issues tcgen05.mma from those stages, accumulating fp32 in tensor memory;
+//   * four warps read the accumulators back with tcgen05.ld (and, in wgrad, stream the gy tiles).
+// The same stage bytes serve as a K-major operand (forward, dgrad: reduction over channels) and as
+// an MN-major operand (wgrad: reduction over pixels).  Stages and accumulators are handed over
+// through mbarriers; every wait is bounded and raises a status word instead of spinning forever.
 //
-// Replaces the per-batch im2col + cublasSgemm + bias sequence of the reference's
-// src/nn/cuda/mapped_convolution_layer.cu:39-70.
+// Replaces the per-batch im2col / col2im + cublasSgemm sequences of the reference's
+// src/nn/cuda/mapped_convolution_layer.cu:39-70, :100-127, :155-190.
+#include <cub/device/device_scan.cuh>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -26,89 +34,176 @@ constexpr int TILE_M = 128;
 constexpr int STAGE_BYTES = TILE_M * 128;  // 128 rows x 64 bf16
 constexpr int N_PRODUCER_WARPS = 16;
 constexpr int N_EPI_WARPS = 4;
-constexpr int FWD_THREADS = (1 + N_EPI_WARPS + N_PRODUCER_WARPS) * 32;
+constexpr int TC_THREADS = (1 + N_EPI_WARPS + N_PRODUCER_WARPS) * 32;
+constexpr size_t SMEM_LIMIT = 220 * 1024;
 
-struct FwdArgs {
-  const bf16* x;      // (B, IH*IW, Cin) channels-last
-  const float* map;   // (OH*OW, K, 2)
-  const uint4* wimg;  // weight slices in their shared-memory image
-  const bf16* bias;   // may be null
-  bf16* y;            // (B, OH*OW, NOUT) channels-last
-  int Cin, IH, IW, OW, K, interp;
-  int nsl;    // number of 64-wide K slices = K * Cin / 64
-  int nst;    // pipeline stages
-  long opix;  // OH*OW
-  long mtot;  // B*OH*OW
-  int tiles;
-  int tile2d, tiles_x, tiles_per_img;
+// How the pixels of the tiled domain are grouped into 128-row tiles.
+struct Tiling {
+  long npix;  // pixels per image of the tiled domain
+  long mtot;  // batch * npix
+  int W;      // width of the tiled domain
+  int tiles, tile2d, tiles_x, tiles_per_img;
 };
 
-// Weight (Cout, Cin, K) -> nsl slices of [Cout rows][64 channels] bf16, each row 128 bytes with
-// its 16-byte chunks XOR-swizzled by (row & 7): exactly what tcgen05.mma expects for a K-major
-// operand with the 128-byte swizzle, so the kernel copies it into shared memory linearly.
-// transpose = 1 builds the dgrad operand instead: rows are input channels, the 64-wide slices run
-// over output channels (requires Cout % 64 == 0).
-__global__ void weight_image_kernel(const bf16* __restrict__ w, uint16_t* __restrict__ img, int rows,
-                                    int red, int K, int transpose, int Cin_w) {
-  // rows: operand rows (N of the GEMM); red: reduction channels per tap (multiple of 64)
-  const int cpb = red / 64;
-  const long total = (long)K * cpb * rows * 64;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
-       i += (long)gridDim.x * blockDim.x) {
-    const int c = (int)(i % 64);
-    const int n = (int)((i / 64) % rows);
-    const int s = (int)(i / (64L * rows));
-    const int tap = s / cpb, cb = s % cpb;
-    const int r = cb * 64 + c;
-    // forward: w[n][r][tap] with n = co, r = ci.   transpose: w[r][n][tap] with r = co, n = ci.
-    const long src = transpose ? ((long)r * Cin_w + n) * K + tap : ((long)n * Cin_w + r) * K + tap;
-    const long dst = (long)s * rows * 64 + (long)n * 64 + ((((c >> 3) ^ (n & 7)) << 3) | (c & 7));
-    img[dst] = reinterpret_cast<const uint16_t*>(w)[src];
-  }
+static bool make_tiling(Tiling& t, int B, int Hd, int Wd) {
+  t.npix = (long)Hd * Wd;
+  t.mtot = (long)B * t.npix;
+  t.W = Wd;
+  t.tile2d = (Hd % 8 == 0 && Wd % 16 == 0) ? 1 : 0;  // 8 x 16 pixel tiles keep the footprint small
+  t.tiles_x = Wd / 16;
+  t.tiles_per_img = (Hd / 8) * (Wd / 16);
+  const long n = t.tile2d ? (long)B * t.tiles_per_img : (t.mtot + TILE_M - 1) / TILE_M;
+  if (n >= (1L << 31)) return false;
+  t.tiles = (int)n;
+  return true;
 }
 
-__device__ __forceinline__ void tile_pixel(const FwdArgs& a, int tile, int r, long& gp, int& img,
+__device__ __forceinline__ void tile_pixel(const Tiling& t, int tile, int r, long& gp, int& img,
                                            long& p, bool& valid) {
-  if (a.tile2d) {
-    img = tile / a.tiles_per_img;
-    const int tt = tile % a.tiles_per_img;
-    const int ty = tt / a.tiles_x, tx = tt % a.tiles_x;
-    p = (long)(ty * 8 + (r >> 4)) * a.OW + tx * 16 + (r & 15);
-    gp = (long)img * a.opix + p;
+  if (t.tile2d) {
+    img = tile / t.tiles_per_img;
+    const int tt = tile % t.tiles_per_img;
+    const int ty = tt / t.tiles_x, tx = tt % t.tiles_x;
+    p = (long)(ty * 8 + (r >> 4)) * t.W + tx * 16 + (r & 15);
+    gp = (long)img * t.npix + p;
     valid = true;
   } else {
     gp = (long)tile * TILE_M + r;
-    valid = gp < a.mtot;
-    img = valid ? (int)(gp / a.opix) : 0;
-    p = valid ? gp % a.opix : 0;
+    valid = gp < t.mtot;
+    img = valid ? (int)(gp / t.npix) : 0;
+    p = valid ? gp % t.npix : 0;
   }
 }
 
-template <int NOUT>
-__global__ void __launch_bounds__(FWD_THREADS, 1) conv_fwd_tc_kernel(const FwdArgs a) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  // carve-up (base is 1024-byte aligned by the runtime for dynamic shared memory of this size)
-  uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* stages = sm;
-  uint8_t* wsm = stages + (size_t)a.nst * STAGE_BYTES;
-  float* bias_s = (float*)(wsm + (size_t)a.nsl * NOUT * 128);
-  uint64_t* bars = (uint64_t*)(bias_s + NOUT);
-  // bars: full[nst], empty[nst], tfull[2], tempty[2], drain
-  uint32_t* misc = (uint32_t*)(bars + 2 * a.nst + 5);
-  volatile int* abort_flag = (volatile int*)(misc + 1);
+// What the producer warps gather from.
+struct Source {
+  const bf16* src;  // (B, spix, C) channels-last tensor that is gathered
+  long spix;        // pixels per image of src
+  int C;            // channels of src (multiple of 64)
+  int SH, SW;       // size of the sampled image (map mode)
+  int K, interp;
+  const float* map;   // map mode: (npix, K, 2)
+  const int* inv_off; // inverse-map mode: (npix * K + 1) list offsets
+  const int2* inv_ent;  //                 (source pixel, weight bits) entries
+};
 
+struct GemmArgs {
+  Source s;
+  Tiling t;
+  const uint4* wimg;  // fwd / dgrad: weight slices in their shared-memory image
+  const bf16* bias;   // fwd / dgrad: per output channel, may be null
+  bf16* y;            // fwd / dgrad: (B, npix, NOUT) channels-last
+  const bf16* gy;     // wgrad: (B, npix, NOUT) channels-last
+  float* gw;          // wgrad: (NOUT, Cin, K) fp32, accumulated atomically
+  float* gb;          // wgrad: (NOUT) fp32 or null
+  int nsl;            // 64-wide slices of the gathered operand = K * C / 64
+  int nst;            // pipeline stages
+};
+
+__device__ __forceinline__ void blend4(const uint4& v, float w, float (&acc)[8]) {
+  bf16x2_fma(v.x, w, acc[0], acc[1]);
+  bf16x2_fma(v.y, w, acc[2], acc[3]);
+  bf16x2_fma(v.z, w, acc[4], acc[5]);
+  bf16x2_fma(v.w, w, acc[6], acc[7]);
+}
+
+// One row (pixel p of image img, tap, 64-channel block cb) of the gathered operand, computed by
+// the 8 lanes of a group: lane lg owns channels [8 lg, 8 lg + 8).
+template <bool CSR>
+__device__ __forceinline__ uint4 produce_row(const Source& s, int img, long p, int tap, int cb, int lg,
+                                             bool valid) {
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  const bf16* sb = s.src + ((long)img * s.spix) * s.C + cb * 64 + lg * 8;
+  if (!CSR) {
+    Tap<float> tp;
+    tp.n = 0;
+    if (valid) {
+      const float2 m = __ldg(reinterpret_cast<const float2*>(s.map) + p * s.K + tap);
+      decode_tap<float, float>(m.x, m.y, s.SH, s.SW, s.interp, tp);
+    }
+    uint4 v[4];
+    float wv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const bool on = i < tp.n && tp.off[i] >= 0 && tp.w[i] != 0.f;
+      wv[i] = on ? tp.w[i] : 0.f;
+      v[i] = on ? ldg16(sb + (long)tp.off[i] * s.C) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) blend4(v[i], wv[i], acc);
+  } else if (valid) {
+    const long key = p * s.K + tap;
+    int e = __ldg(s.inv_off + key);
+    const int end = __ldg(s.inv_off + key + 1);
+    for (; e + 1 < end; e += 2) {
+      const int2 e0 = __ldg(s.inv_ent + e), e1 = __ldg(s.inv_ent + e + 1);
+      const uint4 v0 = ldg16(sb + (long)e0.x * s.C), v1 = ldg16(sb + (long)e1.x * s.C);
+      blend4(v0, __int_as_float(e0.y), acc);
+      blend4(v1, __int_as_float(e1.y), acc);
+    }
+    if (e < end) {
+      const int2 e0 = __ldg(s.inv_ent + e);
+      blend4(ldg16(sb + (long)e0.x * s.C), __int_as_float(e0.y), acc);
+    }
+  }
+  uint4 o;
+  o.x = pack_bf16x2(acc[0], acc[1]);
+  o.y = pack_bf16x2(acc[2], acc[3]);
+  o.z = pack_bf16x2(acc[4], acc[5]);
+  o.w = pack_bf16x2(acc[6], acc[7]);
+  return o;
+}
+
+// Shared-memory carve-up common to both kernels.
+struct Smem {
+  uint32_t stage0, extra0, bar0;
+  float* fl;
+  uint32_t* misc;
+  volatile int* abort_flag;
+};
+
+__device__ __forceinline__ Smem carve(uint8_t* raw, int nst, size_t extra_bytes, int nfloat, int nbar) {
+  uint8_t* sm = (uint8_t*)(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
+  Smem s;
+  uint8_t* extra = sm + (size_t)nst * STAGE_BYTES;
+  s.fl = (float*)(extra + extra_bytes);
+  uint64_t* bars = (uint64_t*)(s.fl + nfloat);
+  s.misc = (uint32_t*)(bars + nbar);
+  s.abort_flag = (volatile int*)(s.misc + 1);
+  s.stage0 = smem_u32(sm);
+  s.extra0 = smem_u32(extra);
+  s.bar0 = smem_u32(bars);
+  return s;
+}
+
+static size_t smem_bytes(int nst, size_t extra_bytes, int nfloat, int nbar) {
+  return 1024 + (size_t)nst * STAGE_BYTES + extra_bytes + (size_t)nfloat * 4 + (size_t)nbar * 8 + 16;
+}
+
+// ------------------------------------------------------------------------------------------------
+// forward / dgrad:  D[128 pixels, NOUT] = gathered[128, nsl * 64] . Wimg^T
+// ------------------------------------------------------------------------------------------------
+template <int NOUT, bool CSR>
+__global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int nst = a.nst;
+  // bars: full[nst], empty[nst], tfull[2], tempty[2], drain
+  const Smem sm = carve(smem_raw, nst, (size_t)a.nsl * NOUT * 128, NOUT, 2 * nst + 5);
+  float* bias_s = sm.fl;
+  volatile int* abort_flag = sm.abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t stage0 = smem_u32(stages), w0 = smem_u32(wsm);
-  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t stage0 = sm.stage0, w0 = sm.extra0, bar0 = sm.bar0;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (a.nst + s); };
-  auto tfull_bar = [&](int i) { return bar0 + 8u * (2 * a.nst + i); };
-  auto tempty_bar = [&](int i) { return bar0 + 8u * (2 * a.nst + 2 + i); };
-  const uint32_t drain_bar = bar0 + 8u * (2 * a.nst + 4);
+  auto empty_bar = [&](int s) { return bar0 + 8u * (nst + s); };
+  auto tfull_bar = [&](int i) { return bar0 + 8u * (2 * nst + i); };
+  auto tempty_bar = [&](int i) { return bar0 + 8u * (2 * nst + 2 + i); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * nst + 4);
   constexpr uint32_t TMEM_COLS = 2 * NOUT < 32 ? 32 : 2 * NOUT;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < a.nst; ++s) {
+    for (int s = 0; s < nst; ++s) {
       mbar_init(full_bar(s), N_PRODUCER_WARPS * 32);
       mbar_init(empty_bar(s), 1);
     }
@@ -121,16 +216,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) conv_fwd_tc_kernel(const FwdAr
     fence_barrier_init();
   }
   // resident operands: weight slices and bias
-  for (int i = threadIdx.x; i < a.nsl * NOUT * 8; i += FWD_THREADS)
+  for (int i = threadIdx.x; i < a.nsl * NOUT * 8; i += TC_THREADS)
     sts16(w0 + 16u * i, ldg16(a.wimg + i));
-  for (int i = threadIdx.x; i < NOUT; i += FWD_THREADS)
+  for (int i = threadIdx.x; i < NOUT; i += TC_THREADS)
     bias_s[i] = a.bias ? __bfloat162float(a.bias[i]) : 0.f;
   fence_proxy_async_smem();
-  if (warp == 0) tmem_alloc(smem_u32(misc), TMEM_COLS);
+  if (warp == 0) tmem_alloc(smem_u32(sm.misc), TMEM_COLS);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = *misc;
+  const uint32_t tmem_base = *sm.misc;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ MMA issuer
@@ -138,14 +233,14 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) conv_fwd_tc_kernel(const FwdAr
       constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 0, 0);
       uint32_t n = 0, it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < a.tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x, ++it) {
         const uint32_t acc = it & 1, aph = (it >> 1) & 1;
         ok = mbar_wait(tempty_bar(acc), aph ^ 1, abort_flag, 0x11);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * NOUT;
         for (int s = 0; s < a.nsl; ++s, ++n) {
-          const uint32_t st = n % a.nst, ph = (n / a.nst) & 1;
+          const uint32_t st = n % nst, ph = (n / nst) & 1;
           ok = mbar_wait(full_bar(st), ph, abort_flag, 0x12);
           if (!ok) break;
           tc_fence_after_sync();
@@ -168,12 +263,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) conv_fwd_tc_kernel(const FwdAr
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int r = q * 32 + lane;
     uint32_t it = 0;
-    for (int tile = blockIdx.x; tile < a.tiles; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < a.t.tiles; tile += gridDim.x, ++it) {
       const uint32_t acc = it & 1, aph = (it >> 1) & 1;
       long gp, p;
       int img;
       bool valid;
-      tile_pixel(a, tile, r, gp, img, p, valid);
+      tile_pixel(a.t, tile, r, gp, img, p, valid);
       if (!mbar_wait(tfull_bar(acc), aph, abort_flag, 0x21)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * NOUT;
@@ -206,13 +301,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) conv_fwd_tc_kernel(const FwdAr
     // ------------------------------------------------------------------ producers
     const int pw = warp - 1 - N_EPI_WARPS;
     const int g = lane >> 3, lg = lane & 7;  // 8 lanes cover the 128 bytes of one row
-    const int cpb = a.Cin / 64;
-    const long ipix = (long)a.IH * a.IW;
+    const int cpb = a.s.C / 64;
     uint32_t n = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < a.tiles && ok; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x) {
       for (int s = 0; s < a.nsl; ++s, ++n) {
-        const uint32_t st = n % a.nst, ph = (n / a.nst) & 1;
+        const uint32_t st = n % nst, ph = (n / nst) & 1;
         const int tap = s / cpb, cb = s % cpb;
         int okw = 1;
         if (lane == 0) okw = mbar_wait(empty_bar(st), ph ^ 1, abort_flag, 0x31) ? 1 : 0;
@@ -223,37 +317,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) conv_fwd_tc_kernel(const FwdAr
           long gp, p;
           int img;
           bool valid;
-          tile_pixel(a, tile, r, gp, img, p, valid);
-          Tap<float> tp;
-          tp.n = 0;
-          if (valid) {
-            const float2 m = __ldg(reinterpret_cast<const float2*>(a.map) + p * a.K + tap);
-            decode_tap<float, float>(m.x, m.y, a.IH, a.IW, a.interp, tp);
-          }
-          const bf16* xb = a.x + ((long)img * ipix) * a.Cin + cb * 64 + lg * 8;
-          uint4 v[4];
-          float wv[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const bool on = i < tp.n && tp.off[i] >= 0 && tp.w[i] != 0.f;
-            wv[i] = on ? tp.w[i] : 0.f;
-            v[i] = on ? ldg16(xb + (long)tp.off[i] * a.Cin) : make_uint4(0, 0, 0, 0);
-          }
-          float acc[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            bf16x2_fma(v[i].x, wv[i], acc[0], acc[1]);
-            bf16x2_fma(v[i].y, wv[i], acc[2], acc[3]);
-            bf16x2_fma(v[i].z, wv[i], acc[4], acc[5]);
-            bf16x2_fma(v[i].w, wv[i], acc[6], acc[7]);
-          }
-          uint4 o;
-          o.x = pack_bf16x2(acc[0], acc[1]);
-          o.y = pack_bf16x2(acc[2], acc[3]);
-          o.z = pack_bf16x2(acc[4], acc[5]);
-          o.w = pack_bf16x2(acc[6], acc[7]);
+          tile_pixel(a.t, tile, r, gp, img, p, valid);
+          const uint4 o = produce_row<CSR>(a.s, img, p, tap, cb, lg, valid);
           sts16(sbase + r * 128 + ((lg ^ (r & 7)) << 4), o);
         }
         fence_proxy_async_smem();
@@ -270,6 +335,282 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) conv_fwd_tc_kernel(const FwdAr
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// wgrad:  D_j[(slice 2j | slice 2j+1) x 64 channels, NOUT] += A_tile^T . gy_tile  over all tiles
+// ------------------------------------------------------------------------------------------------
+// The stage written by the producers, [pixel][64 channels] with the 128-byte swizzle, is read here
+// as an MN-major A operand (M = channels, reduction = pixels); two consecutive stages (leading
+// byte offset = STAGE_BYTES) make one M = 128 tile.  gy tiles [pixel][NOUT] are the MN-major B
+// operand.  Every CTA keeps its partial sums in tensor memory for the whole kernel and adds them
+// to gw with atomics at the end.
+constexpr int GY_STAGES = 2;
+
+template <int NOUT>
+__global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const GemmArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int nst = a.nst;  // even
+  // bars: full[nst], empty[nst], gfull[GY], gempty[GY], done
+  const Smem sm = carve(smem_raw, nst, (size_t)GY_STAGES * STAGE_BYTES, NOUT, 2 * nst + 2 * GY_STAGES + 1);
+  float* gb_s = sm.fl;
+  volatile int* abort_flag = sm.abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t stage0 = sm.stage0, gy0 = sm.extra0, bar0 = sm.bar0;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (nst + s); };
+  auto gfull_bar = [&](int i) { return bar0 + 8u * (2 * nst + i); };
+  auto gempty_bar = [&](int i) { return bar0 + 8u * (2 * nst + GY_STAGES + i); };
+  const uint32_t done_bar = bar0 + 8u * (2 * nst + 2 * GY_STAGES);
+  const int nmt = (a.nsl + 1) / 2;        // M = 128 tiles of the gradient
+  const int nsl_pad = nmt * 2;            // ring slots used per pixel tile
+  const uint32_t tmem_cols = nmt * NOUT <= 32 ? 32 : nmt * NOUT <= 64 ? 64 : nmt * NOUT <= 128 ? 128
+                             : nmt * NOUT <= 256 ? 256 : 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < nst; ++s) {
+      mbar_init(full_bar(s), N_PRODUCER_WARPS * 32);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int i = 0; i < GY_STAGES; ++i) {
+      mbar_init(gfull_bar(i), N_EPI_WARPS * 32);
+      mbar_init(gempty_bar(i), 1);
+    }
+    mbar_init(done_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  for (int i = threadIdx.x; i < NOUT; i += TC_THREADS) gb_s[i] = 0.f;
+  if (warp == 0) tmem_alloc(smem_u32(sm.misc), tmem_cols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *sm.misc;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 1, 1);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x, ++it) {
+        const uint32_t gs = it % GY_STAGES, gph = (it / GY_STAGES) & 1;
+        ok = mbar_wait(gfull_bar(gs), gph, abort_flag, 0x41);
+        if (!ok) break;
+        const uint64_t bdesc = make_desc_sw128(gy0 + gs * STAGE_BYTES, STAGE_BYTES, 1024);
+        for (int j = 0; j < nmt && ok; ++j) {
+          const uint32_t n0 = it * nsl_pad + 2 * j;
+          const uint32_t st = n0 % nst, ph = (n0 / nst) & 1;  // slots st and st + 1 share the phase
+          ok = mbar_wait(full_bar(st), ph, abort_flag, 0x42);
+          if (ok) ok = mbar_wait(full_bar(st + 1), ph, abort_flag, 0x43);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t adesc = make_desc_sw128(stage0 + st * STAGE_BYTES, STAGE_BYTES, 1024);
+#pragma unroll
+          for (int kk = 0; kk < TILE_M / 16; ++kk)  // 16 pixels per MMA: +2048 bytes each
+            mma_bf16_ss(tmem_base + j * NOUT, adesc + 128 * kk, bdesc + 128 * kk, idesc,
+                        (it | kk) != 0);
+          mma_commit(empty_bar(st));
+          mma_commit(empty_bar(st + 1));
+        }
+        if (ok) mma_commit(gempty_bar(gs));
+      }
+      mma_commit(done_bar);
+    }
+    __syncwarp();
+  } else if (warp <= N_EPI_WARPS) {
+    // ------------------------------------------------------------------ gy loader, then epilogue
+    const int lw = warp - 1;
+    const int g = lane >> 3, lg = lane & 7;
+    float bsum[NOUT / 8];  // bias gradient: this lane's 8 channels of every 64-channel block
+#pragma unroll
+    for (int j = 0; j < NOUT / 8; ++j) bsum[j] = 0.f;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x, ++it) {
+      const uint32_t gs = it % GY_STAGES, gph = (it / GY_STAGES) & 1;
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait(gempty_bar(gs), gph ^ 1, abort_flag, 0x51) ? 1 : 0;
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      if (!okw) { ok = false; break; }
+      const uint32_t sbase = gy0 + gs * STAGE_BYTES;
+      for (int r = lw * 4 + g; r < TILE_M; r += N_EPI_WARPS * 4) {
+        long gp, p;
+        int img;
+        bool valid;
+        tile_pixel(a.t, tile, r, gp, img, p, valid);
+#pragma unroll
+        for (int nb = 0; nb < NOUT / 64; ++nb) {
+          const uint4 v = valid ? ldg16(a.gy + gp * NOUT + nb * 64 + lg * 8) : make_uint4(0, 0, 0, 0);
+          // N > 64: consecutive 64-channel blocks are separate swizzle atoms, STAGE_BYTES apart
+          sts16(sbase + nb * STAGE_BYTES + r * 128 + ((lg ^ (r & 7)) << 4), v);
+          float* b8 = bsum + nb * 8;
+          bf16x2_fma(v.x, 1.f, b8[0], b8[1]);
+          bf16x2_fma(v.y, 1.f, b8[2], b8[3]);
+          bf16x2_fma(v.z, 1.f, b8[4], b8[5]);
+          bf16x2_fma(v.w, 1.f, b8[6], b8[7]);
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(gfull_bar(gs));
+    }
+    // bias gradient: lanes -> shared -> global
+    if (a.gb) {
+#pragma unroll
+      for (int nb = 0; nb < NOUT / 64; ++nb)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(gb_s + nb * 64 + lg * 8 + j, bsum[nb * 8 + j]);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(N_EPI_WARPS * 32) : "memory");
+    if (a.gb)
+      for (int i = lw * 32 + lane; i < NOUT; i += N_EPI_WARPS * 32) atomicAdd(a.gb + i, gb_s[i]);
+    // epilogue: partial weight gradient of this CTA
+    if (ok && mbar_wait(done_bar, 0, abort_flag, 0x52)) {
+      tc_fence_after_sync();
+      const int q = warp & 3;
+      const int m = q * 32 + lane;  // row of the M = 128 tile
+      const int cpb = a.s.C / 64;
+      for (int j = 0; j < nmt; ++j) {
+        const int sl = 2 * j + (m >> 6);
+        const bool live = sl < a.nsl;
+        const int tap = live ? sl / cpb : 0, ci = live ? (sl % cpb) * 64 + (m & 63) : 0;
+#pragma unroll
+        for (int cc = 0; cc < NOUT / 32; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + j * NOUT + cc * 32, v);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int co = cc * 32 + c;
+              atomicAdd(a.gw + ((long)co * a.s.C + ci) * a.s.K + tap, __uint_as_float(v[c]));
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ producers
+    const int pw = warp - 1 - N_EPI_WARPS;
+    const int g = lane >> 3, lg = lane & 7;
+    const int cpb = a.s.C / 64;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x, ++it) {
+      for (int s = 0; s < nsl_pad; ++s) {  // an odd slice count is padded with a zero slice
+        const uint32_t n = it * nsl_pad + s;
+        const uint32_t st = n % nst, ph = (n / nst) & 1;
+        const int tap = s / cpb, cb = s % cpb;
+        int okw = 1;
+        if (lane == 0) okw = mbar_wait(empty_bar(st), ph ^ 1, abort_flag, 0x61) ? 1 : 0;
+        okw = __shfl_sync(0xffffffffu, okw, 0);
+        if (!okw) { ok = false; break; }
+        const uint32_t sbase = stage0 + st * STAGE_BYTES;
+        for (int r = pw * 4 + g; r < TILE_M; r += N_PRODUCER_WARPS * 4) {
+          long gp, p;
+          int img;
+          bool valid;
+          tile_pixel(a.t, tile, r, gp, img, p, valid);
+          const uint4 o = produce_row<false>(a.s, img, p, tap, cb, lg, valid && s < a.nsl);
+          sts16(sbase + r * 128 + ((lg ^ (r & 7)) << 4), o);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(full_bar(st));
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    // all MMAs have completed once done_bar fired; if the epilogue gave up, wait for it here
+    if (lane == 0) mbar_wait(done_bar, 0, abort_flag, 0x44);
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// operand preparation
+// ------------------------------------------------------------------------------------------------
+
+// Weight (Cout, Cin, K) -> slices of [rows][64 channels] bf16, each row 128 bytes with its 16-byte
+// chunks XOR-swizzled by (row & 7): exactly what tcgen05.mma expects for a K-major operand with
+// the 128-byte swizzle, so the kernel copies it into shared memory linearly.
+// transpose = 0 (forward): rows = output channels, slices run over (tap, input-channel block).
+// transpose = 1 (dgrad)  : rows = input channels,  slices run over (tap, output-channel block).
+__global__ void weight_image_kernel(const bf16* __restrict__ w, uint16_t* __restrict__ img, int rows,
+                                    int red, int K, int transpose, int Cin_w) {
+  const int cpb = red / 64;
+  const long total = (long)K * cpb * rows * 64;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
+       i += (long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % 64);
+    const int n = (int)((i / 64) % rows);
+    const int s = (int)(i / (64L * rows));
+    const int tap = s / cpb, cb = s % cpb;
+    const int r = cb * 64 + c;
+    const long src = transpose ? ((long)r * Cin_w + n) * K + tap : ((long)n * Cin_w + r) * K + tap;
+    const long dst = (long)s * rows * 64 + (long)n * 64 + ((((c >> 3) ^ (n & 7)) << 3) | (c & 7));
+    img[dst] = reinterpret_cast<const uint16_t*>(w)[src];
+  }
+}
+
+// ---- inverse map -------------------------------------------------------------------------------
+// For every (input pixel q, tap k): the list of (grid pixel p, weight) pairs such that the forward
+// sample of tap k at p reads q with that weight.  Built once per sample map; it turns the
+// scatter-add of the reference's MappedCol2Im2D (include/nn/common/mapped_im2col.h:45-78) into a
+// gather.  Layout of the buffer: int off[nkeys + 1], padded to 16 bytes, then int2 ent[].
+
+struct InvArgs {
+  const float* map;
+  int* cnt;  // pass 1: per-key counts; pass 2: per-key cursors
+  const int* off;
+  int2* ent;
+  long ngrid;  // OH*OW
+  int K, IH, IW, interp;
+};
+
+template <int PASS>
+__global__ void invmap_pass_kernel(InvArgs a) {
+  const long total = a.ngrid * a.K;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
+       i += (long)gridDim.x * blockDim.x) {
+    const long p = i / a.K;
+    const int k = (int)(i % a.K);
+    const float2 m = __ldg(reinterpret_cast<const float2*>(a.map) + i);
+    Tap<float> tp;
+    decode_tap<float, float>(m.x, m.y, a.IH, a.IW, a.interp, tp);
+    for (int c = 0; c < tp.n; ++c) {
+      if (tp.off[c] < 0 || tp.w[c] == 0.f) continue;
+      const long key = (long)tp.off[c] * a.K + k;
+      if (PASS == 1) {
+        atomicAdd(a.cnt + key, 1);
+      } else {
+        const int pos = a.off[key] + atomicAdd(a.cnt + key, 1);
+        a.ent[pos] = make_int2((int)p, __float_as_int(tp.w[c]));
+      }
+    }
+  }
+}
+
+// Lists are filled in arrival order; sorting each by (grid pixel, weight bits) makes the sums, and
+// so the whole backward pass, reproducible from run to run.
+__global__ void invmap_sort_kernel(const int* __restrict__ off, int2* __restrict__ ent, long nkeys) {
+  for (long key = blockIdx.x * (long)blockDim.x + threadIdx.x; key < nkeys;
+       key += (long)gridDim.x * blockDim.x) {
+    const int b = off[key], e = off[key + 1];
+    for (int i = b + 1; i < e; ++i) {
+      const int2 v = ent[i];
+      int j = i - 1;
+      while (j >= b && (ent[j].x > v.x || (ent[j].x == v.x && ent[j].y > v.y))) {
+        ent[j + 1] = ent[j];
+        --j;
+      }
+      ent[j + 1] = v;
+    }
+  }
+}
+
 static int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -281,27 +622,34 @@ static int sm_count() {
   return n;
 }
 
-static size_t fwd_smem_bytes(int nst, int nsl, int nout) {
-  return 1024 + (size_t)nst * STAGE_BYTES + (size_t)nsl * nout * 128 + nout * 4 +
-         (2 * nst + 5) * 8 + 16;
-}
-
-// Number of pipeline stages that fit beside the resident weights (0 = does not fit).
-static int fwd_stages(int nsl, int nout) {
-  for (int nst = 8; nst >= 3; --nst)
-    if (fwd_smem_bytes(nst, nsl, nout) <= 200 * 1024) return nst;
+// Pipeline stages that fit beside `extra` bytes of resident data (0 = does not fit).
+static int pick_stages(size_t extra, int nfloat, int max_st, int min_st, bool even) {
+  for (int nst = max_st; nst >= min_st; --nst) {
+    if (even && (nst & 1)) continue;
+    if (smem_bytes(nst, extra, nfloat, 2 * nst + 8) <= SMEM_LIMIT) return nst;
+  }
   return 0;
 }
+
+template <typename Kern>
+static bool allow_big_smem(Kern k) {
+  return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) ==
+         cudaSuccess;
+}
+
+static bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
 }  // namespace tc
 
 using namespace tc;
 
+// ---- forward ---------------------------------------------------------------------------------------
+
 bool conv_tc_fwd_supported(const mc_desc* d) {
   if (d->dtype != MC_BF16 || d->layout != MC_NHWC || d->P != 0) return false;
   if (d->C_in % 64 != 0 || d->C_out != 64) return false;
   const int nsl = d->K * (d->C_in / 64);
-  return fwd_stages(nsl, d->C_out) > 0;
+  return pick_stages((size_t)nsl * d->C_out * 128, d->C_out, 8, 3, false) > 0;
 }
 
 size_t conv_tc_fwd_ws(const mc_desc* d) {
@@ -311,46 +659,158 @@ size_t conv_tc_fwd_ws(const mc_desc* d) {
 int conv_tc_fwd_launch(const mc_desc* d, const void* x, const void* map, const void* w,
                        const void* bias, void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (!ws || ws_bytes < conv_tc_fwd_ws(d)) return MC_ERR_WORKSPACE;
-  if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)ws | (uintptr_t)map) & 15) return MC_ERR_BAD_ARG;
-  FwdArgs a;
-  a.x = (const bf16*)x; a.map = (const float*)map; a.wimg = (const uint4*)ws;
-  a.bias = (const bf16*)bias; a.y = (bf16*)y;
-  a.Cin = d->C_in; a.IH = d->IH; a.IW = d->IW; a.OW = d->OW; a.K = d->K; a.interp = d->interp;
+  if (!aligned16(x) || !aligned16(y) || !aligned16(ws) || !aligned16(map)) return MC_ERR_BAD_ARG;
+  GemmArgs a = {};
+  a.s.src = (const bf16*)x; a.s.spix = (long)d->IH * d->IW; a.s.C = d->C_in;
+  a.s.SH = d->IH; a.s.SW = d->IW; a.s.K = d->K; a.s.interp = d->interp;
+  a.s.map = (const float*)map;
+  if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
+  a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias; a.y = (bf16*)y;
   a.nsl = d->K * (d->C_in / 64);
-  a.nst = fwd_stages(a.nsl, d->C_out);
-  a.opix = (long)d->OH * d->OW;
-  a.mtot = (long)d->B * a.opix;
-  a.tile2d = (d->OH % 8 == 0 && d->OW % 16 == 0) ? 1 : 0;
-  a.tiles_x = d->OW / 16;
-  a.tiles_per_img = (d->OH / 8) * (d->OW / 16);
-  const long tiles = a.tile2d ? (long)d->B * a.tiles_per_img : (a.mtot + TILE_M - 1) / TILE_M;
-  if (tiles >= (1L << 31)) return MC_ERR_TOO_LARGE;
-  a.tiles = (int)tiles;
+  a.nst = pick_stages((size_t)a.nsl * d->C_out * 128, d->C_out, 8, 3, false);
   const long nw = (long)d->K * d->C_in * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_out,
                                                          d->C_in, d->K, 0, d->C_in), MC_COUNT(1);
-  const size_t smem = fwd_smem_bytes(a.nst, a.nsl, d->C_out);
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(conv_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             220 * 1024) != cudaSuccess)
-      return MC_ERR_LAUNCH;
-    attr_set = true;
-  }
-  const int grid = a.tiles < sm_count() ? a.tiles : sm_count();
-  conv_fwd_tc_kernel<64><<<grid, FWD_THREADS, smem, st>>>(a), MC_COUNT(1);
+  static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, false>);
+  if (!attr) return MC_ERR_LAUNCH;
+  const size_t smem = smem_bytes(a.nst, (size_t)a.nsl * d->C_out * 128, d->C_out, 2 * a.nst + 5);
+  const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
+  conv_gemm_tc_kernel<64, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
 
-bool conv_tc_dgrad_supported(const mc_desc*) { return false; }
-size_t conv_tc_dgrad_ws(const mc_desc*) { return 0; }
-int conv_tc_dgrad_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
-                         void*, size_t, cudaStream_t) { return MC_ERR_UNSUPPORTED; }
-bool conv_tc_wgrad_supported(const mc_desc*) { return false; }
+// ---- inverse map ---------------------------------------------------------------------------------------
+
+static size_t inv_off_bytes(const mc_desc* d) {
+  const size_t nkeys = (size_t)d->IH * d->IW * d->K;
+  return ((nkeys + 1) * sizeof(int) + 15) & ~(size_t)15;
+}
+static size_t inv_max_entries(const mc_desc* d) {
+  const size_t per = (d->interp == 1 || d->interp == 2) ? 4 : 1;
+  return (size_t)d->OH * d->OW * d->K * per;
+}
+
+bool invmap_supported(const mc_desc* d) {
+  if (d->P != 0 || d->dtype == MC_F64) return false;
+  return (size_t)d->IH * d->IW * d->K < (1u << 30) && inv_max_entries(d) < (1u << 31);
+}
+size_t invmap_bytes(const mc_desc* d) { return inv_off_bytes(d) + inv_max_entries(d) * sizeof(int2); }
+
+static size_t scan_temp_bytes(size_t n) {
+  size_t t = 0;
+  cub::DeviceScan::ExclusiveSum(nullptr, t, (const int*)nullptr, (int*)nullptr, (int)n);
+  return (t + 255) & ~(size_t)255;
+}
+size_t invmap_build_ws(const mc_desc* d) {
+  const size_t nkeys = (size_t)d->IH * d->IW * d->K;
+  return (((nkeys + 1) * sizeof(int) + 255) & ~(size_t)255) + scan_temp_bytes(nkeys + 1);
+}
+
+int invmap_build_launch(const mc_desc* d, const void* map, void* inv, void* ws, size_t ws_bytes,
+                        cudaStream_t st) {
+  if (!invmap_supported(d)) return MC_ERR_UNSUPPORTED;
+  if (!ws || ws_bytes < invmap_build_ws(d)) return MC_ERR_WORKSPACE;
+  if (!aligned16(inv) || !aligned16(ws)) return MC_ERR_BAD_ARG;
+  const size_t nkeys = (size_t)d->IH * d->IW * d->K;
+  const size_t cnt_bytes = ((nkeys + 1) * sizeof(int) + 255) & ~(size_t)255;
+  InvArgs a;
+  a.map = (const float*)map;
+  a.cnt = (int*)ws;
+  a.off = (const int*)inv;
+  a.ent = (int2*)((uint8_t*)inv + inv_off_bytes(d));
+  a.ngrid = (long)d->OH * d->OW;
+  a.K = d->K; a.IH = d->IH; a.IW = d->IW; a.interp = d->interp;
+  if (cudaMemsetAsync(a.cnt, 0, (nkeys + 1) * sizeof(int), st) != cudaSuccess) return MC_ERR_LAUNCH;
+  const int grid = grid_for(a.ngrid * a.K, 256);
+  invmap_pass_kernel<1><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  size_t tb = ws_bytes - cnt_bytes;
+  if (cub::DeviceScan::ExclusiveSum((uint8_t*)ws + cnt_bytes, tb, a.cnt, (int*)inv, (int)(nkeys + 1),
+                                    st) != cudaSuccess)
+    return MC_ERR_LAUNCH;
+  if (cudaMemsetAsync(a.cnt, 0, (nkeys + 1) * sizeof(int), st) != cudaSuccess) return MC_ERR_LAUNCH;
+  invmap_pass_kernel<2><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  invmap_sort_kernel<<<grid_for((long)nkeys, 256), 256, 0, st>>>(a.off, a.ent, (long)nkeys), MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
+
+// ---- dgrad through the inverse map ---------------------------------------------------------------------
+
+bool conv_tc_dgrad_supported(const mc_desc* d) {
+  if (d->dtype != MC_BF16 || d->layout != MC_NHWC || d->P != 0) return false;
+  if (d->C_out % 64 != 0 || d->C_in != 64) return false;
+  if (!invmap_supported(d)) return false;
+  const int nsl = d->K * (d->C_out / 64);
+  return pick_stages((size_t)nsl * d->C_in * 128, d->C_in, 8, 3, false) > 0;
+}
+
+size_t conv_tc_dgrad_ws(const mc_desc* d) {
+  return (size_t)d->K * d->C_in * d->C_out * sizeof(bf16);
+}
+
+int conv_tc_dgrad_launch(const mc_desc* d, const void* gy, const void* inv, const void* w,
+                         const void* bias_out, void* gx, void* ws, size_t ws_bytes,
+                         cudaStream_t st) {
+  if (!ws || ws_bytes < conv_tc_dgrad_ws(d)) return MC_ERR_WORKSPACE;
+  if (!aligned16(gy) || !aligned16(gx) || !aligned16(ws) || !aligned16(inv)) return MC_ERR_BAD_ARG;
+  GemmArgs a = {};
+  a.s.src = (const bf16*)gy; a.s.spix = (long)d->OH * d->OW; a.s.C = d->C_out;
+  a.s.K = d->K; a.s.interp = d->interp;
+  a.s.inv_off = (const int*)inv;
+  a.s.inv_ent = (const int2*)((const uint8_t*)inv + inv_off_bytes(d));
+  if (!make_tiling(a.t, d->B, d->IH, d->IW)) return MC_ERR_TOO_LARGE;
+  a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias_out; a.y = (bf16*)gx;
+  a.nsl = d->K * (d->C_out / 64);
+  a.nst = pick_stages((size_t)a.nsl * d->C_in * 128, d->C_in, 8, 3, false);
+  const long nw = (long)d->K * d->C_in * d->C_out;
+  weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_in,
+                                                         d->C_out, d->K, 1, d->C_in), MC_COUNT(1);
+  static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, true>);
+  if (!attr) return MC_ERR_LAUNCH;
+  const size_t smem = smem_bytes(a.nst, (size_t)a.nsl * d->C_in * 128, d->C_in, 2 * a.nst + 5);
+  const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
+  conv_gemm_tc_kernel<64, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
+
+// ---- wgrad -----------------------------------------------------------------------------------------------
+
+bool conv_tc_wgrad_supported(const mc_desc* d) {
+  if (d->dtype != MC_BF16 || d->layout != MC_NHWC || d->P != 0) return false;
+  if (d->C_in % 64 != 0 || d->C_out != 64) return false;
+  const int nsl = d->K * (d->C_in / 64);
+  return ((nsl + 1) / 2) * d->C_out <= 512;  // partial sums must fit the 512 TMEM columns
+}
 size_t conv_tc_wgrad_ws(const mc_desc*) { return 0; }
-int conv_tc_wgrad_launch(const mc_desc*, const void*, const void*, const void*, void*, void*, void*,
-                         size_t, cudaStream_t) { return MC_ERR_UNSUPPORTED; }
+
+int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const void* map, void* gw,
+                         void* gb, void* ws, size_t ws_bytes, cudaStream_t st) {
+  (void)ws; (void)ws_bytes;
+  if (!aligned16(gy) || !aligned16(x) || !aligned16(map)) return MC_ERR_BAD_ARG;
+  GemmArgs a = {};
+  a.s.src = (const bf16*)x; a.s.spix = (long)d->IH * d->IW; a.s.C = d->C_in;
+  a.s.SH = d->IH; a.s.SW = d->IW; a.s.K = d->K; a.s.interp = d->interp;
+  a.s.map = (const float*)map;
+  if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
+  a.gy = (const bf16*)gy; a.gw = (float*)gw; a.gb = (float*)gb;
+  a.nsl = d->K * (d->C_in / 64);
+  a.nst = pick_stages((size_t)GY_STAGES * STAGE_BYTES, d->C_out, 10, 4, true);
+  if (a.nst == 0) return MC_ERR_UNSUPPORTED;
+  if (cudaMemsetAsync(gw, 0, (size_t)d->C_out * d->C_in * d->K * sizeof(float), st) != cudaSuccess)
+    return MC_ERR_LAUNCH;
+  if (gb && cudaMemsetAsync(gb, 0, (size_t)d->C_out * sizeof(float), st) != cudaSuccess)
+    return MC_ERR_LAUNCH;
+  static bool attr = allow_big_smem(conv_wgrad_tc_kernel<64>);
+  if (!attr) return MC_ERR_LAUNCH;
+  const size_t smem = smem_bytes(a.nst, (size_t)GY_STAGES * STAGE_BYTES, d->C_out,
+                                 2 * a.nst + 2 * GY_STAGES + 1);
+  const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
+  conv_wgrad_tc_kernel<64><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
 
 int device_status_read(cudaStream_t st, int reset) {
   int v = 0;

@@ -8,6 +8,8 @@ device.  Differences: tensors must be CUDA tensors (there is no CPU path), bf16 
 accepted (with a float32 sample map), and a 4-D activation may be channels_last, in which case
 the outputs are channels_last too.
 """
+import weakref
+
 import torch
 
 from . import _lib
@@ -95,6 +97,39 @@ def _P(interp_weights):
 
 
 # ------------------------------------------------------------------------------------------
+# inverse-map cache
+# ------------------------------------------------------------------------------------------
+# The inverse map depends only on the sample map tensor and the image sizes.  A layer is called
+# with the same map tensor step after step, so the last few are kept, keyed by the tensor's
+# identity and version counter (an in-place edit of the map invalidates its entry).
+_INV_CACHE = []
+_INV_CACHE_SIZE = 8
+
+
+def _inverse_map(d, sample_map):
+    key = (sample_map.data_ptr(), sample_map._version, tuple(sample_map.shape), d.IH, d.IW,
+           d.interp, sample_map.device.index)
+    for i, (k, ref, inv) in enumerate(_INV_CACHE):
+        if k == key and ref() is sample_map:
+            if i:
+                _INV_CACHE.insert(0, _INV_CACHE.pop(i))
+            return inv
+    L = lib()
+    dev = sample_map.device
+    nbytes = L.mc_invmap_bytes(d)
+    inv = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    wst, wsn, wsp = _ws(L.mc_invmap_build_workspace_bytes(d), dev)
+    check(L.mc_invmap_build(d, sample_map.data_ptr(), inv.data_ptr(), nbytes, wsp, wsn, _stream()))
+    _INV_CACHE.insert(0, (key, weakref.ref(sample_map), inv))
+    del _INV_CACHE[_INV_CACHE_SIZE:]
+    return inv
+
+
+def clear_inverse_map_cache():
+    del _INV_CACHE[:]
+
+
+# ------------------------------------------------------------------------------------------
 # convolution
 # ------------------------------------------------------------------------------------------
 
@@ -135,11 +170,17 @@ def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias,
     gb = torch.empty((Cout,), dtype=acc, device=dev)
     L = lib()
     with torch.cuda.device(dev):
-        wst, wsn, wsp = _ws(max(L.mc_conv_dgrad_workspace_bytes(d),
+        inv = _inverse_map(d, sample_map) if L.mc_conv_dgrad_inv_supported(d) else None
+        wst, wsn, wsp = _ws(max(L.mc_conv_dgrad_workspace_bytes(d) if inv is None else
+                                L.mc_conv_dgrad_inv_workspace_bytes(d),
                                 L.mc_conv_wgrad_workspace_bytes(d)), dev)
-        check(L.mc_conv_dgrad(d, grad_output.data_ptr(), sample_map.data_ptr(),
-                              _ptr(interp_weights), weight.data_ptr(), None, gx.data_ptr(), wsp, wsn,
-                              _stream()))
+        if inv is not None:
+            check(L.mc_conv_dgrad_inv(d, grad_output.data_ptr(), inv.data_ptr(), weight.data_ptr(),
+                                      None, gx.data_ptr(), wsp, wsn, _stream()))
+        else:
+            check(L.mc_conv_dgrad(d, grad_output.data_ptr(), sample_map.data_ptr(),
+                                  _ptr(interp_weights), weight.data_ptr(), None, gx.data_ptr(), wsp,
+                                  wsn, _stream()))
         check(L.mc_conv_wgrad(d, grad_output.data_ptr(), input.data_ptr(), sample_map.data_ptr(),
                               _ptr(interp_weights), gw.data_ptr(), gb.data_ptr(), wsp, wsn,
                               _stream()))

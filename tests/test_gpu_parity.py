@@ -160,6 +160,41 @@ def test_bf16_tensor_core_conv_forward(shape, interp):
     H.assert_close(y.float(), want, 2e-2, "tc fwd")
 
 
+@pytest.mark.parametrize("shape", [
+    (2, 64, 64, 16, 32, 16, 32, 9),
+    (1, 64, 64, 11, 13, 9, 7, 4),
+    (3, 64, 64, 24, 48, 8, 16, 3),
+    (2, 64, 64, 1, 2562, 1, 642, 7),
+    (2, 64, 64, 64, 128, 64, 128, 9),
+])
+@pytest.mark.parametrize("interp", [0, 1, 2])
+def test_bf16_tensor_core_conv_backward(shape, interp):
+    """Input gradient through the inverse map and weight / bias gradient on the tensor cores
+    against the oracle in float32 on the bf16-rounded inputs (2e-2); the input gradient must also
+    repeat bit for bit, since the gather form has no atomics."""
+    from mappedconvolutions_b200 import ops
+    B, Cin, Cout, IH, IW, OH, OW, K = shape
+    g = torch.Generator().manual_seed(sum(shape) + 7 * interp)
+    bf = lambda t: t.to(torch.bfloat16)
+    x = bf(torch.randn(B, Cin, IH, IW, generator=g))
+    gy = bf(torch.randn(B, Cout, OH, OW, generator=g))
+    w = bf(torch.randn(Cout, Cin, K, generator=g))
+    b = bf(torch.randn(Cout, generator=g))
+    m = (torch.rand(OH, OW, K, 2, generator=g) * torch.tensor([IW + 1.0, IH + 1.0]) - 1.0).contiguous()
+    if IH == 1:
+        m[..., 1] = 0
+    want = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, interp)
+    cl = lambda t: t.cuda().contiguous(memory_format=torch.channels_last)
+    md = m.cuda()
+    got = ops.mapped_conv_backward(cl(gy), md, cl(x), w.cuda(), b.cuda(), K, interp)
+    assert _device_status() == 0
+    H.assert_close(got[0].float(), want[0], 2e-2, "tc dgrad")
+    H.assert_close(got[1].float(), want[1], 2e-2, "tc wgrad")
+    H.assert_close(got[2].float(), want[2], 2e-2, "tc bias grad")
+    again = ops.mapped_conv_backward(cl(gy), md, cl(x), w.cuda(), b.cuda(), K, interp)
+    assert torch.equal(got[0], again[0])
+
+
 def test_bf16_pool_and_resample():
     from mappedconvolutions_b200 import ops
     g = torch.Generator().manual_seed(12)
