@@ -107,47 +107,77 @@ __device__ __forceinline__ void blend4(const uint4& v, float w, float (&acc)[8])
   bf16x2_fma(v.w, w, acc[6], acc[7]);
 }
 
-// One row (pixel p of image img, tap, 64-channel block cb) of the gathered operand, computed by
-// the 8 lanes of a group: lane lg owns channels [8 lg, 8 lg + 8).
-template <bool CSR>
-__device__ __forceinline__ uint4 produce_row(const Source& s, int img, long p, int tap, int cb, int lg,
-                                             bool valid) {
-  float acc[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-  const bf16* sb = s.src + ((long)img * s.spix) * s.C + cb * 64 + lg * 8;
-  if (!CSR) {
-    Tap<float> tp;
-    tp.n = 0;
-    if (valid) {
-      const float2 m = __ldg(reinterpret_cast<const float2*>(s.map) + p * s.K + tap);
-      decode_tap<float, float>(m.x, m.y, s.SH, s.SW, s.interp, tp);
-    }
-    uint4 v[4];
-    float wv[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const bool on = i < tp.n && tp.off[i] >= 0 && tp.w[i] != 0.f;
-      wv[i] = on ? tp.w[i] : 0.f;
-      v[i] = on ? ldg16(sb + (long)tp.off[i] * s.C) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) blend4(v[i], wv[i], acc);
-  } else if (valid) {
-    const long key = p * s.K + tap;
-    int e = __ldg(s.inv_off + key);
-    const int end = __ldg(s.inv_off + key + 1);
-    for (; e + 1 < end; e += 2) {
-      const int2 e0 = __ldg(s.inv_ent + e), e1 = __ldg(s.inv_ent + e + 1);
-      const uint4 v0 = ldg16(sb + (long)e0.x * s.C), v1 = ldg16(sb + (long)e1.x * s.C);
-      blend4(v0, __int_as_float(e0.y), acc);
-      blend4(v1, __int_as_float(e1.y), acc);
-    }
-    if (e < end) {
-      const int2 e0 = __ldg(s.inv_ent + e);
-      blend4(ldg16(sb + (long)e0.x * s.C), __int_as_float(e0.y), acc);
-    }
+// ---- producer ------------------------------------------------------------------------------------
+// A group of 8 lanes builds one 128-byte row (pixel, tap, 64-channel block) of the gathered
+// operand; lane lg owns channels [8 lg, 8 lg + 8).
+//
+// Map mode (forward, wgrad): the sample map of a tile is decoded ONCE per (pixel, tap) into a
+// shared-memory table of (4 source pixels, 4 weights) entries - one coalesced pass over the
+// tile's slice of the map by all producer threads - so that the per-row work is two shared loads,
+// four predicated 16-byte global loads and the fp32 blend.  The table is double buffered; one
+// named barrier per tile keeps the producer warps in step.
+// Inverse-map mode (dgrad): every row walks its (source pixel, weight) list straight from global
+// memory.
+
+struct TapEnt {   // 32 bytes
+  int off[4];     // source pixel index inside the whole (B, pix) tensor, or -1
+  float w[4];
+};
+
+constexpr int N_PRODUCER_THREADS = N_PRODUCER_WARPS * 32;
+
+__device__ __forceinline__ void producer_bar() {
+  asm volatile("bar.sync 2, %0;" ::"n"(N_PRODUCER_THREADS) : "memory");
+}
+
+__device__ __forceinline__ void decode_tile(const Source& s, const Tiling& t, int tile, TapEnt* tab,
+                                            int ptid) {
+  // per-tile constants (2-D tiles): image and the pixel of the tile's corner
+  int img0 = 0, ty = 0, tx = 0;
+  if (t.tile2d) {
+    img0 = tile / t.tiles_per_img;
+    const int tt = tile - img0 * t.tiles_per_img;
+    ty = tt / t.tiles_x;
+    tx = tt - ty * t.tiles_x;
   }
+  const int n = TILE_M * s.K;
+  for (int e = ptid; e < n; e += N_PRODUCER_THREADS) {
+    const int r = e / s.K, k = e - r * s.K;
+    long p;
+    int img;
+    bool valid = true;
+    if (t.tile2d) {
+      img = img0;
+      p = (long)(ty * 8 + (r >> 4)) * t.W + tx * 16 + (r & 15);
+    } else {
+      const long gp = (long)tile * TILE_M + r;
+      valid = gp < t.mtot;
+      img = valid ? (int)(gp / t.npix) : 0;
+      p = valid ? gp - (long)img * t.npix : 0;
+    }
+    TapEnt ent;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { ent.off[i] = -1; ent.w[i] = 0.f; }
+    if (valid) {
+      const float2 m = __ldg(reinterpret_cast<const float2*>(s.map) + p * s.K + k);
+      Tap<float> tp;
+      decode_tap<float, float>(m.x, m.y, s.SH, s.SW, s.interp, tp);
+      const int ibase = img * (int)s.spix;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool on = i < tp.n && tp.off[i] >= 0 && tp.w[i] != 0.f;
+        ent.off[i] = on ? ibase + tp.off[i] : -1;
+        ent.w[i] = on ? tp.w[i] : 0.f;
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(tab + e);
+    dst[0] = make_uint4(ent.off[0], ent.off[1], ent.off[2], ent.off[3]);
+    dst[1] = make_uint4(__float_as_uint(ent.w[0]), __float_as_uint(ent.w[1]),
+                        __float_as_uint(ent.w[2]), __float_as_uint(ent.w[3]));
+  }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
   uint4 o;
   o.x = pack_bf16x2(acc[0], acc[1]);
   o.y = pack_bf16x2(acc[2], acc[3]);
@@ -156,9 +186,137 @@ __device__ __forceinline__ uint4 produce_row(const Source& s, int img, long p, i
   return o;
 }
 
+// Map-mode producer warp.  nslots ring slots are consumed per tile, of which the first nsl carry
+// data (an odd slice count of the wgrad kernel is padded with a zero slice).
+__device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling& t, int nsl,
+                                                  int nslots, int nst, uint32_t stage0,
+                                                  uint32_t full0, uint32_t empty0, TapEnt* table,
+                                                  volatile int* abort_flag, int pw, int lane,
+                                                  int code) {
+  const int g = lane >> 3, lg = lane & 7;
+  const int ptid = pw * 32 + lane;
+  const int cpb = s.C / 64;
+  const int r0 = pw * 4 + g, r1 = r0 + N_PRODUCER_WARPS * 4;  // the two rows of a stage this group owns
+  const uint32_t so0 = r0 * 128 + ((lg ^ (r0 & 7)) << 4), so1 = r1 * 128 + ((lg ^ (r1 & 7)) << 4);
+  const bf16* srcl = s.src + lg * 8;
+  uint32_t n = 0, it = 0;
+  for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x, ++it) {
+    TapEnt* tab = table + (size_t)(it & 1) * TILE_M * s.K;
+    decode_tile(s, t, tile, tab, ptid);
+    producer_bar();
+    for (int sl = 0; sl < nslots; ++sl, ++n) {
+      const uint32_t st = n % nst, ph = (n / nst) & 1;
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait(empty0 + 8u * st, ph ^ 1, abort_flag, code) ? 1 : 0;
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      if (!okw) return;
+      const uint32_t sbase = stage0 + st * STAGE_BYTES;
+      float a0[8], a1[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a0[j] = a1[j] = 0.f;
+      if (sl < nsl) {
+        const int tap = sl / cpb, cb = sl - tap * cpb;
+        const uint4* e0 = reinterpret_cast<const uint4*>(tab + r0 * s.K + tap);
+        const uint4* e1 = reinterpret_cast<const uint4*>(tab + r1 * s.K + tap);
+        const uint4 o0 = e0[0], w0 = e0[1], o1 = e1[0], w1 = e1[1];
+        const bf16* sb = srcl + cb * 64;
+        const int of[8] = {(int)o0.x, (int)o0.y, (int)o0.z, (int)o0.w,
+                           (int)o1.x, (int)o1.y, (int)o1.z, (int)o1.w};
+        const float wf[8] = {__uint_as_float(w0.x), __uint_as_float(w0.y), __uint_as_float(w0.z),
+                             __uint_as_float(w0.w), __uint_as_float(w1.x), __uint_as_float(w1.y),
+                             __uint_as_float(w1.z), __uint_as_float(w1.w)};
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          v[i] = of[i] >= 0 ? ldg16(sb + (long)of[i] * s.C) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) blend4(v[i], wf[i], a0);
+#pragma unroll
+        for (int i = 4; i < 8; ++i) blend4(v[i], wf[i], a1);
+      }
+      sts16(sbase + so0, pack8(a0));
+      sts16(sbase + so1, pack8(a1));
+      fence_proxy_async_smem();
+      mbar_arrive(full0 + 8u * st);
+    }
+  }
+}
+
+// Inverse-map producer warp (dgrad).
+__device__ __forceinline__ void producer_loop_inv(const Source& s, const Tiling& t, int nsl, int nst,
+                                                  uint32_t stage0, uint32_t full0, uint32_t empty0,
+                                                  volatile int* abort_flag, int pw, int lane,
+                                                  int code) {
+  const int g = lane >> 3, lg = lane & 7;
+  const int cpb = s.C / 64;
+  const bf16* srcl = s.src + lg * 8;
+  uint32_t n = 0;
+  for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x) {
+    // the two rows of every stage this group owns: pixel and image are the same for all slices
+    long key[2], base[2];
+    uint32_t so[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = pw * 4 + g + h * N_PRODUCER_WARPS * 4;
+      long gp, p;
+      int img;
+      bool valid;
+      tile_pixel(t, tile, r, gp, img, p, valid);
+      key[h] = valid ? p * s.K : -1;
+      base[h] = (long)img * s.spix * s.C;
+      so[h] = r * 128 + ((lg ^ (r & 7)) << 4);
+    }
+    for (int sl = 0; sl < nsl; ++sl, ++n) {
+      const uint32_t st = n % nst, ph = (n / nst) & 1;
+      const int tap = sl / cpb, cb = sl - tap * cpb;
+      // list ranges first, so that they are in flight while we wait for the stage
+      int beg[2], end[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        beg[h] = end[h] = 0;
+        if (key[h] >= 0) {
+          beg[h] = __ldg(s.inv_off + key[h] + tap);
+          end[h] = __ldg(s.inv_off + key[h] + tap + 1);
+        }
+      }
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait(empty0 + 8u * st, ph ^ 1, abort_flag, code) ? 1 : 0;
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      if (!okw) return;
+      const uint32_t sbase = stage0 + st * STAGE_BYTES;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        const bf16* sb = srcl + base[h] + cb * 64;
+        int e = beg[h];
+        for (; e + 3 < end[h]; e += 4) {
+          int2 en[4];
+          uint4 v[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) en[i] = __ldg(s.inv_ent + e + i);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[i] = ldg16(sb + (long)en[i].x * s.C);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) blend4(v[i], __int_as_float(en[i].y), acc);
+        }
+        for (; e < end[h]; ++e) {
+          const int2 en = __ldg(s.inv_ent + e);
+          blend4(ldg16(sb + (long)en.x * s.C), __int_as_float(en.y), acc);
+        }
+        sts16(sbase + so[h], pack8(acc));
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(full0 + 8u * st);
+    }
+  }
+}
+
 // Shared-memory carve-up common to both kernels.
 struct Smem {
   uint32_t stage0, extra0, bar0;
+  uint8_t* extra;  // generic pointer to the region behind the stages
   float* fl;
   uint32_t* misc;
   volatile int* abort_flag;
@@ -174,9 +332,13 @@ __device__ __forceinline__ Smem carve(uint8_t* raw, int nst, size_t extra_bytes,
   s.abort_flag = (volatile int*)(s.misc + 1);
   s.stage0 = smem_u32(sm);
   s.extra0 = smem_u32(extra);
+  s.extra = extra;
   s.bar0 = smem_u32(bars);
   return s;
 }
+
+// Bytes of the double-buffered tap table of the map-mode producers.
+__host__ __device__ inline size_t tap_table_bytes(int K) { return (size_t)2 * TILE_M * K * sizeof(TapEnt); }
 
 static size_t smem_bytes(int nst, size_t extra_bytes, int nfloat, int nbar) {
   return 1024 + (size_t)nst * STAGE_BYTES + extra_bytes + (size_t)nfloat * 4 + (size_t)nbar * 8 + 16;
@@ -190,7 +352,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int nst = a.nst;
   // bars: full[nst], empty[nst], tfull[2], tempty[2], drain
-  const Smem sm = carve(smem_raw, nst, (size_t)a.nsl * NOUT * 128, NOUT, 2 * nst + 5);
+  const size_t wbytes = (size_t)a.nsl * NOUT * 128;
+  const Smem sm = carve(smem_raw, nst, wbytes + (CSR ? 0 : tap_table_bytes(a.s.K)), NOUT, 2 * nst + 5);
   float* bias_s = sm.fl;
   volatile int* abort_flag = sm.abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -299,32 +462,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
     }
   } else {
     // ------------------------------------------------------------------ producers
-    const int pw = warp - 1 - N_EPI_WARPS;
-    const int g = lane >> 3, lg = lane & 7;  // 8 lanes cover the 128 bytes of one row
-    const int cpb = a.s.C / 64;
-    uint32_t n = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x) {
-      for (int s = 0; s < a.nsl; ++s, ++n) {
-        const uint32_t st = n % nst, ph = (n / nst) & 1;
-        const int tap = s / cpb, cb = s % cpb;
-        int okw = 1;
-        if (lane == 0) okw = mbar_wait(empty_bar(st), ph ^ 1, abort_flag, 0x31) ? 1 : 0;
-        okw = __shfl_sync(0xffffffffu, okw, 0);
-        if (!okw) { ok = false; break; }
-        const uint32_t sbase = stage0 + st * STAGE_BYTES;
-        for (int r = pw * 4 + g; r < TILE_M; r += N_PRODUCER_WARPS * 4) {
-          long gp, p;
-          int img;
-          bool valid;
-          tile_pixel(a.t, tile, r, gp, img, p, valid);
-          const uint4 o = produce_row<CSR>(a.s, img, p, tap, cb, lg, valid);
-          sts16(sbase + r * 128 + ((lg ^ (r & 7)) << 4), o);
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(full_bar(st));
-      }
-    }
+    if (CSR)
+      producer_loop_inv(a.s, a.t, a.nsl, nst, stage0, full_bar(0), empty_bar(0), abort_flag,
+                        warp - 1 - N_EPI_WARPS, lane, 0x31);
+    else
+      producer_loop_map(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
+                        (TapEnt*)(sm.extra + wbytes),
+                        abort_flag, warp - 1 - N_EPI_WARPS, lane, 0x32);
   }
 
   tc_fence_before_sync();
@@ -350,7 +494,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int nst = a.nst;  // even
   // bars: full[nst], empty[nst], gfull[GY], gempty[GY], done
-  const Smem sm = carve(smem_raw, nst, (size_t)GY_STAGES * STAGE_BYTES, NOUT, 2 * nst + 2 * GY_STAGES + 1);
+  const Smem sm = carve(smem_raw, nst, (size_t)GY_STAGES * STAGE_BYTES + tap_table_bytes(a.s.K), NOUT,
+                        2 * nst + 2 * GY_STAGES + 1);
   float* gb_s = sm.fl;
   volatile int* abort_flag = sm.abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -489,33 +634,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
     }
   } else {
     // ------------------------------------------------------------------ producers
-    const int pw = warp - 1 - N_EPI_WARPS;
-    const int g = lane >> 3, lg = lane & 7;
-    const int cpb = a.s.C / 64;
-    uint32_t it = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x, ++it) {
-      for (int s = 0; s < nsl_pad; ++s) {  // an odd slice count is padded with a zero slice
-        const uint32_t n = it * nsl_pad + s;
-        const uint32_t st = n % nst, ph = (n / nst) & 1;
-        const int tap = s / cpb, cb = s % cpb;
-        int okw = 1;
-        if (lane == 0) okw = mbar_wait(empty_bar(st), ph ^ 1, abort_flag, 0x61) ? 1 : 0;
-        okw = __shfl_sync(0xffffffffu, okw, 0);
-        if (!okw) { ok = false; break; }
-        const uint32_t sbase = stage0 + st * STAGE_BYTES;
-        for (int r = pw * 4 + g; r < TILE_M; r += N_PRODUCER_WARPS * 4) {
-          long gp, p;
-          int img;
-          bool valid;
-          tile_pixel(a.t, tile, r, gp, img, p, valid);
-          const uint4 o = produce_row<false>(a.s, img, p, tap, cb, lg, valid && s < a.nsl);
-          sts16(sbase + r * 128 + ((lg ^ (r & 7)) << 4), o);
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(full_bar(st));
-      }
-    }
+    producer_loop_map(a.s, a.t, a.nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
+                      (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES),
+                      abort_flag, warp - 1 - N_EPI_WARPS, lane, 0x61);
   }
 
   tc_fence_before_sync();
@@ -649,7 +770,7 @@ bool conv_tc_fwd_supported(const mc_desc* d) {
   if (d->dtype != MC_BF16 || d->layout != MC_NHWC || d->P != 0) return false;
   if (d->C_in % 64 != 0 || d->C_out != 64) return false;
   const int nsl = d->K * (d->C_in / 64);
-  return pick_stages((size_t)nsl * d->C_out * 128, d->C_out, 8, 3, false) > 0;
+  return pick_stages((size_t)nsl * d->C_out * 128 + tap_table_bytes(d->K), d->C_out, 8, 3, false) > 0;
 }
 
 size_t conv_tc_fwd_ws(const mc_desc* d) {
@@ -667,13 +788,14 @@ int conv_tc_fwd_launch(const mc_desc* d, const void* x, const void* map, const v
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
   a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias; a.y = (bf16*)y;
   a.nsl = d->K * (d->C_in / 64);
-  a.nst = pick_stages((size_t)a.nsl * d->C_out * 128, d->C_out, 8, 3, false);
+  const size_t extra = (size_t)a.nsl * d->C_out * 128 + tap_table_bytes(d->K);
+  a.nst = pick_stages(extra, d->C_out, 8, 3, false);
   const long nw = (long)d->K * d->C_in * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_out,
                                                          d->C_in, d->K, 0, d->C_in), MC_COUNT(1);
   static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, false>);
   if (!attr) return MC_ERR_LAUNCH;
-  const size_t smem = smem_bytes(a.nst, (size_t)a.nsl * d->C_out * 128, d->C_out, 2 * a.nst + 5);
+  const size_t smem = smem_bytes(a.nst, extra, d->C_out, 2 * a.nst + 5);
   const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
   conv_gemm_tc_kernel<64, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
@@ -781,7 +903,8 @@ bool conv_tc_wgrad_supported(const mc_desc* d) {
   if (d->dtype != MC_BF16 || d->layout != MC_NHWC || d->P != 0) return false;
   if (d->C_in % 64 != 0 || d->C_out != 64) return false;
   const int nsl = d->K * (d->C_in / 64);
-  return ((nsl + 1) / 2) * d->C_out <= 512;  // partial sums must fit the 512 TMEM columns
+  if (((nsl + 1) / 2) * d->C_out > 512) return false;  // partial sums must fit the 512 TMEM columns
+  return pick_stages((size_t)GY_STAGES * STAGE_BYTES + tap_table_bytes(d->K), d->C_out, 10, 4, true) > 0;
 }
 size_t conv_tc_wgrad_ws(const mc_desc*) { return 0; }
 
@@ -796,7 +919,8 @@ int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const 
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
   a.gy = (const bf16*)gy; a.gw = (float*)gw; a.gb = (float*)gb;
   a.nsl = d->K * (d->C_in / 64);
-  a.nst = pick_stages((size_t)GY_STAGES * STAGE_BYTES, d->C_out, 10, 4, true);
+  const size_t extra = (size_t)GY_STAGES * STAGE_BYTES + tap_table_bytes(d->K);
+  a.nst = pick_stages(extra, d->C_out, 10, 4, true);
   if (a.nst == 0) return MC_ERR_UNSUPPORTED;
   if (cudaMemsetAsync(gw, 0, (size_t)d->C_out * d->C_in * d->K * sizeof(float), st) != cudaSuccess)
     return MC_ERR_LAUNCH;
@@ -804,7 +928,7 @@ int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const 
     return MC_ERR_LAUNCH;
   static bool attr = allow_big_smem(conv_wgrad_tc_kernel<64>);
   if (!attr) return MC_ERR_LAUNCH;
-  const size_t smem = smem_bytes(a.nst, (size_t)GY_STAGES * STAGE_BYTES, d->C_out,
+  const size_t smem = smem_bytes(a.nst, extra, d->C_out,
                                  2 * a.nst + 2 * GY_STAGES + 1);
   const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
   conv_wgrad_tc_kernel<64><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
