@@ -141,8 +141,11 @@ __device__ __forceinline__ void decode_tile(const Source& s, const Tiling& t, in
     tx = tt - ty * t.tiles_x;
   }
   const int n = TILE_M * s.K;
-  for (int e = ptid; e < n; e += N_PRODUCER_THREADS) {
-    const int r = e / s.K, k = e - r * s.K;
+  // entry e = r * K + k; advancing e by the thread count advances (r, k) by fixed steps
+  const int dr = N_PRODUCER_THREADS / s.K, dk = N_PRODUCER_THREADS - dr * s.K;
+  int r = ptid / s.K, k = ptid - r * s.K;
+  for (int e = ptid; e < n; e += N_PRODUCER_THREADS, r += dr, k += dk) {
+    if (k >= s.K) { k -= s.K; ++r; }
     long p;
     int img;
     bool valid = true;
@@ -186,8 +189,46 @@ __device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
   return o;
 }
 
+// Loads of one row in flight: four source rows (16 bytes per lane each) and their weights.
+struct RowLoad {
+  uint4 v[4];
+  float w[4];
+};
+
+__device__ __forceinline__ void issue_row(const TapEnt* ent, const bf16* sb, int C, RowLoad& L) {
+  const uint4* e = reinterpret_cast<const uint4*>(ent);
+  const uint4 o = e[0], w = e[1];
+  const int of[4] = {(int)o.x, (int)o.y, (int)o.z, (int)o.w};
+  L.w[0] = __uint_as_float(w.x); L.w[1] = __uint_as_float(w.y);
+  L.w[2] = __uint_as_float(w.z); L.w[3] = __uint_as_float(w.w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    L.v[i] = of[i] >= 0 ? ldg16(sb + (long)of[i] * C) : make_uint4(0, 0, 0, 0);
+}
+
+__device__ __forceinline__ uint4 blend_row(const RowLoad& L) {
+  float2 acc[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) acc[j] = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 w2 = make_float2(L.w[i], L.w[i]);
+    ffma2_bf16x2(acc[0], w2, L.v[i].x);
+    ffma2_bf16x2(acc[1], w2, L.v[i].y);
+    ffma2_bf16x2(acc[2], w2, L.v[i].z);
+    ffma2_bf16x2(acc[3], w2, L.v[i].w);
+  }
+  uint4 o;
+  o.x = pack_bf16x2(acc[0].x, acc[0].y);
+  o.y = pack_bf16x2(acc[1].x, acc[1].y);
+  o.z = pack_bf16x2(acc[2].x, acc[2].y);
+  o.w = pack_bf16x2(acc[3].x, acc[3].y);
+  return o;
+}
+
 // Map-mode producer warp.  nslots ring slots are consumed per tile, of which the first nsl carry
-// data (an odd slice count of the wgrad kernel is padded with a zero slice).
+// data (an odd slice count of the wgrad kernel is padded with a zero slice).  A group owns two rows
+// of every stage; while it blends one of them the loads of the other are in flight.
 __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling& t, int nsl,
                                                   int nslots, int nst, uint32_t stage0,
                                                   uint32_t full0, uint32_t empty0, TapEnt* table,
@@ -199,45 +240,32 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
   const int r0 = pw * 4 + g, r1 = r0 + N_PRODUCER_WARPS * 4;  // the two rows of a stage this group owns
   const uint32_t so0 = r0 * 128 + ((lg ^ (r0 & 7)) << 4), so1 = r1 * 128 + ((lg ^ (r1 & 7)) << 4);
   const bf16* srcl = s.src + lg * 8;
-  uint32_t n = 0, it = 0;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint32_t st = 0, ph = 0, it = 0;  // ring slot and its phase, advanced without divisions
   for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x, ++it) {
-    TapEnt* tab = table + (size_t)(it & 1) * TILE_M * s.K;
-    decode_tile(s, t, tile, tab, ptid);
+    const TapEnt* tab = table + (size_t)(it & 1) * TILE_M * s.K;
+    decode_tile(s, t, tile, const_cast<TapEnt*>(tab), ptid);
     producer_bar();
-    for (int sl = 0; sl < nslots; ++sl, ++n) {
-      const uint32_t st = n % nst, ph = (n / nst) & 1;
+    const TapEnt* t0 = tab + r0 * s.K;
+    const TapEnt* t1 = tab + r1 * s.K;
+    RowLoad A, B;
+    issue_row(t0, srcl, s.C, A);  // slice 0: tap 0, channel block 0
+    int tap = 0, cb = 0;          // of the current slice
+    for (int sl = 0; sl < nslots; ++sl) {
+      const bool live = sl < nsl;
+      if (live) issue_row(t1 + tap, srcl + cb * 64, s.C, B);
       int okw = 1;
       if (lane == 0) okw = mbar_wait(empty0 + 8u * st, ph ^ 1, abort_flag, code) ? 1 : 0;
       okw = __shfl_sync(0xffffffffu, okw, 0);
       if (!okw) return;
       const uint32_t sbase = stage0 + st * STAGE_BYTES;
-      float a0[8], a1[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) a0[j] = a1[j] = 0.f;
-      if (sl < nsl) {
-        const int tap = sl / cpb, cb = sl - tap * cpb;
-        const uint4* e0 = reinterpret_cast<const uint4*>(tab + r0 * s.K + tap);
-        const uint4* e1 = reinterpret_cast<const uint4*>(tab + r1 * s.K + tap);
-        const uint4 o0 = e0[0], w0 = e0[1], o1 = e1[0], w1 = e1[1];
-        const bf16* sb = srcl + cb * 64;
-        const int of[8] = {(int)o0.x, (int)o0.y, (int)o0.z, (int)o0.w,
-                           (int)o1.x, (int)o1.y, (int)o1.z, (int)o1.w};
-        const float wf[8] = {__uint_as_float(w0.x), __uint_as_float(w0.y), __uint_as_float(w0.z),
-                             __uint_as_float(w0.w), __uint_as_float(w1.x), __uint_as_float(w1.y),
-                             __uint_as_float(w1.z), __uint_as_float(w1.w)};
-        uint4 v[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          v[i] = of[i] >= 0 ? ldg16(sb + (long)of[i] * s.C) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) blend4(v[i], wf[i], a0);
-#pragma unroll
-        for (int i = 4; i < 8; ++i) blend4(v[i], wf[i], a1);
-      }
-      sts16(sbase + so0, pack8(a0));
-      sts16(sbase + so1, pack8(a1));
+      sts16(sbase + so0, live ? blend_row(A) : zero);
+      if (++cb == cpb) { cb = 0; ++tap; }
+      if (sl + 1 < nsl) issue_row(t0 + tap, srcl + cb * 64, s.C, A);
+      sts16(sbase + so1, live ? blend_row(B) : zero);
       fence_proxy_async_smem();
       mbar_arrive(full0 + 8u * st);
+      if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
     }
   }
 }
@@ -250,7 +278,7 @@ __device__ __forceinline__ void producer_loop_inv(const Source& s, const Tiling&
   const int g = lane >> 3, lg = lane & 7;
   const int cpb = s.C / 64;
   const bf16* srcl = s.src + lg * 8;
-  uint32_t n = 0;
+  uint32_t st = 0, ph = 0;
   for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x) {
     // the two rows of every stage this group owns: pixel and image are the same for all slices
     long key[2], base[2];
@@ -266,9 +294,8 @@ __device__ __forceinline__ void producer_loop_inv(const Source& s, const Tiling&
       base[h] = (long)img * s.spix * s.C;
       so[h] = r * 128 + ((lg ^ (r & 7)) << 4);
     }
-    for (int sl = 0; sl < nsl; ++sl, ++n) {
-      const uint32_t st = n % nst, ph = (n / nst) & 1;
-      const int tap = sl / cpb, cb = sl - tap * cpb;
+    int tap = 0, cb = 0;
+    for (int sl = 0; sl < nsl; ++sl) {
       // list ranges first, so that they are in flight while we wait for the stage
       int beg[2], end[2];
 #pragma unroll
@@ -309,6 +336,8 @@ __device__ __forceinline__ void producer_loop_inv(const Source& s, const Tiling&
       }
       fence_proxy_async_smem();
       mbar_arrive(full0 + 8u * st);
+      if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
+      if (++cb == cpb) { cb = 0; ++tap; }
     }
   }
 }
@@ -394,7 +423,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 0, 0);
-      uint32_t n = 0, it = 0;
+      uint32_t st = 0, ph = 0, it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x, ++it) {
         const uint32_t acc = it & 1, aph = (it >> 1) & 1;
@@ -402,8 +431,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * NOUT;
-        for (int s = 0; s < a.nsl; ++s, ++n) {
-          const uint32_t st = n % nst, ph = (n / nst) & 1;
+        for (int s = 0; s < a.nsl; ++s) {
           ok = mbar_wait(full_bar(st), ph, abort_flag, 0x12);
           if (!ok) break;
           tc_fence_after_sync();
@@ -413,6 +441,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
           for (int j = 0; j < 4; ++j)  // four K = 16 steps inside the 64-wide slice: +32 bytes each
             mma_bf16_ss(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, (s | j) != 0);
           mma_commit(empty_bar(st));  // frees the stage when these MMAs have read it
+          if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
         }
         if (ok) mma_commit(tfull_bar(acc));
       }
@@ -534,7 +563,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 1, 1);
-      uint32_t it = 0;
+      uint32_t it = 0, st = 0, ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x, ++it) {
         const uint32_t gs = it % GY_STAGES, gph = (it / GY_STAGES) & 1;
@@ -542,8 +571,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
         if (!ok) break;
         const uint64_t bdesc = make_desc_sw128(gy0 + gs * STAGE_BYTES, STAGE_BYTES, 1024);
         for (int j = 0; j < nmt && ok; ++j) {
-          const uint32_t n0 = it * nsl_pad + 2 * j;
-          const uint32_t st = n0 % nst, ph = (n0 / nst) & 1;  // slots st and st + 1 share the phase
+          // slots st and st + 1 (st is even) share the phase
           ok = mbar_wait(full_bar(st), ph, abort_flag, 0x42);
           if (ok) ok = mbar_wait(full_bar(st + 1), ph, abort_flag, 0x43);
           if (!ok) break;
@@ -555,6 +583,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
                         (it | kk) != 0);
           mma_commit(empty_bar(st));
           mma_commit(empty_bar(st + 1));
+          st += 2;
+          if (st == (uint32_t)nst) { st = 0; ph ^= 1; }
         }
         if (ok) mma_commit(gempty_bar(gs));
       }

@@ -161,6 +161,14 @@ __device__ __forceinline__ void bf16x2_fma(uint32_t packed, float w, float& a0, 
   a0 = fmaf(w, __uint_as_float(packed << 16), a0);
   a1 = fmaf(w, __uint_as_float(packed & 0xFFFF0000u), a1);
 }
+// acc.{x,y} += w.{x,y} * (the two bf16 of `packed` widened to fp32), one packed-fp32 FMA.
+__device__ __forceinline__ void ffma2_bf16x2(float2& acc, const float2& w, uint32_t packed) {
+  const float2 v = make_float2(__uint_as_float(packed << 16), __uint_as_float(packed & 0xFFFF0000u));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;"
+      : "+l"(reinterpret_cast<unsigned long long&>(acc))
+      : "l"(reinterpret_cast<const unsigned long long&>(w)),
+        "l"(reinterpret_cast<const unsigned long long&>(v)));
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
