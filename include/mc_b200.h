@@ -77,6 +77,31 @@ int mc_conv_fwd(const mc_desc* d, const void* x, const void* map, const void* iw
                 const void* bias, void* y, void* ws, size_t ws_bytes, void* stream);
 size_t mc_conv_fwd_workspace_bytes(const mc_desc* d);
 
+/* mc_conv_fwd for callers that cannot hand over scratch memory.  (No counterpart in the
+ * reference, whose drivers allocate their column buffer with torch on every call.)
+ *
+ * Who needs it: code that runs where the device allocator is off limits - a plugin called from
+ * inside another framework's execution step, a serving loop whose memory was carved up once at
+ * start-up, a real-time path in which cudaMalloc's implicit device synchronisation is not
+ * acceptable.  Such callers own their input and output tensors but have no spare buffer, and
+ * mc_conv_fwd's tensor-core path needs one for the weights re-laid-out for the MMA unit.
+ *
+ * Here that buffer is a fixed array in the library's device image
+ * (mc_conv_fwd_static_scratch_limit() bytes, currently 80 KiB, resident on every GPU that loads the
+ * library until the process exits).  The call allocates and frees nothing, and computes exactly
+ * what mc_conv_fwd computes.
+ *  - Supported: the configurations of the tensor-core forward (MC_BF16, MC_NHWC, P == 0,
+ *    C_in % 64 == 0, C_out == 64); anything else returns MC_ERR_UNSUPPORTED.
+ *  - K * C_in * C_out * 2 bytes must fit the array, otherwise MC_ERR_TOO_LARGE.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call outside any stream capture.
+ *  - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
+ *    (different streams, no ordering between them) race on it.  Calls on one stream are safe; the
+ *    array is fully rewritten for the part a call uses, so nothing carries over between calls. */
+size_t mc_conv_fwd_static_scratch_limit(void);
+int mc_conv_fwd_static_scratch(const mc_desc* d, const void* x, const void* map, const void* w,
+                               const void* bias, void* y, void* stream);
+
 /* gx(B,C_in,IH,IW) = col2im_map(W^T . gy) [+ bias_out per channel of gx when bias_out != NULL,
  * which is how the transposed convolution forward uses it].
  * Replaces cuda::MappedConvBackwardInput, src/nn/cuda/mapped_convolution_layer.cu:75-132.

@@ -35,6 +35,8 @@ SIGNATURES = {
     "mc_device_status": (ctypes.c_int, [_vp, ctypes.c_int]),
     "mc_conv_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_fwd_workspace_bytes": (_sz, [_dp]),
+    "mc_conv_fwd_static_scratch_limit": (_sz, []),
+    "mc_conv_fwd_static_scratch": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mc_conv_dgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_dgrad_workspace_bytes": (_sz, [_dp]),
     "mc_invmap_bytes": (_sz, [_dp]),

@@ -966,6 +966,41 @@ int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const 
   return MC_OK;
 }
 
+// ---- forward pass with library-owned scratch ---------------------------------------------------
+// The tensor-core forward needs a small scratch buffer (the weights re-laid-out for the MMA
+// unit).  mc_conv_fwd() takes it from the caller; this variant keeps it in a fixed array inside
+// the library image instead, for callers that have no way to obtain device memory at call time.
+constexpr size_t STATIC_SCRATCH_BYTES = 80 * 1024;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+constexpr int STATIC_SCRATCH_MAX_DEVICES = 64;
+// Device address of g_static_scratch for every device ordinal (the symbol itself is only a host
+// stand-in; kernels must be given the address the runtime reports for the current device).
+static void* g_static_scratch_addr[STATIC_SCRATCH_MAX_DEVICES] = {nullptr};
+
+int check_conv_desc_public(const mc_desc* d);
+
+extern "C" size_t mc_conv_fwd_static_scratch_limit(void) { return STATIC_SCRATCH_BYTES; }
+
+extern "C" int mc_conv_fwd_static_scratch(const mc_desc* d, const void* x, const void* map,
+                                          const void* w, const void* bias, void* y, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!x || !map || !w || !y) return MC_ERR_BAD_ARG;
+  if (!conv_tc_fwd_supported(d)) return MC_ERR_UNSUPPORTED;
+  if (conv_tc_fwd_ws(d) > STATIC_SCRATCH_BYTES) return MC_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= STATIC_SCRATCH_MAX_DEVICES)
+    return MC_ERR_LAUNCH;
+  void* scratch = g_static_scratch_addr[dev];
+  if (!scratch) {  // first call on this device: look the array's device address up once
+    if (cudaGetSymbolAddress(&scratch, g_static_scratch) != cudaSuccess || !scratch)
+      return MC_ERR_LAUNCH;
+    g_static_scratch_addr[dev] = scratch;
+  }
+  return conv_tc_fwd_launch(d, x, map, w, bias, y, scratch, STATIC_SCRATCH_BYTES,
+                            (cudaStream_t)stream);
+}
+
 int device_status_read(cudaStream_t st, int reset) {
   int v = 0;
   if (cudaStreamSynchronize(st) != cudaSuccess) return MC_ERR_LAUNCH;
