@@ -193,6 +193,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from mappedconvolutions_b200 import _lib, ops
+    from mappedconvolutions_b200.dist import allreduce_gradients
     from mapped_convolution.nn import MappedConvolution
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -214,8 +215,7 @@ def run_ours(args):
         y = ops.mapped_conv_forward(x, m, w, b, K, 1)
         gx, gw, gb = ops.mapped_conv_backward(gy, m, x, w, b, K, 1)
         if world > 1:
-            bucket = torch.cat([gw.float().view(-1), gb.float().view(-1)])
-            dist.all_reduce(bucket)
+            allreduce_gradients([gw, gb])
         return y, gx, gw, gb
 
     def barrier():
@@ -265,8 +265,7 @@ def run_ours(args):
         y = layer(xd, m)
         y.backward(gd)
         if world > 1:
-            bucket = torch.cat([layer.weight.grad.float().view(-1), layer.bias.grad.float().view(-1)])
-            dist.all_reduce(bucket)
+            allreduce_gradients([layer.weight.grad, layer.bias.grad])
         outs["y"].copy_(y.detach(), non_blocking=True)
         outs["gx"].copy_(xd.grad, non_blocking=True)
         outs["gw"].copy_(layer.weight.grad, non_blocking=True)
