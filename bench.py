@@ -161,7 +161,11 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS=1 for its workers; the CPU arm is meant to use every host core
+    ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(ncpu)
     import torch
+    torch.set_num_threads(ncpu)
     O, kind = cpu_ops()
     x, gy, w, b, m = make_inputs(1, 1)
     x, gy, w, b = [t.float().contiguous() for t in (x, gy, w, b)]

@@ -1,0 +1,265 @@
+// Bandwidth-oriented kernels for the gather-type ops (mapped max / avg pool, resample gather) on
+// unweighted maps, float32 and bfloat16.
+//
+// The generic kernel decodes the sample map again for every (batch, channel) element.  Here the
+// map entry of an output location is decoded ONCE into registers - up to NT (source pixel,
+// weight) pairs - and reused for every channel and batch element:
+//   * NCHW: one thread per output location walks over a group of (b, c) planes; tap 0 of a
+//     one-ring map and the output are coalesced, the other taps are 4-byte gathers that live in
+//     L1 / L2 (a plane is at most a few MB);
+//   * NHWC: a group of lanes per output location reads every tap as one contiguous 16-byte-per-
+//     lane run across channels and walks over the batch.
+// Arithmetic is the same rounded sequence as the generic kernel, so results are bit-identical
+// (include/nn/common/mapped_max_pool.h:14-58, mapped_avg_pool.h:14-42, resample.h:33-50 of the
+// reference).
+#include "common.cuh"
+
+namespace mc {
+
+enum { FOP_GATHER = 0, FOP_AVG = 1, FOP_MAX = 2 };
+
+struct FastArgs {
+  const void* x;
+  const float* map;
+  void* y;
+  int64_t* idx;
+  int B, C, IH, IW, K, interp;
+  long npix_in, npix_out;
+  int planes_per_block;
+};
+
+// Decoded entries of one output location.  NC = 1: K nearest taps (weight 1).  NC = 4: one
+// bilinear / bispherical tap (K == 1).
+template <int NT>
+struct Entries {
+  int off[NT];
+  float w[NT];
+};
+
+template <int NT, int NC>
+__device__ __forceinline__ void decode_entries(const FastArgs& a, long p, Entries<NT>& e) {
+  if (NC == 1) {
+#pragma unroll
+    for (int k = 0; k < NT; ++k) {
+      const float2 m = __ldg(reinterpret_cast<const float2*>(a.map) + p * NT + k);
+      Tap<float> t;
+      decode_tap<float, float>(m.x, m.y, a.IH, a.IW, 0, t);
+      e.off[k] = t.off[0];
+      e.w[k] = 1.f;
+    }
+  } else {
+    const float2 m = __ldg(reinterpret_cast<const float2*>(a.map) + p);
+    Tap<float> t;
+    decode_tap<float, float>(m.x, m.y, a.IH, a.IW, a.interp, t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { e.off[i] = t.off[i]; e.w[i] = t.w[i]; }
+  }
+}
+
+// Combines the NT loaded values exactly like the generic kernel does.
+template <int NT, int NC, int OP>
+__device__ __forceinline__ float combine(const float (&v)[NT], const Entries<NT>& e, int K, int& best) {
+  if (NC == 4) {
+    float r = __fmul_rn(e.w[0], v[0]);
+    r = __fadd_rn(r, __fmul_rn(e.w[1], v[1]));
+    r = __fadd_rn(r, __fmul_rn(e.w[2], v[2]));
+    r = __fadd_rn(r, __fmul_rn(e.w[3], v[3]));
+    if (OP == FOP_AVG) r = __fdiv_rn(__fadd_rn(0.f, r), (float)K);
+    best = 0;
+    return r;
+  }
+  if (OP == FOP_MAX) {
+    float m = -FLT_MAX;
+    best = -1;
+#pragma unroll
+    for (int k = 0; k < NT; ++k)
+      if (v[k] > m) { m = v[k]; best = k; }
+    return m;
+  }
+  if (OP == FOP_AVG) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NT; ++k) s = __fadd_rn(s, v[k]);
+    return __fdiv_rn(s, (float)K);
+  }
+  best = 0;
+  return v[0];
+}
+
+// ---- NCHW: thread per output location, loop over planes ------------------------------------------
+template <typename T, int NT, int NC, int OP>
+__global__ void __launch_bounds__(256) sample_planes_kernel(const FastArgs a) {
+  const long p = blockIdx.x * 256L + threadIdx.x;
+  if (p >= a.npix_out) return;
+  Entries<NT> e;
+  decode_entries<NT, NC>(a, p, e);
+  const long nplanes = (long)a.B * a.C;
+  const long pl0 = (long)blockIdx.y * a.planes_per_block;
+  long pl1 = pl0 + a.planes_per_block;
+  if (pl1 > nplanes) pl1 = nplanes;
+  const T* x = (const T*)a.x;
+  T* y = (T*)a.y;
+#pragma unroll 2
+  for (long pl = pl0; pl < pl1; ++pl) {
+    const T* src = x + pl * a.npix_in;
+    float v[NT];
+#pragma unroll
+    for (int k = 0; k < NT; ++k) v[k] = e.off[k] >= 0 ? (float)ldv(src + e.off[k]) : 0.f;
+    int best;
+    const float r = combine<NT, NC, OP>(v, e, a.K, best);
+    stv(y + pl * a.npix_out + p, r);
+    if (OP == FOP_MAX) a.idx[pl * a.npix_out + p] = best < 0 ? -1 : 2 * (p * NT + best);
+  }
+}
+
+// ---- NHWC: LPP lanes per output location, 16 bytes per lane, loop over the batch -------------------
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[4]) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y);
+    f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
+                      __float_as_uint(f[3]));
+  }
+};
+template <> struct Vec16<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+template <typename T, int NT, int NC, int OP>
+__global__ void __launch_bounds__(256) sample_cl_kernel(const FastArgs a, int lpp_log2, int chunks) {
+  constexpr int VN = Vec16<T>::N;
+  const int lpp = 1 << lpp_log2;  // lanes per output location (C * sizeof(T) / 16 / chunks)
+  const long gthread = blockIdx.x * 256L + threadIdx.x;
+  const long p = gthread >> lpp_log2;
+  const int lane = (int)(gthread & (lpp - 1));
+  if (p >= a.npix_out) return;
+  Entries<NT> e;
+  decode_entries<NT, NC>(a, p, e);
+  const T* x = (const T*)a.x;
+  T* y = (T*)a.y;
+  for (int b = blockIdx.y; b < a.B; b += gridDim.y) {
+    for (int ch = 0; ch < chunks; ++ch) {
+      const int c0 = (ch * lpp + lane) * VN;
+      const T* src = x + (long)b * a.npix_in * a.C + c0;
+      float v[NT][VN];
+#pragma unroll
+      for (int k = 0; k < NT; ++k) {
+        uint4 u = make_uint4(0, 0, 0, 0);
+        if (e.off[k] >= 0) u = __ldg(reinterpret_cast<const uint4*>(src + (long)e.off[k] * a.C));
+        Vec16<T>::unpack(u, v[k]);
+      }
+      float r[VN];
+      long bi[VN];
+#pragma unroll
+      for (int j = 0; j < VN; ++j) {
+        float col[NT];
+#pragma unroll
+        for (int k = 0; k < NT; ++k) col[k] = v[k][j];
+        int best;
+        r[j] = combine<NT, NC, OP>(col, e, a.K, best);
+        bi[j] = best < 0 ? -1 : 2 * (p * NT + best);
+      }
+      const long o = ((long)b * a.npix_out + p) * a.C + c0;
+      *reinterpret_cast<uint4*>(y + o) = Vec16<T>::pack(r);
+      if (OP == FOP_MAX) {
+#pragma unroll
+        for (int j = 0; j < VN; j += 2)
+          *reinterpret_cast<longlong2*>(a.idx + o + j) = make_longlong2(bi[j], bi[j + 1]);
+      }
+    }
+  }
+}
+
+template <typename T, int NT, int NC, int OP>
+static int launch_fast(const mc_desc* d, FastArgs a, cudaStream_t st) {
+  if (d->layout == MC_NCHW) {
+    const long nplanes = (long)a.B * a.C;
+    const long xblocks = (a.npix_out + 255) / 256;
+    // enough blocks to fill the GPU several times over, at least 8 planes per block for reuse
+    long ppb = nplanes * xblocks / (148L * 16);
+    if (ppb < 8) ppb = 8;
+    if (ppb > 64) ppb = 64;
+    a.planes_per_block = (int)ppb;
+    dim3 grid((unsigned)xblocks, (unsigned)((nplanes + ppb - 1) / ppb));
+    if (grid.y > 65535) return MC_ERR_TOO_LARGE;
+    sample_planes_kernel<T, NT, NC, OP><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  } else {
+    const int row16 = a.C * (int)sizeof(T) / 16;  // 16-byte vectors per location
+    int lpp_log2 = 0;
+    while ((1 << (lpp_log2 + 1)) <= row16 && lpp_log2 < 5 && row16 % (1 << (lpp_log2 + 1)) == 0) ++lpp_log2;
+    const int chunks = row16 >> lpp_log2;
+    const long threads = a.npix_out << lpp_log2;
+    const long xblocks = (threads + 255) / 256;
+    int by = (int)((148L * 8 + xblocks - 1) / xblocks);
+    if (by < 1) by = 1;
+    if (by > a.B) by = a.B;
+    dim3 grid((unsigned)xblocks, (unsigned)by);
+    sample_cl_kernel<T, NT, NC, OP><<<grid, 256, 0, st>>>(a, lpp_log2, chunks), MC_COUNT(1);
+  }
+  return cudaGetLastError() == cudaSuccess ? MC_OK : MC_ERR_LAUNCH;
+}
+
+template <typename T, int OP>
+static bool dispatch_nt(const mc_desc* d, const FastArgs& a, cudaStream_t st, int* rc) {
+  const bool nearest = d->interp != 1 && d->interp != 2;
+  if (nearest) {
+    switch (d->K) {
+      case 1: *rc = launch_fast<T, 1, 1, OP>(d, a, st); return true;
+      case 4: *rc = launch_fast<T, 4, 1, OP>(d, a, st); return true;
+      case 7: *rc = launch_fast<T, 7, 1, OP>(d, a, st); return true;
+      case 9: *rc = launch_fast<T, 9, 1, OP>(d, a, st); return true;
+      default: return false;
+    }
+  }
+  if (d->K == 1 && OP != FOP_MAX) { *rc = launch_fast<T, 4, 4, OP>(d, a, st); return true; }
+  return false;
+}
+
+// Returns true if a fast kernel took the call (its status is in *rc).
+bool sample_fwd_fast(const mc_desc* d, int op, const void* x, const void* map, void* y, int64_t* idx,
+                     cudaStream_t st, int* rc) {
+  if (d->P != 0 || (d->dtype != MC_F32 && d->dtype != MC_BF16)) return false;
+  const size_t esz = d->dtype == MC_F32 ? 4 : 2;
+  if (d->layout == MC_NHWC) {
+    if ((d->C_in * esz) % 16 != 0) return false;
+    if ((((uintptr_t)x | (uintptr_t)y) & 15) || (idx && ((uintptr_t)idx & 15))) return false;
+  }
+  if (((uintptr_t)map & 7) != 0) return false;
+  FastArgs a;
+  a.x = x; a.map = (const float*)map; a.y = y; a.idx = idx;
+  a.B = d->B; a.C = d->C_in; a.IH = d->IH; a.IW = d->IW; a.K = d->K; a.interp = d->interp;
+  a.npix_in = (long)d->IH * d->IW;
+  a.npix_out = (long)d->OH * d->OW;
+  a.planes_per_block = 8;
+  if (d->dtype == MC_F32) {
+    if (op == FOP_MAX) return dispatch_nt<float, FOP_MAX>(d, a, st, rc);
+    if (op == FOP_AVG) return dispatch_nt<float, FOP_AVG>(d, a, st, rc);
+    return dispatch_nt<float, FOP_GATHER>(d, a, st, rc);
+  }
+  if (op == FOP_MAX) return dispatch_nt<bf16, FOP_MAX>(d, a, st, rc);
+  if (op == FOP_AVG) return dispatch_nt<bf16, FOP_AVG>(d, a, st, rc);
+  return dispatch_nt<bf16, FOP_GATHER>(d, a, st, rc);
+}
+
+}  // namespace mc

@@ -13,6 +13,11 @@ namespace mc {
 
 enum { OP_GATHER = 0, OP_AVG = 1, OP_MAX = 2 };
 
+// pool_fast.cu: bandwidth-oriented kernels for unweighted nearest (K in {1,4,7,9}) and single-tap
+// bilinear maps; returns false when the generic kernel below has to take the call.
+bool sample_fwd_fast(const mc_desc* d, int op, const void* x, const void* map, void* y, int64_t* idx,
+                     cudaStream_t st, int* rc);
+
 struct SampleArgs {
   const void* x;
   const void* map;
@@ -176,6 +181,8 @@ static int launch_fwd(const mc_desc* d, const void* x, const void* map, const vo
   a.interp = d->interp; a.layout = d->layout;
   a.npix_in = (long)d->IH * d->IW;
   a.npix_out = (long)d->OH * d->OW;
+  int frc = MC_OK;
+  if (sample_fwd_fast(d, OP, x, map, y, idx, st, &frc)) return frc;  // decode-once kernels
   const long total = (long)a.B * a.C * a.npix_out;
   const int grid = grid_for(total, 256);
   if (d->dtype == MC_F32) sample_fwd_kernel<float, OP><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
