@@ -43,6 +43,11 @@ K = KH * KW
 BATCH = 8  # per GPU
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at batch 8, scaled from ncu captures of
+# the batch-2 case (profiles/conv_tc_kernels_config2_b2.md explains the scaling)
+DRAM_TRAFFIC_BYTES = {"conv_fwd": 1.11e9, "conv_dgrad": 1.34e9, "conv_wgrad": 1.28e9}
+
+
 def flops_per_step(batch):
     return 3 * 2.0 * batch * H * W * COUT * CIN * K
 
@@ -329,10 +334,7 @@ def run_ours(args):
         pk = peaks()
         gemm_flops = flops_per_step(BATCH) / 3
         ach = gemm_flops / (times[top] * 1e-3) / 1e12
-        traffic = None
-        tp = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(tp):
-            traffic = json.load(open(tp)).get(top)
+        traffic = DRAM_TRAFFIC_BYTES.get(top)
         roof = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": pk["bf16"],
                 "unit": "TFLOP/s", "frac": ach / pk["bf16"], "traffic": traffic,
                 "peak_source": pk["source"] + " burst bf16 (kernel timed alone)",

@@ -34,7 +34,10 @@ constexpr int TILE_M = 128;
 constexpr int STAGE_BYTES = TILE_M * 128;  // 128 rows x 64 bf16
 constexpr int N_PRODUCER_WARPS = 16;
 constexpr int N_EPI_WARPS = 4;
-constexpr int TC_THREADS = (1 + N_EPI_WARPS + N_PRODUCER_WARPS) * 32;
+constexpr int N_DEC_WARPS = 3;  // (24 warps in all: the register file is shared out per 4 warps) decode the sample map / inverse map of the NEXT tile
+constexpr int FIRST_DEC_WARP = 1 + N_EPI_WARPS;
+constexpr int FIRST_PROD_WARP = FIRST_DEC_WARP + N_DEC_WARPS;
+constexpr int TC_THREADS = (FIRST_PROD_WARP + N_PRODUCER_WARPS) * 32;
 constexpr size_t SMEM_LIMIT = 220 * 1024;
 
 // How the pixels of the tiled domain are grouped into 128-row tiles.
@@ -124,12 +127,13 @@ struct TapEnt {   // 32 bytes
   float w[4];
 };
 
-constexpr int N_PRODUCER_THREADS = N_PRODUCER_WARPS * 32;
+constexpr int N_DEC_THREADS = N_DEC_WARPS * 32;
 
-__device__ __forceinline__ void producer_bar() {
-  asm volatile("bar.sync 2, %0;" ::"n"(N_PRODUCER_THREADS) : "memory");
-}
+// Set in off[3] of a table entry whose inverse-map list has more than four entries: the producer
+// then walks the rest of the list from global memory (0.5 % of the lists of a gnomonic 3x3 map).
+constexpr int MORE_FLAG = 1 << 30;
 
+template <bool CSR>
 __device__ __forceinline__ void decode_tile(const Source& s, const Tiling& t, int tile, TapEnt* tab,
                                             int ptid) {
   // per-tile constants (2-D tiles): image and the pixel of the tile's corner
@@ -142,41 +146,95 @@ __device__ __forceinline__ void decode_tile(const Source& s, const Tiling& t, in
   }
   const int n = TILE_M * s.K;
   // entry e = r * K + k; advancing e by the thread count advances (r, k) by fixed steps
-  const int dr = N_PRODUCER_THREADS / s.K, dk = N_PRODUCER_THREADS - dr * s.K;
+  const int dr = N_DEC_THREADS / s.K, dk = N_DEC_THREADS - dr * s.K;
   int r = ptid / s.K, k = ptid - r * s.K;
-  for (int e = ptid; e < n; e += N_PRODUCER_THREADS, r += dr, k += dk) {
-    if (k >= s.K) { k -= s.K; ++r; }
-    long p;
-    int img;
-    bool valid = true;
-    if (t.tile2d) {
-      img = img0;
-      p = (long)(ty * 8 + (r >> 4)) * t.W + tx * 16 + (r & 15);
-    } else {
-      const long gp = (long)tile * TILE_M + r;
-      valid = gp < t.mtot;
-      img = valid ? (int)(gp / t.npix) : 0;
-      p = valid ? gp - (long)img * t.npix : 0;
+  // Entries are handled U at a time so that the dependent global loads of a batch (map entry, or
+  // list range and then list entries) are all in flight together instead of one after another.
+  constexpr int U = 4;
+  for (int e0 = ptid; e0 < n; e0 += U * N_DEC_THREADS) {
+    long key[U];
+    int ibase[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int e = e0 + u * N_DEC_THREADS;
+      if (k >= s.K) { k -= s.K; ++r; }
+      key[u] = -1;
+      ibase[u] = 0;
+      if (e < n) {
+        long p;
+        int img;
+        bool valid = true;
+        if (t.tile2d) {
+          img = img0;
+          p = (long)(ty * 8 + (r >> 4)) * t.W + tx * 16 + (r & 15);
+        } else {
+          const long gp = (long)tile * TILE_M + r;
+          valid = gp < t.mtot;
+          img = valid ? (int)(gp / t.npix) : 0;
+          p = valid ? gp - (long)img * t.npix : 0;
+        }
+        if (valid) { key[u] = p * s.K + k; ibase[u] = img * (int)s.spix; }
+      }
+      r += dr;
+      k += dk;
     }
-    TapEnt ent;
+    TapEnt ent[U];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { ent.off[i] = -1; ent.w[i] = 0.f; }
-    if (valid) {
-      const float2 m = __ldg(reinterpret_cast<const float2*>(s.map) + p * s.K + k);
-      Tap<float> tp;
-      decode_tap<float, float>(m.x, m.y, s.SH, s.SW, s.interp, tp);
-      const int ibase = img * (int)s.spix;
+    for (int u = 0; u < U; ++u)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const bool on = i < tp.n && tp.off[i] >= 0 && tp.w[i] != 0.f;
-        ent.off[i] = on ? ibase + tp.off[i] : -1;
-        ent.w[i] = on ? tp.w[i] : 0.f;
+      for (int i = 0; i < 4; ++i) { ent[u].off[i] = -1; ent[u].w[i] = 0.f; }
+    if (CSR) {
+      int beg[U], end[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        beg[u] = end[u] = 0;
+        if (key[u] >= 0) { beg[u] = __ldg(s.inv_off + key[u]); end[u] = __ldg(s.inv_off + key[u] + 1); }
+      }
+      // the first four (grid pixel, weight) pairs of each list
+      int2 en[U][4];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          en[u][i] = beg[u] + i < end[u] ? __ldg(s.inv_ent + beg[u] + i) : make_int2(-1, 0);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (en[u][i].x >= 0) {
+            ent[u].off[i] = ibase[u] + en[u][i].x;
+            ent[u].w[i] = __int_as_float(en[u][i].y);
+          }
+        }
+        if (end[u] - beg[u] > 4) ent[u].off[3] |= MORE_FLAG;
+      }
+    } else {
+      float2 m[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        m[u] = key[u] >= 0 ? __ldg(reinterpret_cast<const float2*>(s.map) + key[u]) : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (key[u] < 0) continue;
+        Tap<float> tp;
+        decode_tap<float, float>(m[u].x, m[u].y, s.SH, s.SW, s.interp, tp);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const bool on = i < tp.n && tp.off[i] >= 0 && tp.w[i] != 0.f;
+          ent[u].off[i] = on ? ibase[u] + tp.off[i] : -1;
+          ent[u].w[i] = on ? tp.w[i] : 0.f;
+        }
       }
     }
-    uint4* dst = reinterpret_cast<uint4*>(tab + e);
-    dst[0] = make_uint4(ent.off[0], ent.off[1], ent.off[2], ent.off[3]);
-    dst[1] = make_uint4(__float_as_uint(ent.w[0]), __float_as_uint(ent.w[1]),
-                        __float_as_uint(ent.w[2]), __float_as_uint(ent.w[3]));
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int e = e0 + u * N_DEC_THREADS;
+      if (e >= n) continue;
+      uint4* dst = reinterpret_cast<uint4*>(tab + e);
+      dst[0] = make_uint4(ent[u].off[0], ent[u].off[1], ent[u].off[2], ent[u].off[3]);
+      dst[1] = make_uint4(__float_as_uint(ent[u].w[0]), __float_as_uint(ent[u].w[1]),
+                          __float_as_uint(ent[u].w[2]), __float_as_uint(ent[u].w[3]));
+    }
   }
 }
 
@@ -193,12 +251,14 @@ __device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
 struct RowLoad {
   uint4 v[4];
   float w[4];
+  bool more;  // inverse-map mode: the list continues beyond these four
 };
 
 __device__ __forceinline__ void issue_row(const TapEnt* ent, const bf16* sb, int C, RowLoad& L) {
   const uint4* e = reinterpret_cast<const uint4*>(ent);
   const uint4 o = e[0], w = e[1];
-  const int of[4] = {(int)o.x, (int)o.y, (int)o.z, (int)o.w};
+  L.more = (int)o.w >= 0 && ((int)o.w & MORE_FLAG) != 0;
+  const int of[4] = {(int)o.x, (int)o.y, (int)o.z, L.more ? (int)o.w & ~MORE_FLAG : (int)o.w};
   L.w[0] = __uint_as_float(w.x); L.w[1] = __uint_as_float(w.y);
   L.w[2] = __uint_as_float(w.z); L.w[3] = __uint_as_float(w.w);
 #pragma unroll
@@ -206,8 +266,7 @@ __device__ __forceinline__ void issue_row(const TapEnt* ent, const bf16* sb, int
     L.v[i] = of[i] >= 0 ? ldg16(sb + (long)of[i] * C) : make_uint4(0, 0, 0, 0);
 }
 
-__device__ __forceinline__ uint4 blend_row(const RowLoad& L) {
-  float2 acc[4];
+__device__ __forceinline__ void blend_row(const RowLoad& L, float2 (&acc)[4]) {
 #pragma unroll
   for (int j = 0; j < 4; ++j) acc[j] = make_float2(0.f, 0.f);
 #pragma unroll
@@ -218,6 +277,9 @@ __device__ __forceinline__ uint4 blend_row(const RowLoad& L) {
     ffma2_bf16x2(acc[2], w2, L.v[i].z);
     ffma2_bf16x2(acc[3], w2, L.v[i].w);
   }
+}
+
+__device__ __forceinline__ uint4 pack_row(const float2 (&acc)[4]) {
   uint4 o;
   o.x = pack_bf16x2(acc[0].x, acc[0].y);
   o.y = pack_bf16x2(acc[1].x, acc[1].y);
@@ -226,16 +288,57 @@ __device__ __forceinline__ uint4 blend_row(const RowLoad& L) {
   return o;
 }
 
-// Map-mode producer warp.  nslots ring slots are consumed per tile, of which the first nsl carry
+// Inverse-map mode, rare: entries five and up of the list of (tile row r, tap).
+__device__ __forceinline__ void blend_list_tail(const Source& s, const Tiling& t, int tile, int r,
+                                                int tap, const bf16* sb, float2 (&acc)[4]) {
+  long gp, p;
+  int img;
+  bool valid;
+  tile_pixel(t, tile, r, gp, img, p, valid);
+  if (!valid) return;
+  const long key = p * s.K + tap;
+  const int end = __ldg(s.inv_off + key + 1);
+  const bf16* base = sb + (long)img * s.spix * s.C;
+  for (int e = __ldg(s.inv_off + key) + 4; e < end; ++e) {
+    const int2 en = __ldg(s.inv_ent + e);
+    const uint4 v = ldg16(base + (long)en.x * s.C);
+    const float w = __int_as_float(en.y);
+    const float2 w2 = make_float2(w, w);
+    ffma2_bf16x2(acc[0], w2, v.x);
+    ffma2_bf16x2(acc[1], w2, v.y);
+    ffma2_bf16x2(acc[2], w2, v.z);
+    ffma2_bf16x2(acc[3], w2, v.w);
+  }
+}
+
+// Decoder warps: fill the table half of tile i while the producers gather tile i - 1.
+// tab_full / tab_empty: two mbarriers each (one per table half) at tabbar0 + 8 i / + 16 + 8 i.
+template <bool CSR>
+__device__ __forceinline__ void decoder_loop(const Source& s, const Tiling& t, TapEnt* table,
+                                             uint32_t tabbar0, volatile int* abort_flag, int dtid,
+                                             int lane) {
+  uint32_t it = 0;
+  for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x, ++it) {
+    const uint32_t half = it & 1, ph = (it >> 1) & 1;
+    int okw = 1;
+    if (lane == 0) okw = mbar_wait(tabbar0 + 16 + 8 * half, ph ^ 1, abort_flag, 0x71) ? 1 : 0;
+    okw = __shfl_sync(0xffffffffu, okw, 0);
+    if (!okw) return;
+    decode_tile<CSR>(s, t, tile, table + (size_t)half * TILE_M * s.K, dtid);
+    mbar_arrive(tabbar0 + 8 * half);
+  }
+}
+
+// Producer warp (CSR = false: sample map; true: inverse map).  nslots ring slots are consumed per tile, of which the first nsl carry
 // data (an odd slice count of the wgrad kernel is padded with a zero slice).  A group owns two rows
 // of every stage; while it blends one of them the loads of the other are in flight.
+template <bool CSR>
 __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling& t, int nsl,
                                                   int nslots, int nst, uint32_t stage0,
                                                   uint32_t full0, uint32_t empty0, TapEnt* table,
-                                                  volatile int* abort_flag, int pw, int lane,
-                                                  int code) {
+                                                  uint32_t tabbar0, volatile int* abort_flag,
+                                                  int pw, int lane, int code) {
   const int g = lane >> 3, lg = lane & 7;
-  const int ptid = pw * 32 + lane;
   const int cpb = s.C / 64;
   const int r0 = pw * 4 + g, r1 = r0 + N_PRODUCER_WARPS * 4;  // the two rows of a stage this group owns
   const uint32_t so0 = r0 * 128 + ((lg ^ (r0 & 7)) << 4), so1 = r1 * 128 + ((lg ^ (r1 & 7)) << 4);
@@ -244,8 +347,12 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
   uint32_t st = 0, ph = 0, it = 0;  // ring slot and its phase, advanced without divisions
   for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x, ++it) {
     const TapEnt* tab = table + (size_t)(it & 1) * TILE_M * s.K;
-    decode_tile(s, t, tile, const_cast<TapEnt*>(tab), ptid);
-    producer_bar();
+    {  // wait until the decoder warps have filled this half of the table
+      int okt = 1;
+      if (lane == 0) okt = mbar_wait(tabbar0 + 8 * (it & 1), (it >> 1) & 1, abort_flag, code) ? 1 : 0;
+      okt = __shfl_sync(0xffffffffu, okt, 0);
+      if (!okt) return;
+    }
     const TapEnt* t0 = tab + r0 * s.K;
     const TapEnt* t1 = tab + r1 * s.K;
     RowLoad A, B;
@@ -259,86 +366,26 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
       okw = __shfl_sync(0xffffffffu, okw, 0);
       if (!okw) return;
       const uint32_t sbase = stage0 + st * STAGE_BYTES;
-      sts16(sbase + so0, live ? blend_row(A) : zero);
+      float2 acc[4];
+      if (live) {
+        blend_row(A, acc);
+        if (CSR && A.more) blend_list_tail(s, t, tile, r0, tap, srcl + cb * 64, acc);
+      }
+      sts16(sbase + so0, live ? pack_row(acc) : zero);
+      const int tap_b = tap, cb_b = cb;
       if (++cb == cpb) { cb = 0; ++tap; }
       if (sl + 1 < nsl) issue_row(t0 + tap, srcl + cb * 64, s.C, A);
-      sts16(sbase + so1, live ? blend_row(B) : zero);
+      if (live) {
+        blend_row(B, acc);
+        if (CSR && B.more) blend_list_tail(s, t, tile, r1, tap_b, srcl + cb_b * 64, acc);
+      }
+      sts16(sbase + so1, live ? pack_row(acc) : zero);
       fence_proxy_async_smem();
       mbar_arrive(full0 + 8u * st);
       if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
     }
-  }
-}
-
-// Inverse-map producer warp (dgrad).
-__device__ __forceinline__ void producer_loop_inv(const Source& s, const Tiling& t, int nsl, int nst,
-                                                  uint32_t stage0, uint32_t full0, uint32_t empty0,
-                                                  volatile int* abort_flag, int pw, int lane,
-                                                  int code) {
-  const int g = lane >> 3, lg = lane & 7;
-  const int cpb = s.C / 64;
-  const bf16* srcl = s.src + lg * 8;
-  uint32_t st = 0, ph = 0;
-  for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x) {
-    // the two rows of every stage this group owns: pixel and image are the same for all slices
-    long key[2], base[2];
-    uint32_t so[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = pw * 4 + g + h * N_PRODUCER_WARPS * 4;
-      long gp, p;
-      int img;
-      bool valid;
-      tile_pixel(t, tile, r, gp, img, p, valid);
-      key[h] = valid ? p * s.K : -1;
-      base[h] = (long)img * s.spix * s.C;
-      so[h] = r * 128 + ((lg ^ (r & 7)) << 4);
-    }
-    int tap = 0, cb = 0;
-    for (int sl = 0; sl < nsl; ++sl) {
-      // list ranges first, so that they are in flight while we wait for the stage
-      int beg[2], end[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        beg[h] = end[h] = 0;
-        if (key[h] >= 0) {
-          beg[h] = __ldg(s.inv_off + key[h] + tap);
-          end[h] = __ldg(s.inv_off + key[h] + tap + 1);
-        }
-      }
-      int okw = 1;
-      if (lane == 0) okw = mbar_wait(empty0 + 8u * st, ph ^ 1, abort_flag, code) ? 1 : 0;
-      okw = __shfl_sync(0xffffffffu, okw, 0);
-      if (!okw) return;
-      const uint32_t sbase = stage0 + st * STAGE_BYTES;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        const bf16* sb = srcl + base[h] + cb * 64;
-        int e = beg[h];
-        for (; e + 3 < end[h]; e += 4) {
-          int2 en[4];
-          uint4 v[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) en[i] = __ldg(s.inv_ent + e + i);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) v[i] = ldg16(sb + (long)en[i].x * s.C);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) blend4(v[i], __int_as_float(en[i].y), acc);
-        }
-        for (; e < end[h]; ++e) {
-          const int2 en = __ldg(s.inv_ent + e);
-          blend4(ldg16(sb + (long)en.x * s.C), __int_as_float(en.y), acc);
-        }
-        sts16(sbase + so[h], pack8(acc));
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(full0 + 8u * st);
-      if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
-      if (++cb == cpb) { cb = 0; ++tap; }
-    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tabbar0 + 16 + 8 * (it & 1));  // this warp is done with the half
   }
 }
 
@@ -382,7 +429,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
   const int nst = a.nst;
   // bars: full[nst], empty[nst], tfull[2], tempty[2], drain
   const size_t wbytes = (size_t)a.nsl * NOUT * 128;
-  const Smem sm = carve(smem_raw, nst, wbytes + (CSR ? 0 : tap_table_bytes(a.s.K)), NOUT, 2 * nst + 5);
+  // bars: full[nst], empty[nst], tfull[2], tempty[2], drain, tab_full[2], tab_empty[2]
+  const Smem sm = carve(smem_raw, nst, wbytes + tap_table_bytes(a.s.K), NOUT, 2 * nst + 9);
   float* bias_s = sm.fl;
   volatile int* abort_flag = sm.abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -392,6 +440,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
   auto tfull_bar = [&](int i) { return bar0 + 8u * (2 * nst + i); };
   auto tempty_bar = [&](int i) { return bar0 + 8u * (2 * nst + 2 + i); };
   const uint32_t drain_bar = bar0 + 8u * (2 * nst + 4);
+  const uint32_t tabbar0 = bar0 + 8u * (2 * nst + 5);
   constexpr uint32_t TMEM_COLS = 2 * NOUT < 32 ? 32 : 2 * NOUT;
 
   if (threadIdx.x == 0) {
@@ -404,6 +453,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
       mbar_init(tempty_bar(i), N_EPI_WARPS * 32);
     }
     mbar_init(drain_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tabbar0 + 8 * i, N_DEC_THREADS);
+      mbar_init(tabbar0 + 16 + 8 * i, N_PRODUCER_WARPS);
+    }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -491,13 +544,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
     }
   } else {
     // ------------------------------------------------------------------ producers
-    if (CSR)
-      producer_loop_inv(a.s, a.t, a.nsl, nst, stage0, full_bar(0), empty_bar(0), abort_flag,
-                        warp - 1 - N_EPI_WARPS, lane, 0x31);
+    if (warp < FIRST_PROD_WARP)
+      decoder_loop<CSR>(a.s, a.t, (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
+                        (warp - FIRST_DEC_WARP) * 32 + lane, lane);
     else
-      producer_loop_map(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
-                        (TapEnt*)(sm.extra + wbytes),
-                        abort_flag, warp - 1 - N_EPI_WARPS, lane, 0x32);
+      producer_loop_map<CSR>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
+                             (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
+                             warp - FIRST_PROD_WARP, lane, CSR ? 0x31 : 0x32);
   }
 
   tc_fence_before_sync();
@@ -524,7 +577,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
   const int nst = a.nst;  // even
   // bars: full[nst], empty[nst], gfull[GY], gempty[GY], done
   const Smem sm = carve(smem_raw, nst, (size_t)GY_STAGES * STAGE_BYTES + tap_table_bytes(a.s.K), NOUT,
-                        2 * nst + 2 * GY_STAGES + 1);
+                        2 * nst + 2 * GY_STAGES + 5);
   float* gb_s = sm.fl;
   volatile int* abort_flag = sm.abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -534,6 +587,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
   auto gfull_bar = [&](int i) { return bar0 + 8u * (2 * nst + i); };
   auto gempty_bar = [&](int i) { return bar0 + 8u * (2 * nst + GY_STAGES + i); };
   const uint32_t done_bar = bar0 + 8u * (2 * nst + 2 * GY_STAGES);
+  const uint32_t tabbar0 = done_bar + 8u;
   const int nmt = (a.nsl + 1) / 2;        // M = 128 tiles of the gradient
   const int nsl_pad = nmt * 2;            // ring slots used per pixel tile
   const uint32_t tmem_cols = nmt * NOUT <= 32 ? 32 : nmt * NOUT <= 64 ? 64 : nmt * NOUT <= 128 ? 128
@@ -549,6 +603,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
       mbar_init(gempty_bar(i), 1);
     }
     mbar_init(done_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tabbar0 + 8 * i, N_DEC_THREADS);
+      mbar_init(tabbar0 + 16 + 8 * i, N_PRODUCER_WARPS);
+    }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -664,9 +722,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
     }
   } else {
     // ------------------------------------------------------------------ producers
-    producer_loop_map(a.s, a.t, a.nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
-                      (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES),
-                      abort_flag, warp - 1 - N_EPI_WARPS, lane, 0x61);
+    if (warp < FIRST_PROD_WARP)
+      decoder_loop<false>(a.s, a.t, (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES), tabbar0,
+                          abort_flag, (warp - FIRST_DEC_WARP) * 32 + lane, lane);
+    else
+      producer_loop_map<false>(a.s, a.t, a.nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
+                               (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES), tabbar0,
+                               abort_flag, warp - FIRST_PROD_WARP, lane, 0x61);
   }
 
   tc_fence_before_sync();
@@ -777,7 +839,7 @@ static int sm_count() {
 static int pick_stages(size_t extra, int nfloat, int max_st, int min_st, bool even) {
   for (int nst = max_st; nst >= min_st; --nst) {
     if (even && (nst & 1)) continue;
-    if (smem_bytes(nst, extra, nfloat, 2 * nst + 8) <= SMEM_LIMIT) return nst;
+    if (smem_bytes(nst, extra, nfloat, 2 * nst + 16) <= SMEM_LIMIT) return nst;
   }
   return 0;
 }
@@ -825,7 +887,7 @@ int conv_tc_fwd_launch(const mc_desc* d, const void* x, const void* map, const v
                                                          d->C_in, d->K, 0, d->C_in), MC_COUNT(1);
   static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, false>);
   if (!attr) return MC_ERR_LAUNCH;
-  const size_t smem = smem_bytes(a.nst, extra, d->C_out, 2 * a.nst + 5);
+  const size_t smem = smem_bytes(a.nst, extra, d->C_out, 2 * a.nst + 9);
   const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
   conv_gemm_tc_kernel<64, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
@@ -894,7 +956,7 @@ bool conv_tc_dgrad_supported(const mc_desc* d) {
   if (d->C_out % 64 != 0 || d->C_in != 64) return false;
   if (!invmap_supported(d)) return false;
   const int nsl = d->K * (d->C_out / 64);
-  return pick_stages((size_t)nsl * d->C_in * 128, d->C_in, 8, 3, false) > 0;
+  return pick_stages((size_t)nsl * d->C_in * 128 + tap_table_bytes(d->K), d->C_in, 8, 3, false) > 0;
 }
 
 size_t conv_tc_dgrad_ws(const mc_desc* d) {
@@ -914,13 +976,14 @@ int conv_tc_dgrad_launch(const mc_desc* d, const void* gy, const void* inv, cons
   if (!make_tiling(a.t, d->B, d->IH, d->IW)) return MC_ERR_TOO_LARGE;
   a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias_out; a.y = (bf16*)gx;
   a.nsl = d->K * (d->C_out / 64);
-  a.nst = pick_stages((size_t)a.nsl * d->C_in * 128, d->C_in, 8, 3, false);
+  const size_t extra = (size_t)a.nsl * d->C_in * 128 + tap_table_bytes(d->K);
+  a.nst = pick_stages(extra, d->C_in, 8, 3, false);
   const long nw = (long)d->K * d->C_in * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_in,
                                                          d->C_out, d->K, 1, d->C_in), MC_COUNT(1);
   static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, true>);
   if (!attr) return MC_ERR_LAUNCH;
-  const size_t smem = smem_bytes(a.nst, (size_t)a.nsl * d->C_in * 128, d->C_in, 2 * a.nst + 5);
+  const size_t smem = smem_bytes(a.nst, extra, d->C_in, 2 * a.nst + 9);
   const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
   conv_gemm_tc_kernel<64, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
@@ -959,7 +1022,7 @@ int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const 
   static bool attr = allow_big_smem(conv_wgrad_tc_kernel<64>);
   if (!attr) return MC_ERR_LAUNCH;
   const size_t smem = smem_bytes(a.nst, extra, d->C_out,
-                                 2 * a.nst + 2 * GY_STAGES + 1);
+                                 2 * a.nst + 2 * GY_STAGES + 5);
   const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
   conv_wgrad_tc_kernel<64><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();

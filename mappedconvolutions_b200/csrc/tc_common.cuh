@@ -15,7 +15,6 @@ namespace tc {
 // relocatable device code.
 static __device__ int g_status = 0;
 
-constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -41,13 +40,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false if another role already gave up, or if the limit ran out (in
-// which case it raises the abort flag of the block and the status word of the device).
+// try_wait that lets the hardware suspend the thread for up to `hint_ns` while the phase is pending,
+// instead of burning issue slots in a polling loop.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait (about one second of SM clock).  Returns false if another role already gave up, or
+// if the limit ran out, in which case it raises the abort flag of the block and the status word
+// of the device.
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int code) {
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63) == 63 && *abort_flag) return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
   }
   *abort_flag = 1;
   atomicCAS(&g_status, 0, code);
