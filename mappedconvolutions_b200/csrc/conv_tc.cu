@@ -325,7 +325,8 @@ __device__ __forceinline__ void decoder_loop(const Source& s, const Tiling& t, T
     okw = __shfl_sync(0xffffffffu, okw, 0);
     if (!okw) return;
     decode_tile<CSR>(s, t, tile, table + (size_t)half * TILE_M * s.K, dtid);
-    mbar_arrive(tabbar0 + 8 * half);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tabbar0 + 8 * half);
   }
 }
 
@@ -380,8 +381,10 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
         if (CSR && B.more) blend_list_tail(s, t, tile, r1, tap_b, srcl + cb_b * 64, acc);
       }
       sts16(sbase + so1, live ? pack_row(acc) : zero);
+      // every lane publishes its own writes to the async proxy; one arrival per warp
       fence_proxy_async_smem();
-      mbar_arrive(full0 + 8u * st);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full0 + 8u * st);
       if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
     }
     __syncwarp();
@@ -445,16 +448,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
-      mbar_init(full_bar(s), N_PRODUCER_WARPS * 32);
+      mbar_init(full_bar(s), N_PRODUCER_WARPS);
       mbar_init(empty_bar(s), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(tfull_bar(i), 1);
-      mbar_init(tempty_bar(i), N_EPI_WARPS * 32);
+      mbar_init(tempty_bar(i), N_EPI_WARPS);
     }
     mbar_init(drain_bar, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(tabbar0 + 8 * i, N_DEC_THREADS);
+      mbar_init(tabbar0 + 8 * i, N_DEC_WARPS);
       mbar_init(tabbar0 + 16 + 8 * i, N_PRODUCER_WARPS);
     }
     *abort_flag = 0;
@@ -526,7 +529,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
         if (cc == NOUT / 32 - 1) {
           // accumulator fully read: hand the buffer back before the global stores
           tc_fence_before_sync();
-          mbar_arrive(tempty_bar(acc));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(acc));
         }
         if (valid) {
 #pragma unroll
@@ -595,16 +599,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
-      mbar_init(full_bar(s), N_PRODUCER_WARPS * 32);
+      mbar_init(full_bar(s), N_PRODUCER_WARPS);
       mbar_init(empty_bar(s), 1);
     }
     for (int i = 0; i < GY_STAGES; ++i) {
-      mbar_init(gfull_bar(i), N_EPI_WARPS * 32);
+      mbar_init(gfull_bar(i), N_EPI_WARPS);
       mbar_init(gempty_bar(i), 1);
     }
     mbar_init(done_bar, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(tabbar0 + 8 * i, N_DEC_THREADS);
+      mbar_init(tabbar0 + 8 * i, N_DEC_WARPS);
       mbar_init(tabbar0 + 16 + 8 * i, N_PRODUCER_WARPS);
     }
     *abort_flag = 0;
@@ -683,7 +687,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
         }
       }
       fence_proxy_async_smem();
-      mbar_arrive(gfull_bar(gs));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(gfull_bar(gs));
     }
     // bias gradient: lanes -> shared -> global
     if (a.gb) {
