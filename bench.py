@@ -324,11 +324,14 @@ def run_ours(args):
             dgrad = lambda: _lib.check(L.mc_conv_dgrad_inv(d, gy.data_ptr(), inv.data_ptr(), w.data_ptr(), None, gx.data_ptr(), ws.data_ptr(), nws, st))
         else:
             dgrad = lambda: _lib.check(L.mc_conv_dgrad(d, gy.data_ptr(), m.data_ptr(), None, w.data_ptr(), None, gx.data_ptr(), ws.data_ptr(), nws, st))
-        fam = {
-            "conv_fwd": lambda: _lib.check(L.mc_conv_fwd(d, x.data_ptr(), m.data_ptr(), None, w.data_ptr(), b.data_ptr(), y.data_ptr(), ws.data_ptr(), nws, st)),
-            "conv_dgrad": dgrad,
-            "conv_wgrad": lambda: _lib.check(L.mc_conv_wgrad(d, gy.data_ptr(), x.data_ptr(), m.data_ptr(), None, gw.data_ptr(), gb.data_ptr(), ws.data_ptr(), nws, st)),
-        }
+        tab = ops._tap_map(d, m)
+        if tab is not None:
+            fwd = lambda: _lib.check(L.mc_conv_fwd_tap(d, x.data_ptr(), tab.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), ws.data_ptr(), nws, st))
+            wgrad = lambda: _lib.check(L.mc_conv_wgrad_tap(d, gy.data_ptr(), x.data_ptr(), tab.data_ptr(), gw.data_ptr(), gb.data_ptr(), st))
+        else:
+            fwd = lambda: _lib.check(L.mc_conv_fwd(d, x.data_ptr(), m.data_ptr(), None, w.data_ptr(), b.data_ptr(), y.data_ptr(), ws.data_ptr(), nws, st))
+            wgrad = lambda: _lib.check(L.mc_conv_wgrad(d, gy.data_ptr(), x.data_ptr(), m.data_ptr(), None, gw.data_ptr(), gb.data_ptr(), ws.data_ptr(), nws, st))
+        fam = {"conv_fwd": fwd, "conv_dgrad": dgrad, "conv_wgrad": wgrad}
         times = {k: timed(f) for k, f in fam.items()}
         top = max(times, key=times.get)
         pk = peaks()

@@ -110,6 +110,20 @@ int mc_conv_dgrad(const mc_desc* d, const void* gy, const void* map, const void*
                   const void* bias_out, void* gx, void* ws, size_t ws_bytes, void* stream);
 size_t mc_conv_dgrad_workspace_bytes(const mc_desc* d);
 
+/* Tap table: the sample map decoded once - for every map entry the (up to four) source pixels and
+ * interpolation weights, 32 bytes each.  Like the inverse map below it depends only on the map and
+ * the image size, so a layer builds it once and passes it to every forward / weight-gradient call;
+ * the tensor-core kernels then stream it with bulk copies instead of decoding the map again for
+ * every batch.  mc_tapmap_bytes() is 0 when the descriptor has no tensor-core path.
+ * mc_conv_fwd_tap / mc_conv_wgrad_tap compute exactly what mc_conv_fwd / mc_conv_wgrad compute
+ * (same reference drivers: src/nn/cuda/mapped_convolution_layer.cu:16-73, :134-193). */
+size_t mc_tapmap_bytes(const mc_desc* d);
+int mc_tapmap_build(const mc_desc* d, const void* map, void* tapmap, size_t tapmap_bytes, void* stream);
+int mc_conv_fwd_tap(const mc_desc* d, const void* x, const void* tapmap, const void* w,
+                    const void* bias, void* y, void* ws, size_t ws_bytes, void* stream);
+int mc_conv_wgrad_tap(const mc_desc* d, const void* gy, const void* x, const void* tapmap, void* gw,
+                      void* gb, void* stream);
+
 /* Inverse map: for every (input pixel, tap) the list of (grid pixel, weight) pairs whose forward
  * sample reads that input pixel.  It depends only on the sample map and the two image sizes, so
  * it is built once per map and reused by every backward pass.  With it the reference's atomic

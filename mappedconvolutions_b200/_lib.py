@@ -39,6 +39,10 @@ SIGNATURES = {
     "mc_conv_fwd_static_scratch": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mc_conv_dgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_dgrad_workspace_bytes": (_sz, [_dp]),
+    "mc_tapmap_bytes": (_sz, [_dp]),
+    "mc_tapmap_build": (ctypes.c_int, [_dp, _vp, _vp, _sz, _vp]),
+    "mc_conv_fwd_tap": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "mc_conv_wgrad_tap": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mc_invmap_bytes": (_sz, [_dp]),
     "mc_invmap_build_workspace_bytes": (_sz, [_dp]),
     "mc_invmap_build": (ctypes.c_int, [_dp, _vp, _vp, _sz, _vp, _sz, _vp]),

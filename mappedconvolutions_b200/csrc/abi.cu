@@ -24,6 +24,12 @@ bool conv_tc_dgrad_supported(const mc_desc*);
 size_t conv_tc_dgrad_ws(const mc_desc*);
 int conv_tc_dgrad_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
                          void*, size_t, cudaStream_t);
+size_t tapmap_bytes(const mc_desc*);
+int tapmap_build_launch(const mc_desc*, const void*, void*, cudaStream_t);
+int conv_tc_fwd_tab_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
+                           void*, size_t, cudaStream_t);
+int conv_tc_wgrad_tab_launch(const mc_desc*, const void*, const void*, const void*, void*, void*,
+                             cudaStream_t);
 bool invmap_supported(const mc_desc*);
 size_t invmap_bytes(const mc_desc*);
 size_t invmap_build_ws(const mc_desc*);
@@ -82,6 +88,37 @@ int mc_conv_fwd(const mc_desc* d, const void* x, const void* map, const void* iw
 size_t mc_conv_dgrad_workspace_bytes(const mc_desc* d) {
   if (!d || check_conv_desc_public(d)) return 0;
   return conv_dgrad_simt_ws(d);
+}
+
+// ---- prebuilt forward tap table ------------------------------------------------------------------
+
+size_t mc_tapmap_bytes(const mc_desc* d) {
+  if (!d || check_conv_desc_public(d)) return 0;
+  return (conv_tc_fwd_supported(d) || conv_tc_wgrad_supported(d)) ? tapmap_bytes(d) : 0;
+}
+int mc_tapmap_build(const mc_desc* d, const void* map, void* tapmap, size_t tapmap_bytes_, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!map || !tapmap) return MC_ERR_BAD_ARG;
+  if (d->P != 0 || d->dtype == MC_F64) return MC_ERR_UNSUPPORTED;
+  if (tapmap_bytes_ < tapmap_bytes(d)) return MC_ERR_WORKSPACE;
+  return tapmap_build_launch(d, map, tapmap, (cudaStream_t)stream);
+}
+int mc_conv_fwd_tap(const mc_desc* d, const void* x, const void* tapmap, const void* w,
+                    const void* bias, void* y, void* ws, size_t ws_bytes, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!x || !tapmap || !w || !y) return MC_ERR_BAD_ARG;
+  if (!conv_tc_fwd_supported(d)) return MC_ERR_UNSUPPORTED;
+  return conv_tc_fwd_tab_launch(d, x, tapmap, w, bias, y, ws, ws_bytes, (cudaStream_t)stream);
+}
+int mc_conv_wgrad_tap(const mc_desc* d, const void* gy, const void* x, const void* tapmap, void* gw,
+                      void* gb, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!gy || !x || !tapmap || !gw) return MC_ERR_BAD_ARG;
+  if (!conv_tc_wgrad_supported(d)) return MC_ERR_UNSUPPORTED;
+  return conv_tc_wgrad_tab_launch(d, gy, x, tapmap, gw, gb, (cudaStream_t)stream);
 }
 
 // ---- inverse map and the gather-form dgrad ---------------------------------------------------

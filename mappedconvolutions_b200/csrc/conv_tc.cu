@@ -78,6 +78,13 @@ __device__ __forceinline__ void tile_pixel(const Tiling& t, int tile, int r, lon
   }
 }
 
+// One decoded (pixel, tap): up to four source pixels and their weights.  The same 32-byte record
+// is used in shared memory and in the prebuilt global tables.
+struct TapEnt {
+  int off[4];  // source pixel index inside its image, or -1; off[3] may carry MORE_FLAG
+  float w[4];
+};
+
 // What the producer warps gather from.
 struct Source {
   const bf16* src;  // (B, spix, C) channels-last tensor that is gathered
@@ -88,6 +95,7 @@ struct Source {
   const float* map;   // map mode: (npix, K, 2)
   const int* inv_off; // inverse-map mode: (npix * K + 1) list offsets
   const int2* inv_ent;  //                 (source pixel, weight bits) entries
+  const TapEnt* tab;    // prebuilt table [pixel of the tiled domain][tap], or null
 };
 
 struct GemmArgs {
@@ -122,10 +130,6 @@ __device__ __forceinline__ void blend4(const uint4& v, float w, float (&acc)[8])
 // Inverse-map mode (dgrad): every row walks its (source pixel, weight) list straight from global
 // memory.
 
-struct TapEnt {   // 32 bytes
-  int off[4];     // source pixel index inside the whole (B, pix) tensor, or -1
-  float w[4];
-};
 
 constexpr int N_DEC_THREADS = N_DEC_WARPS * 32;
 
@@ -202,7 +206,7 @@ __device__ __forceinline__ void decode_tile(const Source& s, const Tiling& t, in
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           if (en[u][i].x >= 0) {
-            ent[u].off[i] = ibase[u] + en[u][i].x;
+            ent[u].off[i] = en[u][i].x;
             ent[u].w[i] = __int_as_float(en[u][i].y);
           }
         }
@@ -221,7 +225,7 @@ __device__ __forceinline__ void decode_tile(const Source& s, const Tiling& t, in
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const bool on = i < tp.n && tp.off[i] >= 0 && tp.w[i] != 0.f;
-          ent[u].off[i] = on ? ibase[u] + tp.off[i] : -1;
+          ent[u].off[i] = on ? tp.off[i] : -1;
           ent[u].w[i] = on ? tp.w[i] : 0.f;
         }
       }
@@ -254,16 +258,19 @@ struct RowLoad {
   bool more;  // inverse-map mode: the list continues beyond these four
 };
 
-__device__ __forceinline__ void issue_row(const TapEnt* ent, const bf16* sb, int C, RowLoad& L) {
+__device__ __forceinline__ void issue_row(const TapEnt* ent, const bf16* sb, int ibase, int C,
+                                          RowLoad& L) {
   const uint4* e = reinterpret_cast<const uint4*>(ent);
   const uint4 o = e[0], w = e[1];
   L.more = (int)o.w >= 0 && ((int)o.w & MORE_FLAG) != 0;
   const int of[4] = {(int)o.x, (int)o.y, (int)o.z, L.more ? (int)o.w & ~MORE_FLAG : (int)o.w};
-  L.w[0] = __uint_as_float(w.x); L.w[1] = __uint_as_float(w.y);
-  L.w[2] = __uint_as_float(w.z); L.w[3] = __uint_as_float(w.w);
+  const bool rowok = ibase >= 0;  // a row beyond the end of the batch contributes zeros
+  L.w[0] = rowok ? __uint_as_float(w.x) : 0.f; L.w[1] = rowok ? __uint_as_float(w.y) : 0.f;
+  L.w[2] = rowok ? __uint_as_float(w.z) : 0.f; L.w[3] = rowok ? __uint_as_float(w.w) : 0.f;
+  L.more = L.more && rowok;
 #pragma unroll
   for (int i = 0; i < 4; ++i)
-    L.v[i] = of[i] >= 0 ? ldg16(sb + (long)of[i] * C) : make_uint4(0, 0, 0, 0);
+    L.v[i] = (of[i] >= 0 && ibase >= 0) ? ldg16(sb + (long)(ibase + of[i]) * C) : make_uint4(0, 0, 0, 0);
 }
 
 __device__ __forceinline__ void blend_row(const RowLoad& L, float2 (&acc)[4]) {
@@ -330,6 +337,43 @@ __device__ __forceinline__ void decoder_loop(const Source& s, const Tiling& t, T
   }
 }
 
+// Prebuilt-table mode: one thread streams the table slice of tile i into its half with bulk
+// copies (the copy engine signals the mbarrier with the byte count) while tile i - 1 is gathered.
+__device__ __forceinline__ void loader_loop(const Source& s, const Tiling& t, uint32_t table0,
+                                            uint32_t tabbar0, volatile int* abort_flag) {
+  const uint32_t entb = (uint32_t)s.K * (uint32_t)sizeof(TapEnt);  // bytes per pixel
+  uint32_t it = 0;
+  for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x, ++it) {
+    const uint32_t half = it & 1, ph = (it >> 1) & 1;
+    if (!mbar_wait(tabbar0 + 16 + 8 * half, ph ^ 1, abort_flag, 0x72)) return;
+    const uint32_t dst0 = table0 + half * TILE_M * entb, bar = tabbar0 + 8 * half;
+    if (t.tile2d) {
+      const int img = tile / t.tiles_per_img;
+      const int tt = tile - img * t.tiles_per_img;
+      const int ty = tt / t.tiles_x, tx = tt - ty * t.tiles_x;
+      mbar_expect_tx(bar, TILE_M * entb);
+      for (int ry = 0; ry < 8; ++ry) {
+        const long p0 = (long)(ty * 8 + ry) * t.W + tx * 16;
+        bulk_g2s(dst0 + ry * 16 * entb, s.tab + p0 * s.K, 16 * entb, bar);
+      }
+    } else {
+      // rows of the tile are consecutive pixels of the batch; a run ends at an image boundary
+      long gp = (long)tile * TILE_M;
+      long left = t.mtot - gp;
+      if (left > TILE_M) left = TILE_M;
+      mbar_expect_tx(bar, (uint32_t)left * entb);
+      int r = 0;
+      while (left > 0) {
+        const long p = gp % t.npix;
+        long len = t.npix - p;
+        if (len > left) len = left;
+        bulk_g2s(dst0 + r * entb, s.tab + p * s.K, (uint32_t)len * entb, bar);
+        r += (int)len; gp += len; left -= len;
+      }
+    }
+  }
+}
+
 // Producer warp (CSR = false: sample map; true: inverse map).  nslots ring slots are consumed per tile, of which the first nsl carry
 // data (an odd slice count of the wgrad kernel is padded with a zero slice).  A group owns two rows
 // of every stage; while it blends one of them the loads of the other are in flight.
@@ -356,12 +400,21 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
     }
     const TapEnt* t0 = tab + r0 * s.K;
     const TapEnt* t1 = tab + r1 * s.K;
+    // first source pixel of the image each of the two rows belongs to (-1: row beyond the end)
+    int ib0, ib1;
+    if (t.tile2d) {
+      ib0 = ib1 = (tile / t.tiles_per_img) * (int)s.spix;
+    } else {
+      const long g0 = (long)tile * TILE_M + r0, g1 = (long)tile * TILE_M + r1;
+      ib0 = g0 < t.mtot ? (int)(g0 / t.npix) * (int)s.spix : -1;
+      ib1 = g1 < t.mtot ? (int)(g1 / t.npix) * (int)s.spix : -1;
+    }
     RowLoad A, B;
-    issue_row(t0, srcl, s.C, A);  // slice 0: tap 0, channel block 0
+    issue_row(t0, srcl, ib0, s.C, A);  // slice 0: tap 0, channel block 0
     int tap = 0, cb = 0;          // of the current slice
     for (int sl = 0; sl < nslots; ++sl) {
       const bool live = sl < nsl;
-      if (live) issue_row(t1 + tap, srcl + cb * 64, s.C, B);
+      if (live) issue_row(t1 + tap, srcl + cb * 64, ib1, s.C, B);
       int okw = 1;
       if (lane == 0) okw = mbar_wait(empty0 + 8u * st, ph ^ 1, abort_flag, code) ? 1 : 0;
       okw = __shfl_sync(0xffffffffu, okw, 0);
@@ -375,7 +428,7 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
       sts16(sbase + so0, live ? pack_row(acc) : zero);
       const int tap_b = tap, cb_b = cb;
       if (++cb == cpb) { cb = 0; ++tap; }
-      if (sl + 1 < nsl) issue_row(t0 + tap, srcl + cb * 64, s.C, A);
+      if (sl + 1 < nsl) issue_row(t0 + tap, srcl + cb * 64, ib0, s.C, A);
       if (live) {
         blend_row(B, acc);
         if (CSR && B.more) blend_list_tail(s, t, tile, r1, tap_b, srcl + cb_b * 64, acc);
@@ -426,7 +479,9 @@ static size_t smem_bytes(int nst, size_t extra_bytes, int nfloat, int nbar) {
 // ------------------------------------------------------------------------------------------------
 // forward / dgrad:  D[128 pixels, NOUT] = gathered[128, nsl * 64] . Wimg^T
 // ------------------------------------------------------------------------------------------------
-template <int NOUT, bool CSR>
+// PRE: the tap table of the tiled domain was built beforehand in global memory (a.s.tab) and is
+// streamed in by bulk copies; otherwise three warps decode the map / the inverse map in the kernel.
+template <int NOUT, bool CSR, bool PRE>
 __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int nst = a.nst;
@@ -457,7 +512,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
     }
     mbar_init(drain_bar, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(tabbar0 + 8 * i, N_DEC_WARPS);
+      mbar_init(tabbar0 + 8 * i, PRE ? 1 : N_DEC_WARPS);
       mbar_init(tabbar0 + 16 + 8 * i, N_PRODUCER_WARPS);
     }
     *abort_flag = 0;
@@ -548,10 +603,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
     }
   } else {
     // ------------------------------------------------------------------ producers
-    if (warp < FIRST_PROD_WARP)
-      decoder_loop<CSR>(a.s, a.t, (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
-                        (warp - FIRST_DEC_WARP) * 32 + lane, lane);
-    else
+    if (warp < FIRST_PROD_WARP) {
+      if (PRE) {
+        if (warp == FIRST_DEC_WARP && lane == 0)
+          loader_loop(a.s, a.t, w0 + (uint32_t)wbytes, tabbar0, abort_flag);
+      } else {
+        decoder_loop<CSR>(a.s, a.t, (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
+                          (warp - FIRST_DEC_WARP) * 32 + lane, lane);
+      }
+    } else
       producer_loop_map<CSR>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
                              (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
                              warp - FIRST_PROD_WARP, lane, CSR ? 0x31 : 0x32);
@@ -575,7 +635,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
 // to gw with atomics at the end.
 constexpr int GY_STAGES = 2;
 
-template <int NOUT>
+template <int NOUT, bool PRE>
 __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const GemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int nst = a.nst;  // even
@@ -608,7 +668,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
     }
     mbar_init(done_bar, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(tabbar0 + 8 * i, N_DEC_WARPS);
+      mbar_init(tabbar0 + 8 * i, PRE ? 1 : N_DEC_WARPS);
       mbar_init(tabbar0 + 16 + 8 * i, N_PRODUCER_WARPS);
     }
     *abort_flag = 0;
@@ -727,10 +787,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
     }
   } else {
     // ------------------------------------------------------------------ producers
-    if (warp < FIRST_PROD_WARP)
-      decoder_loop<false>(a.s, a.t, (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES), tabbar0,
-                          abort_flag, (warp - FIRST_DEC_WARP) * 32 + lane, lane);
-    else
+    if (warp < FIRST_PROD_WARP) {
+      if (PRE) {
+        if (warp == FIRST_DEC_WARP && lane == 0)
+          loader_loop(a.s, a.t, gy0 + (uint32_t)GY_STAGES * STAGE_BYTES, tabbar0, abort_flag);
+      } else {
+        decoder_loop<false>(a.s, a.t, (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES), tabbar0,
+                            abort_flag, (warp - FIRST_DEC_WARP) * 32 + lane, lane);
+      }
+    } else
       producer_loop_map<false>(a.s, a.t, a.nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
                                (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES), tabbar0,
                                abort_flag, warp - FIRST_PROD_WARP, lane, 0x61);
@@ -829,6 +894,55 @@ __global__ void invmap_sort_kernel(const int* __restrict__ off, int2* __restrict
   }
 }
 
+// Forward tap table: TapEnt[(pixel of the map grid) * K + tap], offsets relative to the image.
+__global__ void tapmap_build_kernel(const float* __restrict__ map, TapEnt* __restrict__ out, long n,
+                                    int SH, int SW, int interp) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const float2 m = __ldg(reinterpret_cast<const float2*>(map) + i);
+    Tap<float> tp;
+    decode_tap<float, float>(m.x, m.y, SH, SW, interp, tp);
+    int off[4];
+    float w[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const bool on = c < tp.n && tp.off[c] >= 0 && tp.w[c] != 0.f;
+      off[c] = on ? tp.off[c] : -1;
+      w[c] = on ? tp.w[c] : 0.f;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + i);
+    dst[0] = make_uint4(off[0], off[1], off[2], off[3]);
+    dst[1] = make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]),
+                        __float_as_uint(w[3]));
+  }
+}
+
+// Inverse tap table: the first four entries of every (input pixel, tap) list in TapEnt form;
+// MORE_FLAG marks the lists that go on.
+__global__ void invtap_build_kernel(const int* __restrict__ off, const int2* __restrict__ ent,
+                                    TapEnt* __restrict__ out, long nkeys) {
+  for (long key = blockIdx.x * (long)blockDim.x + threadIdx.x; key < nkeys;
+       key += (long)gridDim.x * blockDim.x) {
+    const int b = off[key], e = off[key + 1];
+    int o[4];
+    float w[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      o[c] = -1;
+      w[c] = 0.f;
+      if (b + c < e) {
+        const int2 en = ent[b + c];
+        o[c] = en.x;
+        w[c] = __int_as_float(en.y);
+      }
+    }
+    if (e - b > 4) o[3] |= MORE_FLAG;
+    uint4* dst = reinterpret_cast<uint4*>(out + key);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]),
+                        __float_as_uint(w[3]));
+  }
+}
+
 static int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -874,14 +988,31 @@ size_t conv_tc_fwd_ws(const mc_desc* d) {
   return (size_t)d->K * d->C_in * d->C_out * sizeof(bf16);
 }
 
-int conv_tc_fwd_launch(const mc_desc* d, const void* x, const void* map, const void* w,
-                       const void* bias, void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+// Forward tap table of a sample map (one TapEnt per map entry).
+size_t tapmap_bytes(const mc_desc* d) { return (size_t)d->OH * d->OW * d->K * sizeof(TapEnt); }
+
+int tapmap_build_launch(const mc_desc* d, const void* map, void* tab, cudaStream_t st) {
+  if (!aligned16(map) || !aligned16(tab)) return MC_ERR_BAD_ARG;
+  const long n = (long)d->OH * d->OW * d->K;
+  tapmap_build_kernel<<<grid_for(n, 256), 256, 0, st>>>((const float*)map, (TapEnt*)tab, n, d->IH,
+                                                        d->IW, d->interp), MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
+
+// map != null: the kernel decodes the map itself; tab != null: prebuilt table (tapmap_build_launch)
+static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, const void* tab,
+                           const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
+                           cudaStream_t st) {
   if (!ws || ws_bytes < conv_tc_fwd_ws(d)) return MC_ERR_WORKSPACE;
-  if (!aligned16(x) || !aligned16(y) || !aligned16(ws) || !aligned16(map)) return MC_ERR_BAD_ARG;
+  if (!aligned16(x) || !aligned16(y) || !aligned16(ws) || !aligned16(map) || !aligned16(tab))
+    return MC_ERR_BAD_ARG;
+  if ((long)d->B * d->IH * d->IW >= (1L << 30)) return MC_ERR_TOO_LARGE;
   GemmArgs a = {};
   a.s.src = (const bf16*)x; a.s.spix = (long)d->IH * d->IW; a.s.C = d->C_in;
   a.s.SH = d->IH; a.s.SW = d->IW; a.s.K = d->K; a.s.interp = d->interp;
   a.s.map = (const float*)map;
+  a.s.tab = (const TapEnt*)tab;
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
   a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias; a.y = (bf16*)y;
   a.nsl = d->K * (d->C_in / 64);
@@ -890,13 +1021,25 @@ int conv_tc_fwd_launch(const mc_desc* d, const void* x, const void* map, const v
   const long nw = (long)d->K * d->C_in * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_out,
                                                          d->C_in, d->K, 0, d->C_in), MC_COUNT(1);
-  static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, false>);
+  static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, false, false>) &&
+                     allow_big_smem(conv_gemm_tc_kernel<64, false, true>);
   if (!attr) return MC_ERR_LAUNCH;
   const size_t smem = smem_bytes(a.nst, extra, d->C_out, 2 * a.nst + 9);
   const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
-  conv_gemm_tc_kernel<64, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  if (tab) conv_gemm_tc_kernel<64, false, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  else conv_gemm_tc_kernel<64, false, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
+}
+
+int conv_tc_fwd_launch(const mc_desc* d, const void* x, const void* map, const void* w,
+                       const void* bias, void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+  return fwd_launch_impl(d, x, map, nullptr, w, bias, y, ws, ws_bytes, st);
+}
+
+int conv_tc_fwd_tab_launch(const mc_desc* d, const void* x, const void* tab, const void* w,
+                           const void* bias, void* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+  return fwd_launch_impl(d, x, nullptr, tab, w, bias, y, ws, ws_bytes, st);
 }
 
 // ---- inverse map ---------------------------------------------------------------------------------------
@@ -914,7 +1057,13 @@ bool invmap_supported(const mc_desc* d) {
   if (d->P != 0 || d->dtype == MC_F64) return false;
   return (size_t)d->IH * d->IW * d->K < (1u << 30) && inv_max_entries(d) < (1u << 31);
 }
-size_t invmap_bytes(const mc_desc* d) { return inv_off_bytes(d) + inv_max_entries(d) * sizeof(int2); }
+// layout: int off[nkeys + 1] | int2 ent[max entries] | TapEnt table[nkeys]   (each part 32-byte aligned)
+static size_t inv_tab_offset(const mc_desc* d) {
+  return (inv_off_bytes(d) + inv_max_entries(d) * sizeof(int2) + 31) & ~(size_t)31;
+}
+size_t invmap_bytes(const mc_desc* d) {
+  return inv_tab_offset(d) + (size_t)d->IH * d->IW * d->K * sizeof(TapEnt);
+}
 
 static size_t scan_temp_bytes(size_t n) {
   size_t t = 0;
@@ -950,6 +1099,8 @@ int invmap_build_launch(const mc_desc* d, const void* map, void* inv, void* ws, 
   if (cudaMemsetAsync(a.cnt, 0, (nkeys + 1) * sizeof(int), st) != cudaSuccess) return MC_ERR_LAUNCH;
   invmap_pass_kernel<2><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
   invmap_sort_kernel<<<grid_for((long)nkeys, 256), 256, 0, st>>>(a.off, a.ent, (long)nkeys), MC_COUNT(1);
+  invtap_build_kernel<<<grid_for((long)nkeys, 256), 256, 0, st>>>(
+      a.off, a.ent, (TapEnt*)((uint8_t*)inv + inv_tab_offset(d)), (long)nkeys), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
@@ -978,6 +1129,8 @@ int conv_tc_dgrad_launch(const mc_desc* d, const void* gy, const void* inv, cons
   a.s.K = d->K; a.s.interp = d->interp;
   a.s.inv_off = (const int*)inv;
   a.s.inv_ent = (const int2*)((const uint8_t*)inv + inv_off_bytes(d));
+  a.s.tab = (const TapEnt*)((const uint8_t*)inv + inv_tab_offset(d));
+  if ((long)d->B * d->OH * d->OW >= (1L << 30)) return MC_ERR_TOO_LARGE;
   if (!make_tiling(a.t, d->B, d->IH, d->IW)) return MC_ERR_TOO_LARGE;
   a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias_out; a.y = (bf16*)gx;
   a.nsl = d->K * (d->C_out / 64);
@@ -986,11 +1139,11 @@ int conv_tc_dgrad_launch(const mc_desc* d, const void* gy, const void* inv, cons
   const long nw = (long)d->K * d->C_in * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_in,
                                                          d->C_out, d->K, 1, d->C_in), MC_COUNT(1);
-  static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, true>);
+  static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, true, true>);
   if (!attr) return MC_ERR_LAUNCH;
   const size_t smem = smem_bytes(a.nst, extra, d->C_in, 2 * a.nst + 9);
   const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
-  conv_gemm_tc_kernel<64, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  conv_gemm_tc_kernel<64, true, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
@@ -1006,14 +1159,15 @@ bool conv_tc_wgrad_supported(const mc_desc* d) {
 }
 size_t conv_tc_wgrad_ws(const mc_desc*) { return 0; }
 
-int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const void* map, void* gw,
-                         void* gb, void* ws, size_t ws_bytes, cudaStream_t st) {
-  (void)ws; (void)ws_bytes;
-  if (!aligned16(gy) || !aligned16(x) || !aligned16(map)) return MC_ERR_BAD_ARG;
+static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, const void* map,
+                             const void* tab, void* gw, void* gb, cudaStream_t st) {
+  if (!aligned16(gy) || !aligned16(x) || !aligned16(map) || !aligned16(tab)) return MC_ERR_BAD_ARG;
+  if ((long)d->B * d->IH * d->IW >= (1L << 30)) return MC_ERR_TOO_LARGE;
   GemmArgs a = {};
   a.s.src = (const bf16*)x; a.s.spix = (long)d->IH * d->IW; a.s.C = d->C_in;
   a.s.SH = d->IH; a.s.SW = d->IW; a.s.K = d->K; a.s.interp = d->interp;
   a.s.map = (const float*)map;
+  a.s.tab = (const TapEnt*)tab;
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
   a.gy = (const bf16*)gy; a.gw = (float*)gw; a.gb = (float*)gb;
   a.nsl = d->K * (d->C_in / 64);
@@ -1024,14 +1178,27 @@ int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const 
     return MC_ERR_LAUNCH;
   if (gb && cudaMemsetAsync(gb, 0, (size_t)d->C_out * sizeof(float), st) != cudaSuccess)
     return MC_ERR_LAUNCH;
-  static bool attr = allow_big_smem(conv_wgrad_tc_kernel<64>);
+  static bool attr = allow_big_smem(conv_wgrad_tc_kernel<64, false>) &&
+                     allow_big_smem(conv_wgrad_tc_kernel<64, true>);
   if (!attr) return MC_ERR_LAUNCH;
   const size_t smem = smem_bytes(a.nst, extra, d->C_out,
                                  2 * a.nst + 2 * GY_STAGES + 5);
   const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
-  conv_wgrad_tc_kernel<64><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  if (tab) conv_wgrad_tc_kernel<64, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  else conv_wgrad_tc_kernel<64, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
+}
+
+int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const void* map, void* gw,
+                         void* gb, void* ws, size_t ws_bytes, cudaStream_t st) {
+  (void)ws; (void)ws_bytes;
+  return wgrad_launch_impl(d, gy, x, map, nullptr, gw, gb, st);
+}
+
+int conv_tc_wgrad_tab_launch(const mc_desc* d, const void* gy, const void* x, const void* tab,
+                             void* gw, void* gb, cudaStream_t st) {
+  return wgrad_launch_impl(d, gy, x, nullptr, tab, gw, gb, st);
 }
 
 // ---- forward pass with library-owned scratch ---------------------------------------------------

@@ -166,6 +166,15 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 
 // ---- small helpers -------------------------------------------------------------------------------
+// Bulk copy global -> shared of `bytes` (multiple of 16, both addresses 16-byte aligned); the
+// copy engine adds `bytes` to the transaction count of the mbarrier when the data has landed.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ uint4 ldg16(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
 }

@@ -106,23 +106,46 @@ _INV_CACHE = []
 _INV_CACHE_SIZE = 8
 
 
-def _inverse_map(d, sample_map):
-    key = (sample_map.data_ptr(), sample_map._version, tuple(sample_map.shape), d.IH, d.IW,
+def _cached(kind, d, sample_map, build):
+    key = (kind, sample_map.data_ptr(), sample_map._version, tuple(sample_map.shape), d.IH, d.IW,
            d.interp, sample_map.device.index)
-    for i, (k, ref, inv) in enumerate(_INV_CACHE):
+    for i, (k, ref, buf) in enumerate(_INV_CACHE):
         if k == key and ref() is sample_map:
             if i:
                 _INV_CACHE.insert(0, _INV_CACHE.pop(i))
-            return inv
-    L = lib()
-    dev = sample_map.device
-    nbytes = L.mc_invmap_bytes(d)
-    inv = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-    wst, wsn, wsp = _ws(L.mc_invmap_build_workspace_bytes(d), dev)
-    check(L.mc_invmap_build(d, sample_map.data_ptr(), inv.data_ptr(), nbytes, wsp, wsn, _stream()))
-    _INV_CACHE.insert(0, (key, weakref.ref(sample_map), inv))
+            return buf
+    buf = build()
+    _INV_CACHE.insert(0, (key, weakref.ref(sample_map), buf))
     del _INV_CACHE[_INV_CACHE_SIZE:]
-    return inv
+    return buf
+
+
+def _inverse_map(d, sample_map):
+    """Inverse map (+ its tap table) of a sample map, built once per map tensor."""
+    def build():
+        L = lib()
+        dev = sample_map.device
+        nbytes = L.mc_invmap_bytes(d)
+        inv = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        wst, wsn, wsp = _ws(L.mc_invmap_build_workspace_bytes(d), dev)
+        check(L.mc_invmap_build(d, sample_map.data_ptr(), inv.data_ptr(), nbytes, wsp, wsn,
+                                _stream()))
+        return inv
+    return _cached("inv", d, sample_map, build)
+
+
+def _tap_map(d, sample_map):
+    """Forward tap table of a sample map (None if the descriptor has no tensor-core path)."""
+    L = lib()
+    nbytes = L.mc_tapmap_bytes(d)
+    if nbytes == 0:
+        return None
+
+    def build():
+        tab = torch.empty(nbytes, dtype=torch.uint8, device=sample_map.device)
+        check(L.mc_tapmap_build(d, sample_map.data_ptr(), tab.data_ptr(), nbytes, _stream()))
+        return tab
+    return _cached("tap", d, sample_map, build)
 
 
 def clear_inverse_map_cache():
@@ -147,9 +170,14 @@ def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, 
     y = _empty((B, Cout, OH, OW), input, layout)
     with torch.cuda.device(dev):
         wst, wsn, wsp = _ws(lib().mc_conv_fwd_workspace_bytes(d), dev)
-        check(lib().mc_conv_fwd(d, input.data_ptr(), sample_map.data_ptr(), _ptr(interp_weights),
-                                weight.data_ptr(), bias.data_ptr(), y.data_ptr(), wsp, wsn,
-                                _stream()))
+        tab = _tap_map(d, sample_map) if wsn and interp_weights is None else None
+        if tab is not None:  # tensor-core path with the map decoded once per map tensor
+            check(lib().mc_conv_fwd_tap(d, input.data_ptr(), tab.data_ptr(), weight.data_ptr(),
+                                        bias.data_ptr(), y.data_ptr(), wsp, wsn, _stream()))
+        else:
+            check(lib().mc_conv_fwd(d, input.data_ptr(), sample_map.data_ptr(),
+                                    _ptr(interp_weights), weight.data_ptr(), bias.data_ptr(),
+                                    y.data_ptr(), wsp, wsn, _stream()))
     return y
 
 
@@ -181,9 +209,17 @@ def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias,
             check(L.mc_conv_dgrad(d, grad_output.data_ptr(), sample_map.data_ptr(),
                                   _ptr(interp_weights), weight.data_ptr(), None, gx.data_ptr(), wsp,
                                   wsn, _stream()))
-        check(L.mc_conv_wgrad(d, grad_output.data_ptr(), input.data_ptr(), sample_map.data_ptr(),
-                              _ptr(interp_weights), gw.data_ptr(), gb.data_ptr(), wsp, wsn,
-                              _stream()))
+        tab = _tap_map(d, sample_map) if interp_weights is None else None
+        rc = -2
+        if tab is not None:  # weight / bias gradient on the tensor cores from the prebuilt table
+            rc = L.mc_conv_wgrad_tap(d, grad_output.data_ptr(), input.data_ptr(), tab.data_ptr(),
+                                     gw.data_ptr(), gb.data_ptr(), _stream())
+        if rc != -2:
+            check(rc)
+        else:  # MC_ERR_UNSUPPORTED: shapes only the generic kernels take
+            check(L.mc_conv_wgrad(d, grad_output.data_ptr(), input.data_ptr(),
+                                  sample_map.data_ptr(), _ptr(interp_weights), gw.data_ptr(),
+                                  gb.data_ptr(), wsp, wsn, _stream()))
     return [gx, gw.to(weight.dtype), gb.to(bias.dtype)]
 
 
