@@ -365,16 +365,183 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------
+# secondary workloads (--workload resample | pool | knn): the other configs of the path, same
+# timing rules, one JSON line each.  The default run (conv) is the headline line.
+# ---------------------------------------------------------------------------------------------
+def run_secondary(args):
+    import torch
+    from mappedconvolutions_b200 import _lib, ops
+    from mappedconvolutions_b200.util import icosphere as ico
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(0)
+    wl = args.workload
+    cpu = None
+    if wl == "resample":
+        # config 3: equirect 512x1024x3 fp32 image (U[0,1]), batch 16, <-> icosphere level-7 vertices
+        img_h = torch.rand(16, 3, 512, 1024, generator=g)
+        m = ico.image_to_sphere_resample_map((512, 1024), 7)
+        img, md = img_h.to(dev), m.to(dev)
+        verts = ops.resample_from_map(img, md, 1)
+
+        def step():
+            v = ops.resample_from_map(img, md, 1)          # image -> vertices (gather, "Unresample")
+            return ops.resample_to_map(v, md, 512, 1024, 1)  # vertices -> image (scatter, "Resample")
+        algo_bytes = 2 * 133.4e6
+        unit, metric = "GB/s", "resample gather+scatter GB/s"
+        fam = {"gather": (lambda: ops.resample_from_map(img, md, 1), 133.4e6),
+               "scatter": (lambda: ops.resample_to_map(verts, md, 512, 1024, 1), 133.4e6)}
+        host_in, host_out = img_h.pin_memory(), torch.empty(16, 3, 512, 1024).pin_memory()
+
+        def e2e_step():
+            d_in = host_in.to(dev, non_blocking=True)
+            v = ops.resample_from_map(d_in, md, 1)
+            host_out.copy_(ops.resample_to_map(v, md, 512, 1024, 1), non_blocking=True)
+        h2d, d2h = host_in.numel() * 4, host_out.numel() * 4
+        workload = ("config3: resample equirect 512x1024x3 fp32 batch 16 -> icosphere-7 vertices "
+                    "(bilinear gather) and back (weighted scatter-add)")
+
+        def cpu_fn():
+            O, kind = cpu_ops()
+            a, mm = img_h[:4].contiguous(), m
+            t0 = time.perf_counter()
+            v = O.resample_from_map(a, mm, 1)
+            O.resample_to_map(v, mm, 512, 1024, 1)
+            dt = time.perf_counter() - t0
+            return dict(value=algo_bytes / 4 / dt / 1e9, unit="GB/s", cores=torch.get_num_threads(),
+                        kind=kind, sample="4 of 16 batch elements, gather + scatter, %.3f s" % dt)
+    elif wl == "pool":
+        # config 4: icosphere level 7 -> 6, 7-tap one-ring, nearest, batch 32, 128 ch, fp32
+        x = torch.randn(32, 128, 1, ico.num_vertices(7), generator=g).to(dev)
+        m = ico.pooling_map(7)
+        md = m.to(dev)
+
+        def step():
+            return ops.mapped_avg_pool(x, md, 7, 0), ops.mapped_max_pool(x, md, 7, 0)
+        algo_bytes = 3.358e9 + 4.700e9
+        unit, metric = "GB/s", "mapped avg+max pool GB/s"
+        fam = {"avg_pool": (lambda: ops.mapped_avg_pool(x, md, 7, 0), 3.358e9),
+               "max_pool": (lambda: ops.mapped_max_pool(x, md, 7, 0), 4.700e9)}
+        xs_h = x[:4].cpu().pin_memory()
+        out_h = torch.empty(4, 128, 1, ico.num_vertices(6)).pin_memory()
+
+        def e2e_step():  # a 4-element slice of the batch keeps the pinned buffers modest
+            xd = xs_h.to(dev, non_blocking=True)
+            out_h.copy_(ops.mapped_avg_pool(xd, md, 7, 0), non_blocking=True)
+            out_h.copy_(ops.mapped_max_pool(xd, md, 7, 0)[0], non_blocking=True)
+        h2d, d2h = xs_h.numel() * 4, 2 * out_h.numel() * 4
+        workload = ("config4: icosphere mapped avg + max pool level 7 -> 6, 7-tap one-ring, nearest, "
+                    "batch 32, 128 ch, fp32 (NCHW)")
+
+        def cpu_fn():
+            O, kind = cpu_ops()
+            a = xs_h[:2].contiguous()
+            t0 = time.perf_counter()
+            O.mapped_avg_pool(a, m, 7, 0)
+            O.mapped_max_pool(a, m, 7, 0)
+            dt = time.perf_counter() - t0
+            return dict(value=algo_bytes / 16 / dt / 1e9, unit="GB/s", cores=torch.get_num_threads(),
+                        kind=kind, sample="2 of 32 batch elements, avg + max pool, %.3f s" % dt)
+    else:
+        # config 4b: k = 9 nearest neighbours among the 163 842 unit-sphere vertices of level 7
+        v, _ = ico.generate_icosphere(7)
+        p_h = torch.from_numpy(v).float().t().contiguous().unsqueeze(0)
+        p = p_h.to(dev)
+        n = p.shape[2]
+
+        def step():
+            return ops.knn_forward(p, p, 9)
+        algo_bytes = float(n) * n  # pairs
+        unit, metric = "Gpairs/s", "knn pairs/s (k=9, 163842 points)"
+        fam = {"knn": (step, float(n) * n)}
+        ph = p_h.pin_memory()
+        idx_h = torch.empty(1, 9, n, dtype=torch.int64).pin_memory()
+
+        def e2e_step():
+            pd = ph.to(dev, non_blocking=True)
+            idx_h.copy_(ops.knn_forward(pd, pd, 9)[0], non_blocking=True)
+        h2d, d2h = ph.numel() * 4, idx_h.numel() * 8
+        workload = "config4: KNN k=9 over 163842 level-7 icosphere vertices (3-D, fp32), ref = query"
+
+        def cpu_fn():
+            from oracle import oracle
+            q = p_h[:, :, :2048].contiguous()
+            t0 = time.perf_counter()
+            oracle.knn_forward(p_h, q, 9)
+            dt = time.perf_counter() - t0
+            return dict(value=2048.0 * n / dt / 1e9, unit="Gpairs/s", cores=os.cpu_count(),
+                        kind="port", sample="2048 of 163842 queries against all references (the "
+                        "reference has no CPU KNN; C restatement), %.3f s" % dt)
+
+    def timed(fn, n):
+        a, c = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(n):
+            fn()
+        c.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(c) / n
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    n0 = L.mc_kernel_launch_count()
+    ms = timed(step, args.steps)
+    launches = L.mc_kernel_launch_count() - n0
+    clocks = sampler.stop()
+    for _ in range(2):
+        e2e_step()
+    ms_e = timed(e2e_step, max(2, min(args.steps, 5)))
+    times = {}
+    for k, (fn, _) in fam.items():
+        fn()
+        times[k] = timed(fn, 10)
+    top = max(times, key=times.get)
+    pk = peaks()
+    scale = 1e9
+    ach = fam[top][1] / (times[top] * 1e-3) / scale
+    if wl == "knn":
+        roof = {"bound": "fp32 CUDA cores (no HBM or tensor roofline applies)", "kernel": top,
+                "achieved": ach, "unit": unit, "peak": None, "frac": None, "traffic": None,
+                "ms_per_launch": {k: round(v, 4) for k, v in times.items()}}
+    else:
+        roof = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": pk["hbm"], "unit": "GB/s",
+                "frac": ach / pk["hbm"], "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
+                "ms_per_launch": {k: round(v, 4) for k, v in times.items()},
+                "gbs": {k: round(fam[k][1] / (v * 1e-3) / 1e9, 1) for k, v in times.items()}}
+    if not args.no_cpu:
+        cpu = cpu_fn()
+    e2e_frac = {"resample": 1.0, "pool": 4.0 / 32.0, "knn": 1.0}[wl]
+    print(json.dumps({
+        "metric": metric, "value": algo_bytes / (ms * 1e-3) / scale, "unit": unit, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": workload}, "clocks": clocks,
+        "e2e": {"value": algo_bytes * e2e_frac / (ms_e * 1e-3) / scale, "unit": unit,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e},
+        "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="conv", choices=["conv", "resample", "pool", "knn"],
+                    help="conv (default) is the headline config; the others are the remaining configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "conv":
+        run_secondary(args)
     else:
         run_ours(args)
 

@@ -345,7 +345,7 @@ __device__ __forceinline__ void loader_loop(const Source& s, const Tiling& t, ui
   uint32_t it = 0;
   for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x, ++it) {
     const uint32_t half = it & 1, ph = (it >> 1) & 1;
-    if (!mbar_wait(tabbar0 + 16 + 8 * half, ph ^ 1, abort_flag, 0x72)) return;
+    if (!mbar_wait(tabbar0 + 16 + 8 * half, ph ^ 1, abort_flag, 0x72, 512)) return;
     const uint32_t dst0 = table0 + half * TILE_M * entb, bar = tabbar0 + 8 * half;
     if (t.tile2d) {
       const int img = tile / t.tiles_per_img;
@@ -572,7 +572,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
       int img;
       bool valid;
       tile_pixel(a.t, tile, r, gp, img, p, valid);
-      if (!mbar_wait(tfull_bar(acc), aph, abort_flag, 0x21)) break;
+      if (!mbar_wait(tfull_bar(acc), aph, abort_flag, 0x21, 512)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * NOUT;
       uint4* out = reinterpret_cast<uint4*>(a.y + gp * NOUT);
@@ -761,7 +761,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
     if (a.gb)
       for (int i = lw * 32 + lane; i < NOUT; i += N_EPI_WARPS * 32) atomicAdd(a.gb + i, gb_s[i]);
     // epilogue: partial weight gradient of this CTA
-    if (ok && mbar_wait(done_bar, 0, abort_flag, 0x52)) {
+    if (ok && mbar_wait(done_bar, 0, abort_flag, 0x52, 1024)) {
       tc_fence_after_sync();
       const int q = warp & 3;
       const int m = q * 32 + lane;  // row of the M = 128 tile
