@@ -80,8 +80,12 @@ __device__ __forceinline__ void tile_pixel(const Tiling& t, int tile, int r, lon
 
 // One decoded (pixel, tap): up to four source pixels and their weights.  The same 32-byte record
 // is used in shared memory and in the prebuilt global tables.
+// Every off[] is a VALID pixel index: a corner that contributes nothing (outside the image, zero
+// weight, list shorter than four) has weight 0 and points at a pixel that is read anyway, so the
+// producers load unconditionally.  (A non-finite input value at such a pixel would therefore leak
+// into the output as 0 * inf; inputs are expected to be finite.)
 struct TapEnt {
-  int off[4];  // source pixel index inside its image, or -1; off[3] may carry MORE_FLAG
+  int off[4];  // source pixel index inside its image; off[3] may carry MORE_FLAG
   float w[4];
 };
 
@@ -97,6 +101,17 @@ struct Source {
   const int2* inv_ent;  //                 (source pixel, weight bits) entries
   const TapEnt* tab;    // prebuilt table [pixel of the tiled domain][tap], or null
 };
+
+// Replace the inactive corners of a decoded tap by (some active pixel of the tap, weight 0).
+__device__ __forceinline__ void seal_entry(int (&off)[4], float (&w)[4]) {
+  int fb = 0;
+#pragma unroll
+  for (int i = 3; i >= 0; --i)
+    if (off[i] >= 0 && w[i] != 0.f) fb = off[i];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (off[i] < 0 || w[i] == 0.f) { off[i] = fb; w[i] = 0.f; }
+}
 
 struct GemmArgs {
   Source s;
@@ -234,6 +249,10 @@ __device__ __forceinline__ void decode_tile(const Source& s, const Tiling& t, in
     for (int u = 0; u < U; ++u) {
       const int e = e0 + u * N_DEC_THREADS;
       if (e >= n) continue;
+      const int more = (ent[u].off[3] >= 0) ? (ent[u].off[3] & MORE_FLAG) : 0;
+      if (more) ent[u].off[3] &= ~MORE_FLAG;
+      seal_entry(ent[u].off, ent[u].w);
+      ent[u].off[3] |= more;
       uint4* dst = reinterpret_cast<uint4*>(tab + e);
       dst[0] = make_uint4(ent[u].off[0], ent[u].off[1], ent[u].off[2], ent[u].off[3]);
       dst[1] = make_uint4(__float_as_uint(ent[u].w[0]), __float_as_uint(ent[u].w[1]),
@@ -258,19 +277,22 @@ struct RowLoad {
   bool more;  // inverse-map mode: the list continues beyond these four
 };
 
-__device__ __forceinline__ void issue_row(const TapEnt* ent, const bf16* sb, int ibase, int C,
-                                          RowLoad& L) {
+template <bool CSR>
+__device__ __forceinline__ void issue_row(const TapEnt* ent, const bf16* sb, int C, RowLoad& L) {
   const uint4* e = reinterpret_cast<const uint4*>(ent);
   const uint4 o = e[0], w = e[1];
-  L.more = (int)o.w >= 0 && ((int)o.w & MORE_FLAG) != 0;
-  const int of[4] = {(int)o.x, (int)o.y, (int)o.z, L.more ? (int)o.w & ~MORE_FLAG : (int)o.w};
-  const bool rowok = ibase >= 0;  // a row beyond the end of the batch contributes zeros
-  L.w[0] = rowok ? __uint_as_float(w.x) : 0.f; L.w[1] = rowok ? __uint_as_float(w.y) : 0.f;
-  L.w[2] = rowok ? __uint_as_float(w.z) : 0.f; L.w[3] = rowok ? __uint_as_float(w.w) : 0.f;
-  L.more = L.more && rowok;
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-    L.v[i] = (of[i] >= 0 && ibase >= 0) ? ldg16(sb + (long)(ibase + of[i]) * C) : make_uint4(0, 0, 0, 0);
+  int o3 = (int)o.w;
+  L.more = false;
+  if (CSR) {
+    L.more = (o3 & MORE_FLAG) != 0;
+    o3 &= ~MORE_FLAG;
+  }
+  L.w[0] = __uint_as_float(w.x); L.w[1] = __uint_as_float(w.y);
+  L.w[2] = __uint_as_float(w.z); L.w[3] = __uint_as_float(w.w);
+  L.v[0] = ldg16(sb + (long)(int)o.x * C);
+  L.v[1] = ldg16(sb + (long)(int)o.y * C);
+  L.v[2] = ldg16(sb + (long)(int)o.z * C);
+  L.v[3] = ldg16(sb + (long)o3 * C);
 }
 
 __device__ __forceinline__ void blend_row(const RowLoad& L, float2 (&acc)[4]) {
@@ -295,14 +317,26 @@ __device__ __forceinline__ uint4 pack_row(const float2 (&acc)[4]) {
   return o;
 }
 
-// Inverse-map mode, rare: entries five and up of the list of (tile row r, tap).
-__device__ __forceinline__ void blend_list_tail(const Source& s, const Tiling& t, int tile, int r,
-                                                int tap, const bf16* sb, float2 (&acc)[4]) {
+// Inverse-map mode, rare (0.5 % of the lists of a gnomonic 3x3 map): entries five and up of the
+// list of (tile row r, tap).  Runs after the row has been written: it re-reads the bf16 row from the
+// stage, adds the remaining terms and writes it back, so that the hot loop keeps no state for it.
+__device__ __noinline__ void add_list_tail(const Source* sp, const Tiling* tp, int tile, int r,
+                                           int tap, const bf16* sb, uint32_t saddr) {
+  const Source& s = *sp;
   long gp, p;
   int img;
   bool valid;
-  tile_pixel(t, tile, r, gp, img, p, valid);
+  tile_pixel(*tp, tile, r, gp, img, p, valid);
   if (!valid) return;
+  uint4 cur;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(cur.x), "=r"(cur.y), "=r"(cur.z), "=r"(cur.w)
+               : "r"(saddr));
+  float2 acc[4];
+  acc[0] = make_float2(__uint_as_float(cur.x << 16), __uint_as_float(cur.x & 0xFFFF0000u));
+  acc[1] = make_float2(__uint_as_float(cur.y << 16), __uint_as_float(cur.y & 0xFFFF0000u));
+  acc[2] = make_float2(__uint_as_float(cur.z << 16), __uint_as_float(cur.z & 0xFFFF0000u));
+  acc[3] = make_float2(__uint_as_float(cur.w << 16), __uint_as_float(cur.w & 0xFFFF0000u));
   const long key = p * s.K + tap;
   const int end = __ldg(s.inv_off + key + 1);
   const bf16* base = sb + (long)img * s.spix * s.C;
@@ -316,6 +350,7 @@ __device__ __forceinline__ void blend_list_tail(const Source& s, const Tiling& t
     ffma2_bf16x2(acc[2], w2, v.z);
     ffma2_bf16x2(acc[3], w2, v.w);
   }
+  sts16(saddr, pack_row(acc));
 }
 
 // Decoder warps: fill the table half of tile i while the producers gather tile i - 1.
@@ -377,7 +412,7 @@ __device__ __forceinline__ void loader_loop(const Source& s, const Tiling& t, ui
 // Producer warp (CSR = false: sample map; true: inverse map).  nslots ring slots are consumed per tile, of which the first nsl carry
 // data (an odd slice count of the wgrad kernel is padded with a zero slice).  A group owns two rows
 // of every stage; while it blends one of them the loads of the other are in flight.
-template <bool CSR>
+template <bool CSR, bool PAD>
 __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling& t, int nsl,
                                                   int nslots, int nst, uint32_t stage0,
                                                   uint32_t full0, uint32_t empty0, TapEnt* table,
@@ -400,40 +435,42 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
     }
     const TapEnt* t0 = tab + r0 * s.K;
     const TapEnt* t1 = tab + r1 * s.K;
-    // first source pixel of the image each of the two rows belongs to (-1: row beyond the end)
-    int ib0, ib1;
+    // source image of each of the two rows; a row beyond the end of the batch reads the K
+    // all-zero-weight entries that follow the two table halves
+    const bf16 *s0, *s1;
     if (t.tile2d) {
-      ib0 = ib1 = (tile / t.tiles_per_img) * (int)s.spix;
+      s0 = s1 = srcl + (long)(tile / t.tiles_per_img) * s.spix * s.C;
     } else {
       const long g0 = (long)tile * TILE_M + r0, g1 = (long)tile * TILE_M + r1;
-      ib0 = g0 < t.mtot ? (int)(g0 / t.npix) * (int)s.spix : -1;
-      ib1 = g1 < t.mtot ? (int)(g1 / t.npix) * (int)s.spix : -1;
+      const TapEnt* zero_ent = table + (size_t)2 * TILE_M * s.K;
+      s0 = s1 = srcl;
+      if (g0 < t.mtot) s0 = srcl + (g0 / t.npix) * s.spix * s.C; else t0 = zero_ent;
+      if (g1 < t.mtot) s1 = srcl + (g1 / t.npix) * s.spix * s.C; else t1 = zero_ent;
     }
     RowLoad A, B;
-    issue_row(t0, srcl, ib0, s.C, A);  // slice 0: tap 0, channel block 0
+    issue_row<CSR>(t0, s0, s.C, A);  // slice 0: tap 0, channel block 0
     int tap = 0, cb = 0;          // of the current slice
     for (int sl = 0; sl < nslots; ++sl) {
-      const bool live = sl < nsl;
-      if (live) issue_row(t1 + tap, srcl + cb * 64, ib1, s.C, B);
+      const bool live = !PAD || sl < nsl;
+      if (live) issue_row<CSR>(t1 + tap, s1 + cb * 64, s.C, B);
       int okw = 1;
       if (lane == 0) okw = mbar_wait(empty0 + 8u * st, ph ^ 1, abort_flag, code) ? 1 : 0;
       okw = __shfl_sync(0xffffffffu, okw, 0);
       if (!okw) return;
       const uint32_t sbase = stage0 + st * STAGE_BYTES;
       float2 acc[4];
-      if (live) {
-        blend_row(A, acc);
-        if (CSR && A.more) blend_list_tail(s, t, tile, r0, tap, srcl + cb * 64, acc);
-      }
+      if (live) blend_row(A, acc);
       sts16(sbase + so0, live ? pack_row(acc) : zero);
+      const bool more_a = CSR && A.more;
       const int tap_b = tap, cb_b = cb;
       if (++cb == cpb) { cb = 0; ++tap; }
-      if (sl + 1 < nsl) issue_row(t0 + tap, srcl + cb * 64, ib0, s.C, A);
-      if (live) {
-        blend_row(B, acc);
-        if (CSR && B.more) blend_list_tail(s, t, tile, r1, tap_b, srcl + cb_b * 64, acc);
-      }
+      if (sl + 1 < nsl) issue_row<CSR>(t0 + tap, s0 + cb * 64, s.C, A);
+      if (live) blend_row(B, acc);
       sts16(sbase + so1, live ? pack_row(acc) : zero);
+      if (CSR) {
+        if (more_a) add_list_tail(&s, &t, tile, r0, tap_b, srcl + cb_b * 64, sbase + so0);
+        if (B.more) add_list_tail(&s, &t, tile, r1, tap_b, srcl + cb_b * 64, sbase + so1);
+      }
       // every lane publishes its own writes to the async proxy; one arrival per warp
       fence_proxy_async_smem();
       __syncwarp();
@@ -470,7 +507,10 @@ __device__ __forceinline__ Smem carve(uint8_t* raw, int nst, size_t extra_bytes,
 }
 
 // Bytes of the double-buffered tap table of the map-mode producers.
-__host__ __device__ inline size_t tap_table_bytes(int K) { return (size_t)2 * TILE_M * K * sizeof(TapEnt); }
+// (two halves of TILE_M * K entries, then K entries with zero weights for rows past the end)
+__host__ __device__ inline size_t tap_table_bytes(int K) {
+  return ((size_t)2 * TILE_M * K + K) * sizeof(TapEnt);
+}
 
 static size_t smem_bytes(int nst, size_t extra_bytes, int nfloat, int nbar) {
   return 1024 + (size_t)nst * STAGE_BYTES + extra_bytes + (size_t)nfloat * 4 + (size_t)nbar * 8 + 16;
@@ -524,6 +564,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
   for (int i = threadIdx.x; i < NOUT; i += TC_THREADS)
     bias_s[i] = a.bias ? __bfloat162float(a.bias[i]) : 0.f;
   fence_proxy_async_smem();
+  {  // the K zero-weight entries behind the two table halves
+    uint4* z = reinterpret_cast<uint4*>((TapEnt*)(sm.extra + wbytes) + (size_t)2 * TILE_M * a.s.K);
+    for (int i = threadIdx.x; i < 2 * a.s.K; i += TC_THREADS) z[i] = make_uint4(0, 0, 0, 0);
+  }
   if (warp == 0) tmem_alloc(smem_u32(sm.misc), TMEM_COLS);
   tc_fence_before_sync();
   __syncthreads();
@@ -612,7 +656,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
                           (warp - FIRST_DEC_WARP) * 32 + lane, lane);
       }
     } else
-      producer_loop_map<CSR>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
+      producer_loop_map<CSR, false>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
                              (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
                              warp - FIRST_PROD_WARP, lane, CSR ? 0x31 : 0x32);
   }
@@ -675,6 +719,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
     fence_barrier_init();
   }
   for (int i = threadIdx.x; i < NOUT; i += TC_THREADS) gb_s[i] = 0.f;
+  {  // the K zero-weight entries behind the two table halves
+    uint4* z = reinterpret_cast<uint4*>((TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES) +
+                                        (size_t)2 * TILE_M * a.s.K);
+    for (int i = threadIdx.x; i < 2 * a.s.K; i += TC_THREADS) z[i] = make_uint4(0, 0, 0, 0);
+  }
   if (warp == 0) tmem_alloc(smem_u32(sm.misc), tmem_cols);
   tc_fence_before_sync();
   __syncthreads();
@@ -796,7 +845,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
                             abort_flag, (warp - FIRST_DEC_WARP) * 32 + lane, lane);
       }
     } else
-      producer_loop_map<false>(a.s, a.t, a.nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
+      producer_loop_map<false, true>(a.s, a.t, a.nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
                                (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES), tabbar0,
                                abort_flag, warp - FIRST_PROD_WARP, lane, 0x61);
   }
@@ -909,6 +958,7 @@ __global__ void tapmap_build_kernel(const float* __restrict__ map, TapEnt* __res
       off[c] = on ? tp.off[c] : -1;
       w[c] = on ? tp.w[c] : 0.f;
     }
+    seal_entry(off, w);
     uint4* dst = reinterpret_cast<uint4*>(out + i);
     dst[0] = make_uint4(off[0], off[1], off[2], off[3]);
     dst[1] = make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]),
@@ -935,6 +985,7 @@ __global__ void invtap_build_kernel(const int* __restrict__ off, const int2* __r
         w[c] = __int_as_float(en.y);
       }
     }
+    seal_entry(o, w);
     if (e - b > 4) o[3] |= MORE_FLAG;
     uint4* dst = reinterpret_cast<uint4*>(out + key);
     dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
