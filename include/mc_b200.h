@@ -184,6 +184,14 @@ int mc_pool_avg_bwd(const mc_desc* d, const void* gy, const void* map, const voi
 /* Scratch needed by the scatter-type kernels (pool backward, resample scatter). */
 size_t mc_scatter_workspace_bytes(const mc_desc* d);
 
+/* Average unpooling and resample scatter as gathers through the inverse map (mc_invmap_build with
+ * the same descriptor): one thread per image pixel sums its contributions - no atomics, no
+ * zero-fill pass, bit-reproducible.  MC_F32 / MC_BF16, unweighted maps; MC_ERR_UNSUPPORTED
+ * otherwise (use the map-based entry points then).  Same reference kernels as mc_pool_avg_bwd /
+ * mc_resample_scatter: include/nn/cuda/mapped_avg_pool.cuh:92-130, resample.cuh:14-52. */
+int mc_pool_avg_bwd_inv(const mc_desc* d, const void* gy, const void* inv, void* gx, void* stream);
+int mc_resample_scatter_inv(const mc_desc* d, const void* x, const void* inv, void* y, void* stream);
+
 /* ---- resample ---------------------------------------------------------------------------
  * gather  ("Unresample"): y(B,C,OH,OW)[p] = interp(x(B,C,IH,IW), map(OH,OW,[P,]2)[p]);
  *   replaces ResampleFromMap2DLauncher, include/nn/cuda/resample.cuh:54-92 (+weighted :128-160).

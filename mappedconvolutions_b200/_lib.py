@@ -60,6 +60,8 @@ SIGNATURES = {
     "mc_pool_avg_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp]),
     "mc_pool_avg_bwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_scatter_workspace_bytes": (_sz, [_dp]),
+    "mc_pool_avg_bwd_inv": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp]),
+    "mc_resample_scatter_inv": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp]),
     "mc_resample_gather": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp]),
     "mc_resample_scatter": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_knn": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),

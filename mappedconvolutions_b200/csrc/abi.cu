@@ -31,6 +31,8 @@ int conv_tc_fwd_tab_launch(const mc_desc*, const void*, const void*, const void*
 int conv_tc_wgrad_tab_launch(const mc_desc*, const void*, const void*, const void*, void*, void*,
                              cudaStream_t);
 bool invmap_supported(const mc_desc*);
+size_t invmap_off_bytes(const mc_desc*);
+int scatter_inv_launch(const mc_desc*, const void*, const void*, size_t, void*, int, cudaStream_t);
 size_t invmap_bytes(const mc_desc*);
 size_t invmap_build_ws(const mc_desc*);
 int invmap_build_launch(const mc_desc*, const void*, void*, void*, size_t, cudaStream_t);
@@ -140,6 +142,29 @@ int mc_invmap_build(const mc_desc* d, const void* map, void* inv, size_t inv_byt
   if (inv_bytes < invmap_bytes(d)) return MC_ERR_WORKSPACE;
   return invmap_build_launch(d, map, inv, ws, ws_bytes, (cudaStream_t)stream);
 }
+// adjoint ops (average unpooling, resample scatter) as gathers through the inverse map
+static int scatter_inv_check(const mc_desc* d, const void* a, const void* b, const void* c) {
+  if (!d || d->B <= 0 || d->C_in <= 0 || d->IH <= 0 || d->IW <= 0 || d->OH <= 0 || d->OW <= 0 ||
+      d->K <= 0 || !a || !b || !c)
+    return MC_ERR_BAD_ARG;
+  mc_desc t = *d;
+  t.C_out = t.C_in;
+  int rc = check_conv_desc_public(&t);
+  if (rc) return rc;
+  return invmap_supported(&t) ? MC_OK : MC_ERR_UNSUPPORTED;
+}
+int mc_pool_avg_bwd_inv(const mc_desc* d, const void* gy, const void* inv, void* gx, void* stream) {
+  int rc = scatter_inv_check(d, gy, inv, gx);
+  if (rc) return rc;
+  return scatter_inv_launch(d, gy, inv, invmap_off_bytes(d), gx, 1, (cudaStream_t)stream);
+}
+int mc_resample_scatter_inv(const mc_desc* d, const void* x, const void* inv, void* y, void* stream) {
+  int rc = scatter_inv_check(d, x, inv, y);
+  if (rc) return rc;
+  if (d->K != 1) return MC_ERR_BAD_ARG;
+  return scatter_inv_launch(d, x, inv, invmap_off_bytes(d), y, 0, (cudaStream_t)stream);
+}
+
 int mc_conv_dgrad_inv_supported(const mc_desc* d) {
   return d && !check_conv_desc_public(d) && conv_tc_dgrad_supported(d) ? 1 : 0;
 }

@@ -1104,6 +1104,8 @@ static size_t inv_max_entries(const mc_desc* d) {
   return (size_t)d->OH * d->OW * d->K * per;
 }
 
+size_t invmap_off_bytes(const mc_desc* d) { return inv_off_bytes(d); }
+
 bool invmap_supported(const mc_desc* d) {
   if (d->P != 0 || d->dtype == MC_F64) return false;
   return (size_t)d->IH * d->IW * d->K < (1u << 30) && inv_max_entries(d) < (1u << 31);

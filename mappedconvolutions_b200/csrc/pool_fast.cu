@@ -263,3 +263,146 @@ bool sample_fwd_fast(const mc_desc* d, int op, const void* x, const void* map, v
 }
 
 }  // namespace mc
+
+// ---- adjoints as gathers through the inverse map ---------------------------------------------------
+// The reference scatters every grid value into the image with atomicAdd
+// (include/nn/cuda/mapped_avg_pool.cuh:92-130, resample.cuh:14-52).  With the inverse map (for every
+// image pixel the list of (grid location, weight) pairs that land on it, built once per map by
+// mc_invmap_build) the same sums are formed by ONE thread per image pixel: no atomics, no
+// zero-fill pass, coalesced stores, and results that repeat bit for bit.  The lists of the K taps
+// of a pixel are adjacent in the CSR, so the pixel's entries are one contiguous range.
+namespace mc {
+
+struct InvGatherArgs {
+  const void* g;     // values on the map grid (B, C, ngrid)
+  void* out;         // image (B, C, npix), fully written
+  const int* off;    // (npix * K + 1)
+  const int2* ent;   // (grid location, weight bits)
+  int B, C, K;
+  long npix, ngrid;
+  float inv_k;       // 1 for resample, divide by K for average unpooling
+  int planes_per_block;
+};
+
+template <typename T, bool AVG>
+__global__ void __launch_bounds__(256) inv_gather_planes_kernel(const InvGatherArgs a) {
+  const long q = blockIdx.x * 256L + threadIdx.x;
+  if (q >= a.npix) return;
+  const int beg = __ldg(a.off + q * a.K), end = __ldg(a.off + (q + 1) * a.K);
+  const long nplanes = (long)a.B * a.C;
+  const long pl0 = (long)blockIdx.y * a.planes_per_block;
+  long pl1 = pl0 + a.planes_per_block;
+  if (pl1 > nplanes) pl1 = nplanes;
+  const T* g = (const T*)a.g;
+  T* out = (T*)a.out;
+  // the common short lists stay in registers; longer ones are re-read per plane
+  int2 e4[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) e4[i] = beg + i < end ? __ldg(a.ent + beg + i) : make_int2(0, 0);
+  const int n4 = end - beg < 4 ? end - beg : 4;
+  for (long pl = pl0; pl < pl1; ++pl) {
+    const T* src = g + pl * a.ngrid;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (i < n4) {
+        float v = (float)ldv(src + e4[i].x);
+        if (AVG) v = __fdiv_rn(v, (float)a.K);
+        acc = __fadd_rn(acc, __fmul_rn(__int_as_float(e4[i].y), v));
+      }
+    }
+    for (int e = beg + 4; e < end; ++e) {
+      const int2 en = __ldg(a.ent + e);
+      float v = (float)ldv(src + en.x);
+      if (AVG) v = __fdiv_rn(v, (float)a.K);
+      acc = __fadd_rn(acc, __fmul_rn(__int_as_float(en.y), v));
+    }
+    stv(out + pl * a.npix + q, acc);
+  }
+}
+
+template <typename T, bool AVG>
+__global__ void __launch_bounds__(256) inv_gather_cl_kernel(const InvGatherArgs a, int lpp_log2,
+                                                            int chunks) {
+  constexpr int VN = Vec16<T>::N;
+  const int lpp = 1 << lpp_log2;
+  const long gthread = blockIdx.x * 256L + threadIdx.x;
+  const long q = gthread >> lpp_log2;
+  const int lane = (int)(gthread & (lpp - 1));
+  if (q >= a.npix) return;
+  const int beg = __ldg(a.off + q * a.K), end = __ldg(a.off + (q + 1) * a.K);
+  const T* g = (const T*)a.g;
+  T* out = (T*)a.out;
+  for (int b = blockIdx.y; b < a.B; b += gridDim.y) {
+    for (int ch = 0; ch < chunks; ++ch) {
+      const int c0 = (ch * lpp + lane) * VN;
+      const T* src = g + (long)b * a.ngrid * a.C + c0;
+      float acc[VN];
+#pragma unroll
+      for (int j = 0; j < VN; ++j) acc[j] = 0.f;
+      for (int e = beg; e < end; ++e) {
+        const int2 en = __ldg(a.ent + e);
+        const float w = __int_as_float(en.y);
+        float v[VN];
+        Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(src + (long)en.x * a.C)), v);
+#pragma unroll
+        for (int j = 0; j < VN; ++j) {
+          const float t = AVG ? __fdiv_rn(v[j], (float)a.K) : v[j];
+          acc[j] = __fadd_rn(acc[j], __fmul_rn(w, t));
+        }
+      }
+      *reinterpret_cast<uint4*>(out + ((long)b * a.npix + q) * a.C + c0) = Vec16<T>::pack(acc);
+    }
+  }
+}
+
+template <typename T, bool AVG>
+static int launch_inv_gather(const mc_desc* d, InvGatherArgs a, cudaStream_t st) {
+  if (d->layout == MC_NCHW) {
+    const long nplanes = (long)a.B * a.C;
+    const long xblocks = (a.npix + 255) / 256;
+    long ppb = nplanes * xblocks / (148L * 16);
+    if (ppb < 4) ppb = 4;
+    if (ppb > 64) ppb = 64;
+    a.planes_per_block = (int)ppb;
+    dim3 grid((unsigned)xblocks, (unsigned)((nplanes + ppb - 1) / ppb));
+    if (grid.y > 65535) return MC_ERR_TOO_LARGE;
+    inv_gather_planes_kernel<T, AVG><<<grid, 256, 0, st>>>(a), MC_COUNT(1);
+  } else {
+    const int row16 = a.C * (int)sizeof(T) / 16;
+    int lpp_log2 = 0;
+    while ((1 << (lpp_log2 + 1)) <= row16 && lpp_log2 < 5 && row16 % (1 << (lpp_log2 + 1)) == 0) ++lpp_log2;
+    const int chunks = row16 >> lpp_log2;
+    const long xblocks = ((a.npix << lpp_log2) + 255) / 256;
+    int by = (int)((148L * 8 + xblocks - 1) / xblocks);
+    if (by < 1) by = 1;
+    if (by > a.B) by = a.B;
+    dim3 grid((unsigned)xblocks, (unsigned)by);
+    inv_gather_cl_kernel<T, AVG><<<grid, 256, 0, st>>>(a, lpp_log2, chunks), MC_COUNT(1);
+  }
+  return cudaGetLastError() == cudaSuccess ? MC_OK : MC_ERR_LAUNCH;
+}
+
+// inv: buffer built by mc_invmap_build for the same descriptor.  avg != 0: average unpooling
+// (values divided by K first), else resample scatter.
+int scatter_inv_launch(const mc_desc* d, const void* g, const void* inv, size_t inv_off_bytes,
+                       void* out, int avg, cudaStream_t st) {
+  if (d->P != 0 || (d->dtype != MC_F32 && d->dtype != MC_BF16)) return MC_ERR_UNSUPPORTED;
+  const size_t esz = d->dtype == MC_F32 ? 4 : 2;
+  if (d->layout == MC_NHWC && ((d->C_in * esz) % 16 != 0 || (((uintptr_t)g | (uintptr_t)out) & 15)))
+    return MC_ERR_UNSUPPORTED;
+  InvGatherArgs a;
+  a.g = g; a.out = out;
+  a.off = (const int*)inv;
+  a.ent = (const int2*)((const uint8_t*)inv + inv_off_bytes);
+  a.B = d->B; a.C = d->C_in; a.K = d->K;
+  a.npix = (long)d->IH * d->IW;
+  a.ngrid = (long)d->OH * d->OW;
+  a.inv_k = 1.f / d->K;
+  a.planes_per_block = 8;
+  if (d->dtype == MC_F32)
+    return avg ? launch_inv_gather<float, true>(d, a, st) : launch_inv_gather<float, false>(d, a, st);
+  return avg ? launch_inv_gather<bf16, true>(d, a, st) : launch_inv_gather<bf16, false>(d, a, st);
+}
+
+}  // namespace mc

@@ -395,9 +395,18 @@ def _avg_unpool(grad_output, sample_map, interp_weights, input_height, input_wid
     gx = _empty((d.B, d.C_in, IH, IW), grad_output, layout)
     L = lib()
     with torch.cuda.device(dev):
-        wst, wsn, wsp = _ws(L.mc_scatter_workspace_bytes(d), dev)
-        check(L.mc_pool_avg_bwd(d, grad_output.data_ptr(), sample_map.data_ptr(),
-                                _ptr(interp_weights), gx.data_ptr(), wsp, wsn, _stream()))
+        rc = -2
+        if interp_weights is None and L.mc_invmap_bytes(d) > 0:
+            # gather through the inverse map (built once per map tensor): no atomics
+            inv = _inverse_map(d, sample_map)
+            rc = L.mc_pool_avg_bwd_inv(d, grad_output.data_ptr(), inv.data_ptr(), gx.data_ptr(),
+                                       _stream())
+        if rc != -2:
+            check(rc)
+        else:
+            wst, wsn, wsp = _ws(L.mc_scatter_workspace_bytes(d), dev)
+            check(L.mc_pool_avg_bwd(d, grad_output.data_ptr(), sample_map.data_ptr(),
+                                    _ptr(interp_weights), gx.data_ptr(), wsp, wsn, _stream()))
     return gx
 
 
@@ -464,9 +473,17 @@ def _resample_to_map(input, sample_map, interp_weights, output_height, output_wi
     y = _empty((B, C, OH, OW), input, layout)
     L = lib()
     with torch.cuda.device(dev):
-        wst, wsn, wsp = _ws(L.mc_scatter_workspace_bytes(d), dev)
-        check(L.mc_resample_scatter(d, input.data_ptr(), sample_map.data_ptr(),
-                                    _ptr(interp_weights), y.data_ptr(), wsp, wsn, _stream()))
+        rc = -2
+        if interp_weights is None and L.mc_invmap_bytes(d) > 0:
+            inv = _inverse_map(d, sample_map)
+            rc = L.mc_resample_scatter_inv(d, input.data_ptr(), inv.data_ptr(), y.data_ptr(),
+                                           _stream())
+        if rc != -2:
+            check(rc)
+        else:
+            wst, wsn, wsp = _ws(L.mc_scatter_workspace_bytes(d), dev)
+            check(L.mc_resample_scatter(d, input.data_ptr(), sample_map.data_ptr(),
+                                        _ptr(interp_weights), y.data_ptr(), wsp, wsn, _stream()))
     return y
 
 
