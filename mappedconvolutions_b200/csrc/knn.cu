@@ -91,12 +91,92 @@ __global__ void __launch_bounds__(KNN_THREADS) knn_kernel(const float* __restric
 }
 
 template <int DT>
+static void knn_launch_big_k(const float* ref, const float* query, int B, int M, int N, int k,
+                             int64_t* idx, float* dist, cudaStream_t st);
+
+// D <= 4: reference points are staged as one float4 each, so that a pair costs one 16-byte
+// broadcast load instead of D 4-byte ones (the shared-memory pipe, not the FMA pipe, was the limit).
+constexpr int KNN2_THREADS = 256;
+constexpr int KNN2_TILE = 1024;
+
+template <int DT, int KMAX>
+__global__ void __launch_bounds__(KNN2_THREADS) knn_small_d_kernel(const float* __restrict__ ref,
+                                                                   const float* __restrict__ query,
+                                                                   int M, int N, int k,
+                                                                   int64_t* __restrict__ idx,
+                                                                   float* __restrict__ dist) {
+  __shared__ float4 tile[KNN2_TILE];
+  const int b = blockIdx.y;
+  const float* rb = ref + (long)b * DT * M;
+  const float* qb = query + (long)b * DT * N;
+  const int n = blockIdx.x * KNN2_THREADS + threadIdx.x;
+  const bool live = n < N;
+  float q[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < DT; ++i)
+    if (live) q[i] = qb[(long)i * N + n];
+  TopK<KMAX> top;
+  top.init();
+  for (int m0 = 0; m0 < M; m0 += KNN2_TILE) {
+    const int cnt = min(KNN2_TILE, M - m0);
+    __syncthreads();
+    for (int j = threadIdx.x; j < cnt; j += KNN2_THREADS) {
+      float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+      r.x = rb[m0 + j];
+      if (DT > 1) r.y = rb[(long)M + m0 + j];
+      if (DT > 2) r.z = rb[2L * M + m0 + j];
+      if (DT > 3) r.w = rb[3L * M + m0 + j];
+      tile[j] = r;
+    }
+    __syncthreads();
+    if (live) {
+#pragma unroll 8
+      for (int j = 0; j < cnt; ++j) {
+        const float4 r = tile[j];
+        const float rr[4] = {r.x, r.y, r.z, r.w};
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < DT; ++i) {
+          const float a = rr[i] - q[i];
+          s = fmaf(a, a, s);
+        }
+        if (s < top.d[KMAX - 1]) top.insert(s, m0 + j);
+      }
+    }
+  }
+  if (!live) return;
+#pragma unroll
+  for (int t = 0; t < KMAX; ++t) {
+    if (t < k) {
+      const long o = ((long)b * k + t) * N + n;
+      idx[o] = (int64_t)top.i[t] + 1;
+      dist[o] = __fsqrt_rn(top.d[t]);
+    }
+  }
+}
+
+template <int DT>
+static void knn_small_d_launch(const float* ref, const float* query, int B, int M, int N, int k,
+                               int64_t* idx, float* dist, cudaStream_t st) {
+  dim3 grid((unsigned)((N + KNN2_THREADS - 1) / KNN2_THREADS), (unsigned)B);
+  if (k <= 8) knn_small_d_kernel<DT, 8><<<grid, KNN2_THREADS, 0, st>>>(ref, query, M, N, k, idx, dist), MC_COUNT(1);
+  else if (k <= 16) knn_small_d_kernel<DT, 16><<<grid, KNN2_THREADS, 0, st>>>(ref, query, M, N, k, idx, dist), MC_COUNT(1);
+  else knn_launch_big_k<DT>(ref, query, B, M, N, k, idx, dist, st);
+}
+
+template <int DT>
 static void knn_launch_k(const float* ref, const float* query, int B, int D, int M, int N, int k,
                          int64_t* idx, float* dist, cudaStream_t st) {
   dim3 grid((unsigned)((N + KNN_THREADS - 1) / KNN_THREADS), (unsigned)B);
   if (k <= 8) knn_kernel<DT, 8><<<grid, KNN_THREADS, 0, st>>>(ref, query, D, M, N, k, idx, dist), MC_COUNT(1);
   else if (k <= 16) knn_kernel<DT, 16><<<grid, KNN_THREADS, 0, st>>>(ref, query, D, M, N, k, idx, dist), MC_COUNT(1);
   else knn_kernel<DT, 32><<<grid, KNN_THREADS, 0, st>>>(ref, query, D, M, N, k, idx, dist), MC_COUNT(1);
+}
+
+template <int DT>
+static void knn_launch_big_k(const float* ref, const float* query, int B, int M, int N, int k,
+                             int64_t* idx, float* dist, cudaStream_t st) {
+  knn_launch_k<DT>(ref, query, B, DT, M, N, k, idx, dist, st);
 }
 
 }  // namespace mc
@@ -110,9 +190,10 @@ extern "C" int mc_knn(const float* ref, const float* query, int32_t B, int32_t D
   if (k > M) return MC_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   switch (D) {
-    case 2: knn_launch_k<2>(ref, query, B, D, M, N, k, idx, dist, st); break;
-    case 3: knn_launch_k<3>(ref, query, B, D, M, N, k, idx, dist, st); break;
-    case 4: knn_launch_k<4>(ref, query, B, D, M, N, k, idx, dist, st); break;
+    case 1: knn_small_d_launch<1>(ref, query, B, M, N, k, idx, dist, st); break;
+    case 2: knn_small_d_launch<2>(ref, query, B, M, N, k, idx, dist, st); break;
+    case 3: knn_small_d_launch<3>(ref, query, B, M, N, k, idx, dist, st); break;
+    case 4: knn_small_d_launch<4>(ref, query, B, M, N, k, idx, dist, st); break;
     default: knn_launch_k<0>(ref, query, B, D, M, N, k, idx, dist, st); break;
   }
   MC_CHECK_LAUNCH();
