@@ -124,6 +124,8 @@ struct GemmArgs {
   float* gb;          // wgrad: (NOUT) fp32 or null
   int nsl;            // 64-wide slices of the gathered operand = K * C / 64
   int nst;            // pipeline stages
+  int ncol;           // channels of y / gy rows (a CTA works on a chunk of NOUT of them)
+  int mtpg;           // wgrad: M = 128 gradient tiles per CTA (blockIdx.y picks the group)
 };
 
 __device__ __forceinline__ void blend4(const uint4& v, float w, float (&acc)[8]) {
@@ -417,9 +419,10 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
                                                   int nslots, int nst, uint32_t stage0,
                                                   uint32_t full0, uint32_t empty0, TapEnt* table,
                                                   uint32_t tabbar0, volatile int* abort_flag,
-                                                  int pw, int lane, int code) {
+                                                  int pw, int lane, int code, int sl0 = 0) {
   const int g = lane >> 3, lg = lane & 7;
   const int cpb = s.C / 64;
+  const int tap0 = sl0 / cpb, cb0 = sl0 - tap0 * cpb;  // first slice this CTA gathers
   const int r0 = pw * 4 + g, r1 = r0 + N_PRODUCER_WARPS * 4;  // the two rows of a stage this group owns
   const uint32_t so0 = r0 * 128 + ((lg ^ (r0 & 7)) << 4), so1 = r1 * 128 + ((lg ^ (r1 & 7)) << 4);
   const bf16* srcl = s.src + lg * 8;
@@ -448,8 +451,8 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
       if (g1 < t.mtot) s1 = srcl + (g1 / t.npix) * s.spix * s.C; else t1 = zero_ent;
     }
     RowLoad A, B;
-    issue_row<CSR>(t0, s0, s.C, A);  // slice 0: tap 0, channel block 0
-    int tap = 0, cb = 0;          // of the current slice
+    issue_row<CSR>(t0 + tap0, s0 + cb0 * 64, s.C, A);  // first slice
+    int tap = tap0, cb = cb0;     // of the current slice
     for (int sl = 0; sl < nslots; ++sl) {
       const bool live = !PAD || sl < nsl;
       if (live) issue_row<CSR>(t1 + tap, s1 + cb * 64, s.C, B);
@@ -521,12 +524,17 @@ static size_t smem_bytes(int nst, size_t extra_bytes, int nfloat, int nbar) {
 // ------------------------------------------------------------------------------------------------
 // PRE: the tap table of the tiled domain was built beforehand in global memory (a.s.tab) and is
 // streamed in by bulk copies; otherwise three warps decode the map / the inverse map in the kernel.
-template <int NOUT, bool CSR, bool PRE>
+// WRES: all weight slices of the CTA's NOUT output channels stay in shared memory; otherwise the
+// slice of every pipeline step is streamed in beside its stage by a bulk copy (needs PRE, whose
+// idle decoder warps provide the thread that issues the copies).
+// blockIdx.y selects the chunk of NOUT output channels.
+template <int NOUT, bool CSR, bool PRE, bool WRES>
 __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int nst = a.nst;
-  // bars: full[nst], empty[nst], tfull[2], tempty[2], drain
-  const size_t wbytes = (size_t)a.nsl * NOUT * 128;
+  const int co0 = blockIdx.y * NOUT;
+  constexpr uint32_t WSLICE = NOUT * 128;  // bytes of one weight slice
+  const size_t wbytes = (size_t)(WRES ? a.nsl : nst) * WSLICE;
   // bars: full[nst], empty[nst], tfull[2], tempty[2], drain, tab_full[2], tab_empty[2]
   const Smem sm = carve(smem_raw, nst, wbytes + tap_table_bytes(a.s.K), NOUT, 2 * nst + 9);
   float* bias_s = sm.fl;
@@ -543,7 +551,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
-      mbar_init(full_bar(s), N_PRODUCER_WARPS);
+      mbar_init(full_bar(s), N_PRODUCER_WARPS + (WRES ? 0 : 1));
       mbar_init(empty_bar(s), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -559,10 +567,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
     fence_barrier_init();
   }
   // resident operands: weight slices and bias
-  for (int i = threadIdx.x; i < a.nsl * NOUT * 8; i += TC_THREADS)
-    sts16(w0 + 16u * i, ldg16(a.wimg + i));
+  if (WRES) {
+    for (int i = threadIdx.x; i < a.nsl * NOUT * 8; i += TC_THREADS) {
+      const int sl = i / (NOUT * 8), j = i - sl * (NOUT * 8);
+      sts16(w0 + 16u * i, ldg16(a.wimg + ((size_t)sl * a.ncol + co0) * 8 + j));
+    }
+  }
   for (int i = threadIdx.x; i < NOUT; i += TC_THREADS)
-    bias_s[i] = a.bias ? __bfloat162float(a.bias[i]) : 0.f;
+    bias_s[i] = a.bias ? __bfloat162float(a.bias[co0 + i]) : 0.f;
   fence_proxy_async_smem();
   {  // the K zero-weight entries behind the two table halves
     uint4* z = reinterpret_cast<uint4*>((TapEnt*)(sm.extra + wbytes) + (size_t)2 * TILE_M * a.s.K);
@@ -591,7 +603,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
           if (!ok) break;
           tc_fence_after_sync();
           const uint64_t adesc = make_desc_sw128(stage0 + st * STAGE_BYTES, 16, 1024);
-          const uint64_t bdesc = make_desc_sw128(w0 + (uint32_t)s * NOUT * 128, 16, 1024);
+          const uint64_t bdesc = make_desc_sw128(w0 + (uint32_t)(WRES ? s : st) * WSLICE, 16, 1024);
 #pragma unroll
           for (int j = 0; j < 4; ++j)  // four K = 16 steps inside the 64-wide slice: +32 bytes each
             mma_bf16_ss(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, (s | j) != 0);
@@ -619,7 +631,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
       if (!mbar_wait(tfull_bar(acc), aph, abort_flag, 0x21, 512)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * NOUT;
-      uint4* out = reinterpret_cast<uint4*>(a.y + gp * NOUT);
+      uint4* out = reinterpret_cast<uint4*>(a.y + gp * a.ncol + co0);
 #pragma unroll
       for (int cc = 0; cc < NOUT / 32; ++cc) {
         uint32_t v[32];
@@ -651,6 +663,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
       if (PRE) {
         if (warp == FIRST_DEC_WARP && lane == 0)
           loader_loop(a.s, a.t, w0 + (uint32_t)wbytes, tabbar0, abort_flag);
+        if (!WRES && warp == FIRST_DEC_WARP + 1 && lane == 0) {
+          // weight streamer: slice s of every tile goes into the ring slot of pipeline step s
+          uint32_t st = 0, ph = 0;
+          bool ok = true;
+          for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x) {
+            for (int s = 0; s < a.nsl; ++s) {
+              ok = mbar_wait(empty_bar(st), ph ^ 1, abort_flag, 0x73, 256);
+              if (!ok) break;
+              mbar_expect_tx(full_bar(st), WSLICE);
+              bulk_g2s(w0 + st * WSLICE, a.wimg + ((size_t)s * a.ncol + co0) * 8, WSLICE, full_bar(st));
+              if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
+            }
+          }
+        }
       } else {
         decoder_loop<CSR>(a.s, a.t, (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
                           (warp - FIRST_DEC_WARP) * 32 + lane, lane);
@@ -683,8 +709,9 @@ template <int NOUT, bool PRE>
 __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const GemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int nst = a.nst;  // even
+  constexpr uint32_t GYB = (NOUT / 64) * STAGE_BYTES;  // one gy tile: 128 pixels x NOUT channels
   // bars: full[nst], empty[nst], gfull[GY], gempty[GY], done
-  const Smem sm = carve(smem_raw, nst, (size_t)GY_STAGES * STAGE_BYTES + tap_table_bytes(a.s.K), NOUT,
+  const Smem sm = carve(smem_raw, nst, (size_t)GY_STAGES * GYB + tap_table_bytes(a.s.K), NOUT,
                         2 * nst + 2 * GY_STAGES + 5);
   float* gb_s = sm.fl;
   volatile int* abort_flag = sm.abort_flag;
@@ -696,10 +723,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
   auto gempty_bar = [&](int i) { return bar0 + 8u * (2 * nst + GY_STAGES + i); };
   const uint32_t done_bar = bar0 + 8u * (2 * nst + 2 * GY_STAGES);
   const uint32_t tabbar0 = done_bar + 8u;
-  const int nmt = (a.nsl + 1) / 2;        // M = 128 tiles of the gradient
+  // This CTA's share of the gradient: output channels [co0, co0 + NOUT) and the M = 128 tiles
+  // [j0, j0 + nmt) of the (tap, input channel) axis, i.e. slices [sl0, sl0 + nsl).
+  const int co0 = blockIdx.z * NOUT;
+  const int j0 = blockIdx.y * a.mtpg;
+  const int nmt_all = (a.nsl + 1) / 2;
+  const int nmt = nmt_all - j0 < a.mtpg ? nmt_all - j0 : a.mtpg;
+  const int sl0 = 2 * j0;
+  const int nsl = a.nsl - sl0 < 2 * nmt ? a.nsl - sl0 : 2 * nmt;
   const int nsl_pad = nmt * 2;            // ring slots used per pixel tile
-  const uint32_t tmem_cols = nmt * NOUT <= 32 ? 32 : nmt * NOUT <= 64 ? 64 : nmt * NOUT <= 128 ? 128
-                             : nmt * NOUT <= 256 ? 256 : 512;
+  const int ccols = a.mtpg * NOUT;
+  const uint32_t tmem_cols = ccols <= 32 ? 32 : ccols <= 64 ? 64 : ccols <= 128 ? 128
+                             : ccols <= 256 ? 256 : 512;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
@@ -720,7 +755,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
   }
   for (int i = threadIdx.x; i < NOUT; i += TC_THREADS) gb_s[i] = 0.f;
   {  // the K zero-weight entries behind the two table halves
-    uint4* z = reinterpret_cast<uint4*>((TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES) +
+    uint4* z = reinterpret_cast<uint4*>((TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB) +
                                         (size_t)2 * TILE_M * a.s.K);
     for (int i = threadIdx.x; i < 2 * a.s.K; i += TC_THREADS) z[i] = make_uint4(0, 0, 0, 0);
   }
@@ -740,7 +775,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
         const uint32_t gs = it % GY_STAGES, gph = (it / GY_STAGES) & 1;
         ok = mbar_wait(gfull_bar(gs), gph, abort_flag, 0x41);
         if (!ok) break;
-        const uint64_t bdesc = make_desc_sw128(gy0 + gs * STAGE_BYTES, STAGE_BYTES, 1024);
+        const uint64_t bdesc = make_desc_sw128(gy0 + gs * GYB, STAGE_BYTES, 1024);
         for (int j = 0; j < nmt && ok; ++j) {
           // slots st and st + 1 (st is even) share the phase
           ok = mbar_wait(full_bar(st), ph, abort_flag, 0x42);
@@ -777,7 +812,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
       if (lane == 0) okw = mbar_wait(gempty_bar(gs), gph ^ 1, abort_flag, 0x51) ? 1 : 0;
       okw = __shfl_sync(0xffffffffu, okw, 0);
       if (!okw) { ok = false; break; }
-      const uint32_t sbase = gy0 + gs * STAGE_BYTES;
+      const uint32_t sbase = gy0 + gs * GYB;
       for (int r = lw * 4 + g; r < TILE_M; r += N_EPI_WARPS * 4) {
         long gp, p;
         int img;
@@ -785,7 +820,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
         tile_pixel(a.t, tile, r, gp, img, p, valid);
 #pragma unroll
         for (int nb = 0; nb < NOUT / 64; ++nb) {
-          const uint4 v = valid ? ldg16(a.gy + gp * NOUT + nb * 64 + lg * 8) : make_uint4(0, 0, 0, 0);
+          const uint4 v = valid ? ldg16(a.gy + gp * a.ncol + co0 + nb * 64 + lg * 8)
+                                : make_uint4(0, 0, 0, 0);
           // N > 64: consecutive 64-channel blocks are separate swizzle atoms, STAGE_BYTES apart
           sts16(sbase + nb * STAGE_BYTES + r * 128 + ((lg ^ (r & 7)) << 4), v);
           float* b8 = bsum + nb * 8;
@@ -800,15 +836,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
       if (lane == 0) mbar_arrive(gfull_bar(gs));
     }
     // bias gradient: lanes -> shared -> global
-    if (a.gb) {
+    const bool do_gb = a.gb != nullptr && blockIdx.y == 0;
+    if (do_gb) {
 #pragma unroll
       for (int nb = 0; nb < NOUT / 64; ++nb)
 #pragma unroll
         for (int j = 0; j < 8; ++j) atomicAdd(gb_s + nb * 64 + lg * 8 + j, bsum[nb * 8 + j]);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(N_EPI_WARPS * 32) : "memory");
-    if (a.gb)
-      for (int i = lw * 32 + lane; i < NOUT; i += N_EPI_WARPS * 32) atomicAdd(a.gb + i, gb_s[i]);
+    if (do_gb)
+      for (int i = lw * 32 + lane; i < NOUT; i += N_EPI_WARPS * 32) atomicAdd(a.gb + co0 + i, gb_s[i]);
     // epilogue: partial weight gradient of this CTA
     if (ok && mbar_wait(done_bar, 0, abort_flag, 0x52, 1024)) {
       tc_fence_after_sync();
@@ -816,7 +853,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
       const int m = q * 32 + lane;  // row of the M = 128 tile
       const int cpb = a.s.C / 64;
       for (int j = 0; j < nmt; ++j) {
-        const int sl = 2 * j + (m >> 6);
+        const int sl = sl0 + 2 * j + (m >> 6);
         const bool live = sl < a.nsl;
         const int tap = live ? sl / cpb : 0, ci = live ? (sl % cpb) * 64 + (m & 63) : 0;
 #pragma unroll
@@ -827,7 +864,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
           if (live) {
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-              const int co = cc * 32 + c;
+              const int co = co0 + cc * 32 + c;
               atomicAdd(a.gw + ((long)co * a.s.C + ci) * a.s.K + tap, __uint_as_float(v[c]));
             }
           }
@@ -839,15 +876,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
     if (warp < FIRST_PROD_WARP) {
       if (PRE) {
         if (warp == FIRST_DEC_WARP && lane == 0)
-          loader_loop(a.s, a.t, gy0 + (uint32_t)GY_STAGES * STAGE_BYTES, tabbar0, abort_flag);
+          loader_loop(a.s, a.t, gy0 + (uint32_t)GY_STAGES * GYB, tabbar0, abort_flag);
       } else {
-        decoder_loop<false>(a.s, a.t, (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES), tabbar0,
+        decoder_loop<false>(a.s, a.t, (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
                             abort_flag, (warp - FIRST_DEC_WARP) * 32 + lane, lane);
       }
     } else
-      producer_loop_map<false, true>(a.s, a.t, a.nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
-                               (TapEnt*)(sm.extra + (size_t)GY_STAGES * STAGE_BYTES), tabbar0,
-                               abort_flag, warp - FIRST_PROD_WARP, lane, 0x61);
+      producer_loop_map<false, true>(a.s, a.t, nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
+                               (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
+                               abort_flag, warp - FIRST_PROD_WARP, lane, 0x61, sl0);
   }
 
   tc_fence_before_sync();
@@ -1028,15 +1065,94 @@ using namespace tc;
 
 // ---- forward ---------------------------------------------------------------------------------------
 
+// How a forward / dgrad GEMM with `ncol` output columns and `nsl` slices is run.
+struct GemmPlan {
+  int nout;   // columns per CTA: 64, 128 or 256 (ncol is a multiple of it)
+  bool wres;  // weight slices resident in shared memory
+  int nst;
+  size_t extra;  // shared memory behind the stages: weights + tap table
+};
+
+static bool plan_gemm(int ncol, int nsl, int K, GemmPlan& p) {
+  if (ncol <= 0 || ncol % 64 != 0) return false;
+  // resident weights when they fit with a reasonable pipeline (needs ncol <= 256)
+  if (ncol <= 256 && (ncol == 64 || ncol == 128 || ncol == 256)) {
+    const size_t extra = (size_t)nsl * ncol * 128 + tap_table_bytes(K);
+    const int nst = pick_stages(extra, ncol, 8, 3, false);
+    if (nst > 0) { p = {ncol, true, nst, extra}; return true; }
+  }
+  const int nout = ncol % 256 == 0 ? 256 : ncol % 128 == 0 ? 128 : 64;
+  // streamed weights: every stage carries its weight slice
+  for (int nst = 6; nst >= 3; --nst) {
+    const size_t extra = (size_t)nst * nout * 128 + tap_table_bytes(K);
+    if (smem_bytes(nst, extra, nout, 2 * nst + 16) <= SMEM_LIMIT) {
+      p = {nout, false, nst, extra};
+      return true;
+    }
+  }
+  return false;
+}
+
 bool conv_tc_fwd_supported(const mc_desc* d) {
   if (d->dtype != MC_BF16 || d->layout != MC_NHWC || d->P != 0) return false;
-  if (d->C_in % 64 != 0 || d->C_out != 64) return false;
-  const int nsl = d->K * (d->C_in / 64);
-  return pick_stages((size_t)nsl * d->C_out * 128 + tap_table_bytes(d->K), d->C_out, 8, 3, false) > 0;
+  if (d->C_in % 64 != 0) return false;
+  GemmPlan p;
+  return plan_gemm(d->C_out, d->K * (d->C_in / 64), d->K, p);
+}
+
+// Streamed weights need the prebuilt tap table; when the caller passes the raw sample map the
+// table is built into the workspace first.
+static bool fwd_needs_table(const mc_desc* d) {
+  GemmPlan p;
+  return plan_gemm(d->C_out, d->K * (d->C_in / 64), d->K, p) && !p.wres;
+}
+
+size_t conv_tc_fwd_wimg_bytes(const mc_desc* d) {
+  return ((size_t)d->K * d->C_in * d->C_out * sizeof(bf16) + 255) & ~(size_t)255;
 }
 
 size_t conv_tc_fwd_ws(const mc_desc* d) {
-  return (size_t)d->K * d->C_in * d->C_out * sizeof(bf16);
+  return conv_tc_fwd_wimg_bytes(d) +
+         (fwd_needs_table(d) ? (size_t)d->OH * d->OW * d->K * sizeof(TapEnt) : 0);
+}
+
+template <int NOUT, bool CSR>
+static int launch_gemm_n(const GemmArgs& a, const GemmPlan& p, bool pre, cudaStream_t st) {
+  const size_t smem = smem_bytes(a.nst, p.extra, NOUT, 2 * a.nst + 9);
+  const int ny = a.ncol / NOUT;
+  int gx = sm_count() / ny;
+  if (gx < 1) gx = 1;
+  if (gx > a.t.tiles) gx = a.t.tiles;
+  const dim3 grid(gx, ny);
+  if (p.wres) {
+    if (pre) {
+      static bool attr = allow_big_smem(conv_gemm_tc_kernel<NOUT, CSR, true, true>);
+      if (!attr) return MC_ERR_LAUNCH;
+      conv_gemm_tc_kernel<NOUT, CSR, true, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+    } else {
+      if (CSR) return MC_ERR_UNSUPPORTED;
+      static bool attr = allow_big_smem(conv_gemm_tc_kernel<NOUT, false, false, true>);
+      if (!attr) return MC_ERR_LAUNCH;
+      conv_gemm_tc_kernel<NOUT, false, false, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+    }
+  } else {
+    if (!pre) return MC_ERR_UNSUPPORTED;
+    static bool attr = allow_big_smem(conv_gemm_tc_kernel<NOUT, CSR, true, false>);
+    if (!attr) return MC_ERR_LAUNCH;
+    conv_gemm_tc_kernel<NOUT, CSR, true, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  }
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
+
+template <bool CSR>
+static int launch_gemm(const GemmArgs& a, const GemmPlan& p, bool pre, cudaStream_t st) {
+  switch (p.nout) {
+    case 64: return launch_gemm_n<64, CSR>(a, p, pre, st);
+    case 128: return launch_gemm_n<128, CSR>(a, p, pre, st);
+    case 256: return launch_gemm_n<256, CSR>(a, p, pre, st);
+  }
+  return MC_ERR_UNSUPPORTED;
 }
 
 // Forward tap table of a sample map (one TapEnt per map entry).
@@ -1055,7 +1171,8 @@ int tapmap_build_launch(const mc_desc* d, const void* map, void* tab, cudaStream
 static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, const void* tab,
                            const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
                            cudaStream_t st) {
-  if (!ws || ws_bytes < conv_tc_fwd_ws(d)) return MC_ERR_WORKSPACE;
+  if (!ws || ws_bytes < (tab ? (size_t)d->K * d->C_in * d->C_out * sizeof(bf16) : conv_tc_fwd_ws(d)))
+    return MC_ERR_WORKSPACE;
   if (!aligned16(x) || !aligned16(y) || !aligned16(ws) || !aligned16(map) || !aligned16(tab))
     return MC_ERR_BAD_ARG;
   if ((long)d->B * d->IH * d->IW >= (1L << 30)) return MC_ERR_TOO_LARGE;
@@ -1067,20 +1184,20 @@ static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, con
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
   a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias; a.y = (bf16*)y;
   a.nsl = d->K * (d->C_in / 64);
-  const size_t extra = (size_t)a.nsl * d->C_out * 128 + tap_table_bytes(d->K);
-  a.nst = pick_stages(extra, d->C_out, 8, 3, false);
+  a.ncol = d->C_out;
+  GemmPlan p;
+  if (!plan_gemm(a.ncol, a.nsl, d->K, p)) return MC_ERR_UNSUPPORTED;
+  a.nst = p.nst;
   const long nw = (long)d->K * d->C_in * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_out,
                                                          d->C_in, d->K, 0, d->C_in), MC_COUNT(1);
-  static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, false, false>) &&
-                     allow_big_smem(conv_gemm_tc_kernel<64, false, true>);
-  if (!attr) return MC_ERR_LAUNCH;
-  const size_t smem = smem_bytes(a.nst, extra, d->C_out, 2 * a.nst + 9);
-  const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
-  if (tab) conv_gemm_tc_kernel<64, false, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
-  else conv_gemm_tc_kernel<64, false, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
-  MC_CHECK_LAUNCH();
-  return MC_OK;
+  if (!tab && !p.wres) {  // build the table behind the weight image
+    void* t = (uint8_t*)ws + conv_tc_fwd_wimg_bytes(d);
+    const int rc = tapmap_build_launch(d, map, t, st);
+    if (rc) return rc;
+    a.s.tab = (const TapEnt*)t;
+  }
+  return launch_gemm<false>(a, p, a.s.tab != nullptr, st);
 }
 
 int conv_tc_fwd_launch(const mc_desc* d, const void* x, const void* map, const void* w,
@@ -1162,10 +1279,10 @@ int invmap_build_launch(const mc_desc* d, const void* map, void* inv, void* ws, 
 
 bool conv_tc_dgrad_supported(const mc_desc* d) {
   if (d->dtype != MC_BF16 || d->layout != MC_NHWC || d->P != 0) return false;
-  if (d->C_out % 64 != 0 || d->C_in != 64) return false;
+  if (d->C_out % 64 != 0) return false;
   if (!invmap_supported(d)) return false;
-  const int nsl = d->K * (d->C_out / 64);
-  return pick_stages((size_t)nsl * d->C_in * 128 + tap_table_bytes(d->K), d->C_in, 8, 3, false) > 0;
+  GemmPlan p;
+  return plan_gemm(d->C_in, d->K * (d->C_out / 64), d->K, p);
 }
 
 size_t conv_tc_dgrad_ws(const mc_desc* d) {
@@ -1187,30 +1304,62 @@ int conv_tc_dgrad_launch(const mc_desc* d, const void* gy, const void* inv, cons
   if (!make_tiling(a.t, d->B, d->IH, d->IW)) return MC_ERR_TOO_LARGE;
   a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias_out; a.y = (bf16*)gx;
   a.nsl = d->K * (d->C_out / 64);
-  const size_t extra = (size_t)a.nsl * d->C_in * 128 + tap_table_bytes(d->K);
-  a.nst = pick_stages(extra, d->C_in, 8, 3, false);
+  a.ncol = d->C_in;
+  GemmPlan p;
+  if (!plan_gemm(a.ncol, a.nsl, d->K, p)) return MC_ERR_UNSUPPORTED;
+  a.nst = p.nst;
   const long nw = (long)d->K * d->C_in * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_in,
                                                          d->C_out, d->K, 1, d->C_in), MC_COUNT(1);
-  static bool attr = allow_big_smem(conv_gemm_tc_kernel<64, true, true>);
-  if (!attr) return MC_ERR_LAUNCH;
-  const size_t smem = smem_bytes(a.nst, extra, d->C_in, 2 * a.nst + 9);
-  const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
-  conv_gemm_tc_kernel<64, true, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
-  MC_CHECK_LAUNCH();
-  return MC_OK;
+  return launch_gemm<true>(a, p, true, st);
 }
 
 // ---- wgrad -----------------------------------------------------------------------------------------------
 
+// How the weight gradient is split over CTAs: chunks of `nout` output channels (blockIdx.z) times
+// groups of `mtpg` M = 128 tiles of the (tap, input channel) axis (blockIdx.y); mtpg * nout partial
+// sums per pixel-tile row must fit the 512 TMEM columns.
+struct WgradPlan {
+  int nout, mtpg, groups, chunks, nst;
+  size_t extra;
+};
+
+static bool plan_wgrad(const mc_desc* d, WgradPlan& p) {
+  if (d->C_in % 64 != 0 || d->C_out % 64 != 0) return false;
+  const int nsl = d->K * (d->C_in / 64);
+  const int nmt = (nsl + 1) / 2;
+  p.nout = d->C_out % 128 == 0 ? 128 : 64;
+  p.chunks = d->C_out / p.nout;
+  const int cap = 512 / p.nout;
+  p.groups = (nmt + cap - 1) / cap;
+  p.mtpg = (nmt + p.groups - 1) / p.groups;
+  p.extra = (size_t)GY_STAGES * (p.nout / 64) * STAGE_BYTES + tap_table_bytes(d->K);
+  p.nst = pick_stages(p.extra, p.nout, 10, 4, true);
+  return p.nst > 0;
+}
+
 bool conv_tc_wgrad_supported(const mc_desc* d) {
   if (d->dtype != MC_BF16 || d->layout != MC_NHWC || d->P != 0) return false;
-  if (d->C_in % 64 != 0 || d->C_out != 64) return false;
-  const int nsl = d->K * (d->C_in / 64);
-  if (((nsl + 1) / 2) * d->C_out > 512) return false;  // partial sums must fit the 512 TMEM columns
-  return pick_stages((size_t)GY_STAGES * STAGE_BYTES + tap_table_bytes(d->K), d->C_out, 10, 4, true) > 0;
+  WgradPlan p;
+  return plan_wgrad(d, p);
 }
 size_t conv_tc_wgrad_ws(const mc_desc*) { return 0; }
+
+template <int NOUT>
+static int launch_wgrad_n(const GemmArgs& a, const WgradPlan& p, bool pre, cudaStream_t st) {
+  const size_t smem = smem_bytes(a.nst, p.extra, NOUT, 2 * a.nst + 2 * GY_STAGES + 5);
+  int gx = sm_count() / (p.groups * p.chunks);
+  if (gx < 1) gx = 1;
+  if (gx > a.t.tiles) gx = a.t.tiles;
+  const dim3 grid(gx, p.groups, p.chunks);
+  static bool attr = allow_big_smem(conv_wgrad_tc_kernel<NOUT, false>) &&
+                     allow_big_smem(conv_wgrad_tc_kernel<NOUT, true>);
+  if (!attr) return MC_ERR_LAUNCH;
+  if (pre) conv_wgrad_tc_kernel<NOUT, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  else conv_wgrad_tc_kernel<NOUT, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
 
 static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, const void* map,
                              const void* tab, void* gw, void* gb, cudaStream_t st) {
@@ -1224,23 +1373,17 @@ static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, co
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
   a.gy = (const bf16*)gy; a.gw = (float*)gw; a.gb = (float*)gb;
   a.nsl = d->K * (d->C_in / 64);
-  const size_t extra = (size_t)GY_STAGES * STAGE_BYTES + tap_table_bytes(d->K);
-  a.nst = pick_stages(extra, d->C_out, 10, 4, true);
-  if (a.nst == 0) return MC_ERR_UNSUPPORTED;
+  a.ncol = d->C_out;
+  WgradPlan p;
+  if (!plan_wgrad(d, p)) return MC_ERR_UNSUPPORTED;
+  a.nst = p.nst;
+  a.mtpg = p.mtpg;
   if (cudaMemsetAsync(gw, 0, (size_t)d->C_out * d->C_in * d->K * sizeof(float), st) != cudaSuccess)
     return MC_ERR_LAUNCH;
   if (gb && cudaMemsetAsync(gb, 0, (size_t)d->C_out * sizeof(float), st) != cudaSuccess)
     return MC_ERR_LAUNCH;
-  static bool attr = allow_big_smem(conv_wgrad_tc_kernel<64, false>) &&
-                     allow_big_smem(conv_wgrad_tc_kernel<64, true>);
-  if (!attr) return MC_ERR_LAUNCH;
-  const size_t smem = smem_bytes(a.nst, extra, d->C_out,
-                                 2 * a.nst + 2 * GY_STAGES + 5);
-  const int grid = a.t.tiles < sm_count() ? a.t.tiles : sm_count();
-  if (tab) conv_wgrad_tc_kernel<64, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
-  else conv_wgrad_tc_kernel<64, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
-  MC_CHECK_LAUNCH();
-  return MC_OK;
+  return p.nout == 128 ? launch_wgrad_n<128>(a, p, tab != nullptr, st)
+                       : launch_wgrad_n<64>(a, p, tab != nullptr, st);
 }
 
 int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const void* map, void* gw,

@@ -137,10 +137,17 @@ def _device_status():
     (3, 128, 64, 20, 24, 24, 48, 3),
     (2, 64, 64, 1, 2562, 1, 642, 7),
     (4, 64, 64, 64, 128, 64, 128, 9),
+    # wider layers: 128 / 256 output channels per CTA, weight slices streamed beside the stages,
+    # several output-channel chunks (192 = 3 x 64, 512 = 2 x 256)
+    (2, 64, 128, 1, 642, 1, 642, 7),
+    (1, 128, 256, 1, 300, 1, 300, 7),
+    (1, 256, 256, 1, 200, 1, 162, 7),
+    (1, 64, 192, 8, 16, 8, 16, 3),
+    (1, 64, 512, 8, 16, 8, 16, 2),
 ])
 @pytest.mark.parametrize("interp", [0, 1, 2])
 def test_bf16_tensor_core_conv_forward(shape, interp):
-    """The tcgen05 implicit-GEMM forward (bf16, channels-last, C_in % 64 == 0, C_out == 64)
+    """The tcgen05 implicit-GEMM forward (bf16, channels-last, C_in % 64 == 0, C_out % 64 == 0)
     against the oracle run in float32 on the bf16-rounded inputs; tolerance 2e-2."""
     from mappedconvolutions_b200 import ops
     B, Cin, Cout, IH, IW, OH, OW, K = shape
@@ -166,6 +173,14 @@ def test_bf16_tensor_core_conv_forward(shape, interp):
     (3, 64, 64, 24, 48, 8, 16, 3),
     (2, 64, 64, 1, 2562, 1, 642, 7),
     (2, 64, 64, 64, 128, 64, 128, 9),
+    # wider layers: the weight gradient is split into output-channel chunks and groups of
+    # (tap, input channel) tiles; the input gradient streams its weight slices
+    (2, 64, 128, 1, 642, 1, 642, 7),
+    (1, 128, 64, 9, 14, 16, 32, 5),
+    (1, 128, 256, 1, 300, 1, 300, 7),
+    (1, 256, 256, 1, 200, 1, 162, 7),
+    (1, 64, 192, 8, 16, 8, 16, 3),
+    (1, 128, 512, 8, 16, 8, 16, 2),
 ])
 @pytest.mark.parametrize("interp", [0, 1, 2])
 def test_bf16_tensor_core_conv_backward(shape, interp):
