@@ -528,18 +528,153 @@ def run_secondary(args):
         "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu}))
 
 
+# ---------------------------------------------------------------------------------------------
+# --workload encoder: config 5, an icosphere level-7 encoder training step.  Four mapped
+# convolutions (3 -> 64 -> 128 -> 256 -> 256 channels, 7-tap one-ring maps, nearest) each followed
+# by ReLU, mapped average pooling 7 -> 6 -> 5 between them; batch 64 in all, sharded over the
+# ranks (strong scaling); weight gradients all-reduced over NCCL; plain SGD update.
+# ---------------------------------------------------------------------------------------------
+ENC_CH = (3, 64, 128, 256, 256)
+ENC_LEVEL = (7, 6, 5, 5)  # mesh level each convolution runs at
+ENC_BATCH = 64
+
+
+def encoder_flops(batch):
+    """fwd + dgrad + wgrad GEMM flops of the four convolutions (the first has no dgrad)."""
+    from mappedconvolutions_b200.util import icosphere as ico
+    tot = 0.0
+    for i in range(4):
+        gemm = 2.0 * batch * ico.num_vertices(ENC_LEVEL[i]) * 7 * ENC_CH[i] * ENC_CH[i + 1]
+        tot += gemm * (2 if i == 0 else 3)
+    return tot
+
+
+def run_encoder(args):
+    import torch
+    import torch.distributed as dist
+    from mappedconvolutions_b200 import _lib, nn as mnn, dist as mdist
+    from mappedconvolutions_b200.util import icosphere as ico
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+    lo, hi = mdist.shard_batch(ENC_BATCH, rank, world)
+    nb = hi - lo
+    torch.manual_seed(0)
+    convs = torch.nn.ModuleList(
+        [mnn.MappedConvolution(ENC_CH[i], ENC_CH[i + 1], 7, "nearest") for i in range(4)]).to(dev).to(torch.bfloat16)
+    kmap = {l: ico.vertex_kernel_map(l).to(dev) for l in (7, 6, 5)}
+    pmap = {l: ico.pooling_map(l).to(dev) for l in (7, 6)}
+    pool = mnn.MappedAvgPool(7, "nearest")
+    g = torch.Generator().manual_seed(1)
+    x_h = torch.randn(ENC_BATCH, 3, 1, ico.num_vertices(7), generator=g).to(torch.bfloat16)[lo:hi]
+    x_h = x_h.contiguous(memory_format=torch.channels_last).pin_memory()
+    x = x_h.to(dev)
+    params = [p for p in convs.parameters()]
+    lr = 1e-3
+
+    def step(xin):
+        h = torch.relu(convs[0](xin, kmap[7]))
+        h = pool(h, pmap[7])
+        h = torch.relu(convs[1](h, kmap[6]))
+        h = pool(h, pmap[6])
+        h = torch.relu(convs[2](h, kmap[5]))
+        h = torch.relu(convs[3](h, kmap[5]))
+        loss = h.float().mean()
+        loss.backward()
+        grads = [p.grad for p in params]
+        if world > 1:
+            mdist.allreduce_gradients(grads)
+        with torch.no_grad():
+            torch._foreach_add_(params, grads, alpha=-lr)
+        for p in params:
+            p.grad = None
+        return loss
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, n):
+        a, c = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync()
+        a.record()
+        for _ in range(n):
+            fn()
+        c.record()
+        sync()
+        t = torch.tensor([a.elapsed_time(c)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step(x)
+    sampler = ClockSampler(dev.index) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    n0 = L.mc_kernel_launch_count()
+    ms = timed(lambda: step(x), args.steps) / args.steps
+    launches = L.mc_kernel_launch_count() - n0
+    clocks = sampler.stop() if sampler else None
+    loss_h = torch.empty(1, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        xd = x_h.to(dev, non_blocking=True)
+        loss_h.copy_(step(xd).detach().reshape(1), non_blocking=True)
+    for _ in range(2):
+        e2e_step()
+    ne = max(2, min(args.steps, 5))
+    ms_e = timed(e2e_step, ne) / ne
+    status = L.mc_device_status(torch.cuda.current_stream().cuda_stream, 1)
+    fl = encoder_flops(ENC_BATCH)
+    if rank == 0:
+        pk = peaks()
+        val = fl / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "mapped-conv fwd+bwd TFLOP/s (encoder step)", "value": val, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "config5: icosphere level-7 encoder training step, batch 64 in all, "
+                                   "conv 3->64->128->256->256 (7-tap one-ring, nearest) + ReLU, avg pool "
+                                   "7->6->5, SGD, channels-last bf16",
+                       "l2": "activations of the first two levels (1.3 GB, 0.7 GB per rank at N=1) are larger than L2",
+                       "parallelism": "batch-sharded dp%d, NCCL allreduce of weight gradients" % world,
+                       "flops": "conv GEMM flops only (fwd + dgrad + wgrad; no dgrad for the first layer)"},
+            "clocks": clocks,
+            "e2e": {"value": fl / (ms_e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": x_h.numel() * 2, "d2h_bytes_per_step": 4, "ms_per_step": ms_e},
+            "gpu_launches": int(launches), "device_status": int(status),
+            "roofline": {"bound": "tensor", "achieved": val / world, "peak": pk["bf16_sustained"],
+                         "unit": "TFLOP/s", "frac": val / world / pk["bf16_sustained"],
+                         "traffic": None, "note": "whole step (conv kernels, ReLU, pooling, update) per GPU against the bf16 GEMM peak"},
+            "cpu_baseline": None}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="conv", choices=["conv", "resample", "pool", "knn"],
+    ap.add_argument("--workload", default="conv", choices=["conv", "resample", "pool", "knn", "encoder"],
                     help="conv (default) is the headline config; the others are the remaining configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "encoder":
+        run_encoder(args)
     elif args.workload != "conv":
         run_secondary(args)
     else:

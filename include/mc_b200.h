@@ -152,6 +152,12 @@ int mc_conv_wgrad(const mc_desc* d, const void* gy, const void* x, const void* m
                   void* gw, void* gb, void* ws, size_t ws_bytes, void* stream);
 size_t mc_conv_wgrad_workspace_bytes(const mc_desc* d);
 
+/* gb[c] = sum over batch and pixels of gy (B, C_out, OH, OW); gb is float32 (float64 for float64
+ * tensors).  The reference takes it from grad_output.sum({0, 2, 3}),
+ * include/nn/layers/mapped_convolution_layer.h:113; mc_conv_wgrad fuses it, this entry point
+ * serves callers that obtain the weight gradient some other way. */
+int mc_bias_grad(const mc_desc* d, const void* gy, void* gb, void* stream);
+
 /* ---- mapped transposed convolution ----------------------------------------------------
  * Here d->C_in / d->C_out are the transposed layer's own in/out channels, weight is
  * (C_in, C_out, K), the map has the size of the layer *input* (d->OH, d->OW = input size) and

@@ -55,6 +55,7 @@ SIGNATURES = {
     "mc_tconv_dgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_tconv_wgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_tconv_workspace_bytes": (_sz, [_dp]),
+    "mc_bias_grad": (ctypes.c_int, [_dp, _vp, _vp, _vp]),
     "mc_pool_max_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mc_pool_max_bwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_pool_avg_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp]),

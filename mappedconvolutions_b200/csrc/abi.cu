@@ -208,6 +208,13 @@ int mc_conv_wgrad(const mc_desc* d, const void* gy, const void* x, const void* m
   return rc;
 }
 
+int mc_bias_grad(const mc_desc* d, const void* gy, void* gb, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!gy || !gb) return MC_ERR_BAD_ARG;
+  return bias_grad_launch(d, gy, gb, (cudaStream_t)stream);
+}
+
 // ---- transposed conv: the same three primitives with the roles of the tensors swapped --------
 // (design note of the reference: src/nn/cuda/mapped_transposed_convolution_layer.cu:17-51)
 
@@ -222,7 +229,9 @@ size_t mc_tconv_workspace_bytes(const mc_desc* d) {
   if (!d) return 0;
   mc_desc s = swap_roles(d);
   size_t a = mc_conv_dgrad_workspace_bytes(&s), b = mc_conv_wgrad_workspace_bytes(&s);
-  return a > b ? a : b;
+  const size_t c = mc_conv_fwd_workspace_bytes(&s);  // the transposed layer's dgrad is a forward
+  if (b > a) a = b;
+  return c > a ? c : a;
 }
 
 int mc_tconv_fwd(const mc_desc* d, const void* x, const void* map, const void* iw, const void* w,

@@ -305,6 +305,46 @@ __global__ void __launch_bounds__(256) bias_grad_kernel(const T* gy, CT* gb, int
   if (threadIdx.x == 0) atomicAdd(gb + c, red[0]);
 }
 
+__device__ __forceinline__ float widen(float v) { return v; }
+__device__ __forceinline__ double widen(double v) { return v; }
+__device__ __forceinline__ float widen(bf16 v) { return __bfloat162float(v); }
+
+// Channels-last variant: a thread owns one 16-byte group of channels and walks the pixels, so a
+// warp reads whole rows; the partial sums of the threads that share a channel group are folded in
+// shared memory.  NV = channels per 16 bytes.
+template <typename T, typename CT, int NV>
+__global__ void __launch_bounds__(256) bias_grad_cl_kernel(const T* __restrict__ gy, CT* gb, int C,
+                                                           long total, long pix_per_block) {
+  const int ng = C / NV;              // channel groups per pixel
+  const int lanes = 256 / ng;         // pixels handled side by side (ng <= 256)
+  const int cg = threadIdx.x % ng, pl = threadIdx.x / ng;
+  const long beg = (long)blockIdx.x * pix_per_block;
+  long end = beg + pix_per_block;
+  if (end > total) end = total;
+  CT s[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) s[j] = CT(0);
+  if (pl < lanes) {
+    for (long g = beg + pl; g < end; g += lanes) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(gy + g * C + cg * NV));
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int j = 0; j < NV; ++j) s[j] += (CT)widen(e[j]);
+    }
+  }
+  extern __shared__ unsigned char red_raw[];
+  CT* red = reinterpret_cast<CT*>(red_raw);  // [256][NV]
+#pragma unroll
+  for (int j = 0; j < NV; ++j) red[threadIdx.x * NV + j] = s[j];
+  __syncthreads();
+  for (int i = threadIdx.x; i < C; i += 256) {
+    const int g = i / NV, j = i % NV;
+    CT t = CT(0);
+    for (int l = 0; l < lanes; ++l) t += red[(l * ng + g) * NV + j];
+    atomicAdd(gb + i, t);
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------
 
 static int check_conv_desc(const mc_desc* d) {
@@ -389,6 +429,21 @@ int bias_grad_launch(const mc_desc* d, const void* gy, void* gb, cudaStream_t st
   dim3 grid((unsigned)d->C_out, (unsigned)splits);
   const size_t esz = d->dtype == MC_F64 ? 8 : 4;
   if (cudaMemsetAsync(gb, 0, d->C_out * esz, st) != cudaSuccess) return MC_ERR_LAUNCH;
+  const int tsz = d->dtype == MC_F64 ? 8 : d->dtype == MC_F32 ? 4 : 2;
+  const int nv = 16 / tsz;
+  if (d->layout == MC_NHWC && d->C_out % nv == 0 && d->C_out / nv <= 256 &&
+      (((uintptr_t)gy) & 15) == 0) {
+    long blocks = (total + 4095) / 4096;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    const long ppb = (total + blocks - 1) / blocks;
+    const size_t sm = 256 * 16 / tsz * esz;
+    if (d->dtype == MC_F32) bias_grad_cl_kernel<float, float, 4><<<(unsigned)blocks, 256, sm, st>>>((const float*)gy, (float*)gb, d->C_out, total, ppb), MC_COUNT(1);
+    else if (d->dtype == MC_F64) bias_grad_cl_kernel<double, double, 2><<<(unsigned)blocks, 256, sm, st>>>((const double*)gy, (double*)gb, d->C_out, total, ppb), MC_COUNT(1);
+    else bias_grad_cl_kernel<bf16, float, 8><<<(unsigned)blocks, 256, sm, st>>>((const bf16*)gy, (float*)gb, d->C_out, total, ppb), MC_COUNT(1);
+    MC_CHECK_LAUNCH();
+    return MC_OK;
+  }
   if (d->dtype == MC_F32) bias_grad_kernel<float, float><<<grid, 256, 0, st>>>((const float*)gy, (float*)gb, d->layout, d->B, d->C_out, npix, pps), MC_COUNT(1);
   else if (d->dtype == MC_F64) bias_grad_kernel<double, double><<<grid, 256, 0, st>>>((const double*)gy, (double*)gb, d->layout, d->B, d->C_out, npix, pps), MC_COUNT(1);
   else bias_grad_kernel<bf16, float><<<grid, 256, 0, st>>>((const bf16*)gy, (float*)gb, d->layout, d->B, d->C_out, npix, pps), MC_COUNT(1);

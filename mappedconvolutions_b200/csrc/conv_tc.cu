@@ -319,17 +319,14 @@ __device__ __forceinline__ uint4 pack_row(const float2 (&acc)[4]) {
   return o;
 }
 
-// Inverse-map mode, rare (0.5 % of the lists of a gnomonic 3x3 map): entries five and up of the
-// list of (tile row r, tap).  Runs after the row has been written: it re-reads the bf16 row from the
-// stage, adds the remaining terms and writes it back, so that the hot loop keeps no state for it.
-__device__ __noinline__ void add_list_tail(const Source* sp, const Tiling* tp, int tile, int r,
-                                           int tap, const bf16* sb, uint32_t saddr) {
-  const Source& s = *sp;
-  long gp, p;
-  int img;
-  bool valid;
-  tile_pixel(*tp, tile, r, gp, img, p, valid);
-  if (!valid) return;
+// Inverse-map mode, rare (0.5 % of the lists of a gnomonic 3x3 map): entries `first` and up of the
+// list `key` = (input pixel, tap).  Runs after the row has been written: it re-reads the bf16 row
+// from the stage, adds the remaining terms and writes it back, so that the hot loop keeps no state
+// for it.  All arguments are scalars on purpose (no pointers to the kernel's structs, which would
+// push them into local memory).
+__device__ __noinline__ void add_list_tail(const int* __restrict__ inv_off,
+                                           const int2* __restrict__ inv_ent, int C, long key,
+                                           const bf16* base, uint32_t saddr, int first) {
   uint4 cur;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                : "=r"(cur.x), "=r"(cur.y), "=r"(cur.z), "=r"(cur.w)
@@ -339,12 +336,10 @@ __device__ __noinline__ void add_list_tail(const Source* sp, const Tiling* tp, i
   acc[1] = make_float2(__uint_as_float(cur.y << 16), __uint_as_float(cur.y & 0xFFFF0000u));
   acc[2] = make_float2(__uint_as_float(cur.z << 16), __uint_as_float(cur.z & 0xFFFF0000u));
   acc[3] = make_float2(__uint_as_float(cur.w << 16), __uint_as_float(cur.w & 0xFFFF0000u));
-  const long key = p * s.K + tap;
-  const int end = __ldg(s.inv_off + key + 1);
-  const bf16* base = sb + (long)img * s.spix * s.C;
-  for (int e = __ldg(s.inv_off + key) + 4; e < end; ++e) {
-    const int2 en = __ldg(s.inv_ent + e);
-    const uint4 v = ldg16(base + (long)en.x * s.C);
+  const int end = __ldg(inv_off + key + 1);
+  for (int e = __ldg(inv_off + key) + first; e < end; ++e) {
+    const int2 en = __ldg(inv_ent + e);
+    const uint4 v = ldg16(base + (long)en.x * C);
     const float w = __int_as_float(en.y);
     const float2 w2 = make_float2(w, w);
     ffma2_bf16x2(acc[0], w2, v.x);
@@ -353,6 +348,15 @@ __device__ __noinline__ void add_list_tail(const Source* sp, const Tiling* tp, i
     ffma2_bf16x2(acc[3], w2, v.w);
   }
   sts16(saddr, pack_row(acc));
+}
+
+// Pixel index inside its image of row r of a tile (0 for rows past the end of the batch).
+__device__ __forceinline__ int tile_row_pixel(const Tiling& t, int tile, int r) {
+  long gp, p;
+  int img;
+  bool valid;
+  tile_pixel(t, tile, r, gp, img, p, valid);
+  return valid ? (int)p : 0;
 }
 
 // Decoder warps: fill the table half of tile i while the producers gather tile i - 1.
@@ -450,6 +454,7 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
       if (g0 < t.mtot) s0 = srcl + (g0 / t.npix) * s.spix * s.C; else t0 = zero_ent;
       if (g1 < t.mtot) s1 = srcl + (g1 / t.npix) * s.spix * s.C; else t1 = zero_ent;
     }
+    const int p0 = CSR ? tile_row_pixel(t, tile, r0) : 0, p1 = CSR ? tile_row_pixel(t, tile, r1) : 0;
     RowLoad A, B;
     issue_row<CSR>(t0 + tap0, s0 + cb0 * 64, s.C, A);  // first slice
     int tap = tap0, cb = cb0;     // of the current slice
@@ -471,14 +476,162 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
       if (live) blend_row(B, acc);
       sts16(sbase + so1, live ? pack_row(acc) : zero);
       if (CSR) {
-        if (more_a) add_list_tail(&s, &t, tile, r0, tap_b, srcl + cb_b * 64, sbase + so0);
-        if (B.more) add_list_tail(&s, &t, tile, r1, tap_b, srcl + cb_b * 64, sbase + so1);
+        if (more_a)
+          add_list_tail(s.inv_off, s.inv_ent, s.C, (long)p0 * s.K + tap_b, s0 + cb_b * 64, sbase + so0, 4);
+        if (B.more)
+          add_list_tail(s.inv_off, s.inv_ent, s.C, (long)p1 * s.K + tap_b, s1 + cb_b * 64, sbase + so1, 4);
       }
       // every lane publishes its own writes to the async proxy; one arrival per warp
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(full0 + 8u * st);
       if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tabbar0 + 16 + 8 * (it & 1));  // this warp is done with the half
+  }
+}
+
+// Producer warp for nearest-neighbour maps: every (pixel, tap) reads ONE source pixel with weight 1
+// (or nothing), so a row is a 128-byte copy.  There is no arithmetic to hide the load latency
+// behind; instead the loads of the next COPY_AHEAD slices are kept in flight.  Inverse-map mode:
+// the first list entry is copied, the (rare) further ones are added by add_list_tail.
+constexpr int COPY_AHEAD = 4;
+
+struct CopyLoad {
+  uint4 v;
+  bool on, more;
+};
+
+template <bool CSR>
+__device__ __forceinline__ void issue_copy(const TapEnt* ent, const bf16* sb, int C, CopyLoad& L) {
+  const uint2 ow = *reinterpret_cast<const uint2*>(&ent->w[0]);  // weights of entries 0 and 1
+  const int off = ent->off[0];
+  L.on = ow.x != 0u;
+  L.more = CSR && ow.y != 0u;
+  L.v = ldg16(sb + (long)off * C);
+  if (CSR && L.more)  // a second list entry (1.4 % of the lists of a one-ring map): warm L1 for it
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(sb + (long)ent->off[1] * C));
+}
+
+// Entries 1 and up of an inverse-map list whose first entry `row` is already loaded: entries 1-3
+// from the table entry, the rest (MORE_FLAG) from the global list.  Accumulates in fp32.
+__device__ __forceinline__ uint4 finish_list(const TapEnt* ent, const bf16* sb, int C, const uint4& row,
+                                             const int* __restrict__ inv_off,
+                                             const int2* __restrict__ inv_ent, long key) {
+  float2 acc[4];
+  acc[0] = make_float2(__uint_as_float(row.x << 16), __uint_as_float(row.x & 0xFFFF0000u));
+  acc[1] = make_float2(__uint_as_float(row.y << 16), __uint_as_float(row.y & 0xFFFF0000u));
+  acc[2] = make_float2(__uint_as_float(row.z << 16), __uint_as_float(row.z & 0xFFFF0000u));
+  acc[3] = make_float2(__uint_as_float(row.w << 16), __uint_as_float(row.w & 0xFFFF0000u));
+  const int o3 = ent->off[3];
+#pragma unroll 1
+  for (int i = 1; i < 4; ++i) {
+    const float w = ent->w[i];
+    if (w == 0.f) break;
+    const int off = i == 3 ? (o3 & ~MORE_FLAG) : ent->off[i];
+    const uint4 v = ldg16(sb + (long)off * C);
+    const float2 w2 = make_float2(w, w);
+    ffma2_bf16x2(acc[0], w2, v.x);
+    ffma2_bf16x2(acc[1], w2, v.y);
+    ffma2_bf16x2(acc[2], w2, v.z);
+    ffma2_bf16x2(acc[3], w2, v.w);
+  }
+  if (o3 & MORE_FLAG) {
+    const int end = __ldg(inv_off + key + 1);
+#pragma unroll 1
+    for (int e = __ldg(inv_off + key) + 4; e < end; ++e) {
+      const int2 en = __ldg(inv_ent + e);
+      const uint4 v = ldg16(sb + (long)en.x * C);
+      const float w = __int_as_float(en.y);
+      const float2 w2 = make_float2(w, w);
+      ffma2_bf16x2(acc[0], w2, v.x);
+      ffma2_bf16x2(acc[1], w2, v.y);
+      ffma2_bf16x2(acc[2], w2, v.z);
+      ffma2_bf16x2(acc[3], w2, v.w);
+    }
+  }
+  return pack_row(acc);
+}
+
+template <bool CSR, bool PAD>
+__device__ __forceinline__ void producer_loop_copy(const Source& s, const Tiling& t, int nsl,
+                                                   int nslots, int nst, uint32_t stage0,
+                                                   uint32_t full0, uint32_t empty0, TapEnt* table,
+                                                   uint32_t tabbar0, volatile int* abort_flag,
+                                                   int pw, int lane, int code, int sl0 = 0) {
+  const int g = lane >> 3, lg = lane & 7;
+  const int cpb = s.C / 64;
+  const int tap0 = sl0 / cpb, cb0 = sl0 - tap0 * cpb;
+  const int r0 = pw * 4 + g, r1 = r0 + N_PRODUCER_WARPS * 4;
+  const uint32_t so0 = r0 * 128 + ((lg ^ (r0 & 7)) << 4), so1 = r1 * 128 + ((lg ^ (r1 & 7)) << 4);
+  const bf16* srcl = s.src + lg * 8;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint32_t st = 0, ph = 0, it = 0;
+  for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x, ++it) {
+    const TapEnt* tab = table + (size_t)(it & 1) * TILE_M * s.K;
+    {
+      int okt = 1;
+      if (lane == 0) okt = mbar_wait(tabbar0 + 8 * (it & 1), (it >> 1) & 1, abort_flag, code) ? 1 : 0;
+      okt = __shfl_sync(0xffffffffu, okt, 0);
+      if (!okt) return;
+    }
+    const TapEnt* t0 = tab + r0 * s.K;
+    const TapEnt* t1 = tab + r1 * s.K;
+    const bf16 *s0, *s1;
+    if (t.tile2d) {
+      s0 = s1 = srcl + (long)(tile / t.tiles_per_img) * s.spix * s.C;
+    } else {
+      const long g0 = (long)tile * TILE_M + r0, g1 = (long)tile * TILE_M + r1;
+      const TapEnt* zero_ent = table + (size_t)2 * TILE_M * s.K;
+      s0 = s1 = srcl;
+      if (g0 < t.mtot) s0 = srcl + (g0 / t.npix) * s.spix * s.C; else t0 = zero_ent;
+      if (g1 < t.mtot) s1 = srcl + (g1 / t.npix) * s.spix * s.C; else t1 = zero_ent;
+    }
+    const int p0 = CSR ? tile_row_pixel(t, tile, r0) : 0, p1 = CSR ? tile_row_pixel(t, tile, r1) : 0;
+    CopyLoad A[COPY_AHEAD], B[COPY_AHEAD];
+    int tap_i = tap0, cb_i = cb0;  // slice whose loads are issued next
+    int tap_c = tap0, cb_c = cb0;  // slice that is stored next
+#pragma unroll
+    for (int u = 0; u < COPY_AHEAD; ++u) {
+      if (u < nsl) {
+        issue_copy<CSR>(t0 + tap_i, s0 + cb_i * 64, s.C, A[u]);
+        issue_copy<CSR>(t1 + tap_i, s1 + cb_i * 64, s.C, B[u]);
+        if (++cb_i == cpb) { cb_i = 0; ++tap_i; }
+      }
+    }
+    for (int slb = 0; slb < nslots; slb += COPY_AHEAD) {
+#pragma unroll
+      for (int u = 0; u < COPY_AHEAD; ++u) {
+        const int sl = slb + u;
+        if (sl < nslots) {
+          const bool live = !PAD || sl < nsl;
+          int okw = 1;
+          if (lane == 0) okw = mbar_wait(empty0 + 8u * st, ph ^ 1, abort_flag, code) ? 1 : 0;
+          okw = __shfl_sync(0xffffffffu, okw, 0);
+          if (!okw) return;
+          const uint32_t sbase = stage0 + st * STAGE_BYTES;
+          uint4 ra = live && A[u].on ? A[u].v : zero, rb = live && B[u].on ? B[u].v : zero;
+          if (CSR && live) {
+            if (A[u].more)
+              ra = finish_list(t0 + tap_c, s0 + cb_c * 64, s.C, ra, s.inv_off, s.inv_ent, (long)p0 * s.K + tap_c);
+            if (B[u].more)
+              rb = finish_list(t1 + tap_c, s1 + cb_c * 64, s.C, rb, s.inv_off, s.inv_ent, (long)p1 * s.K + tap_c);
+          }
+          sts16(sbase + so0, ra);
+          sts16(sbase + so1, rb);
+          if (++cb_c == cpb) { cb_c = 0; ++tap_c; }
+          if (sl + COPY_AHEAD < nsl) {
+            issue_copy<CSR>(t0 + tap_i, s0 + cb_i * 64, s.C, A[u]);
+            issue_copy<CSR>(t1 + tap_i, s1 + cb_i * 64, s.C, B[u]);
+            if (++cb_i == cpb) { cb_i = 0; ++tap_i; }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full0 + 8u * st);
+          if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
+        }
+      }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(tabbar0 + 16 + 8 * (it & 1));  // this warp is done with the half
@@ -681,10 +834,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
         decoder_loop<CSR>(a.s, a.t, (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
                           (warp - FIRST_DEC_WARP) * 32 + lane, lane);
       }
-    } else
+    } else if (a.s.interp == 0) {
+      producer_loop_copy<CSR, false>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
+                                     (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
+                                     warp - FIRST_PROD_WARP, lane, CSR ? 0x33 : 0x34);
+    } else {
       producer_loop_map<CSR, false>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
                              (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
                              warp - FIRST_PROD_WARP, lane, CSR ? 0x31 : 0x32);
+    }
   }
 
   tc_fence_before_sync();
@@ -881,10 +1039,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
         decoder_loop<false>(a.s, a.t, (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
                             abort_flag, (warp - FIRST_DEC_WARP) * 32 + lane, lane);
       }
-    } else
+    } else if (a.s.interp == 0) {
+      producer_loop_copy<false, true>(a.s, a.t, nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
+                                      (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
+                                      abort_flag, warp - FIRST_PROD_WARP, lane, 0x62, sl0);
+    } else {
       producer_loop_map<false, true>(a.s, a.t, nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
                                (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
                                abort_flag, warp - FIRST_PROD_WARP, lane, 0x61, sl0);
+    }
   }
 
   tc_fence_before_sync();

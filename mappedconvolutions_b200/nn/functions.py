@@ -30,7 +30,7 @@ class MappedConvFn(Function):
                                                            ctx.k, ctx.interp)
         else:
             gx, gw, gb = ops.mapped_conv_backward(gy, sample_map, x, weight, bias, ctx.k,
-                                                  ctx.interp)
+                                                  ctx.interp, ctx.needs_input_grad[0])
         return gx, gw, gb, None, None, None, None
 
 

@@ -182,7 +182,7 @@ def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, 
 
 
 def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
-                   interpolation):
+                   interpolation, need_input_grad=True):
     dev = _need_cuda(grad_output, sample_map, interp_weights, input, weight, bias)
     layout = _layout(input)
     grad_output = _as_layout(grad_output, layout)
@@ -193,16 +193,18 @@ def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias,
     d = _desc(input.dtype, layout, B, Cin, Cout, IH, IW, OH, OW, kernel_size, _P(interp_weights),
               interpolation)
     acc = torch.float64 if input.dtype == torch.float64 else torch.float32
-    gx = _empty(input.shape, input, layout)
+    gx = _empty(input.shape, input, layout) if need_input_grad else None
     gw = torch.empty(weight.shape, dtype=acc, device=dev)
     gb = torch.empty((Cout,), dtype=acc, device=dev)
     L = lib()
     with torch.cuda.device(dev):
-        inv = _inverse_map(d, sample_map) if L.mc_conv_dgrad_inv_supported(d) else None
+        inv = _inverse_map(d, sample_map) if need_input_grad and L.mc_conv_dgrad_inv_supported(d) else None
         wst, wsn, wsp = _ws(max(L.mc_conv_dgrad_workspace_bytes(d) if inv is None else
                                 L.mc_conv_dgrad_inv_workspace_bytes(d),
                                 L.mc_conv_wgrad_workspace_bytes(d)), dev)
-        if inv is not None:
+        if not need_input_grad:
+            pass
+        elif inv is not None:
             check(L.mc_conv_dgrad_inv(d, grad_output.data_ptr(), inv.data_ptr(), weight.data_ptr(),
                                       None, gx.data_ptr(), wsp, wsn, _stream()))
         else:
@@ -228,11 +230,13 @@ def mapped_conv_forward(input, sample_map, weight, bias, kernel_size, interpolat
     return _conv_forward(input, sample_map, None, weight, bias, kernel_size, interpolation)
 
 
-def mapped_conv_backward(grad_output, sample_map, input, weight, bias, kernel_size, interpolation):
+def mapped_conv_backward(grad_output, sample_map, input, weight, bias, kernel_size, interpolation,
+                         need_input_grad=True):
     """MappedConvBackward, include/nn/layers/mapped_convolution_layer.h:90-135.
-    Returns [grad_input, grad_weight, grad_bias]."""
+    Returns [grad_input, grad_weight, grad_bias].  need_input_grad=False (not in the reference's
+    signature) skips the input gradient and returns None in its place."""
     return _conv_backward(grad_output, sample_map, None, input, weight, bias, kernel_size,
-                          interpolation)
+                          interpolation, need_input_grad)
 
 
 def weighted_mapped_conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size,
@@ -266,7 +270,17 @@ def _tconv_forward(input, sample_map, interp_weights, weight, bias, output_heigh
               _P(interp_weights), interpolation)
     y = _empty((B, Cout, int(output_height), int(output_width)), input, layout)
     L = lib()
+    # The same layer seen as a convolution: the sampled image carries C_out channels, the map grid
+    # C_in.  Its input gradient IS this forward pass, so the gather-form tensor-core dgrad serves.
+    ds = _desc(input.dtype, layout, B, Cout, Cin, output_height, output_width, H, W, kernel_size,
+               _P(interp_weights), interpolation)
     with torch.cuda.device(dev):
+        if interp_weights is None and L.mc_conv_dgrad_inv_supported(ds):
+            inv = _inverse_map(ds, sample_map)
+            wst, wsn, wsp = _ws(L.mc_conv_dgrad_inv_workspace_bytes(ds), dev)
+            check(L.mc_conv_dgrad_inv(ds, input.data_ptr(), inv.data_ptr(), weight.data_ptr(),
+                                      bias.data_ptr(), y.data_ptr(), wsp, wsn, _stream()))
+            return y
         wst, wsn, wsp = _ws(L.mc_tconv_workspace_bytes(d), dev)
         check(L.mc_tconv_fwd(d, input.data_ptr(), sample_map.data_ptr(), _ptr(interp_weights),
                              weight.data_ptr(), bias.data_ptr(), y.data_ptr(), wsp, wsn, _stream()))
@@ -289,7 +303,26 @@ def _tconv_backward(grad_output, sample_map, interp_weights, input, weight, bias
     gw = torch.empty(weight.shape, dtype=acc, device=dev)
     gb = torch.empty((Cout,), dtype=acc, device=dev)
     L = lib()
+    ds = _desc(input.dtype, layout, B, Cout, Cin, OHt, OWt, H, W, kernel_size, _P(interp_weights),
+               interpolation)
     with torch.cuda.device(dev):
+        tab = _tap_map(ds, sample_map) if interp_weights is None else None
+        if tab is not None and L.mc_conv_fwd_workspace_bytes(ds):
+            # tensor-core path: input gradient = forward of the equivalent convolution applied to
+            # grad_output; weight gradient = its weight gradient with the two tensors swapped
+            wst, wsn, wsp = _ws(L.mc_conv_fwd_workspace_bytes(ds), dev)
+            check(L.mc_conv_fwd_tap(ds, grad_output.data_ptr(), tab.data_ptr(), weight.data_ptr(),
+                                    None, gx.data_ptr(), wsp, wsn, _stream()))
+            rc = L.mc_conv_wgrad_tap(ds, input.data_ptr(), grad_output.data_ptr(), tab.data_ptr(),
+                                     gw.data_ptr(), None, _stream())
+            if rc == -2:
+                rc = L.mc_conv_wgrad(ds, input.data_ptr(), grad_output.data_ptr(),
+                                     sample_map.data_ptr(), None, gw.data_ptr(), None, wsp, wsn,
+                                     _stream())
+            check(rc)
+            db = _desc(input.dtype, layout, B, Cout, Cout, OHt, OWt, OHt, OWt, 1, 0, interpolation)
+            check(L.mc_bias_grad(db, grad_output.data_ptr(), gb.data_ptr(), _stream()))
+            return [gx, gw.to(weight.dtype), gb.to(bias.dtype)]
         wst, wsn, wsp = _ws(L.mc_tconv_workspace_bytes(d), dev)
         check(L.mc_tconv_dgrad(d, grad_output.data_ptr(), sample_map.data_ptr(),
                                _ptr(interp_weights), weight.data_ptr(), gx.data_ptr(), wsp, wsn,

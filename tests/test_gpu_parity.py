@@ -210,6 +210,63 @@ def test_bf16_tensor_core_conv_backward(shape, interp):
     assert torch.equal(got[0], again[0])
 
 
+@pytest.mark.parametrize("shape", [
+    # B, Cin, Cout, H, W (layer input = map grid), OH, OW (layer output), K
+    (2, 64, 64, 8, 16, 16, 32, 4),
+    (1, 128, 64, 9, 14, 16, 32, 5),
+    (1, 64, 128, 1, 300, 1, 642, 7),
+    (1, 256, 128, 8, 16, 12, 20, 3),
+])
+@pytest.mark.parametrize("interp", [0, 1, 2])
+def test_bf16_tensor_core_transposed_conv(shape, interp):
+    """Transposed convolution on the tensor-core primitives (its forward is the gather-form input
+    gradient of the equivalent convolution, its input gradient that convolution's forward, its
+    weight gradient the same GEMM with the two tensors swapped) against the oracle in float32 on
+    the bf16-rounded inputs; tolerance 2e-2."""
+    from mappedconvolutions_b200 import ops
+    B, Cin, Cout, Hh, Ww, OH, OW, K = shape
+    g = torch.Generator().manual_seed(sum(shape) + 13 * interp)
+    bf = lambda t: t.to(torch.bfloat16)
+    x = bf(torch.randn(B, Cin, Hh, Ww, generator=g))
+    gy = bf(torch.randn(B, Cout, OH, OW, generator=g))
+    w = bf(torch.randn(Cin, Cout, K, generator=g))
+    b = bf(torch.randn(Cout, generator=g))
+    m = (torch.rand(Hh, Ww, K, 2, generator=g) * torch.tensor([OW + 1.0, OH + 1.0]) - 1.0).contiguous()
+    if OH == 1:
+        m[..., 1] = 0
+    want_y = oracle.mapped_transposed_conv_forward(x.float(), m, w.float(), b.float(), OH, OW, K, interp)
+    want_g = oracle.mapped_transposed_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, interp)
+    cl = lambda t: t.cuda().contiguous(memory_format=torch.channels_last)
+    md = m.cuda()
+    y = ops.mapped_transposed_conv_forward(cl(x), md, w.cuda(), b.cuda(), OH, OW, K, interp)
+    got = ops.mapped_transposed_conv_backward(cl(gy), md, cl(x), w.cuda(), b.cuda(), K, interp)
+    assert _device_status() == 0
+    H.assert_close(y.float(), want_y, 2e-2, "tc tconv fwd")
+    H.assert_close(got[0].float(), want_g[0], 2e-2, "tc tconv dgrad")
+    H.assert_close(got[1].float(), want_g[1], 2e-2, "tc tconv wgrad")
+    H.assert_close(got[2].float(), want_g[2], 2e-2, "tc tconv bias grad")
+
+
+def test_bias_grad_entry_point():
+    """mc_bias_grad against a float64 sum, both layouts and all dtypes (1e-5 / 2e-2)."""
+    from mappedconvolutions_b200 import _lib
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(5)
+    for dt, code, tol in ((torch.float32, _lib.MC_F32, 1e-5), (torch.float64, _lib.MC_F64, 1e-12),
+                          (torch.bfloat16, _lib.MC_BF16, 2e-2)):
+        for C in (6, 64, 200):
+            gy = torch.randn(3, C, 7, 33, generator=g).to(dt).cuda()
+            want = gy.double().sum((0, 2, 3))
+            for layout, t in ((_lib.MC_NCHW, gy.contiguous()),
+                              (_lib.MC_NHWC, gy.contiguous(memory_format=torch.channels_last))):
+                gb = torch.empty(C, dtype=torch.float64 if dt == torch.float64 else torch.float32,
+                                 device="cuda")
+                d = _lib.McDesc(3, C, C, 7, 33, 7, 33, 1, 0, 0, code, layout)
+                _lib.check(L.mc_bias_grad(d, t.data_ptr(), gb.data_ptr(),
+                                          torch.cuda.current_stream().cuda_stream))
+                H.assert_close(gb.double().cpu(), want.cpu(), tol, "bias grad")
+
+
 def test_bf16_pool_and_resample():
     from mappedconvolutions_b200 import ops
     g = torch.Generator().manual_seed(12)
