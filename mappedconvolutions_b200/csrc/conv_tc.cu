@@ -100,6 +100,9 @@ struct Source {
   const int* inv_off; // inverse-map mode: (npix * K + 1) list offsets
   const int2* inv_ent;  //                 (source pixel, weight bits) entries
   const TapEnt* tab;    // prebuilt table [pixel of the tiled domain][tap], or null
+  int KC;      // K * C: length of the gathered (tap, channel) axis
+  int packed;  // C is not a multiple of 64: a 64-wide slice holds elements tap * C + c of several
+               // taps (map mode only)
 };
 
 // Replace the inactive corners of a decoded tap by (some active pixel of the tap, weight 0).
@@ -492,11 +495,111 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
   }
 }
 
+// Producer warp for channel counts that are not a multiple of 64 (map mode).  The gathered axis is
+// e = tap * C + c, cut into 64-element slices and zero-padded at the end; a lane owns 8 consecutive
+// elements of a row.  With C % 8 == 0 those lie in one tap and are fetched as 16-byte vectors like
+// in the regular producer, only with a tap of the lane's own; otherwise (e.g. the 3 input channels
+// of a first layer) every element is gathered on its own.
+__device__ __forceinline__ float gather_element(const TapEnt* ent, const bf16* sb, int C, int c) {
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int off = i == 3 ? (ent->off[3] & ~MORE_FLAG) : ent->off[i];
+    const float v = __bfloat162float(__ldg(sb + (long)off * C + c));
+    acc = fmaf(ent->w[i], v, acc);
+  }
+  return acc;
+}
+
+__device__ __forceinline__ uint4 gather_elements8(const TapEnt* trow, const bf16* sb, int C, int KC,
+                                                  int e0) {
+  float v[8];
+  int k = e0 / C, c = e0 - k * C;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    v[j] = e0 + j < KC ? gather_element(trow + k, sb, C, c) : 0.f;
+    if (++c == C) { c = 0; ++k; }
+  }
+  return pack8(v);
+}
+
+template <bool PAD>
+__device__ __forceinline__ void producer_loop_packed(const Source& s, const Tiling& t, int nsl,
+                                                     int nslots, int nst, uint32_t stage0,
+                                                     uint32_t full0, uint32_t empty0, TapEnt* table,
+                                                     uint32_t tabbar0, volatile int* abort_flag,
+                                                     int pw, int lane, int code, int sl0 = 0) {
+  const int g = lane >> 3, lg = lane & 7;
+  const int C = s.C, KC = s.KC;
+  const bool vec = (C & 7) == 0;
+  const int r0 = pw * 4 + g, r1 = r0 + N_PRODUCER_WARPS * 4;
+  const uint32_t so0 = r0 * 128 + ((lg ^ (r0 & 7)) << 4), so1 = r1 * 128 + ((lg ^ (r1 & 7)) << 4);
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint32_t st = 0, ph = 0, it = 0;
+  for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x, ++it) {
+    const TapEnt* tab = table + (size_t)(it & 1) * TILE_M * s.K;
+    {
+      int okt = 1;
+      if (lane == 0) okt = mbar_wait(tabbar0 + 8 * (it & 1), (it >> 1) & 1, abort_flag, code) ? 1 : 0;
+      okt = __shfl_sync(0xffffffffu, okt, 0);
+      if (!okt) return;
+    }
+    const TapEnt* t0 = tab + r0 * s.K;
+    const TapEnt* t1 = tab + r1 * s.K;
+    const bf16 *s0, *s1;
+    if (t.tile2d) {
+      s0 = s1 = s.src + (long)(tile / t.tiles_per_img) * s.spix * C;
+    } else {
+      const long g0 = (long)tile * TILE_M + r0, g1 = (long)tile * TILE_M + r1;
+      // rows past the end of the batch: entries of tap 0..K-1 with zero weights
+      const TapEnt* zero_ent = table + (size_t)2 * TILE_M * s.K;
+      s0 = s1 = s.src;
+      if (g0 < t.mtot) s0 = s.src + (g0 / t.npix) * s.spix * C; else t0 = zero_ent;
+      if (g1 < t.mtot) s1 = s.src + (g1 / t.npix) * s.spix * C; else t1 = zero_ent;
+    }
+    int e0 = sl0 * 64 + lg * 8;
+    for (int sl = 0; sl < nslots; ++sl, e0 += 64) {
+      const bool live = (!PAD || sl < nsl) && e0 < KC;
+      uint4 ra = zero, rb = zero;
+      if (live) {
+        if (vec) {
+          const int k = e0 / C, c = e0 - k * C;
+          RowLoad A, B;
+          issue_row<false>(t0 + k, s0 + c, C, A);
+          issue_row<false>(t1 + k, s1 + c, C, B);
+          float2 acc[4];
+          blend_row(A, acc);
+          ra = pack_row(acc);
+          blend_row(B, acc);
+          rb = pack_row(acc);
+        } else {
+          ra = gather_elements8(t0, s0, C, KC, e0);
+          rb = gather_elements8(t1, s1, C, KC, e0);
+        }
+      }
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait(empty0 + 8u * st, ph ^ 1, abort_flag, code) ? 1 : 0;
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      if (!okw) return;
+      const uint32_t sbase = stage0 + st * STAGE_BYTES;
+      sts16(sbase + so0, ra);
+      sts16(sbase + so1, rb);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full0 + 8u * st);
+      if (++st == (uint32_t)nst) { st = 0; ph ^= 1; }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tabbar0 + 16 + 8 * (it & 1));
+  }
+}
+
 // Producer warp for nearest-neighbour maps: every (pixel, tap) reads ONE source pixel with weight 1
 // (or nothing), so a row is a 128-byte copy.  There is no arithmetic to hide the load latency
 // behind; instead the loads of the next COPY_AHEAD slices are kept in flight.  Inverse-map mode:
 // the first list entry is copied, the (rare) further ones are added by add_list_tail.
 constexpr int COPY_AHEAD = 4;
+constexpr int COPY_AHEAD_CSR = 2;  // inverse-map mode keeps more state per row
 
 struct CopyLoad {
   uint4 v;
@@ -560,6 +663,7 @@ __device__ __forceinline__ void producer_loop_copy(const Source& s, const Tiling
                                                    uint32_t full0, uint32_t empty0, TapEnt* table,
                                                    uint32_t tabbar0, volatile int* abort_flag,
                                                    int pw, int lane, int code, int sl0 = 0) {
+  constexpr int AHEAD = CSR ? COPY_AHEAD_CSR : COPY_AHEAD;
   const int g = lane >> 3, lg = lane & 7;
   const int cpb = s.C / 64;
   const int tap0 = sl0 / cpb, cb0 = sl0 - tap0 * cpb;
@@ -589,20 +693,20 @@ __device__ __forceinline__ void producer_loop_copy(const Source& s, const Tiling
       if (g1 < t.mtot) s1 = srcl + (g1 / t.npix) * s.spix * s.C; else t1 = zero_ent;
     }
     const int p0 = CSR ? tile_row_pixel(t, tile, r0) : 0, p1 = CSR ? tile_row_pixel(t, tile, r1) : 0;
-    CopyLoad A[COPY_AHEAD], B[COPY_AHEAD];
+    CopyLoad A[AHEAD], B[AHEAD];
     int tap_i = tap0, cb_i = cb0;  // slice whose loads are issued next
     int tap_c = tap0, cb_c = cb0;  // slice that is stored next
 #pragma unroll
-    for (int u = 0; u < COPY_AHEAD; ++u) {
+    for (int u = 0; u < AHEAD; ++u) {
       if (u < nsl) {
         issue_copy<CSR>(t0 + tap_i, s0 + cb_i * 64, s.C, A[u]);
         issue_copy<CSR>(t1 + tap_i, s1 + cb_i * 64, s.C, B[u]);
         if (++cb_i == cpb) { cb_i = 0; ++tap_i; }
       }
     }
-    for (int slb = 0; slb < nslots; slb += COPY_AHEAD) {
+    for (int slb = 0; slb < nslots; slb += AHEAD) {
 #pragma unroll
-      for (int u = 0; u < COPY_AHEAD; ++u) {
+      for (int u = 0; u < AHEAD; ++u) {
         const int sl = slb + u;
         if (sl < nslots) {
           const bool live = !PAD || sl < nsl;
@@ -621,7 +725,7 @@ __device__ __forceinline__ void producer_loop_copy(const Source& s, const Tiling
           sts16(sbase + so0, ra);
           sts16(sbase + so1, rb);
           if (++cb_c == cpb) { cb_c = 0; ++tap_c; }
-          if (sl + COPY_AHEAD < nsl) {
+          if (sl + AHEAD < nsl) {
             issue_copy<CSR>(t0 + tap_i, s0 + cb_i * 64, s.C, A[u]);
             issue_copy<CSR>(t1 + tap_i, s1 + cb_i * 64, s.C, B[u]);
             if (++cb_i == cpb) { cb_i = 0; ++tap_i; }
@@ -834,6 +938,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
         decoder_loop<CSR>(a.s, a.t, (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
                           (warp - FIRST_DEC_WARP) * 32 + lane, lane);
       }
+    } else if (!CSR && a.s.packed) {
+      producer_loop_packed<false>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
+                                  (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
+                                  warp - FIRST_PROD_WARP, lane, 0x35);
     } else if (a.s.interp == 0) {
       producer_loop_copy<CSR, false>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
                                      (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
@@ -1009,11 +1117,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
       tc_fence_after_sync();
       const int q = warp & 3;
       const int m = q * 32 + lane;  // row of the M = 128 tile
-      const int cpb = a.s.C / 64;
       for (int j = 0; j < nmt; ++j) {
-        const int sl = sl0 + 2 * j + (m >> 6);
-        const bool live = sl < a.nsl;
-        const int tap = live ? sl / cpb : 0, ci = live ? (sl % cpb) * 64 + (m & 63) : 0;
+        const int e = (sl0 + 2 * j) * 64 + m;  // element tap * C + ci of the gathered axis
+        const bool live = e < a.s.KC;
+        const int tap = live ? e / a.s.C : 0, ci = live ? e - tap * a.s.C : 0;
 #pragma unroll
         for (int cc = 0; cc < NOUT / 32; ++cc) {
           uint32_t v[32];
@@ -1039,6 +1146,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
         decoder_loop<false>(a.s, a.t, (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
                             abort_flag, (warp - FIRST_DEC_WARP) * 32 + lane, lane);
       }
+    } else if (a.s.packed) {
+      producer_loop_packed<true>(a.s, a.t, nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
+                                 (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
+                                 abort_flag, warp - FIRST_PROD_WARP, lane, 0x63, sl0);
     } else if (a.s.interp == 0) {
       producer_loop_copy<false, true>(a.s, a.t, nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
                                       (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
@@ -1070,20 +1181,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
 // the 128-byte swizzle, so the kernel copies it into shared memory linearly.
 // transpose = 0 (forward): rows = output channels, slices run over (tap, input-channel block).
 // transpose = 1 (dgrad)  : rows = input channels,  slices run over (tap, output-channel block).
+// The reduction axis is e = tap * red + r, cut into 64-element slices and zero-padded at the end.
 __global__ void weight_image_kernel(const bf16* __restrict__ w, uint16_t* __restrict__ img, int rows,
                                     int red, int K, int transpose, int Cin_w) {
-  const int cpb = red / 64;
-  const long total = (long)K * cpb * rows * 64;
+  const int nsl = (K * red + 63) / 64;
+  const long total = (long)nsl * rows * 64;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
        i += (long)gridDim.x * blockDim.x) {
     const int c = (int)(i % 64);
     const int n = (int)((i / 64) % rows);
     const int s = (int)(i / (64L * rows));
-    const int tap = s / cpb, cb = s % cpb;
-    const int r = cb * 64 + c;
+    const int e = s * 64 + c;
+    const int tap = e / red, r = e - tap * red;
     const long src = transpose ? ((long)r * Cin_w + n) * K + tap : ((long)n * Cin_w + r) * K + tap;
     const long dst = (long)s * rows * 64 + (long)n * 64 + ((((c >> 3) ^ (n & 7)) << 3) | (c & 7));
-    img[dst] = reinterpret_cast<const uint16_t*>(w)[src];
+    img[dst] = e < K * red ? reinterpret_cast<const uint16_t*>(w)[src] : (uint16_t)0;
   }
 }
 
@@ -1256,22 +1368,25 @@ static bool plan_gemm(int ncol, int nsl, int K, GemmPlan& p) {
   return false;
 }
 
+// 64-element slices of the gathered (tap, input channel) axis of forward / wgrad
+static int fwd_slices(const mc_desc* d) { return (int)(((long)d->K * d->C_in + 63) / 64); }
+
 bool conv_tc_fwd_supported(const mc_desc* d) {
   if (d->dtype != MC_BF16 || d->layout != MC_NHWC || d->P != 0) return false;
-  if (d->C_in % 64 != 0) return false;
+  if ((long)d->K * d->C_in >= (1L << 24)) return false;
   GemmPlan p;
-  return plan_gemm(d->C_out, d->K * (d->C_in / 64), d->K, p);
+  return plan_gemm(d->C_out, fwd_slices(d), d->K, p);
 }
 
 // Streamed weights need the prebuilt tap table; when the caller passes the raw sample map the
 // table is built into the workspace first.
 static bool fwd_needs_table(const mc_desc* d) {
   GemmPlan p;
-  return plan_gemm(d->C_out, d->K * (d->C_in / 64), d->K, p) && !p.wres;
+  return plan_gemm(d->C_out, fwd_slices(d), d->K, p) && !p.wres;
 }
 
 size_t conv_tc_fwd_wimg_bytes(const mc_desc* d) {
-  return ((size_t)d->K * d->C_in * d->C_out * sizeof(bf16) + 255) & ~(size_t)255;
+  return ((size_t)fwd_slices(d) * 64 * d->C_out * sizeof(bf16) + 255) & ~(size_t)255;
 }
 
 size_t conv_tc_fwd_ws(const mc_desc* d) {
@@ -1334,7 +1449,7 @@ int tapmap_build_launch(const mc_desc* d, const void* map, void* tab, cudaStream
 static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, const void* tab,
                            const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
                            cudaStream_t st) {
-  if (!ws || ws_bytes < (tab ? (size_t)d->K * d->C_in * d->C_out * sizeof(bf16) : conv_tc_fwd_ws(d)))
+  if (!ws || ws_bytes < (tab ? (size_t)fwd_slices(d) * 64 * d->C_out * sizeof(bf16) : conv_tc_fwd_ws(d)))
     return MC_ERR_WORKSPACE;
   if (!aligned16(x) || !aligned16(y) || !aligned16(ws) || !aligned16(map) || !aligned16(tab))
     return MC_ERR_BAD_ARG;
@@ -1346,12 +1461,14 @@ static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, con
   a.s.tab = (const TapEnt*)tab;
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
   a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias; a.y = (bf16*)y;
-  a.nsl = d->K * (d->C_in / 64);
+  a.nsl = fwd_slices(d);
+  a.s.KC = d->K * d->C_in;
+  a.s.packed = d->C_in % 64 != 0;
   a.ncol = d->C_out;
   GemmPlan p;
   if (!plan_gemm(a.ncol, a.nsl, d->K, p)) return MC_ERR_UNSUPPORTED;
   a.nst = p.nst;
-  const long nw = (long)d->K * d->C_in * d->C_out;
+  const long nw = (long)a.nsl * 64 * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_out,
                                                          d->C_in, d->K, 0, d->C_in), MC_COUNT(1);
   if (!tab && !p.wres) {  // build the table behind the weight image
@@ -1488,8 +1605,8 @@ struct WgradPlan {
 };
 
 static bool plan_wgrad(const mc_desc* d, WgradPlan& p) {
-  if (d->C_in % 64 != 0 || d->C_out % 64 != 0) return false;
-  const int nsl = d->K * (d->C_in / 64);
+  if (d->C_out % 64 != 0 || (long)d->K * d->C_in >= (1L << 24)) return false;
+  const int nsl = fwd_slices(d);
   const int nmt = (nsl + 1) / 2;
   p.nout = d->C_out % 128 == 0 ? 128 : 64;
   p.chunks = d->C_out / p.nout;
@@ -1535,7 +1652,9 @@ static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, co
   a.s.tab = (const TapEnt*)tab;
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
   a.gy = (const bf16*)gy; a.gw = (float*)gw; a.gb = (float*)gb;
-  a.nsl = d->K * (d->C_in / 64);
+  a.nsl = fwd_slices(d);
+  a.s.KC = d->K * d->C_in;
+  a.s.packed = d->C_in % 64 != 0;
   a.ncol = d->C_out;
   WgradPlan p;
   if (!plan_wgrad(d, p)) return MC_ERR_UNSUPPORTED;
