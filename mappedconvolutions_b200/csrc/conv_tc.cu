@@ -38,7 +38,10 @@ constexpr int N_DEC_WARPS = 3;  // (24 warps in all: the register file is shared
 constexpr int FIRST_DEC_WARP = 1 + N_EPI_WARPS;
 constexpr int FIRST_PROD_WARP = FIRST_DEC_WARP + N_DEC_WARPS;
 constexpr int TC_THREADS = (FIRST_PROD_WARP + N_PRODUCER_WARPS) * 32;
-constexpr size_t SMEM_LIMIT = 220 * 1024;
+constexpr size_t SMEM_LIMIT = 227 * 1024;  // the most a block may ask for
+// forward / dgrad epilogue: every warp turns its 32 rows x 32 columns around in 2 KB of shared
+// memory so that its global stores cover whole 64-byte row segments
+constexpr size_t EPI_STAGING_BYTES = N_EPI_WARPS * 2048;
 
 // How the pixels of the tiled domain are grouped into 128-row tiles.
 struct Tiling {
@@ -793,7 +796,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
   constexpr uint32_t WSLICE = NOUT * 128;  // bytes of one weight slice
   const size_t wbytes = (size_t)(WRES ? a.nsl : nst) * WSLICE;
   // bars: full[nst], empty[nst], tfull[2], tempty[2], drain, tab_full[2], tab_empty[2]
-  const Smem sm = carve(smem_raw, nst, wbytes + tap_table_bytes(a.s.K), NOUT, 2 * nst + 9);
+  const Smem sm = carve(smem_raw, nst, wbytes + tap_table_bytes(a.s.K) + EPI_STAGING_BYTES, NOUT,
+                        2 * nst + 9);
   float* bias_s = sm.fl;
   volatile int* abort_flag = sm.abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -876,19 +880,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
     __syncwarp();
   } else if (warp <= N_EPI_WARPS) {
     // ------------------------------------------------------------------ epilogue
+    // A lane reads its own row (TMEM lane) 32 columns at a time, adds the bias and packs to bf16.
+    // Storing that directly would scatter 16-byte pieces over 32 rows per instruction; instead the
+    // warp passes the 32 x 64-byte block through shared memory and stores 8 rows x 64 bytes per
+    // instruction (lane -> row 8 i + lane / 4, 16-byte piece lane % 4).
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const int r = q * 32 + lane;
+    const uint32_t stg = w0 + (uint32_t)(wbytes + tap_table_bytes(a.s.K)) + (uint32_t)(warp - 1) * 2048u;
+    const uint32_t wr_row = stg + lane * 64, wr_x = (lane >> 1) & 3;
+    uint32_t rd_addr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = 8 * i + (lane >> 2);
+      rd_addr[i] = stg + row * 64 + (((lane & 3) ^ ((row >> 1) & 3)) << 4);
+    }
     uint32_t it = 0;
     for (int tile = blockIdx.x; tile < a.t.tiles; tile += gridDim.x, ++it) {
       const uint32_t acc = it & 1, aph = (it >> 1) & 1;
-      long gp, p;
-      int img;
-      bool valid;
-      tile_pixel(a.t, tile, r, gp, img, p, valid);
+      // where the four rows this lane stores live in global memory
+      bf16* orow[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        long gp, p;
+        int img;
+        bool valid;
+        tile_pixel(a.t, tile, q * 32 + 8 * i + (lane >> 2), gp, img, p, valid);
+        orow[i] = valid ? a.y + gp * a.ncol + co0 + (lane & 3) * 8 : nullptr;
+      }
       if (!mbar_wait(tfull_bar(acc), aph, abort_flag, 0x21, 512)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * NOUT;
-      uint4* out = reinterpret_cast<uint4*>(a.y + gp * a.ncol + co0);
 #pragma unroll
       for (int cc = 0; cc < NOUT / 32; ++cc) {
         uint32_t v[32];
@@ -900,18 +920,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_bar(acc));
         }
-        if (valid) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 o;
-            const float* bs = bias_s + cc * 32 + j * 8;
-            o.x = pack_bf16x2(__uint_as_float(v[j * 8 + 0]) + bs[0], __uint_as_float(v[j * 8 + 1]) + bs[1]);
-            o.y = pack_bf16x2(__uint_as_float(v[j * 8 + 2]) + bs[2], __uint_as_float(v[j * 8 + 3]) + bs[3]);
-            o.z = pack_bf16x2(__uint_as_float(v[j * 8 + 4]) + bs[4], __uint_as_float(v[j * 8 + 5]) + bs[5]);
-            o.w = pack_bf16x2(__uint_as_float(v[j * 8 + 6]) + bs[6], __uint_as_float(v[j * 8 + 7]) + bs[7]);
-            out[cc * 4 + j] = o;
-          }
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          const float* bs = bias_s + cc * 32 + j * 8;
+          o.x = pack_bf16x2(__uint_as_float(v[j * 8 + 0]) + bs[0], __uint_as_float(v[j * 8 + 1]) + bs[1]);
+          o.y = pack_bf16x2(__uint_as_float(v[j * 8 + 2]) + bs[2], __uint_as_float(v[j * 8 + 3]) + bs[3]);
+          o.z = pack_bf16x2(__uint_as_float(v[j * 8 + 4]) + bs[4], __uint_as_float(v[j * 8 + 5]) + bs[5]);
+          o.w = pack_bf16x2(__uint_as_float(v[j * 8 + 6]) + bs[6], __uint_as_float(v[j * 8 + 7]) + bs[7]);
+          sts16(wr_row + ((j ^ wr_x) << 4), o);
         }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 o;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
+                       : "r"(rd_addr[i]));
+#ifdef MC_EXP_NOSTORE
+          if (o.x == 0x12345679u)
+#endif
+          if (orow[i]) *reinterpret_cast<uint4*>(orow[i] + cc * 32) = o;
+        }
+        __syncwarp();  // the block is read out before the next one is written
       }
     }
   } else {
@@ -1352,14 +1383,14 @@ static bool plan_gemm(int ncol, int nsl, int K, GemmPlan& p) {
   if (ncol <= 0 || ncol % 64 != 0) return false;
   // resident weights when they fit with a reasonable pipeline (needs ncol <= 256)
   if (ncol <= 256 && (ncol == 64 || ncol == 128 || ncol == 256)) {
-    const size_t extra = (size_t)nsl * ncol * 128 + tap_table_bytes(K);
+    const size_t extra = (size_t)nsl * ncol * 128 + tap_table_bytes(K) + EPI_STAGING_BYTES;
     const int nst = pick_stages(extra, ncol, 8, 3, false);
     if (nst > 0) { p = {ncol, true, nst, extra}; return true; }
   }
   const int nout = ncol % 256 == 0 ? 256 : ncol % 128 == 0 ? 128 : 64;
   // streamed weights: every stage carries its weight slice
   for (int nst = 6; nst >= 3; --nst) {
-    const size_t extra = (size_t)nst * nout * 128 + tap_table_bytes(K);
+    const size_t extra = (size_t)nst * nout * 128 + tap_table_bytes(K) + EPI_STAGING_BYTES;
     if (smem_bytes(nst, extra, nout, 2 * nst + 16) <= SMEM_LIMIT) {
       p = {nout, false, nst, extra};
       return true;
