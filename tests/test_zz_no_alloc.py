@@ -70,6 +70,6 @@ def test_static_scratch_rejects_what_does_not_fit():
                                         y.data_ptr(), st)
     assert rc == -6 and b"limit" in lib.mc_strerror(rc)
     # and a shape the tensor-core forward does not take at all is refused, not silently rerouted
-    d2 = _lib.McDesc(1, 48, 64, 8, 16, 8, 16, 3, 0, 1, _lib.MC_BF16, _lib.MC_NHWC)
+    d2 = _lib.McDesc(1, 64, 40, 8, 16, 8, 16, 3, 0, 1, _lib.MC_BF16, _lib.MC_NHWC)  # C_out % 64 != 0
     assert lib.mc_conv_fwd_static_scratch(d2, x.data_ptr(), m.data_ptr(), w.data_ptr(),
                                           b.data_ptr(), y.data_ptr(), st) == -2
