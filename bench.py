@@ -267,18 +267,36 @@ def run_ours(args):
     h2d = xp.numel() * 2 + gyp.numel() * 2
     d2h = sum(t.numel() * t.element_size() for t in outs.values())
 
+    # One batch element at a time, so that the upload of element i + 1 and the download of the
+    # results of element i - 1 (separate copy engines, separate streams) run under the kernels of
+    # element i; the weight / bias gradients accumulate across the elements in the layer.
+    in_s, out_s = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
     def e2e_step():
-        xd = xp.to(dev, non_blocking=True).requires_grad_(True)
-        gd = gyp.to(dev, non_blocking=True)
+        main = torch.cuda.current_stream()
         layer.zero_grad(set_to_none=True)
-        y = layer(xd, m)
-        y.backward(gd)
+        in_s.wait_stream(main)
+        for i in range(BATCH):
+            with torch.cuda.stream(in_s):
+                xd = xp[i:i + 1].to(dev, non_blocking=True)
+                gd = gyp[i:i + 1].to(dev, non_blocking=True)
+            main.wait_stream(in_s)
+            xd.record_stream(main)
+            gd.record_stream(main)
+            xd.requires_grad_(True)
+            y = layer(xd, m)
+            y.backward(gd)
+            out_s.wait_stream(main)
+            with torch.cuda.stream(out_s):
+                y.record_stream(out_s)
+                xd.grad.record_stream(out_s)
+                outs["y"][i:i + 1].copy_(y.detach(), non_blocking=True)
+                outs["gx"][i:i + 1].copy_(xd.grad, non_blocking=True)
         if world > 1:
             allreduce_gradients([layer.weight.grad, layer.bias.grad])
-        outs["y"].copy_(y.detach(), non_blocking=True)
-        outs["gx"].copy_(xd.grad, non_blocking=True)
         outs["gw"].copy_(layer.weight.grad, non_blocking=True)
         outs["gb"].copy_(layer.bias.grad, non_blocking=True)
+        main.wait_stream(out_s)
 
     e2e_steps = max(2, min(args.steps, 5))
     for _ in range(2):
