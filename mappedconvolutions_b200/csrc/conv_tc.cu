@@ -105,7 +105,8 @@ struct Source {
   const TapEnt* tab;    // prebuilt table [pixel of the tiled domain][tap], or null
   int KC;      // K * C: length of the gathered (tap, channel) axis
   int packed;  // C is not a multiple of 64: a 64-wide slice holds elements tap * C + c of several
-               // taps (map mode only)
+               // taps (map mode only).  2: the whole axis fits one slice and the row-per-thread
+               // producer builds it straight from the global tap table
 };
 
 // Replace the inactive corners of a decoded tap by (some active pixel of the tap, weight 0).
@@ -131,6 +132,7 @@ struct GemmArgs {
   int nsl;            // 64-wide slices of the gathered operand = K * C / 64
   int nst;            // pipeline stages
   int ncol;           // channels of y / gy rows (a CTA works on a chunk of NOUT of them)
+  int full_cnt;       // producer warps that arrive on a stage's "full" barrier
   int mtpg;           // wgrad: M = 128 gradient tiles per CTA (blockIdx.y picks the group)
 };
 
@@ -597,6 +599,153 @@ __device__ __forceinline__ void producer_loop_packed(const Source& s, const Tili
   }
 }
 
+// Producer for a gathered axis that fits ONE slice (K * C <= 64, e.g. a 3-channel first layer with
+// 7 or 9 taps).  Such a layer is a stream of tiny tiles - one stage, one MMA group and one
+// epilogue each - so the cost per tile is what matters: a thread builds a whole 128-byte row by
+// itself (tap records read straight from the global table, which stays in L2; no shared-memory
+// table, no idle lanes), four warps build a stage, and the four teams of four warps work on four
+// consecutive ring slots at once.
+constexpr int ROW_TEAMS = 4;
+
+__device__ __forceinline__ void load_entry(const TapEnt* ent, int (&off)[4], float (&w)[4]) {
+  const uint4 o = ldg16(ent), ww = ldg16(reinterpret_cast<const uint4*>(ent) + 1);
+  off[0] = (int)o.x; off[1] = (int)o.y; off[2] = (int)o.z; off[3] = (int)o.w & ~MORE_FLAG;
+  w[0] = __uint_as_float(ww.x); w[1] = __uint_as_float(ww.y);
+  w[2] = __uint_as_float(ww.z); w[3] = __uint_as_float(ww.w);
+}
+
+__device__ __forceinline__ void gather_row_elements(const TapEnt* ent, const bf16* xb, int C, int K,
+                                                    int KC, bool nearest, uint4 (&row)[8]) {
+  int k = 0, c = 0;
+  int off[4];
+  float w[4];
+  load_entry(ent, off, w);
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    if (ch * 8 < KC) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (ch * 8 + j < KC) {
+          if (nearest) {
+            v[j] = w[0] * __bfloat162float(__ldg(xb + (long)off[0] * C + c));
+          } else {
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              acc = fmaf(w[i], __bfloat162float(__ldg(xb + (long)off[i] * C + c)), acc);
+            v[j] = acc;
+          }
+          if (++c == C) {
+            c = 0;
+            if (++k < K) load_entry(ent + k, off, w);
+          }
+        }
+      }
+    }
+    row[ch] = pack8(v);
+  }
+}
+
+// Nearest maps: one source pixel per tap.  The K (pixel, weight) pairs of the row are fetched
+// first, all loads in flight together, and parked in the thread's private strip of shared memory;
+// the element loop then reads them back with short shared loads, so that its global loads do not
+// wait on one another.
+__device__ __forceinline__ void gather_row_nearest(const TapEnt* ent, const bf16* xb, int C, int K,
+                                                   int KC, uint2* mine, uint4 (&row)[8]) {
+#pragma unroll 4
+  for (int k = 0; k < K; ++k)
+    mine[k] = make_uint2((uint32_t)__ldg(&ent[k].off[0]), __float_as_uint(__ldg(&ent[k].w[0])));
+  int k = 0, c = 0;
+  uint2 e = mine[0];
+  // 24 elements (three 16-byte chunks) per pass, so that all loads of a typical row (21 or 27
+  // elements) are in flight before the first of them is converted
+#pragma unroll
+  for (int pass = 0; pass < 3; ++pass) {
+    constexpr int PE = 24;
+    float v[PE];
+#pragma unroll
+    for (int j = 0; j < PE; ++j) v[j] = 0.f;
+    if (pass * PE < KC) {
+#pragma unroll
+      for (int j = 0; j < PE; ++j) {
+        if (pass * PE + j < 64 && pass * PE + j < KC) {
+          v[j] = __uint_as_float(e.y) * __bfloat162float(__ldg(xb + (long)(int)e.x * C + c));
+          if (++c == C) {
+            c = 0;
+            if (++k < K) e = mine[k];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      if (pass * 3 + q < 8) {
+        uint4 o;
+        o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+        o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+        o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+        o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+        row[pass * 3 + q] = o;
+      }
+    }
+  }
+}
+
+template <bool PAD>
+__device__ __forceinline__ void producer_rowwise(const Source& s, const Tiling& t, int nsl, int nslots,
+                                                 int nst, uint32_t stage0, uint32_t full0,
+                                                 uint32_t empty0, TapEnt* table,
+                                                 volatile int* abort_flag, int pw,
+                                                 int lane, int code) {
+  // the shared-memory tap table is not used in this mode; its space holds the threads' strips
+  uint2* mine = reinterpret_cast<uint2*>(table) + (size_t)(pw * 32 + lane) * s.K;
+  constexpr int TW = N_PRODUCER_WARPS / ROW_TEAMS;  // warps per team: 4 x 32 threads = 128 rows
+  const int team = pw / TW, r = (pw % TW) * 32 + lane;
+  const uint32_t rowaddr = r * 128;
+  const int rx = r & 7;
+  // this team's ring slots: team, team + ROW_TEAMS, ... of the CTA's slot sequence
+  int tile = blockIdx.x, sl = team;
+  uint32_t st = team, ph = 0;
+  while (sl >= nslots) { sl -= nslots; tile += gridDim.x; }
+  while (tile < t.tiles) {
+    uint4 row[8];
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) row[ch] = make_uint4(0, 0, 0, 0);
+    if (!PAD || sl < nsl) {
+      long gp, p;
+      int img;
+      bool valid;
+      tile_pixel(t, tile, r, gp, img, p, valid);
+#ifdef MC_EXP_NOGATHER
+      valid = false;
+#endif
+      if (valid) {
+        const TapEnt* ent = s.tab + p * s.K;
+        const bf16* xb = s.src + (long)img * s.spix * s.C;
+        if (s.interp == 0) gather_row_nearest(ent, xb, s.C, s.K, s.KC, mine, row);
+        else gather_row_elements(ent, xb, s.C, s.K, s.KC, false, row);
+      }
+    }
+    int okw = 1;
+    if (lane == 0) okw = mbar_wait(empty0 + 8u * st, ph ^ 1, abort_flag, code) ? 1 : 0;
+    okw = __shfl_sync(0xffffffffu, okw, 0);
+    if (!okw) return;
+    const uint32_t sbase = stage0 + st * STAGE_BYTES + rowaddr;
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) sts16(sbase + ((ch ^ rx) << 4), row[ch]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(full0 + 8u * st);
+    sl += ROW_TEAMS;
+    while (sl >= nslots) { sl -= nslots; tile += gridDim.x; }
+    st += ROW_TEAMS;
+    if (st >= (uint32_t)nst) { st -= nst; ph ^= 1; }
+  }
+}
+
 // Producer warp for nearest-neighbour maps: every (pixel, tap) reads ONE source pixel with weight 1
 // (or nothing), so a row is a 128-byte copy.  There is no arithmetic to hide the load latency
 // behind; instead the loads of the next COPY_AHEAD slices are kept in flight.  Inverse-map mode:
@@ -812,7 +961,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
-      mbar_init(full_bar(s), N_PRODUCER_WARPS + (WRES ? 0 : 1));
+      mbar_init(full_bar(s), a.full_cnt + (WRES ? 0 : 1));
       mbar_init(empty_bar(s), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -949,7 +1098,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
     // ------------------------------------------------------------------ producers
     if (warp < FIRST_PROD_WARP) {
       if (PRE) {
-        if (warp == FIRST_DEC_WARP && lane == 0)
+        if (warp == FIRST_DEC_WARP && lane == 0 && a.s.packed != 2)
           loader_loop(a.s, a.t, w0 + (uint32_t)wbytes, tabbar0, abort_flag);
         if (!WRES && warp == FIRST_DEC_WARP + 1 && lane == 0) {
           // weight streamer: slice s of every tile goes into the ring slot of pipeline step s
@@ -969,6 +1118,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
         decoder_loop<CSR>(a.s, a.t, (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
                           (warp - FIRST_DEC_WARP) * 32 + lane, lane);
       }
+    } else if (!CSR && PRE && a.s.packed == 2) {
+      producer_rowwise<false>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
+                              (TapEnt*)(sm.extra + wbytes), abort_flag, warp - FIRST_PROD_WARP, lane,
+                              0x36);
     } else if (!CSR && a.s.packed) {
       producer_loop_packed<false>(a.s, a.t, a.nsl, a.nsl, nst, stage0, full_bar(0), empty_bar(0),
                                   (TapEnt*)(sm.extra + wbytes), tabbar0, abort_flag,
@@ -1035,7 +1188,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < nst; ++s) {
-      mbar_init(full_bar(s), N_PRODUCER_WARPS);
+      mbar_init(full_bar(s), a.full_cnt);
       mbar_init(empty_bar(s), 1);
     }
     for (int i = 0; i < GY_STAGES; ++i) {
@@ -1110,22 +1263,54 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
       okw = __shfl_sync(0xffffffffu, okw, 0);
       if (!okw) { ok = false; break; }
       const uint32_t sbase = gy0 + gs * GYB;
-      for (int r = lw * 4 + g; r < TILE_M; r += N_EPI_WARPS * 4) {
-        long gp, p;
-        int img;
-        bool valid;
-        tile_pixel(a.t, tile, r, gp, img, p, valid);
+      if (nsl_pad <= 2 || (a.s.interp == 0 && a.s.C <= 64)) {
+        // Few, cheap slices per tile (one-slice layers, 64-channel copies): the gy tile's load
+        // latency is on the critical path, so all eight rows of a group are requested before the
+        // first is stored.
 #pragma unroll
         for (int nb = 0; nb < NOUT / 64; ++nb) {
-          const uint4 v = valid ? ldg16(a.gy + gp * a.ncol + co0 + nb * 64 + lg * 8)
-                                : make_uint4(0, 0, 0, 0);
-          // N > 64: consecutive 64-channel blocks are separate swizzle atoms, STAGE_BYTES apart
-          sts16(sbase + nb * STAGE_BYTES + r * 128 + ((lg ^ (r & 7)) << 4), v);
-          float* b8 = bsum + nb * 8;
-          bf16x2_fma(v.x, 1.f, b8[0], b8[1]);
-          bf16x2_fma(v.y, 1.f, b8[2], b8[3]);
-          bf16x2_fma(v.z, 1.f, b8[4], b8[5]);
-          bf16x2_fma(v.w, 1.f, b8[6], b8[7]);
+          uint4 v[TILE_M / (N_EPI_WARPS * 4)];
+#pragma unroll
+          for (int i = 0; i < TILE_M / (N_EPI_WARPS * 4); ++i) {
+            const int r = lw * 4 + g + i * (N_EPI_WARPS * 4);
+            long gp, p;
+            int img;
+            bool valid;
+            tile_pixel(a.t, tile, r, gp, img, p, valid);
+            v[i] = valid ? ldg16(a.gy + gp * a.ncol + co0 + nb * 64 + lg * 8)
+                         : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int i = 0; i < TILE_M / (N_EPI_WARPS * 4); ++i) {
+            const int r = lw * 4 + g + i * (N_EPI_WARPS * 4);
+            sts16(sbase + nb * STAGE_BYTES + r * 128 + ((lg ^ (r & 7)) << 4), v[i]);
+            float* b8 = bsum + nb * 8;
+            bf16x2_fma(v[i].x, 1.f, b8[0], b8[1]);
+            bf16x2_fma(v[i].y, 1.f, b8[2], b8[3]);
+            bf16x2_fma(v[i].z, 1.f, b8[4], b8[5]);
+            bf16x2_fma(v[i].w, 1.f, b8[6], b8[7]);
+          }
+        }
+      } else {
+        // Otherwise the gy tile is far off the critical path; one row at a time keeps the loader
+        // out of the producers' way (measured: bursts cost 5-10 % on the wide layers).
+        for (int r = lw * 4 + g; r < TILE_M; r += N_EPI_WARPS * 4) {
+          long gp, p;
+          int img;
+          bool valid;
+          tile_pixel(a.t, tile, r, gp, img, p, valid);
+#pragma unroll
+          for (int nb = 0; nb < NOUT / 64; ++nb) {
+            const uint4 v = valid ? ldg16(a.gy + gp * a.ncol + co0 + nb * 64 + lg * 8)
+                                  : make_uint4(0, 0, 0, 0);
+            // N > 64: consecutive 64-channel blocks are separate swizzle atoms, STAGE_BYTES apart
+            sts16(sbase + nb * STAGE_BYTES + r * 128 + ((lg ^ (r & 7)) << 4), v);
+            float* b8 = bsum + nb * 8;
+            bf16x2_fma(v.x, 1.f, b8[0], b8[1]);
+            bf16x2_fma(v.y, 1.f, b8[2], b8[3]);
+            bf16x2_fma(v.z, 1.f, b8[4], b8[5]);
+            bf16x2_fma(v.w, 1.f, b8[6], b8[7]);
+          }
         }
       }
       fence_proxy_async_smem();
@@ -1171,12 +1356,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
     // ------------------------------------------------------------------ producers
     if (warp < FIRST_PROD_WARP) {
       if (PRE) {
-        if (warp == FIRST_DEC_WARP && lane == 0)
+        if (warp == FIRST_DEC_WARP && lane == 0 && a.s.packed != 2)
           loader_loop(a.s, a.t, gy0 + (uint32_t)GY_STAGES * GYB, tabbar0, abort_flag);
       } else {
         decoder_loop<false>(a.s, a.t, (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
                             abort_flag, (warp - FIRST_DEC_WARP) * 32 + lane, lane);
       }
+    } else if (PRE && a.s.packed == 2) {
+      producer_rowwise<true>(a.s, a.t, nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
+                             (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), abort_flag,
+                             warp - FIRST_PROD_WARP, lane, 0x64);
     } else if (a.s.packed) {
       producer_loop_packed<true>(a.s, a.t, nsl, nsl_pad, nst, stage0, full_bar(0), empty_bar(0),
                                  (TapEnt*)(sm.extra + (size_t)GY_STAGES * GYB), tabbar0,
@@ -1411,9 +1600,14 @@ bool conv_tc_fwd_supported(const mc_desc* d) {
 
 // Streamed weights need the prebuilt tap table; when the caller passes the raw sample map the
 // table is built into the workspace first.
+// One-slice layers (K * C_in <= 64) use the row-per-thread producer, which reads the table from
+// global memory.
+static bool rowwise_shape(const mc_desc* d) { return d->C_in % 64 != 0 && (long)d->K * d->C_in <= 64; }
+
 static bool fwd_needs_table(const mc_desc* d) {
   GemmPlan p;
-  return plan_gemm(d->C_out, fwd_slices(d), d->K, p) && !p.wres;
+  if (!plan_gemm(d->C_out, fwd_slices(d), d->K, p)) return false;
+  return !p.wres || (rowwise_shape(d) && p.nst >= ROW_TEAMS);
 }
 
 size_t conv_tc_fwd_wimg_bytes(const mc_desc* d) {
@@ -1502,11 +1696,16 @@ static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, con
   const long nw = (long)a.nsl * 64 * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_out,
                                                          d->C_in, d->K, 0, d->C_in), MC_COUNT(1);
-  if (!tab && !p.wres) {  // build the table behind the weight image
+  if (!tab && fwd_needs_table(d)) {  // build the table behind the weight image
     void* t = (uint8_t*)ws + conv_tc_fwd_wimg_bytes(d);
     const int rc = tapmap_build_launch(d, map, t, st);
     if (rc) return rc;
     a.s.tab = (const TapEnt*)t;
+  }
+  a.full_cnt = N_PRODUCER_WARPS;
+  if (a.s.tab && rowwise_shape(d) && p.nst >= ROW_TEAMS) {
+    a.s.packed = 2;
+    a.full_cnt = N_PRODUCER_WARPS / ROW_TEAMS;
   }
   return launch_gemm<false>(a, p, a.s.tab != nullptr, st);
 }
@@ -1619,6 +1818,7 @@ int conv_tc_dgrad_launch(const mc_desc* d, const void* gy, const void* inv, cons
   GemmPlan p;
   if (!plan_gemm(a.ncol, a.nsl, d->K, p)) return MC_ERR_UNSUPPORTED;
   a.nst = p.nst;
+  a.full_cnt = N_PRODUCER_WARPS;
   const long nw = (long)d->K * d->C_in * d->C_out;
   weight_image_kernel<<<grid_for(nw, 256), 256, 0, st>>>((const bf16*)w, (uint16_t*)ws, d->C_in,
                                                          d->C_out, d->K, 1, d->C_in), MC_COUNT(1);
@@ -1691,6 +1891,11 @@ static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, co
   if (!plan_wgrad(d, p)) return MC_ERR_UNSUPPORTED;
   a.nst = p.nst;
   a.mtpg = p.mtpg;
+  a.full_cnt = N_PRODUCER_WARPS;
+  if (tab && rowwise_shape(d) && p.nst >= ROW_TEAMS) {
+    a.s.packed = 2;
+    a.full_cnt = N_PRODUCER_WARPS / ROW_TEAMS;
+  }
   if (cudaMemsetAsync(gw, 0, (size_t)d->C_out * d->C_in * d->K * sizeof(float), st) != cudaSuccess)
     return MC_ERR_LAUNCH;
   if (gb && cudaMemsetAsync(gb, 0, (size_t)d->C_out * sizeof(float), st) != cudaSuccess)

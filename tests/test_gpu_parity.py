@@ -150,6 +150,9 @@ def _device_status():
     (1, 16, 64, 12, 20, 10, 18, 9),
     (1, 96, 128, 12, 20, 10, 18, 3),
     (1, 20, 64, 9, 9, 9, 9, 5),
+    # K * C_in <= 64: one slice per tile, built row-per-thread from the global tap table
+    (1, 4, 128, 16, 32, 16, 32, 9),
+    (3, 3, 64, 5, 50, 5, 50, 9),
 ])
 @pytest.mark.parametrize("interp", [0, 1, 2])
 def test_bf16_tensor_core_conv_forward(shape, interp):
@@ -192,6 +195,8 @@ def test_bf16_tensor_core_conv_forward(shape, interp):
     (1, 16, 64, 12, 20, 10, 18, 9),
     (1, 96, 128, 12, 20, 10, 18, 3),
     (1, 20, 64, 9, 9, 9, 9, 5),
+    (1, 4, 128, 16, 32, 16, 32, 9),
+    (3, 3, 64, 5, 50, 5, 50, 9),
 ])
 @pytest.mark.parametrize("interp", [0, 1, 2])
 def test_bf16_tensor_core_conv_backward(shape, interp):
