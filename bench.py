@@ -689,6 +689,17 @@ def run_profile_case(args):
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
     B = args.batch
+    if args.profile_case == "pool":  # config 4 at a reduced batch: avg pool, max pool, avg unpool
+        from mappedconvolutions_b200.util import icosphere as ico
+        x = torch.randn(B, 128, 1, ico.num_vertices(7), device=dev)
+        pm = ico.pooling_map(7).to(dev)
+        for _ in range(3):
+            y = ops.mapped_avg_pool(x, pm, 7, 0)
+            ops.mapped_max_pool(x, pm, 7, 0)
+            ops.mapped_avg_unpool(y, pm, 1, x.shape[3], 7, 0)
+        torch.cuda.synchronize()
+        print("profile case pool batch %d done" % B)
+        return
     bf = lambda *shape: torch.randn(*shape, device=dev).to(torch.bfloat16)
     x = bf(B, CIN, H, W).contiguous(memory_format=torch.channels_last)
     gy = bf(B, COUT, H, W).contiguous(memory_format=torch.channels_last)
@@ -712,7 +723,7 @@ def main():
     ap.add_argument("--workload", default="conv", choices=["conv", "resample", "pool", "knn", "encoder"],
                     help="conv (default) is the headline config; the others are the remaining configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", choices=["fwd", "bwd"],
+    ap.add_argument("--profile-case", choices=["fwd", "bwd", "pool"],
                     help="run three calls of the config-2 forward / backward at --batch and exit "
                          "(small case for profiler captures)")
     ap.add_argument("--batch", type=int, default=2, help="batch of --profile-case")

@@ -719,9 +719,6 @@ __device__ __forceinline__ void producer_rowwise(const Source& s, const Tiling& 
       int img;
       bool valid;
       tile_pixel(t, tile, r, gp, img, p, valid);
-#ifdef MC_EXP_NOGATHER
-      valid = false;
-#endif
       if (valid) {
         const TapEnt* ent = s.tab + p * s.K;
         const bf16* xb = s.src + (long)img * s.spix * s.C;
@@ -1086,9 +1083,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                        : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
                        : "r"(rd_addr[i]));
-#ifdef MC_EXP_NOSTORE
-          if (o.x == 0x12345679u)
-#endif
           if (orow[i]) *reinterpret_cast<uint4*>(orow[i] + cc * 32) = o;
         }
         __syncwarp();  // the block is read out before the next one is written

@@ -300,22 +300,30 @@ __global__ void __launch_bounds__(256) inv_gather_planes_kernel(const InvGatherA
 #pragma unroll
   for (int i = 0; i < 4; ++i) e4[i] = beg + i < end ? __ldg(a.ent + beg + i) : make_int2(0, 0);
   const int n4 = end - beg < 4 ? end - beg : 4;
+  const bool longer = end - beg > 4;
+  // four planes per trip: their (independent) loads are in flight together
+#pragma unroll 4
   for (long pl = pl0; pl < pl1; ++pl) {
     const T* src = g + pl * a.ngrid;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = i < n4 ? (float)ldv(src + e4[i].x) : 0.f;
     float acc = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       if (i < n4) {
-        float v = (float)ldv(src + e4[i].x);
-        if (AVG) v = __fdiv_rn(v, (float)a.K);
-        acc = __fadd_rn(acc, __fmul_rn(__int_as_float(e4[i].y), v));
+        float t = v[i];
+        if (AVG) t = __fdiv_rn(t, (float)a.K);
+        acc = __fadd_rn(acc, __fmul_rn(__int_as_float(e4[i].y), t));
       }
     }
-    for (int e = beg + 4; e < end; ++e) {
-      const int2 en = __ldg(a.ent + e);
-      float v = (float)ldv(src + en.x);
-      if (AVG) v = __fdiv_rn(v, (float)a.K);
-      acc = __fadd_rn(acc, __fmul_rn(__int_as_float(en.y), v));
+    if (longer) {
+      for (int e = beg + 4; e < end; ++e) {
+        const int2 en = __ldg(a.ent + e);
+        float t = (float)ldv(src + en.x);
+        if (AVG) t = __fdiv_rn(t, (float)a.K);
+        acc = __fadd_rn(acc, __fmul_rn(__int_as_float(en.y), t));
+      }
     }
     stv(out + pl * a.npix + q, acc);
   }
