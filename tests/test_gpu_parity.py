@@ -264,6 +264,51 @@ def test_bf16_tensor_core_transposed_conv(shape, interp):
     H.assert_close(got[2].float(), want_g[2], 2e-2, "tc tconv bias grad")
 
 
+@pytest.mark.parametrize("shape", [
+    # shapes whose forward needs the prebuilt tap table even when the caller brings only the map:
+    # streamed weight slices (256 columns) and the one-slice row-per-thread producer
+    (1, 128, 256, 1, 300, 1, 300, 7),
+    (2, 3, 64, 6, 40, 6, 40, 9),
+    (1, 64, 64, 16, 32, 16, 32, 9),
+])
+@pytest.mark.parametrize("interp", [0, 1])
+def test_c_abi_forward_and_wgrad_with_a_bare_map(shape, interp):
+    """mc_conv_fwd / mc_conv_wgrad called directly with the float map (no plan objects): the
+    library builds what it needs inside the caller's workspace.  Against the oracle, 2e-2."""
+    from mappedconvolutions_b200 import _lib
+    L = _lib.lib()
+    B, Cin, Cout, IH, IW, OH, OW, K = shape
+    g = torch.Generator().manual_seed(sum(shape) + interp)
+    bf = lambda t: t.to(torch.bfloat16)
+    x = bf(torch.randn(B, Cin, IH, IW, generator=g))
+    gy = bf(torch.randn(B, Cout, OH, OW, generator=g))
+    w = bf(torch.randn(Cout, Cin, K, generator=g))
+    b = bf(torch.randn(Cout, generator=g))
+    m = (torch.rand(OH, OW, K, 2, generator=g) * torch.tensor([IW + 1.0, IH + 1.0]) - 1.0).contiguous()
+    if IH == 1:
+        m[..., 1] = 0
+    want_y = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, interp)
+    want_g = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, interp)
+    cl = lambda t: t.cuda().contiguous(memory_format=torch.channels_last)
+    xd, gd, wd, bd, md = cl(x), cl(gy), w.cuda(), b.cuda(), m.cuda()
+    d = _lib.McDesc(B, Cin, Cout, IH, IW, OH, OW, K, 0, interp, _lib.MC_BF16, _lib.MC_NHWC)
+    st = torch.cuda.current_stream().cuda_stream
+    n = max(L.mc_conv_fwd_workspace_bytes(d), L.mc_conv_wgrad_workspace_bytes(d), 16)
+    assert L.mc_conv_fwd_workspace_bytes(d) > 0, "expected the tensor-core forward for this shape"
+    ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+    y = torch.empty_like(gd)
+    _lib.check(L.mc_conv_fwd(d, xd.data_ptr(), md.data_ptr(), None, wd.data_ptr(), bd.data_ptr(),
+                             y.data_ptr(), ws.data_ptr(), n, st))
+    gw = torch.empty(Cout, Cin, K, dtype=torch.float32, device="cuda")
+    gb = torch.empty(Cout, dtype=torch.float32, device="cuda")
+    _lib.check(L.mc_conv_wgrad(d, gd.data_ptr(), xd.data_ptr(), md.data_ptr(), None, gw.data_ptr(),
+                               gb.data_ptr(), ws.data_ptr(), n, st))
+    assert _device_status() == 0
+    H.assert_close(y.float(), want_y, 2e-2, "mc_conv_fwd")
+    H.assert_close(gw, want_g[1], 2e-2, "mc_conv_wgrad")
+    H.assert_close(gb, want_g[2], 2e-2, "mc_conv_wgrad bias")
+
+
 def test_bias_grad_entry_point():
     """mc_bias_grad against a float64 sum, both layouts and all dtypes (1e-5 / 2e-2)."""
     from mappedconvolutions_b200 import _lib
