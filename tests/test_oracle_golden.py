@@ -109,3 +109,27 @@ def test_oracle_max_pool_cpu_start_value():
 def test_oracle_config1():
     c = H.load_cases("config1.npz")["config1"]
     H.compare_case(H.run_conv(IMPL, c), c, 1e-5, "config1")
+
+
+@pytest.mark.parametrize("D,M,N,k", [(3, 2000, 500, 9), (2, 800, 800, 4), (5, 300, 64, 16)])
+def test_oracle_knn_against_independent_searches(D, M, N, k):
+    """The reference ships no CPU k-NN and no k-NN test, so its semantics are cross-checked against
+    two independent exact searches instead: SciPy's k-d tree and a float64 brute force.  Same
+    neighbour sets, 1-based indices, ascending Euclidean distances (1e-5 relative: the oracle
+    accumulates in float32 like the reference's kernel)."""
+    import numpy as np
+    from scipy.spatial import cKDTree
+    g = torch.Generator().manual_seed(D * 1000 + k)
+    ref = torch.randn(1, D, M, generator=g)
+    q = torch.randn(1, D, N, generator=g)
+    idx, dist = oracle.knn_forward(ref, q, k)
+    idx, dist = idx[0].numpy(), dist[0].numpy()                     # (k, N)
+    assert idx.min() >= 1 and idx.max() <= M
+    assert (np.diff(dist, axis=0) >= 0).all()
+    r64, q64 = ref[0].double().numpy().T, q[0].double().numpy().T   # (M, D), (N, D)
+    tree_d, tree_i = cKDTree(r64).query(q64, k=k)
+    brute = np.sqrt(((q64[:, None, :] - r64[None, :, :]) ** 2).sum(-1))
+    brute_i = np.argsort(brute, axis=1, kind="stable")[:, :k]
+    for n in range(N):
+        assert set(idx[:, n] - 1) == set(tree_i[n]) == set(brute_i[n]), n
+    np.testing.assert_allclose(dist.T, tree_d, rtol=1e-5, atol=1e-6)
