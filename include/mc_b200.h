@@ -91,8 +91,10 @@ size_t mc_conv_fwd_workspace_bytes(const mc_desc* d);
  * library until the process exits).  The call allocates and frees nothing, and computes exactly
  * what mc_conv_fwd computes.
  *  - Supported: the configurations of the tensor-core forward (MC_BF16, MC_NHWC, P == 0,
- *    C_in % 64 == 0, C_out == 64); anything else returns MC_ERR_UNSUPPORTED.
- *  - K * C_in * C_out * 2 bytes must fit the array, otherwise MC_ERR_TOO_LARGE.
+ *    C_out % 64 == 0); anything else returns MC_ERR_UNSUPPORTED.
+ *  - The scratch mc_conv_fwd would ask for (mc_conv_fwd_workspace_bytes: the re-laid-out weights,
+ *    K * C_in * C_out * 2 bytes rounded up to whole 64-element slices, plus a tap table for the
+ *    wide or very narrow layers that need one) must fit the array, otherwise MC_ERR_TOO_LARGE.
  *  - The first call on each device looks up the array's device address (with that device
  *    current); make that first call outside any stream capture.
  *  - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
@@ -136,7 +138,7 @@ size_t mc_invmap_build_workspace_bytes(const mc_desc* d);
 int mc_invmap_build(const mc_desc* d, const void* map, void* inv, size_t inv_bytes, void* ws,
                     size_t ws_bytes, void* stream);
 /* Same result as mc_conv_dgrad, computed on the tensor cores from a prebuilt inverse map.
- * bf16, MC_NHWC, C_in == 64, C_out % 64 == 0 (mc_conv_dgrad_inv_supported() tells).
+ * bf16, MC_NHWC, C_in % 64 == 0, C_out % 64 == 0 (mc_conv_dgrad_inv_supported() tells).
  * Replaces cuda::MappedConvBackwardInput, src/nn/cuda/mapped_convolution_layer.cu:75-132. */
 int mc_conv_dgrad_inv_supported(const mc_desc* d);
 size_t mc_conv_dgrad_inv_workspace_bytes(const mc_desc* d);
