@@ -309,6 +309,44 @@ def test_c_abi_forward_and_wgrad_with_a_bare_map(shape, interp):
     H.assert_close(gb, want_g[2], 2e-2, "mc_conv_wgrad bias")
 
 
+@pytest.mark.parametrize("interp", [0, 1])
+def test_bf16_nchw_tensors_take_the_tensor_core_path_and_keep_their_layout(interp):
+    """bfloat16 tensors in the reference's NCHW layout are rerouted through channels-last copies;
+    results come back in NCHW and match the oracle (2e-2)."""
+    from mappedconvolutions_b200 import ops, _lib
+    B, Cin, Cout, IH, IW, OH, OW, K = 2, 64, 128, 12, 20, 16, 32, 5
+    g = torch.Generator().manual_seed(77 + interp)
+    bf = lambda t: t.to(torch.bfloat16)
+    x = bf(torch.randn(B, Cin, IH, IW, generator=g))
+    gy = bf(torch.randn(B, Cout, OH, OW, generator=g))
+    w = bf(torch.randn(Cout, Cin, K, generator=g))
+    b = bf(torch.randn(Cout, generator=g))
+    m = (torch.rand(OH, OW, K, 2, generator=g) * torch.tensor([IW + 1.0, IH + 1.0]) - 1.0).contiguous()
+    want_y = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, interp)
+    want_g = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, interp)
+    n0 = _lib.lib().mc_kernel_launch_count()
+    y = ops.mapped_conv_forward(x.cuda(), m.cuda(), w.cuda(), b.cuda(), K, interp)
+    got = ops.mapped_conv_backward(gy.cuda(), m.cuda(), x.cuda(), w.cuda(), b.cuda(), K, interp)
+    assert _device_status() == 0
+    assert y.is_contiguous() and got[0].is_contiguous()
+    H.assert_close(y.float(), want_y, 2e-2, "nchw y")
+    H.assert_close(got[0].float(), want_g[0], 2e-2, "nchw gx")
+    H.assert_close(got[1].float(), want_g[1], 2e-2, "nchw gw")
+    H.assert_close(got[2].float(), want_g[2], 2e-2, "nchw gb")
+    # transposed layer, same tensors with the roles of the two images exchanged
+    wt = bf(torch.randn(Cout, Cin, K, generator=g))      # (C_in of the layer = Cout here, C_out = Cin)
+    bt = bf(torch.randn(Cin, generator=g))
+    want_t = oracle.mapped_transposed_conv_forward(gy.float(), m, wt.float(), bt.float(), IH, IW, K, interp)
+    yt = ops.mapped_transposed_conv_forward(gy.cuda(), m.cuda(), wt.cuda(), bt.cuda(), IH, IW, K, interp)
+    assert yt.is_contiguous()
+    H.assert_close(yt.float(), want_t, 2e-2, "nchw tconv y")
+    want_tg = oracle.mapped_transposed_conv_backward(x.float(), m, gy.float(), wt.float(), bt.float(), K, interp)
+    gt = ops.mapped_transposed_conv_backward(x.cuda(), m.cuda(), gy.cuda(), wt.cuda(), bt.cuda(), K, interp)
+    assert gt[0].is_contiguous()
+    for a, r, what in zip(gt, want_tg, ("gx", "gw", "gb")):
+        H.assert_close(a.float(), r, 2e-2, "nchw tconv " + what)
+
+
 def test_bias_grad_entry_point():
     """mc_bias_grad against a float64 sum, both layouts and all dtypes (1e-5 / 2e-2)."""
     from mappedconvolutions_b200 import _lib
