@@ -1271,7 +1271,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
             int img;
             bool valid;
             tile_pixel(a.t, tile, r, gp, img, p, valid);
-            v[i] = valid ? ldg16(a.gy + gp * a.ncol + co0 + nb * 64 + lg * 8)
+            v[i] = valid ? ldcg16(a.gy + gp * a.ncol + co0 + nb * 64 + lg * 8)
                          : make_uint4(0, 0, 0, 0);
           }
 #pragma unroll
@@ -1295,7 +1295,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_wgrad_tc_kernel(const Gemm
           tile_pixel(a.t, tile, r, gp, img, p, valid);
 #pragma unroll
           for (int nb = 0; nb < NOUT / 64; ++nb) {
-            const uint4 v = valid ? ldg16(a.gy + gp * a.ncol + co0 + nb * 64 + lg * 8)
+            const uint4 v = valid ? ldcg16(a.gy + gp * a.ncol + co0 + nb * 64 + lg * 8)
                                   : make_uint4(0, 0, 0, 0);
             // N > 64: consecutive 64-channel blocks are separate swizzle atoms, STAGE_BYTES apart
             sts16(sbase + nb * STAGE_BYTES + r * 128 + ((lg ^ (r & 7)) << 4), v);

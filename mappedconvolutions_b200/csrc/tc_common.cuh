@@ -183,6 +183,11 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
 __device__ __forceinline__ uint4 ldg16(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
 }
+// Streaming 16-byte load that stays out of L1 (ld.global.cg): for data that is read once and would
+// only evict the source rows the producers keep re-reading from the small L1.
+__device__ __forceinline__ uint4 ldcg16(const void* p) {
+  return __ldcg(reinterpret_cast<const uint4*>(p));
+}
 __device__ __forceinline__ void sts16(uint32_t saddr, const uint4& v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w)
