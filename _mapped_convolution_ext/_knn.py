@@ -1,1 +1,3 @@
-from mappedconvolutions_b200.ops import knn_forward  # noqa: F401
+from mappedconvolutions_b200.host import impl as _impl
+
+knn_forward = _impl.knn_forward

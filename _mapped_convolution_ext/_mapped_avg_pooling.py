@@ -1,1 +1,4 @@
-from mappedconvolutions_b200.ops import mapped_avg_pool, mapped_avg_unpool  # noqa: F401
+from mappedconvolutions_b200.host import impl as _impl
+
+mapped_avg_pool = _impl.mapped_avg_pool
+mapped_avg_unpool = _impl.mapped_avg_unpool

@@ -1,1 +1,4 @@
-from mappedconvolutions_b200.ops import mapped_conv_forward, mapped_conv_backward  # noqa: F401
+from mappedconvolutions_b200.host import impl as _impl
+
+mapped_conv_forward = _impl.mapped_conv_forward
+mapped_conv_backward = _impl.mapped_conv_backward

@@ -1,1 +1,4 @@
-from mappedconvolutions_b200.ops import mapped_max_pool, mapped_max_unpool  # noqa: F401
+from mappedconvolutions_b200.host import impl as _impl
+
+mapped_max_pool = _impl.mapped_max_pool
+mapped_max_unpool = _impl.mapped_max_unpool

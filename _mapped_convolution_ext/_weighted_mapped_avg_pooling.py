@@ -1,1 +1,4 @@
-from mappedconvolutions_b200.ops import weighted_mapped_avg_pool, weighted_mapped_avg_unpool  # noqa: F401
+from mappedconvolutions_b200.host import impl as _impl
+
+weighted_mapped_avg_pool = _impl.weighted_mapped_avg_pool
+weighted_mapped_avg_unpool = _impl.weighted_mapped_avg_unpool

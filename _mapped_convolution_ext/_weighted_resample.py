@@ -1,1 +1,4 @@
-from mappedconvolutions_b200.ops import weighted_resample_to_map, weighted_resample_from_map  # noqa: F401
+from mappedconvolutions_b200.host import impl as _impl
+
+weighted_resample_to_map = _impl.weighted_resample_to_map
+weighted_resample_from_map = _impl.weighted_resample_from_map

@@ -61,5 +61,45 @@ def build(force=False, verbose=False):
     return LIB
 
 
+TORCH_EXT_SRC = os.path.join(PKG, "csrc_torch", "mc_torch_ext.cpp")
+TORCH_EXT_NAME = "_mc_torch_ext"
+
+
+def torch_ext_path():
+    import sysconfig
+    return os.path.join(PKG, TORCH_EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_torch_ext(force=False):
+    """Compiles the PyTorch C++ extension (the reference's pybind surface on top of the C ABI)
+    in-tree with the host compiler; it links against libmc_b200.so through an $ORIGIN rpath."""
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    out = torch_ext_path()
+    hdrs = glob.glob(os.path.join(ROOT, "include", "*.h"))
+    if not force and not _newer(out, [TORCH_EXT_SRC, LIB] + hdrs):
+        return out
+    cxx = os.environ.get("CXX", "g++")
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(NVCC)), "include")
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wno-deprecated-declarations",
+           "-DTORCH_EXTENSION_NAME=" + TORCH_EXT_NAME, "-DTORCH_API_INCLUDE_EXTENSION_H",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch.compiled_with_cxx11_abi())]
+    for inc in ce.include_paths() + [sysconfig.get_paths()["include"], cuda_inc,
+                                     os.path.join(ROOT, "include")]:
+        cmd += ["-I", inc]
+    cmd += [TORCH_EXT_SRC, "-o", out]
+    for lp in ce.library_paths():
+        cmd += ["-L", lp, "-Wl,-rpath," + lp]
+    cmd += ["-lc10", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10_cuda",
+            "-L", LIBDIR, "-lmc_b200", "-Wl,-rpath,$ORIGIN/lib"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("compiling the torch extension failed")
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_torch_ext(force="--force" in sys.argv))

@@ -1,0 +1,588 @@
+// PyTorch C++ extension: the operator surface of the reference's pybind modules
+// (_mapped_convolution_ext.<module>, package/ext_modules/src/*.cpp of the reference) bound to the
+// sm_100a library through its C ABI (include/mc_b200.h).
+//
+// Function names, argument order and return values follow the reference's functions
+// (include/nn/layers/*.h, include/util/layers/knn_layer.h); each binding cites the one it mirrors.
+// As in the reference, outputs are freshly allocated and returned, and inputs must be contiguous
+// and on one device.  Differences: tensors must be CUDA tensors (there is no CPU path), bfloat16
+// activations are accepted (with a float32 sample map), and a 4-D activation may be channels_last,
+// in which case the outputs are channels_last too.
+//
+// mappedconvolutions_b200/ops.py is the same host logic on ctypes; the tests use it to reach the
+// C ABI without a compiler, and check the two against each other.
+#include <torch/extension.h>
+
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+
+#include <list>
+#include <tuple>
+#include <vector>
+
+#include "mc_b200.h"
+
+namespace {
+
+using torch::Tensor;
+using OptTensor = c10::optional<Tensor>;
+
+void check(int rc) {
+  TORCH_CHECK(rc == 0, "mc_b200: ", mc_strerror(rc), " (code ", rc, ")");
+}
+
+void* cur_stream() { return (void*)c10::cuda::getCurrentCUDAStream().stream(); }
+
+c10::Device need_cuda(std::initializer_list<const Tensor*> ts) {
+  c10::optional<c10::Device> dev;
+  for (const Tensor* t : ts) {
+    if (!t || !t->defined()) continue;
+    TORCH_CHECK(t->is_cuda(), "mapped convolution ops are CUDA only: got a CPU tensor "
+                              "(this build has no CPU path)");
+    if (!dev) dev = t->device();
+    else TORCH_CHECK(t->device() == *dev, "all tensors must be on the same device");
+  }
+  TORCH_CHECK(dev.has_value(), "no tensor given");
+  return *dev;
+}
+
+const Tensor* opt(const OptTensor& t) { return t.has_value() ? &*t : nullptr; }
+const void* ptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+int layout_of(const Tensor& x) {
+  if (x.is_contiguous()) return MC_NCHW;
+  if (x.dim() == 4 && x.is_contiguous(at::MemoryFormat::ChannelsLast)) return MC_NHWC;
+  TORCH_CHECK(false, "input must be contiguous");
+}
+
+Tensor as_layout(const Tensor& t, int layout) {
+  return layout == MC_NHWC ? t.contiguous(at::MemoryFormat::ChannelsLast) : t.contiguous();
+}
+
+Tensor empty_in(at::IntArrayRef shape, const Tensor& like, int layout,
+                c10::optional<at::ScalarType> dtype = c10::nullopt) {
+  auto o = like.options().dtype(dtype.value_or(like.scalar_type()));
+  return at::empty(shape, o, layout == MC_NHWC ? at::MemoryFormat::ChannelsLast
+                                               : at::MemoryFormat::Contiguous);
+}
+
+void check_map(const Tensor& x, const Tensor& map, const OptTensor& iw) {
+  const auto want = x.scalar_type() == at::kDouble ? at::kDouble : at::kFloat;
+  if (map.scalar_type() != want) {
+    TORCH_CHECK(!(x.scalar_type() == at::kBFloat16 && map.scalar_type() == at::kBFloat16),
+                "sample map of a bfloat16 input must be float32");
+    TORCH_CHECK(false, "sample map dtype ", map.scalar_type(), " does not match input dtype ",
+                x.scalar_type());
+  }
+  TORCH_CHECK(map.is_contiguous(), "sample_map must be contiguous");
+  if (iw.has_value()) {
+    TORCH_CHECK(iw->scalar_type() == want, "interp_weights dtype must match the sample map");
+    TORCH_CHECK(iw->is_contiguous(), "interp_weights must be contiguous");
+  }
+}
+
+mc_desc make_desc(at::ScalarType dt, int layout, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                  int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int64_t interp) {
+  mc_desc d{};
+  d.B = (int32_t)B; d.C_in = (int32_t)Cin; d.C_out = (int32_t)Cout;
+  d.IH = (int32_t)IH; d.IW = (int32_t)IW; d.OH = (int32_t)OH; d.OW = (int32_t)OW;
+  d.K = (int32_t)K; d.P = (int32_t)P; d.interp = (int32_t)interp;
+  if (dt == at::kFloat) d.dtype = MC_F32;
+  else if (dt == at::kDouble) d.dtype = MC_F64;
+  else if (dt == at::kBFloat16) d.dtype = MC_BF16;
+  else TORCH_CHECK(false, "unsupported dtype ", dt, " (float32, float64, bfloat16)");
+  d.layout = layout;
+  return d;
+}
+
+int64_t n_interp(const OptTensor& iw) { return iw.has_value() ? iw->size(-1) : 0; }
+
+// Scratch buffer of at least n bytes (undefined tensor for n == 0).
+struct Scratch {
+  Tensor t;
+  void* p = nullptr;
+  size_t n = 0;
+};
+Scratch scratch(size_t n, const c10::Device& dev) {
+  Scratch s;
+  if (n == 0) return s;
+  s.t = at::empty({(int64_t)n}, at::TensorOptions().dtype(at::kByte).device(dev));
+  s.p = s.t.data_ptr();
+  s.n = n;
+  return s;
+}
+
+// ---- per-map plans ----------------------------------------------------------------------------------
+// The inverse map and the tap table depend only on the sample map tensor and the image sizes.  A
+// layer is called with the same map tensor step after step, so the last few are kept, keyed by the
+// tensor's identity and version counter (an in-place edit of the map invalidates its entry).
+struct PlanKey {
+  int kind;
+  const void* data;
+  int64_t version;
+  std::vector<int64_t> shape;
+  int IH, IW, interp, device;
+  bool operator==(const PlanKey& o) const {
+    return kind == o.kind && data == o.data && version == o.version && shape == o.shape &&
+           IH == o.IH && IW == o.IW && interp == o.interp && device == o.device;
+  }
+};
+struct PlanEntry {
+  PlanKey key;
+  c10::weak_intrusive_ptr<c10::TensorImpl> owner;
+  Tensor buf;
+};
+std::list<PlanEntry>& plan_cache() {
+  static std::list<PlanEntry> c;
+  return c;
+}
+constexpr size_t PLAN_CACHE_SIZE = 8;
+
+template <typename Build>
+Tensor cached_plan(int kind, const mc_desc& d, const Tensor& map, Build build) {
+  PlanKey key{kind, map.data_ptr(), (int64_t)map._version(), map.sizes().vec(), d.IH, d.IW, d.interp,
+              (int)map.device().index()};
+  auto& c = plan_cache();
+  for (auto it = c.begin(); it != c.end(); ++it) {
+    if (it->key == key && !it->owner.expired() &&
+        it->owner.lock().get() == map.unsafeGetTensorImpl()) {
+      if (it != c.begin()) c.splice(c.begin(), c, it);
+      return c.front().buf;
+    }
+  }
+  Tensor buf = build();
+  c.push_front(PlanEntry{key, c10::weak_intrusive_ptr<c10::TensorImpl>(map.getIntrusivePtr()), buf});
+  while (c.size() > PLAN_CACHE_SIZE) c.pop_back();
+  return buf;
+}
+
+Tensor inverse_map(const mc_desc& d, const Tensor& map) {
+  return cached_plan(0, d, map, [&]() {
+    const size_t n = mc_invmap_bytes(&d);
+    Tensor inv = at::empty({(int64_t)n}, at::TensorOptions().dtype(at::kByte).device(map.device()));
+    Scratch ws = scratch(mc_invmap_build_workspace_bytes(&d), map.device());
+    check(mc_invmap_build(&d, map.data_ptr(), inv.data_ptr(), n, ws.p, ws.n, cur_stream()));
+    return inv;
+  });
+}
+
+// Forward tap table (undefined tensor if the descriptor has no tensor-core path).
+Tensor tap_map(const mc_desc& d, const Tensor& map) {
+  const size_t n = mc_tapmap_bytes(&d);
+  if (n == 0) return Tensor();
+  return cached_plan(1, d, map, [&]() {
+    Tensor tab = at::empty({(int64_t)n}, at::TensorOptions().dtype(at::kByte).device(map.device()));
+    check(mc_tapmap_build(&d, map.data_ptr(), tab.data_ptr(), n, cur_stream()));
+    return tab;
+  });
+}
+
+void clear_plan_cache() { plan_cache().clear(); }
+
+Tensor channels_last(const Tensor& t) { return t.contiguous(at::MemoryFormat::ChannelsLast); }
+
+// bfloat16 tensors in the reference's NCHW layout: the tensor-core kernels want channels-last, and
+// two extra layout passes cost far less than the generic kernels.
+bool via_channels_last(const Tensor& input, const OptTensor& iw, mc_desc d_nhwc) {
+  if (iw.has_value() || input.scalar_type() != at::kBFloat16 || input.dim() != 4) return false;
+  if (layout_of(input) != MC_NCHW || input.is_contiguous(at::MemoryFormat::ChannelsLast)) return false;
+  d_nhwc.layout = MC_NHWC;
+  return mc_conv_fwd_workspace_bytes(&d_nhwc) > 0;
+}
+
+// ---- convolution ---------------------------------------------------------------------------------------
+
+Tensor conv_forward(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
+                    const Tensor& weight, const Tensor& bias, int64_t K, int64_t interp) {
+  const auto dev = need_cuda({&input, &sample_map, opt(iw), &weight, &bias});
+  TORCH_CHECK(input.dim() == 4 && sample_map.dim() >= 3, "input must be 4-D, the map (OH, OW, K, ..)");
+  const int64_t B = input.size(0), Cin = input.size(1), IH = input.size(2), IW = input.size(3);
+  const int64_t Cout = weight.size(0), OH = sample_map.size(0), OW = sample_map.size(1);
+  if (via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH, IW, OH,
+                                             OW, K, 0, interp)))
+    return conv_forward(channels_last(input), sample_map, c10::nullopt, weight, bias, K, interp)
+        .contiguous();
+  const int layout = layout_of(input);
+  check_map(input, sample_map, iw);
+  TORCH_CHECK(weight.is_contiguous() && bias.is_contiguous(), "weight and bias must be contiguous");
+  const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, IH, IW, OH, OW, K,
+                              n_interp(iw), interp);
+  Tensor y = empty_in({B, Cout, OH, OW}, input, layout);
+  c10::cuda::CUDAGuard guard(dev);
+  Scratch ws = scratch(mc_conv_fwd_workspace_bytes(&d), dev);
+  Tensor tab = (ws.n && !iw.has_value()) ? tap_map(d, sample_map) : Tensor();
+  if (tab.defined())  // tensor-core path with the map decoded once per map tensor
+    check(mc_conv_fwd_tap(&d, input.data_ptr(), tab.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                          y.data_ptr(), ws.p, ws.n, cur_stream()));
+  else
+    check(mc_conv_fwd(&d, input.data_ptr(), sample_map.data_ptr(), ptr(iw), weight.data_ptr(),
+                      bias.data_ptr(), y.data_ptr(), ws.p, ws.n, cur_stream()));
+  return y;
+}
+
+std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sample_map,
+                                  const OptTensor& iw, const Tensor& input, const Tensor& weight,
+                                  const Tensor& bias, int64_t K, int64_t interp,
+                                  bool need_input_grad) {
+  const auto dev = need_cuda({&grad_output_in, &sample_map, opt(iw), &input, &weight, &bias});
+  const int64_t B = input.size(0), Cin = input.size(1), IH = input.size(2), IW = input.size(3);
+  const int64_t Cout = weight.size(0), OH = sample_map.size(0), OW = sample_map.size(1);
+  if (via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH, IW, OH,
+                                             OW, K, 0, interp))) {
+    auto g = conv_backward(channels_last(grad_output_in), sample_map, c10::nullopt,
+                           channels_last(input), weight, bias, K, interp, need_input_grad);
+    if (g[0].defined()) g[0] = g[0].contiguous();
+    return g;
+  }
+  const int layout = layout_of(input);
+  const Tensor grad_output = as_layout(grad_output_in, layout);
+  check_map(input, sample_map, iw);
+  const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, IH, IW, OH, OW, K,
+                              n_interp(iw), interp);
+  const auto acc = input.scalar_type() == at::kDouble ? at::kDouble : at::kFloat;
+  Tensor gx = need_input_grad ? empty_in(input.sizes(), input, layout) : Tensor();
+  Tensor gw = at::empty(weight.sizes(), weight.options().dtype(acc));
+  Tensor gb = at::empty({Cout}, weight.options().dtype(acc));
+  c10::cuda::CUDAGuard guard(dev);
+  Tensor inv = (need_input_grad && mc_conv_dgrad_inv_supported(&d)) ? inverse_map(d, sample_map)
+                                                                     : Tensor();
+  const size_t n_dgrad = inv.defined() ? mc_conv_dgrad_inv_workspace_bytes(&d)
+                                       : mc_conv_dgrad_workspace_bytes(&d);
+  Scratch ws = scratch(std::max(n_dgrad, mc_conv_wgrad_workspace_bytes(&d)), dev);
+  if (!need_input_grad) {
+  } else if (inv.defined()) {
+    check(mc_conv_dgrad_inv(&d, grad_output.data_ptr(), inv.data_ptr(), weight.data_ptr(), nullptr,
+                            gx.data_ptr(), ws.p, ws.n, cur_stream()));
+  } else {
+    check(mc_conv_dgrad(&d, grad_output.data_ptr(), sample_map.data_ptr(), ptr(iw),
+                        weight.data_ptr(), nullptr, gx.data_ptr(), ws.p, ws.n, cur_stream()));
+  }
+  Tensor tab = iw.has_value() ? Tensor() : tap_map(d, sample_map);
+  int rc = MC_ERR_UNSUPPORTED;
+  if (tab.defined())  // weight / bias gradient on the tensor cores from the prebuilt table
+    rc = mc_conv_wgrad_tap(&d, grad_output.data_ptr(), input.data_ptr(), tab.data_ptr(),
+                           gw.data_ptr(), gb.data_ptr(), cur_stream());
+  if (rc == MC_ERR_UNSUPPORTED)  // shapes only the generic kernels take
+    rc = mc_conv_wgrad(&d, grad_output.data_ptr(), input.data_ptr(), sample_map.data_ptr(), ptr(iw),
+                       gw.data_ptr(), gb.data_ptr(), ws.p, ws.n, cur_stream());
+  check(rc);
+  return {gx, gw.to(weight.scalar_type()), gb.to(bias.scalar_type())};
+}
+
+// ---- transposed convolution ------------------------------------------------------------------------------
+
+Tensor tconv_forward(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
+                     const Tensor& weight, const Tensor& bias, int64_t OHt, int64_t OWt, int64_t K,
+                     int64_t interp) {
+  const auto dev = need_cuda({&input, &sample_map, opt(iw), &weight, &bias});
+  const int64_t B = input.size(0), Cin = input.size(1), H = input.size(2), W = input.size(3);
+  const int64_t Cout = weight.size(1);
+  // the same layer seen as a convolution: the sampled image carries C_out channels, the grid C_in
+  if (via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cout, Cin, OHt, OWt, H,
+                                             W, K, 0, interp)))
+    return tconv_forward(channels_last(input), sample_map, c10::nullopt, weight, bias, OHt, OWt, K,
+                         interp).contiguous();
+  const int layout = layout_of(input);
+  check_map(input, sample_map, iw);
+  TORCH_CHECK(weight.is_contiguous() && bias.is_contiguous(), "weight and bias must be contiguous");
+  const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, OHt, OWt, H, W, K,
+                              n_interp(iw), interp);
+  const mc_desc ds = make_desc(input.scalar_type(), layout, B, Cout, Cin, OHt, OWt, H, W, K,
+                               n_interp(iw), interp);
+  Tensor y = empty_in({B, Cout, OHt, OWt}, input, layout);
+  c10::cuda::CUDAGuard guard(dev);
+  if (!iw.has_value() && mc_conv_dgrad_inv_supported(&ds)) {
+    // its input gradient IS this forward pass: the gather-form tensor-core dgrad serves
+    Tensor inv = inverse_map(ds, sample_map);
+    Scratch ws = scratch(mc_conv_dgrad_inv_workspace_bytes(&ds), dev);
+    check(mc_conv_dgrad_inv(&ds, input.data_ptr(), inv.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                            y.data_ptr(), ws.p, ws.n, cur_stream()));
+    return y;
+  }
+  Scratch ws = scratch(mc_tconv_workspace_bytes(&d), dev);
+  check(mc_tconv_fwd(&d, input.data_ptr(), sample_map.data_ptr(), ptr(iw), weight.data_ptr(),
+                     bias.data_ptr(), y.data_ptr(), ws.p, ws.n, cur_stream()));
+  return y;
+}
+
+std::vector<Tensor> tconv_backward(const Tensor& grad_output_in, const Tensor& sample_map,
+                                   const OptTensor& iw, const Tensor& input, const Tensor& weight,
+                                   const Tensor& bias, int64_t K, int64_t interp) {
+  const auto dev = need_cuda({&grad_output_in, &sample_map, opt(iw), &input, &weight, &bias});
+  const int64_t B = input.size(0), Cin = input.size(1), H = input.size(2), W = input.size(3);
+  const int64_t Cout = weight.size(1);
+  const int64_t OHt = grad_output_in.size(2), OWt = grad_output_in.size(3);
+  if (via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cout, Cin, OHt, OWt, H,
+                                             W, K, 0, interp))) {
+    auto g = tconv_backward(channels_last(grad_output_in), sample_map, c10::nullopt,
+                            channels_last(input), weight, bias, K, interp);
+    g[0] = g[0].contiguous();
+    return g;
+  }
+  const int layout = layout_of(input);
+  const Tensor grad_output = as_layout(grad_output_in, layout);
+  check_map(input, sample_map, iw);
+  const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, OHt, OWt, H, W, K,
+                              n_interp(iw), interp);
+  const mc_desc ds = make_desc(input.scalar_type(), layout, B, Cout, Cin, OHt, OWt, H, W, K,
+                               n_interp(iw), interp);
+  const auto acc = input.scalar_type() == at::kDouble ? at::kDouble : at::kFloat;
+  Tensor gx = empty_in(input.sizes(), input, layout);
+  Tensor gw = at::empty(weight.sizes(), weight.options().dtype(acc));
+  Tensor gb = at::empty({Cout}, weight.options().dtype(acc));
+  c10::cuda::CUDAGuard guard(dev);
+  Tensor tab = iw.has_value() ? Tensor() : tap_map(ds, sample_map);
+  if (tab.defined() && mc_conv_fwd_workspace_bytes(&ds)) {
+    // tensor-core path: input gradient = forward of the equivalent convolution applied to
+    // grad_output; weight gradient = its weight gradient with the two tensors swapped
+    Scratch ws = scratch(mc_conv_fwd_workspace_bytes(&ds), dev);
+    check(mc_conv_fwd_tap(&ds, grad_output.data_ptr(), tab.data_ptr(), weight.data_ptr(), nullptr,
+                          gx.data_ptr(), ws.p, ws.n, cur_stream()));
+    int rc = mc_conv_wgrad_tap(&ds, input.data_ptr(), grad_output.data_ptr(), tab.data_ptr(),
+                               gw.data_ptr(), nullptr, cur_stream());
+    if (rc == MC_ERR_UNSUPPORTED)
+      rc = mc_conv_wgrad(&ds, input.data_ptr(), grad_output.data_ptr(), sample_map.data_ptr(),
+                         nullptr, gw.data_ptr(), nullptr, ws.p, ws.n, cur_stream());
+    check(rc);
+    const mc_desc db = make_desc(input.scalar_type(), layout, B, Cout, Cout, OHt, OWt, OHt, OWt, 1, 0,
+                                 interp);
+    check(mc_bias_grad(&db, grad_output.data_ptr(), gb.data_ptr(), cur_stream()));
+    return {gx, gw.to(weight.scalar_type()), gb.to(bias.scalar_type())};
+  }
+  Scratch ws = scratch(mc_tconv_workspace_bytes(&d), dev);
+  check(mc_tconv_dgrad(&d, grad_output.data_ptr(), sample_map.data_ptr(), ptr(iw), weight.data_ptr(),
+                       gx.data_ptr(), ws.p, ws.n, cur_stream()));
+  check(mc_tconv_wgrad(&d, grad_output.data_ptr(), input.data_ptr(), sample_map.data_ptr(), ptr(iw),
+                       gw.data_ptr(), gb.data_ptr(), ws.p, ws.n, cur_stream()));
+  return {gx, gw.to(weight.scalar_type()), gb.to(bias.scalar_type())};
+}
+
+// ---- pooling ----------------------------------------------------------------------------------------------
+
+// x lives on the image for forward, on the map grid for backward (then img gives the image size)
+mc_desc pool_desc(const Tensor& x, const Tensor& map, const OptTensor& iw, int64_t K, int64_t interp,
+                  int layout, int64_t IH = -1, int64_t IW = -1) {
+  if (IH < 0) { IH = x.size(2); IW = x.size(3); }
+  return make_desc(x.scalar_type(), layout, x.size(0), x.size(1), x.size(1), IH, IW, map.size(0),
+                   map.size(1), K, n_interp(iw), interp);
+}
+
+std::vector<Tensor> max_pool(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
+                             int64_t K, int64_t interp) {
+  const auto dev = need_cuda({&input, &sample_map, opt(iw)});
+  check_map(input, sample_map, iw);
+  const int layout = layout_of(input);
+  const mc_desc d = pool_desc(input, sample_map, iw, K, interp, layout);
+  Tensor y = empty_in({d.B, d.C_in, d.OH, d.OW}, input, layout);
+  Tensor idx = empty_in({d.B, d.C_in, d.OH, d.OW}, input, layout, at::kLong);
+  c10::cuda::CUDAGuard guard(dev);
+  check(mc_pool_max_fwd(&d, input.data_ptr(), sample_map.data_ptr(), ptr(iw), y.data_ptr(),
+                        idx.data_ptr<int64_t>(), cur_stream()));
+  return {y, idx};
+}
+
+Tensor max_unpool(const Tensor& grad_output_in, const Tensor& idx_mask, const Tensor& sample_map,
+                  const OptTensor& iw, int64_t IH, int64_t IW, int64_t K, int64_t interp) {
+  const auto dev = need_cuda({&grad_output_in, &idx_mask, &sample_map, opt(iw)});
+  const int layout = idx_mask.dim() == 4 ? layout_of(idx_mask) : MC_NCHW;
+  const Tensor grad_output = as_layout(grad_output_in, layout);
+  check_map(grad_output, sample_map, iw);
+  const mc_desc d = pool_desc(grad_output, sample_map, iw, K, interp, layout, IH, IW);
+  Tensor gx = empty_in({d.B, d.C_in, IH, IW}, grad_output, layout);
+  c10::cuda::CUDAGuard guard(dev);
+  Scratch ws = scratch(mc_scatter_workspace_bytes(&d), dev);
+  check(mc_pool_max_bwd(&d, grad_output.data_ptr(), idx_mask.data_ptr<int64_t>(),
+                        sample_map.data_ptr(), ptr(iw), gx.data_ptr(), ws.p, ws.n, cur_stream()));
+  return gx;
+}
+
+Tensor avg_pool(const Tensor& input, const Tensor& sample_map, const OptTensor& iw, int64_t K,
+                int64_t interp) {
+  const auto dev = need_cuda({&input, &sample_map, opt(iw)});
+  check_map(input, sample_map, iw);
+  const int layout = layout_of(input);
+  const mc_desc d = pool_desc(input, sample_map, iw, K, interp, layout);
+  Tensor y = empty_in({d.B, d.C_in, d.OH, d.OW}, input, layout);
+  c10::cuda::CUDAGuard guard(dev);
+  check(mc_pool_avg_fwd(&d, input.data_ptr(), sample_map.data_ptr(), ptr(iw), y.data_ptr(),
+                        cur_stream()));
+  return y;
+}
+
+Tensor avg_unpool(const Tensor& grad_output, const Tensor& sample_map, const OptTensor& iw,
+                  int64_t IH, int64_t IW, int64_t K, int64_t interp) {
+  const auto dev = need_cuda({&grad_output, &sample_map, opt(iw)});
+  const int layout = layout_of(grad_output);
+  check_map(grad_output, sample_map, iw);
+  const mc_desc d = pool_desc(grad_output, sample_map, iw, K, interp, layout, IH, IW);
+  Tensor gx = empty_in({d.B, d.C_in, IH, IW}, grad_output, layout);
+  c10::cuda::CUDAGuard guard(dev);
+  int rc = MC_ERR_UNSUPPORTED;
+  if (!iw.has_value() && mc_invmap_bytes(&d) > 0) {
+    // gather through the inverse map (built once per map tensor): no atomics
+    Tensor inv = inverse_map(d, sample_map);
+    rc = mc_pool_avg_bwd_inv(&d, grad_output.data_ptr(), inv.data_ptr(), gx.data_ptr(), cur_stream());
+  }
+  if (rc == MC_ERR_UNSUPPORTED) {
+    Scratch ws = scratch(mc_scatter_workspace_bytes(&d), dev);
+    rc = mc_pool_avg_bwd(&d, grad_output.data_ptr(), sample_map.data_ptr(), ptr(iw), gx.data_ptr(),
+                         ws.p, ws.n, cur_stream());
+  }
+  check(rc);
+  return gx;
+}
+
+// ---- resample ---------------------------------------------------------------------------------------------
+
+Tensor resample_to(const Tensor& input, const Tensor& sample_map, const OptTensor& iw, int64_t OH,
+                   int64_t OW, int64_t interp) {
+  const auto dev = need_cuda({&input, &sample_map, opt(iw)});
+  const int layout = layout_of(input);
+  check_map(input, sample_map, iw);
+  const int64_t B = input.size(0), C = input.size(1), H = input.size(2), W = input.size(3);
+  const mc_desc d = make_desc(input.scalar_type(), layout, B, C, C, OH, OW, H, W, 1, n_interp(iw),
+                              interp);
+  Tensor y = empty_in({B, C, OH, OW}, input, layout);
+  c10::cuda::CUDAGuard guard(dev);
+  int rc = MC_ERR_UNSUPPORTED;
+  if (!iw.has_value() && mc_invmap_bytes(&d) > 0) {
+    Tensor inv = inverse_map(d, sample_map);
+    rc = mc_resample_scatter_inv(&d, input.data_ptr(), inv.data_ptr(), y.data_ptr(), cur_stream());
+  }
+  if (rc == MC_ERR_UNSUPPORTED) {
+    Scratch ws = scratch(mc_scatter_workspace_bytes(&d), dev);
+    rc = mc_resample_scatter(&d, input.data_ptr(), sample_map.data_ptr(), ptr(iw), y.data_ptr(), ws.p,
+                             ws.n, cur_stream());
+  }
+  check(rc);
+  return y;
+}
+
+Tensor resample_from(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
+                     int64_t interp) {
+  const auto dev = need_cuda({&input, &sample_map, opt(iw)});
+  const int layout = layout_of(input);
+  check_map(input, sample_map, iw);
+  const int64_t B = input.size(0), C = input.size(1), H = input.size(2), W = input.size(3);
+  const int64_t OH = sample_map.size(0), OW = sample_map.size(1);
+  const mc_desc d = make_desc(input.scalar_type(), layout, B, C, C, H, W, OH, OW, 1, n_interp(iw),
+                              interp);
+  Tensor y = empty_in({B, C, OH, OW}, input, layout);
+  c10::cuda::CUDAGuard guard(dev);
+  check(mc_resample_gather(&d, input.data_ptr(), sample_map.data_ptr(), ptr(iw), y.data_ptr(),
+                           cur_stream()));
+  return y;
+}
+
+// ---- knn ----------------------------------------------------------------------------------------------------
+
+std::vector<Tensor> knn_forward(const Tensor& ref, const Tensor& query, int64_t k) {
+  const auto dev = need_cuda({&ref, &query});
+  TORCH_CHECK(ref.is_contiguous() && query.is_contiguous(), "ref and query must be contiguous");
+  TORCH_CHECK(ref.scalar_type() == at::kFloat && query.scalar_type() == at::kFloat,
+              "knn works on float32 points");
+  const int64_t B = ref.size(0), D = ref.size(1), M = ref.size(2), N = query.size(2);
+  Tensor idx = at::empty({B, k, N}, ref.options().dtype(at::kLong));
+  Tensor dist = at::empty({B, k, N}, ref.options());
+  c10::cuda::CUDAGuard guard(dev);
+  check(mc_knn(ref.data_ptr<float>(), query.data_ptr<float>(), (int32_t)B, (int32_t)D, (int32_t)M,
+               (int32_t)N, (int32_t)k, idx.data_ptr<int64_t>(), dist.data_ptr<float>(), cur_stream()));
+  return {idx, dist};
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  namespace py = pybind11;
+  m.doc() = "mapped convolution ops on the sm_100a C-ABI library (reference pybind surface)";
+  // MappedConvForward / Backward, include/nn/layers/mapped_convolution_layer.h:64-88, :90-135
+  m.def("mapped_conv_forward",
+        [](const Tensor& x, const Tensor& map, const Tensor& w, const Tensor& b, int64_t k, int64_t i) {
+          return conv_forward(x, map, c10::nullopt, w, b, k, i);
+        });
+  m.def("mapped_conv_backward",
+        [](const Tensor& gy, const Tensor& map, const Tensor& x, const Tensor& w, const Tensor& b,
+           int64_t k, int64_t i, bool need_input_grad) {
+          return conv_backward(gy, map, c10::nullopt, x, w, b, k, i, need_input_grad);
+        },
+        py::arg("grad_output"), py::arg("sample_map"), py::arg("input"), py::arg("weight"),
+        py::arg("bias"), py::arg("kernel_size"), py::arg("interpolation"),
+        py::arg("need_input_grad") = true);
+  // include/nn/layers/weighted_mapped_convolution_layer.h:65-93, :95-150
+  m.def("weighted_mapped_conv_forward",
+        [](const Tensor& x, const Tensor& map, const Tensor& iw, const Tensor& w, const Tensor& b,
+           int64_t k, int64_t i) { return conv_forward(x, map, iw, w, b, k, i); });
+  m.def("weighted_mapped_conv_backward",
+        [](const Tensor& gy, const Tensor& map, const Tensor& iw, const Tensor& x, const Tensor& w,
+           const Tensor& b, int64_t k, int64_t i) {
+          return conv_backward(gy, map, iw, x, w, b, k, i, true);
+        });
+  // include/nn/layers/mapped_transposed_convolution_layer.h:64-92, :94-143
+  m.def("mapped_transposed_conv_forward",
+        [](const Tensor& x, const Tensor& map, const Tensor& w, const Tensor& b, int64_t oh,
+           int64_t ow, int64_t k, int64_t i) {
+          return tconv_forward(x, map, c10::nullopt, w, b, oh, ow, k, i);
+        });
+  m.def("mapped_transposed_conv_backward",
+        [](const Tensor& gy, const Tensor& map, const Tensor& x, const Tensor& w, const Tensor& b,
+           int64_t k, int64_t i) { return tconv_backward(gy, map, c10::nullopt, x, w, b, k, i); });
+  // include/nn/layers/weighted_mapped_transposed_convolution_layer.h:66-98, :100-155
+  m.def("weighted_mapped_transposed_conv_forward",
+        [](const Tensor& x, const Tensor& map, const Tensor& iw, const Tensor& w, const Tensor& b,
+           int64_t oh, int64_t ow, int64_t k, int64_t i) {
+          return tconv_forward(x, map, iw, w, b, oh, ow, k, i);
+        });
+  m.def("weighted_mapped_transposed_conv_backward",
+        [](const Tensor& gy, const Tensor& map, const Tensor& iw, const Tensor& x, const Tensor& w,
+           const Tensor& b, int64_t k, int64_t i) { return tconv_backward(gy, map, iw, x, w, b, k, i); });
+  // include/nn/layers/mapped_max_pooling_layer.h:46-71, :73-98 and the weighted variants
+  m.def("mapped_max_pool", [](const Tensor& x, const Tensor& map, int64_t k, int64_t i) {
+    return max_pool(x, map, c10::nullopt, k, i);
+  });
+  m.def("mapped_max_unpool", [](const Tensor& gy, const Tensor& idx, const Tensor& map, int64_t ih,
+                                int64_t iw_, int64_t k, int64_t i) {
+    return max_unpool(gy, idx, map, c10::nullopt, ih, iw_, k, i);
+  });
+  m.def("weighted_mapped_max_pool",
+        [](const Tensor& x, const Tensor& map, const Tensor& iw, int64_t k, int64_t i) {
+          return max_pool(x, map, iw, k, i);
+        });
+  m.def("weighted_mapped_max_unpool",
+        [](const Tensor& gy, const Tensor& idx, const Tensor& map, const Tensor& iw, int64_t ih,
+           int64_t iw_, int64_t k, int64_t i) { return max_unpool(gy, idx, map, iw, ih, iw_, k, i); });
+  // include/nn/layers/mapped_avg_pooling_layer.h:42-64, :66-88 and the weighted variants
+  m.def("mapped_avg_pool", [](const Tensor& x, const Tensor& map, int64_t k, int64_t i) {
+    return avg_pool(x, map, c10::nullopt, k, i);
+  });
+  m.def("mapped_avg_unpool", [](const Tensor& gy, const Tensor& map, int64_t ih, int64_t iw_,
+                                int64_t k, int64_t i) {
+    return avg_unpool(gy, map, c10::nullopt, ih, iw_, k, i);
+  });
+  m.def("weighted_mapped_avg_pool",
+        [](const Tensor& x, const Tensor& map, const Tensor& iw, int64_t k, int64_t i) {
+          return avg_pool(x, map, iw, k, i);
+        });
+  m.def("weighted_mapped_avg_unpool",
+        [](const Tensor& gy, const Tensor& map, const Tensor& iw, int64_t ih, int64_t iw_, int64_t k,
+           int64_t i) { return avg_unpool(gy, map, iw, ih, iw_, k, i); });
+  // ResampleToMap (scatter) / ResampleFromMap (gather), include/nn/layers/resample_layer.h:38-80,
+  // and include/nn/layers/weighted_resample_layer.h:49-103
+  m.def("resample_to_map", [](const Tensor& x, const Tensor& map, int64_t oh, int64_t ow, int64_t i) {
+    return resample_to(x, map, c10::nullopt, oh, ow, i);
+  });
+  m.def("resample_from_map", [](const Tensor& x, const Tensor& map, int64_t i) {
+    return resample_from(x, map, c10::nullopt, i);
+  });
+  m.def("weighted_resample_to_map", [](const Tensor& x, const Tensor& map, const Tensor& iw,
+                                       int64_t oh, int64_t ow, int64_t i) {
+    return resample_to(x, map, iw, oh, ow, i);
+  });
+  m.def("weighted_resample_from_map",
+        [](const Tensor& x, const Tensor& map, const Tensor& iw, int64_t i) {
+          return resample_from(x, map, iw, i);
+        });
+  // KNNForward, include/util/layers/knn_layer.h:25-35 -> [idx (B,k,N) int64 1-based, dist]
+  m.def("knn_forward", &knn_forward);
+  m.def("clear_plan_cache", &clear_plan_cache);
+  m.def("abi_version", []() { return mc_abi_version(); });
+}

@@ -7,7 +7,7 @@ Resample (scatter) <-> Unresample (gather).
 import torch
 from torch.autograd import Function
 
-from .. import ops
+from ..host import impl as ops
 
 
 class MappedConvFn(Function):

@@ -1,4 +1,4 @@
-from .. import ops
+from ..host import impl as ops
 
 
 def knn(ref, query, k):

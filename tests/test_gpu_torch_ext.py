@@ -1,0 +1,108 @@
+"""The compiled PyTorch C++ extension (csrc_torch/mc_torch_ext.cpp: the reference's pybind surface
+on top of the C ABI) against its ctypes twin ops.py: same kernels, so outputs are identical bit for
+bit wherever no atomics are involved, and within the float tolerances elsewhere."""
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from mappedconvolutions_b200 import host
+    assert host.COMPILED, "extension not built: python -m mappedconvolutions_b200.build"
+    return host.impl
+
+
+def _cl(t):
+    return t.contiguous(memory_format=torch.channels_last)
+
+
+def _case(dtype, B, Cin, Cout, IH, IW, OH, OW, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    c = lambda t: t.to(dtype).cuda()
+    x, gy = c(torch.randn(B, Cin, IH, IW, generator=g)), c(torch.randn(B, Cout, OH, OW, generator=g))
+    w, b = c(torch.randn(Cout, Cin, K, generator=g)), c(torch.randn(Cout, generator=g))
+    m = (torch.rand(OH, OW, K, 2, generator=g) * torch.tensor([IW + 1.0, IH + 1.0]) - 1.0)
+    m = m.to(torch.float64 if dtype == torch.float64 else torch.float32).cuda().contiguous()
+    return x, gy, w, b, m
+
+
+@pytest.mark.parametrize("dtype,layout,shape", [
+    (torch.float32, "nchw", (2, 5, 7, 9, 11, 8, 10, 4)),
+    (torch.float64, "nchw", (1, 3, 4, 6, 7, 5, 6, 3)),
+    (torch.float32, "nhwc", (2, 8, 8, 9, 11, 8, 10, 4)),
+    (torch.bfloat16, "nhwc", (2, 64, 128, 12, 20, 16, 32, 5)),   # tensor cores, plans cached
+    (torch.bfloat16, "nchw", (2, 64, 64, 12, 20, 16, 32, 5)),    # rerouted through channels-last
+])
+@pytest.mark.parametrize("interp", [0, 1])
+def test_conv_and_transposed_conv_match_the_ctypes_twin(ext, dtype, layout, shape, interp):
+    from mappedconvolutions_b200 import ops
+    B, Cin, Cout, IH, IW, OH, OW, K = shape
+    x, gy, w, b, m = _case(dtype, *shape, seed=sum(shape) + interp)
+    if layout == "nhwc":
+        x, gy = _cl(x), _cl(gy)
+    tol = H.TOL[dtype]
+    for _ in range(2):  # the second round runs on cached plans
+        y0, y1 = ops.mapped_conv_forward(x, m, w, b, K, interp), ext.mapped_conv_forward(x, m, w, b, K, interp)
+        assert torch.equal(y0, y1) and y0.stride() == y1.stride()
+        g0 = ops.mapped_conv_backward(gy, m, x, w, b, K, interp)
+        g1 = ext.mapped_conv_backward(gy, m, x, w, b, K, interp)
+        for a, c in zip(g0, g1):
+            assert a.dtype == c.dtype and a.shape == c.shape
+            H.assert_close(c.float(), a.float(), tol, "conv backward")
+    assert ext.mapped_conv_backward(gy, m, x, w, b, K, interp, False)[0] is None
+    # transposed layer: x plays grad_output's role
+    wt = torch.randn(Cout, Cin, K, device="cuda").to(dtype)
+    bt = torch.randn(Cin, device="cuda").to(dtype)
+    t0 = ops.mapped_transposed_conv_forward(gy, m, wt, bt, IH, IW, K, interp)
+    t1 = ext.mapped_transposed_conv_forward(gy, m, wt, bt, IH, IW, K, interp)
+    H.assert_close(t1.float(), t0.float(), tol, "tconv forward")
+    b0 = ops.mapped_transposed_conv_backward(x, m, gy, wt, bt, K, interp)
+    b1 = ext.mapped_transposed_conv_backward(x, m, gy, wt, bt, K, interp)
+    for a, c in zip(b0, b1):
+        H.assert_close(c.float(), a.float(), tol, "tconv backward")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+def test_pool_resample_knn_match_the_ctypes_twin(ext, dtype, layout):
+    from mappedconvolutions_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    B, C, IH, IW, OH, OW, K = 2, 8, 10, 14, 6, 9, 7
+    x = torch.randn(B, C, IH, IW, generator=g).to(dtype).cuda()
+    gy = torch.randn(B, C, OH, OW, generator=g).to(dtype).cuda()
+    if layout == "nhwc":
+        x, gy = _cl(x), _cl(gy)
+    m = (torch.rand(OH, OW, K, 2, generator=g) * torch.tensor([IW - 1.0, IH - 1.0])).cuda().contiguous()
+    tol = H.TOL[dtype]
+    for interp in (0, 1):
+        y0, i0 = ops.mapped_max_pool(x, m, K, interp)
+        y1, i1 = ext.mapped_max_pool(x, m, K, interp)
+        assert torch.equal(y0, y1) and torch.equal(i0, i1)
+        assert torch.equal(ops.mapped_avg_pool(x, m, K, interp), ext.mapped_avg_pool(x, m, K, interp))
+        H.assert_close(ext.mapped_max_unpool(gy, i1, m, IH, IW, K, interp).float(),
+                       ops.mapped_max_unpool(gy, i0, m, IH, IW, K, interp).float(), tol, "max unpool")
+        H.assert_close(ext.mapped_avg_unpool(gy, m, IH, IW, K, interp).float(),
+                       ops.mapped_avg_unpool(gy, m, IH, IW, K, interp).float(), tol, "avg unpool")
+        m1 = m[:, :, :1, :].squeeze(2).contiguous()          # (OH, OW, 2) resample map
+        assert torch.equal(ops.resample_from_map(x, m1, interp), ext.resample_from_map(x, m1, interp))
+        H.assert_close(ext.resample_to_map(gy, m1, IH, IW, interp).float(),
+                       ops.resample_to_map(gy, m1, IH, IW, interp).float(), tol, "resample_to_map")
+    if dtype == torch.float32 and layout == "nchw":
+        p = torch.randn(1, 3, 500, generator=g).cuda()
+        a, c = ops.knn_forward(p, p, 5), ext.knn_forward(p, p, 5)
+        assert torch.equal(a[0], c[0]) and torch.equal(a[1], c[1])
+
+
+def test_errors_are_raised_like_in_the_ctypes_twin(ext):
+    x = torch.zeros(1, 4, 4, 4)
+    m = torch.zeros(4, 4, 1, 2)
+    with pytest.raises(RuntimeError, match="CUDA only"):
+        ext.mapped_avg_pool(x, m, 1, 0)
+    with pytest.raises(RuntimeError, match="sample map"):
+        ext.mapped_avg_pool(x.cuda(), m.double().cuda(), 1, 0)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        ext.mapped_avg_pool(x.cuda().transpose(2, 3), m.cuda(), 1, 0)

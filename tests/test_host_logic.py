@@ -88,3 +88,17 @@ def test_product_does_not_import_the_oracle():
                 if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                     src = open(os.path.join(dp, f)).read()
                     assert "oracle" not in src, os.path.join(dp, f)
+
+
+def test_compiled_extension_carries_the_reference_surface():
+    """The PyTorch C++ extension is built in-tree and exports every op function of its ctypes twin."""
+    import inspect
+    from mappedconvolutions_b200 import build, host, ops
+    build.build_torch_ext()
+    import importlib
+    importlib.reload(host)
+    assert host.COMPILED
+    public = [n for n, f in inspect.getmembers(ops, inspect.isfunction)
+              if not n.startswith("_") and f.__module__ == ops.__name__ and n != "clear_inverse_map_cache"]
+    assert len(public) >= 21 and all(hasattr(host.impl, n) for n in public)
+    assert host.impl.abi_version() == 1
