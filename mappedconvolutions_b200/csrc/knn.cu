@@ -94,10 +94,23 @@ template <int DT>
 static void knn_launch_big_k(const float* ref, const float* query, int B, int M, int N, int k,
                              int64_t* idx, float* dist, cudaStream_t st);
 
-// D <= 4: reference points are staged as one float4 each, so that a pair costs one 16-byte
-// broadcast load instead of D 4-byte ones (the shared-memory pipe, not the FMA pipe, was the limit).
+// D <= 4: reference points are staged per coordinate and visited two at a time with packed
+// fp32 arithmetic (fma.rn.f32x2): difference and square-accumulate of a PAIR of references cost
+// one instruction each per dimension.  Every lane of a packed operation is the same correctly
+// rounded operation as its scalar form (r - q as fma(r, 1, -q), then s = fma(t, t, s) from 0), so
+// distances - and with them the order of near ties - are bit-identical to the scalar kernel.
 constexpr int KNN2_THREADS = 256;
 constexpr int KNN2_TILE = 1024;
+
+__device__ __forceinline__ float2 fma2(const float2& a, const float2& b, const float2& c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<const unsigned long long&>(a)),
+        "l"(reinterpret_cast<const unsigned long long&>(b)),
+        "l"(reinterpret_cast<const unsigned long long&>(c)));
+  return d;
+}
 
 template <int DT, int KMAX>
 __global__ void __launch_bounds__(KNN2_THREADS) knn_small_d_kernel(const float* __restrict__ ref,
@@ -105,42 +118,49 @@ __global__ void __launch_bounds__(KNN2_THREADS) knn_small_d_kernel(const float* 
                                                                    int M, int N, int k,
                                                                    int64_t* __restrict__ idx,
                                                                    float* __restrict__ dist) {
-  __shared__ float4 tile[KNN2_TILE];
+  __shared__ __align__(16) float tile[DT][KNN2_TILE];
   const int b = blockIdx.y;
   const float* rb = ref + (long)b * DT * M;
   const float* qb = query + (long)b * DT * N;
   const int n = blockIdx.x * KNN2_THREADS + threadIdx.x;
   const bool live = n < N;
-  float q[4] = {0.f, 0.f, 0.f, 0.f};
+  float2 nq[DT];  // (-q_i, -q_i)
 #pragma unroll
-  for (int i = 0; i < DT; ++i)
-    if (live) q[i] = qb[(long)i * N + n];
+  for (int i = 0; i < DT; ++i) {
+    const float v = live ? qb[(long)i * N + n] : 0.f;
+    nq[i] = make_float2(-v, -v);
+  }
+  const float2 one = make_float2(1.f, 1.f), zero = make_float2(0.f, 0.f);
   TopK<KMAX> top;
   top.init();
   for (int m0 = 0; m0 < M; m0 += KNN2_TILE) {
     const int cnt = min(KNN2_TILE, M - m0);
+    const int cnt2 = (cnt + 3) & ~3;  // the tail is padded with points at infinity
     __syncthreads();
-    for (int j = threadIdx.x; j < cnt; j += KNN2_THREADS) {
-      float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-      r.x = rb[m0 + j];
-      if (DT > 1) r.y = rb[(long)M + m0 + j];
-      if (DT > 2) r.z = rb[2L * M + m0 + j];
-      if (DT > 3) r.w = rb[3L * M + m0 + j];
-      tile[j] = r;
+    for (int j = threadIdx.x; j < cnt2; j += KNN2_THREADS) {
+#pragma unroll
+      for (int i = 0; i < DT; ++i) tile[i][j] = j < cnt ? rb[(long)i * M + m0 + j] : INFINITY;
     }
     __syncthreads();
     if (live) {
-#pragma unroll 8
-      for (int j = 0; j < cnt; ++j) {
-        const float4 r = tile[j];
-        const float rr[4] = {r.x, r.y, r.z, r.w};
-        float s = 0.f;
+#pragma unroll 2
+      for (int j = 0; j < cnt2; j += 4) {
+        float2 s0 = zero, s1 = zero;
 #pragma unroll
         for (int i = 0; i < DT; ++i) {
-          const float a = rr[i] - q[i];
-          s = fmaf(a, a, s);
+          const float4 r = *reinterpret_cast<const float4*>(&tile[i][j]);
+          const float2 t0 = fma2(make_float2(r.x, r.y), one, nq[i]);  // r - q
+          const float2 t1 = fma2(make_float2(r.z, r.w), one, nq[i]);
+          s0 = fma2(t0, t0, s0);
+          s1 = fma2(t1, t1, s1);
         }
-        if (s < top.d[KMAX - 1]) top.insert(s, m0 + j);
+        // one test for the four candidates; the list is rarely touched after the first few tiles
+        if (fminf(fminf(s0.x, s0.y), fminf(s1.x, s1.y)) < top.d[KMAX - 1]) {
+          if (s0.x < top.d[KMAX - 1]) top.insert(s0.x, m0 + j);
+          if (s0.y < top.d[KMAX - 1]) top.insert(s0.y, m0 + j + 1);
+          if (s1.x < top.d[KMAX - 1]) top.insert(s1.x, m0 + j + 2);
+          if (s1.y < top.d[KMAX - 1]) top.insert(s1.y, m0 + j + 3);
+        }
       }
     }
   }
