@@ -202,6 +202,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from mappedconvolutions_b200 import _lib, ops
+    from mappedconvolutions_b200.host import impl as host_ops  # the PyTorch C++ extension
     from mappedconvolutions_b200.dist import allreduce_gradients
     from mapped_convolution.nn import MappedConvolution
 
@@ -221,8 +222,8 @@ def run_ours(args):
     gy = gy.contiguous(memory_format=torch.channels_last)
 
     def step():
-        y = ops.mapped_conv_forward(x, m, w, b, K, 1)
-        gx, gw, gb = ops.mapped_conv_backward(gy, m, x, w, b, K, 1)
+        y = host_ops.mapped_conv_forward(x, m, w, b, K, 1)
+        gx, gw, gb = host_ops.mapped_conv_backward(gy, m, x, w, b, K, 1)
         if world > 1:
             allreduce_gradients([gw, gb])
         return y, gx, gw, gb
@@ -389,7 +390,8 @@ def run_ours(args):
 # ---------------------------------------------------------------------------------------------
 def run_secondary(args):
     import torch
-    from mappedconvolutions_b200 import _lib, ops
+    from mappedconvolutions_b200 import _lib
+    from mappedconvolutions_b200.host import impl as ops  # the PyTorch C++ extension
     from mappedconvolutions_b200.util import icosphere as ico
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
