@@ -694,6 +694,15 @@ def run_profile_case(args):
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
     B = args.batch
+    if args.profile_case == "knn":  # config 4's k-NN on the 40 962 vertices of level 6
+        from mappedconvolutions_b200.util import icosphere as ico
+        v, _ = ico.generate_icosphere(6)
+        p = torch.from_numpy(v).float().t().contiguous().unsqueeze(0).to(dev)
+        for _ in range(3):
+            ops.knn_forward(p, p, 9)
+        torch.cuda.synchronize()
+        print("profile case knn done")
+        return
     if args.profile_case == "pool":  # config 4 at a reduced batch: avg pool, max pool, avg unpool
         from mappedconvolutions_b200.util import icosphere as ico
         x = torch.randn(B, 128, 1, ico.num_vertices(7), device=dev)
@@ -728,7 +737,7 @@ def main():
     ap.add_argument("--workload", default="conv", choices=["conv", "resample", "pool", "knn", "encoder"],
                     help="conv (default) is the headline config; the others are the remaining configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", choices=["fwd", "bwd", "pool"],
+    ap.add_argument("--profile-case", choices=["fwd", "bwd", "pool", "knn"],
                     help="run three calls of the config-2 forward / backward at --batch and exit "
                          "(small case for profiler captures)")
     ap.add_argument("--batch", type=int, default=2, help="batch of --profile-case")
