@@ -32,9 +32,7 @@ int conv_tc_wgrad_tab_launch(const mc_desc*, const void*, const void*, const voi
                              cudaStream_t);
 bool invmap_supported(const mc_desc*);
 size_t invmap_off_bytes(const mc_desc*);
-size_t invmap_pix_offset(const mc_desc*);
-int scatter_inv_launch(const mc_desc*, const void*, const void*, size_t, size_t, void*, int,
-                       cudaStream_t);
+int scatter_inv_launch(const mc_desc*, const void*, const void*, size_t, void*, int, cudaStream_t);
 size_t invmap_bytes(const mc_desc*);
 size_t invmap_build_ws(const mc_desc*);
 int invmap_build_launch(const mc_desc*, const void*, void*, void*, size_t, cudaStream_t);
@@ -158,15 +156,13 @@ static int scatter_inv_check(const mc_desc* d, const void* a, const void* b, con
 int mc_pool_avg_bwd_inv(const mc_desc* d, const void* gy, const void* inv, void* gx, void* stream) {
   int rc = scatter_inv_check(d, gy, inv, gx);
   if (rc) return rc;
-  return scatter_inv_launch(d, gy, inv, invmap_off_bytes(d), invmap_pix_offset(d), gx, 1,
-                            (cudaStream_t)stream);
+  return scatter_inv_launch(d, gy, inv, invmap_off_bytes(d), gx, 1, (cudaStream_t)stream);
 }
 int mc_resample_scatter_inv(const mc_desc* d, const void* x, const void* inv, void* y, void* stream) {
   int rc = scatter_inv_check(d, x, inv, y);
   if (rc) return rc;
   if (d->K != 1) return MC_ERR_BAD_ARG;
-  return scatter_inv_launch(d, x, inv, invmap_off_bytes(d), invmap_pix_offset(d), y, 0,
-                            (cudaStream_t)stream);
+  return scatter_inv_launch(d, x, inv, invmap_off_bytes(d), y, 0, (cudaStream_t)stream);
 }
 
 int mc_conv_dgrad_inv_supported(const mc_desc* d) {

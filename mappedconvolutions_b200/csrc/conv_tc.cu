@@ -1492,37 +1492,6 @@ __global__ void tapmap_build_kernel(const float* __restrict__ map, TapEnt* __res
   }
 }
 
-// Pixel table: for every input pixel the first four entries of its lists over ALL taps (they are
-// adjacent in the CSR), as int p[4], float w[4].  p[3] also carries the number of valid entries
-// (bits 27-29) and a "list goes on" flag (bit 30); unused entries point at grid pixel 0 with
-// weight 0.  It saves the adjoint gathers (average unpooling, resample scatter) one of their three
-// dependent loads per pixel.  Only built when grid pixel indices fit 27 bits.
-constexpr int PIX_COUNT_SHIFT = 27;
-__global__ void invpix_build_kernel(const int* __restrict__ off, const int2* __restrict__ ent,
-                                    uint4* __restrict__ out, long npix, int K) {
-  for (long q = blockIdx.x * (long)blockDim.x + threadIdx.x; q < npix;
-       q += (long)gridDim.x * blockDim.x) {
-    const int b = off[q * K], e = off[(q + 1) * K];
-    int p[4];
-    float w[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      p[c] = 0;
-      w[c] = 0.f;
-      if (b + c < e) {
-        const int2 en = ent[b + c];
-        p[c] = en.x;
-        w[c] = __int_as_float(en.y);
-      }
-    }
-    const int n = e - b < 4 ? e - b : 4;
-    p[3] |= (n << PIX_COUNT_SHIFT) | (e - b > 4 ? MORE_FLAG : 0);
-    out[2 * q] = make_uint4(p[0], p[1], p[2], p[3]);
-    out[2 * q + 1] = make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]),
-                                __float_as_uint(w[3]));
-  }
-}
-
 // Inverse tap table: the first four entries of every (input pixel, tap) list in TapEnt form;
 // MORE_FLAG marks the lists that go on.
 __global__ void invtap_build_kernel(const int* __restrict__ off, const int2* __restrict__ ent,
@@ -1766,13 +1735,8 @@ bool invmap_supported(const mc_desc* d) {
 static size_t inv_tab_offset(const mc_desc* d) {
   return (inv_off_bytes(d) + inv_max_entries(d) * sizeof(int2) + 31) & ~(size_t)31;
 }
-// layout, continued: ... | TapEnt table[nkeys] | pixel table[IH * IW] (32 bytes each)
-static size_t inv_pix_offset(const mc_desc* d) {
-  return inv_tab_offset(d) + (size_t)d->IH * d->IW * d->K * sizeof(TapEnt);
-}
-size_t invmap_pix_offset(const mc_desc* d) { return inv_pix_offset(d); }
 size_t invmap_bytes(const mc_desc* d) {
-  return inv_pix_offset(d) + (size_t)d->IH * d->IW * 32;
+  return inv_tab_offset(d) + (size_t)d->IH * d->IW * d->K * sizeof(TapEnt);
 }
 
 static size_t scan_temp_bytes(size_t n) {
@@ -1811,9 +1775,6 @@ int invmap_build_launch(const mc_desc* d, const void* map, void* inv, void* ws, 
   invmap_sort_kernel<<<grid_for((long)nkeys, 256), 256, 0, st>>>(a.off, a.ent, (long)nkeys), MC_COUNT(1);
   invtap_build_kernel<<<grid_for((long)nkeys, 256), 256, 0, st>>>(
       a.off, a.ent, (TapEnt*)((uint8_t*)inv + inv_tab_offset(d)), (long)nkeys), MC_COUNT(1);
-  const long npix = (long)d->IH * d->IW;
-  invpix_build_kernel<<<grid_for(npix, 256), 256, 0, st>>>(
-      a.off, a.ent, (uint4*)((uint8_t*)inv + inv_pix_offset(d)), npix, d->K), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }

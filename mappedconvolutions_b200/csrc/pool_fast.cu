@@ -278,42 +278,17 @@ struct InvGatherArgs {
   void* out;         // image (B, C, npix), fully written
   const int* off;    // (npix * K + 1)
   const int2* ent;   // (grid location, weight bits)
-  const uint4* pix;  // per image pixel: int p[4], float w[4]; p[3] bits 27-29 = valid entries,
-                     // bit 30 = the list goes on (or null: walk off / ent)
   int B, C, K;
   long npix, ngrid;
   float inv_k;       // 1 for resample, divide by K for average unpooling
   int planes_per_block;
 };
 
-// First four (grid location, weight) entries of pixel q's list, from the pixel table (one 32-byte
-// load) or, without it, from the CSR (two dependent loads).  beg / end are only filled in when the
-// list is longer than four.
-__device__ __forceinline__ void load_list_head(const InvGatherArgs& a, long q, int2 (&e4)[4], int& n4,
-                                               bool& longer, int& beg, int& end) {
-  if (a.pix) {
-    const uint4 p = __ldg(a.pix + 2 * q), w = __ldg(a.pix + 2 * q + 1);
-    n4 = (int)((p.w >> 27) & 7u);
-    longer = ((p.w >> 30) & 1u) != 0;
-    e4[0] = make_int2((int)p.x, (int)w.x);
-    e4[1] = make_int2((int)p.y, (int)w.y);
-    e4[2] = make_int2((int)p.z, (int)w.z);
-    e4[3] = make_int2((int)(p.w & 0x07FFFFFFu), (int)w.w);
-    if (longer) { beg = __ldg(a.off + q * a.K); end = __ldg(a.off + (q + 1) * a.K); }
-  } else {
-    beg = __ldg(a.off + q * a.K);
-    end = __ldg(a.off + (q + 1) * a.K);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) e4[i] = beg + i < end ? __ldg(a.ent + beg + i) : make_int2(0, 0);
-    n4 = end - beg < 4 ? end - beg : 4;
-    longer = end - beg > 4;
-  }
-}
-
 template <typename T, bool AVG>
 __global__ void __launch_bounds__(256) inv_gather_planes_kernel(const InvGatherArgs a) {
   const long q = blockIdx.x * 256L + threadIdx.x;
   if (q >= a.npix) return;
+  const int beg = __ldg(a.off + q * a.K), end = __ldg(a.off + (q + 1) * a.K);
   const long nplanes = (long)a.B * a.C;
   const long pl0 = (long)blockIdx.y * a.planes_per_block;
   long pl1 = pl0 + a.planes_per_block;
@@ -322,9 +297,10 @@ __global__ void __launch_bounds__(256) inv_gather_planes_kernel(const InvGatherA
   T* out = (T*)a.out;
   // the common short lists stay in registers; longer ones are re-read per plane
   int2 e4[4];
-  int n4, beg = 0, end = 0;
-  bool longer;
-  load_list_head(a, q, e4, n4, longer, beg, end);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) e4[i] = beg + i < end ? __ldg(a.ent + beg + i) : make_int2(0, 0);
+  const int n4 = end - beg < 4 ? end - beg : 4;
+  const bool longer = end - beg > 4;
   // four planes per trip: their (independent) loads are in flight together
 #pragma unroll 4
   for (long pl = pl0; pl < pl1; ++pl) {
@@ -362,10 +338,7 @@ __global__ void __launch_bounds__(256) inv_gather_cl_kernel(const InvGatherArgs 
   const long q = gthread >> lpp_log2;
   const int lane = (int)(gthread & (lpp - 1));
   if (q >= a.npix) return;
-  int2 e4[4];
-  int n4, beg = 0, end = 0;
-  bool longer;
-  load_list_head(a, q, e4, n4, longer, beg, end);
+  const int beg = __ldg(a.off + q * a.K), end = __ldg(a.off + (q + 1) * a.K);
   const T* g = (const T*)a.g;
   T* out = (T*)a.out;
   for (int b = blockIdx.y; b < a.B; b += gridDim.y) {
@@ -375,30 +348,15 @@ __global__ void __launch_bounds__(256) inv_gather_cl_kernel(const InvGatherArgs 
       float acc[VN];
 #pragma unroll
       for (int j = 0; j < VN; ++j) acc[j] = 0.f;
+      for (int e = beg; e < end; ++e) {
+        const int2 en = __ldg(a.ent + e);
+        const float w = __int_as_float(en.y);
+        float v[VN];
+        Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(src + (long)en.x * a.C)), v);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (i < n4) {
-          const float w = __int_as_float(e4[i].y);
-          float v[VN];
-          Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(src + (long)e4[i].x * a.C)), v);
-#pragma unroll
-          for (int j = 0; j < VN; ++j) {
-            const float t = AVG ? __fdiv_rn(v[j], (float)a.K) : v[j];
-            acc[j] = __fadd_rn(acc[j], __fmul_rn(w, t));
-          }
-        }
-      }
-      if (longer) {
-        for (int e = beg + 4; e < end; ++e) {
-          const int2 en = __ldg(a.ent + e);
-          const float w = __int_as_float(en.y);
-          float v[VN];
-          Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(src + (long)en.x * a.C)), v);
-#pragma unroll
-          for (int j = 0; j < VN; ++j) {
-            const float t = AVG ? __fdiv_rn(v[j], (float)a.K) : v[j];
-            acc[j] = __fadd_rn(acc[j], __fmul_rn(w, t));
-          }
+        for (int j = 0; j < VN; ++j) {
+          const float t = AVG ? __fdiv_rn(v[j], (float)a.K) : v[j];
+          acc[j] = __fadd_rn(acc[j], __fmul_rn(w, t));
         }
       }
       *reinterpret_cast<uint4*>(out + ((long)b * a.npix + q) * a.C + c0) = Vec16<T>::pack(acc);
@@ -436,7 +394,7 @@ static int launch_inv_gather(const mc_desc* d, InvGatherArgs a, cudaStream_t st)
 // inv: buffer built by mc_invmap_build for the same descriptor.  avg != 0: average unpooling
 // (values divided by K first), else resample scatter.
 int scatter_inv_launch(const mc_desc* d, const void* g, const void* inv, size_t inv_off_bytes,
-                       size_t inv_pix_offset, void* out, int avg, cudaStream_t st) {
+                       void* out, int avg, cudaStream_t st) {
   if (d->P != 0 || (d->dtype != MC_F32 && d->dtype != MC_BF16)) return MC_ERR_UNSUPPORTED;
   const size_t esz = d->dtype == MC_F32 ? 4 : 2;
   if (d->layout == MC_NHWC && ((d->C_in * esz) % 16 != 0 || (((uintptr_t)g | (uintptr_t)out) & 15)))
@@ -445,9 +403,6 @@ int scatter_inv_launch(const mc_desc* d, const void* g, const void* inv, size_t 
   a.g = g; a.out = out;
   a.off = (const int*)inv;
   a.ent = (const int2*)((const uint8_t*)inv + inv_off_bytes);
-  // the pixel table packs grid locations into 27 bits
-  a.pix = (long)d->OH * d->OW < (1L << 27) ? (const uint4*)((const uint8_t*)inv + inv_pix_offset)
-                                           : nullptr;
   a.B = d->B; a.C = d->C_in; a.K = d->K;
   a.npix = (long)d->IH * d->IW;
   a.ngrid = (long)d->OH * d->OW;
