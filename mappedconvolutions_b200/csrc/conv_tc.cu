@@ -103,6 +103,8 @@ struct Source {
   const int* inv_off; // inverse-map mode: (npix * K + 1) list offsets
   const int2* inv_ent;  //                 (source pixel, weight bits) entries
   const TapEnt* tab;    // prebuilt table [pixel of the tiled domain][tap], or null
+  const int* tab32;     // nearest maps: the same table as one int per entry (source pixel or -1)
+  long src_elems;       // elements of src (batch * spix * C)
   int KC;      // K * C: length of the gathered (tap, channel) axis
   int packed;  // C is not a multiple of 64: a 64-wide slice holds elements tap * C + c of several
                // taps (map mode only).  2: the whole axis fits one slice and the row-per-thread
@@ -694,6 +696,79 @@ __device__ __forceinline__ void gather_row_nearest(const TapEnt* ent, const bf16
   }
 }
 
+// Nearest maps with 1, 3 or 4 channels (depth, RGB, RGB-D first layers), compact table.  A row is
+// K pixels of C channels side by side.  What bounds this layer is the number of load instructions
+// whose lanes all hit different cache lines (one line per lane and instruction goes through L1),
+// so a pixel is fetched with as few loads as its alignment allows - two aligned 32-bit words for a
+// 6-byte RGB pixel, one 64-bit word for four channels - and shifted into place in registers; the
+// element loads of the generic path cost three to four times as many.
+template <int C>
+__device__ __forceinline__ void gather_row_nearest_c(const int* offs, const bf16* src, long pix0,
+                                                     long src_elems, int K, uint4 (&row)[8]) {
+  static_assert(C == 1 || C == 3 || C == 4, "unsupported channel count");
+  constexpr int KMAX = 64 / C;
+  constexpr int TPP = C == 1 ? 16 : 8;  // taps per pass (<= 16 registers of loads in flight)
+  constexpr int NPASS = (KMAX + TPP - 1) / TPP;
+  uint32_t wd[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) wd[i] = 0u;
+  const uint32_t* xw = reinterpret_cast<const uint32_t*>(src);
+  const uint16_t* xh = reinterpret_cast<const uint16_t*>(src);
+#pragma unroll
+  for (int pass = 0; pass < NPASS; ++pass) {
+    if (pass * TPP < K) {
+      uint32_t lo[TPP], hi[TPP], sh[TPP];
+#pragma unroll
+      for (int j = 0; j < TPP; ++j) {
+        const int k = pass * TPP + j;
+        lo[j] = hi[j] = sh[j] = 0u;
+        if (k < KMAX && k < K) {
+          const int off = offs[k];
+          if (off >= 0) {
+            const long g = (pix0 + off) * C;  // first element of the pixel
+            if (C == 4) {
+              const uint2 v = __ldg(reinterpret_cast<const uint2*>(xw + (g >> 1)));
+              lo[j] = v.x; hi[j] = v.y;
+            } else if (C == 3) {
+              const long wi = g >> 1;
+              sh[j] = (uint32_t)(g & 1) << 4;
+              lo[j] = __ldg(xw + wi);
+              // the second word may straddle the end of the tensor: then only its low half exists
+              hi[j] = 2 * wi + 3 < src_elems ? __ldg(xw + wi + 1) : (uint32_t)__ldg(xh + 2 * wi + 2);
+            } else {
+              lo[j] = __ldg(xh + g);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < TPP; ++j) {
+        const int k = pass * TPP + j;
+        if (k < KMAX) {
+          if (C == 4) {
+            wd[2 * k] = lo[j]; wd[2 * k + 1] = hi[j];
+          } else if (C == 3) {
+            const uint32_t e01 = __funnelshift_r(lo[j], hi[j], sh[j]);
+            const uint32_t e2 = (hi[j] >> sh[j]) & 0xFFFFu;
+            const int P = 3 * k;  // element position in the row (compile-time after unrolling)
+            if ((P & 1) == 0) {
+              wd[P / 2] = e01;
+              wd[P / 2 + 1] |= e2;
+            } else {
+              wd[(P - 1) / 2] |= e01 << 16;
+              wd[(P + 1) / 2] = (e01 >> 16) | (e2 << 16);
+            }
+          } else {
+            wd[k / 2] |= lo[j] << (16 * (k & 1));
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) row[i] = make_uint4(wd[4 * i], wd[4 * i + 1], wd[4 * i + 2], wd[4 * i + 3]);
+}
+
 template <bool PAD>
 __device__ __forceinline__ void producer_rowwise(const Source& s, const Tiling& t, int nsl, int nslots,
                                                  int nst, uint32_t stage0, uint32_t full0,
@@ -702,6 +777,9 @@ __device__ __forceinline__ void producer_rowwise(const Source& s, const Tiling& 
                                                  int lane, int code) {
   // the shared-memory tap table is not used in this mode; its space holds the threads' strips
   uint2* mine = reinterpret_cast<uint2*>(table) + (size_t)(pw * 32 + lane) * s.K;
+  // compact-table mode: the warp's 32 x K offsets, [row][tap]
+  int* wstrip = reinterpret_cast<int*>(table) + (size_t)pw * 32 * s.K;
+  const bool compact = s.interp == 0 && s.tab32 != nullptr && (s.C == 1 || s.C == 3 || s.C == 4);
   constexpr int TW = N_PRODUCER_WARPS / ROW_TEAMS;  // warps per team: 4 x 32 threads = 128 rows
   const int team = pw / TW, r = (pw % TW) * 32 + lane;
   const uint32_t rowaddr = r * 128;
@@ -719,7 +797,26 @@ __device__ __forceinline__ void producer_rowwise(const Source& s, const Tiling& 
       int img;
       bool valid;
       tile_pixel(t, tile, r, gp, img, p, valid);
-      if (valid) {
+      if (compact) {
+        // The 32 rows of a warp are consecutive pixels of one image unless the tile is a 2-D block
+        // or crosses an image / the end: then their K x 32 table words are one contiguous run and
+        // are fetched with coalesced loads; otherwise every lane fetches its own K words.
+        const long p0 = __shfl_sync(0xffffffffu, p, 0);
+        const bool run = __all_sync(0xffffffffu, valid && p == p0 + lane);
+        __syncwarp();
+        if (run) {
+          const int* tw = s.tab32 + p0 * s.K;
+          for (int i = lane; i < 32 * s.K; i += 32) wstrip[i] = __ldg(tw + i);
+        } else {
+          for (int k = 0; k < s.K; ++k) wstrip[lane * s.K + k] = valid ? __ldg(s.tab32 + p * s.K + k) : -1;
+        }
+        __syncwarp();
+        const int* offs = wstrip + lane * s.K;
+        const long pix0 = (long)img * s.spix;
+        if (s.C == 3) gather_row_nearest_c<3>(offs, s.src, pix0, s.src_elems, s.K, row);
+        else if (s.C == 4) gather_row_nearest_c<4>(offs, s.src, pix0, s.src_elems, s.K, row);
+        else gather_row_nearest_c<1>(offs, s.src, pix0, s.src_elems, s.K, row);
+      } else if (valid) {
         const TapEnt* ent = s.tab + p * s.K;
         const bf16* xb = s.src + (long)img * s.spix * s.C;
         if (s.interp == 0) gather_row_nearest(ent, xb, s.C, s.K, s.KC, mine, row);
@@ -1470,8 +1567,8 @@ __global__ void invmap_sort_kernel(const int* __restrict__ off, int2* __restrict
 }
 
 // Forward tap table: TapEnt[(pixel of the map grid) * K + tap], offsets relative to the image.
-__global__ void tapmap_build_kernel(const float* __restrict__ map, TapEnt* __restrict__ out, long n,
-                                    int SH, int SW, int interp) {
+__global__ void tapmap_build_kernel(const float* __restrict__ map, TapEnt* __restrict__ out,
+                                    int* __restrict__ out32, long n, int SH, int SW, int interp) {
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
     const float2 m = __ldg(reinterpret_cast<const float2*>(map) + i);
     Tap<float> tp;
@@ -1484,6 +1581,7 @@ __global__ void tapmap_build_kernel(const float* __restrict__ map, TapEnt* __res
       off[c] = on ? tp.off[c] : -1;
       w[c] = on ? tp.w[c] : 0.f;
     }
+    if (out32) out32[i] = off[0];  // nearest: the one source pixel, -1 when the tap reads nothing
     seal_entry(off, w);
     uint4* dst = reinterpret_cast<uint4*>(out + i);
     dst[0] = make_uint4(off[0], off[1], off[2], off[3]);
@@ -1608,9 +1706,10 @@ size_t conv_tc_fwd_wimg_bytes(const mc_desc* d) {
   return ((size_t)fwd_slices(d) * 64 * d->C_out * sizeof(bf16) + 255) & ~(size_t)255;
 }
 
+size_t tapmap_bytes(const mc_desc* d);
+
 size_t conv_tc_fwd_ws(const mc_desc* d) {
-  return conv_tc_fwd_wimg_bytes(d) +
-         (fwd_needs_table(d) ? (size_t)d->OH * d->OW * d->K * sizeof(TapEnt) : 0);
+  return conv_tc_fwd_wimg_bytes(d) + (fwd_needs_table(d) ? tapmap_bytes(d) : 0);
 }
 
 template <int NOUT, bool CSR>
@@ -1653,13 +1752,25 @@ static int launch_gemm(const GemmArgs& a, const GemmPlan& p, bool pre, cudaStrea
 }
 
 // Forward tap table of a sample map (one TapEnt per map entry).
-size_t tapmap_bytes(const mc_desc* d) { return (size_t)d->OH * d->OW * d->K * sizeof(TapEnt); }
+// Nearest maps carry a second, compact form behind the records: one int per entry (the source
+// pixel, or -1), which the row-per-thread producer reads with coalesced loads.
+static bool tapmap_has_compact(const mc_desc* d) { return d->interp != 1 && d->interp != 2; }
+static const int* tapmap_compact(const mc_desc* d, const void* tab) {
+  if (!tab || !tapmap_has_compact(d)) return nullptr;
+  return reinterpret_cast<const int*>((const uint8_t*)tab + (size_t)d->OH * d->OW * d->K * sizeof(TapEnt));
+}
+
+size_t tapmap_bytes(const mc_desc* d) {
+  const size_t n = (size_t)d->OH * d->OW * d->K;
+  return n * sizeof(TapEnt) + (tapmap_has_compact(d) ? ((n * sizeof(int) + 15) & ~(size_t)15) : 0);
+}
 
 int tapmap_build_launch(const mc_desc* d, const void* map, void* tab, cudaStream_t st) {
   if (!aligned16(map) || !aligned16(tab)) return MC_ERR_BAD_ARG;
   const long n = (long)d->OH * d->OW * d->K;
-  tapmap_build_kernel<<<grid_for(n, 256), 256, 0, st>>>((const float*)map, (TapEnt*)tab, n, d->IH,
-                                                        d->IW, d->interp), MC_COUNT(1);
+  tapmap_build_kernel<<<grid_for(n, 256), 256, 0, st>>>((const float*)map, (TapEnt*)tab,
+                                                        const_cast<int*>(tapmap_compact(d, tab)), n,
+                                                        d->IH, d->IW, d->interp), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
@@ -1676,6 +1787,7 @@ static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, con
   GemmArgs a = {};
   a.s.src = (const bf16*)x; a.s.spix = (long)d->IH * d->IW; a.s.C = d->C_in;
   a.s.SH = d->IH; a.s.SW = d->IW; a.s.K = d->K; a.s.interp = d->interp;
+  a.s.src_elems = (long)d->B * d->IH * d->IW * d->C_in;
   a.s.map = (const float*)map;
   a.s.tab = (const TapEnt*)tab;
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
@@ -1700,6 +1812,7 @@ static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, con
   if (a.s.tab && rowwise_shape(d) && p.nst >= ROW_TEAMS) {
     a.s.packed = 2;
     a.full_cnt = N_PRODUCER_WARPS / ROW_TEAMS;
+    a.s.tab32 = tapmap_compact(d, a.s.tab);
   }
   return launch_gemm<false>(a, p, a.s.tab != nullptr, st);
 }
@@ -1873,6 +1986,7 @@ static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, co
   GemmArgs a = {};
   a.s.src = (const bf16*)x; a.s.spix = (long)d->IH * d->IW; a.s.C = d->C_in;
   a.s.SH = d->IH; a.s.SW = d->IW; a.s.K = d->K; a.s.interp = d->interp;
+  a.s.src_elems = (long)d->B * d->IH * d->IW * d->C_in;
   a.s.map = (const float*)map;
   a.s.tab = (const TapEnt*)tab;
   if (!make_tiling(a.t, d->B, d->OH, d->OW)) return MC_ERR_TOO_LARGE;
@@ -1889,6 +2003,7 @@ static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, co
   if (tab && rowwise_shape(d) && p.nst >= ROW_TEAMS) {
     a.s.packed = 2;
     a.full_cnt = N_PRODUCER_WARPS / ROW_TEAMS;
+    a.s.tab32 = tapmap_compact(d, tab);
   }
   if (cudaMemsetAsync(gw, 0, (size_t)d->C_out * d->C_in * d->K * sizeof(float), st) != cudaSuccess)
     return MC_ERR_LAUNCH;

@@ -64,7 +64,7 @@ __device__ __forceinline__ float combine(const float (&v)[NT], const Entries<NT>
     r = __fadd_rn(r, __fmul_rn(e.w[1], v[1]));
     r = __fadd_rn(r, __fmul_rn(e.w[2], v[2]));
     r = __fadd_rn(r, __fmul_rn(e.w[3], v[3]));
-    if (OP == FOP_AVG) r = __fdiv_rn(__fadd_rn(0.f, r), (float)K);
+    if (OP == FOP_AVG) r = div_by_const(__fadd_rn(0.f, r), (float)K, __frcp_rn((float)K));
     best = 0;
     return r;
   }
@@ -80,7 +80,7 @@ __device__ __forceinline__ float combine(const float (&v)[NT], const Entries<NT>
     float s = 0.f;
 #pragma unroll
     for (int k = 0; k < NT; ++k) s = __fadd_rn(s, v[k]);
-    return __fdiv_rn(s, (float)K);
+    return div_by_const(s, (float)K, __frcp_rn((float)K));
   }
   best = 0;
   return v[0];
@@ -280,7 +280,7 @@ struct InvGatherArgs {
   const int2* ent;   // (grid location, weight bits)
   int B, C, K;
   long npix, ngrid;
-  float inv_k;       // 1 for resample, divide by K for average unpooling
+  float inv_k;       // 1 / K, correctly rounded (average unpooling divides by K)
   int planes_per_block;
 };
 
@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(256) inv_gather_planes_kernel(const InvGatherA
     for (int i = 0; i < 4; ++i) {
       if (i < n4) {
         float t = v[i];
-        if (AVG) t = __fdiv_rn(t, (float)a.K);
+        if (AVG) t = div_by_const(t, (float)a.K, a.inv_k);
         acc = __fadd_rn(acc, __fmul_rn(__int_as_float(e4[i].y), t));
       }
     }
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(256) inv_gather_planes_kernel(const InvGatherA
       for (int e = beg + 4; e < end; ++e) {
         const int2 en = __ldg(a.ent + e);
         float t = (float)ldv(src + en.x);
-        if (AVG) t = __fdiv_rn(t, (float)a.K);
+        if (AVG) t = div_by_const(t, (float)a.K, a.inv_k);
         acc = __fadd_rn(acc, __fmul_rn(__int_as_float(en.y), t));
       }
     }
@@ -355,7 +355,7 @@ __global__ void __launch_bounds__(256) inv_gather_cl_kernel(const InvGatherArgs 
         Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(src + (long)en.x * a.C)), v);
 #pragma unroll
         for (int j = 0; j < VN; ++j) {
-          const float t = AVG ? __fdiv_rn(v[j], (float)a.K) : v[j];
+          const float t = AVG ? div_by_const(v[j], (float)a.K, a.inv_k) : v[j];
           acc[j] = __fadd_rn(acc[j], __fmul_rn(w, t));
         }
       }

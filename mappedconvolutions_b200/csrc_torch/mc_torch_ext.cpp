@@ -182,10 +182,12 @@ void clear_plan_cache() { plan_cache().clear(); }
 Tensor channels_last(const Tensor& t) { return t.contiguous(at::MemoryFormat::ChannelsLast); }
 
 // bfloat16 tensors in the reference's NCHW layout: the tensor-core kernels want channels-last, and
-// two extra layout passes cost far less than the generic kernels.
+// two extra layout passes cost far less than the generic kernels.  (A single-channel tensor is
+// contiguous in both layouts at once and counts as NCHW: it is rerouted too, at no cost, and the
+// result comes back in NCHW.  The rerouted call passes nhwc = true.)
 bool via_channels_last(const Tensor& input, const OptTensor& iw, mc_desc d_nhwc) {
   if (iw.has_value() || input.scalar_type() != at::kBFloat16 || input.dim() != 4) return false;
-  if (layout_of(input) != MC_NCHW || input.is_contiguous(at::MemoryFormat::ChannelsLast)) return false;
+  if (layout_of(input) != MC_NCHW) return false;
   d_nhwc.layout = MC_NHWC;
   return mc_conv_fwd_workspace_bytes(&d_nhwc) > 0;
 }
@@ -193,16 +195,17 @@ bool via_channels_last(const Tensor& input, const OptTensor& iw, mc_desc d_nhwc)
 // ---- convolution ---------------------------------------------------------------------------------------
 
 Tensor conv_forward(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
-                    const Tensor& weight, const Tensor& bias, int64_t K, int64_t interp) {
+                    const Tensor& weight, const Tensor& bias, int64_t K, int64_t interp,
+                    bool nhwc = false) {
   const auto dev = need_cuda({&input, &sample_map, opt(iw), &weight, &bias});
   TORCH_CHECK(input.dim() == 4 && sample_map.dim() >= 3, "input must be 4-D, the map (OH, OW, K, ..)");
   const int64_t B = input.size(0), Cin = input.size(1), IH = input.size(2), IW = input.size(3);
   const int64_t Cout = weight.size(0), OH = sample_map.size(0), OW = sample_map.size(1);
-  if (via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH, IW, OH,
-                                             OW, K, 0, interp)))
-    return conv_forward(channels_last(input), sample_map, c10::nullopt, weight, bias, K, interp)
+  if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH,
+                                                      IW, OH, OW, K, 0, interp)))
+    return conv_forward(channels_last(input), sample_map, c10::nullopt, weight, bias, K, interp, true)
         .contiguous();
-  const int layout = layout_of(input);
+  const int layout = nhwc ? MC_NHWC : layout_of(input);
   check_map(input, sample_map, iw);
   TORCH_CHECK(weight.is_contiguous() && bias.is_contiguous(), "weight and bias must be contiguous");
   const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, IH, IW, OH, OW, K,
@@ -223,18 +226,18 @@ Tensor conv_forward(const Tensor& input, const Tensor& sample_map, const OptTens
 std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sample_map,
                                   const OptTensor& iw, const Tensor& input, const Tensor& weight,
                                   const Tensor& bias, int64_t K, int64_t interp,
-                                  bool need_input_grad) {
+                                  bool need_input_grad, bool nhwc = false) {
   const auto dev = need_cuda({&grad_output_in, &sample_map, opt(iw), &input, &weight, &bias});
   const int64_t B = input.size(0), Cin = input.size(1), IH = input.size(2), IW = input.size(3);
   const int64_t Cout = weight.size(0), OH = sample_map.size(0), OW = sample_map.size(1);
-  if (via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH, IW, OH,
-                                             OW, K, 0, interp))) {
+  if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH,
+                                                      IW, OH, OW, K, 0, interp))) {
     auto g = conv_backward(channels_last(grad_output_in), sample_map, c10::nullopt,
-                           channels_last(input), weight, bias, K, interp, need_input_grad);
+                           channels_last(input), weight, bias, K, interp, need_input_grad, true);
     if (g[0].defined()) g[0] = g[0].contiguous();
     return g;
   }
-  const int layout = layout_of(input);
+  const int layout = nhwc ? MC_NHWC : layout_of(input);
   const Tensor grad_output = as_layout(grad_output_in, layout);
   check_map(input, sample_map, iw);
   const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, IH, IW, OH, OW, K,
@@ -273,16 +276,16 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
 
 Tensor tconv_forward(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
                      const Tensor& weight, const Tensor& bias, int64_t OHt, int64_t OWt, int64_t K,
-                     int64_t interp) {
+                     int64_t interp, bool nhwc = false) {
   const auto dev = need_cuda({&input, &sample_map, opt(iw), &weight, &bias});
   const int64_t B = input.size(0), Cin = input.size(1), H = input.size(2), W = input.size(3);
   const int64_t Cout = weight.size(1);
   // the same layer seen as a convolution: the sampled image carries C_out channels, the grid C_in
-  if (via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cout, Cin, OHt, OWt, H,
-                                             W, K, 0, interp)))
+  if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cout, Cin, OHt,
+                                                      OWt, H, W, K, 0, interp)))
     return tconv_forward(channels_last(input), sample_map, c10::nullopt, weight, bias, OHt, OWt, K,
-                         interp).contiguous();
-  const int layout = layout_of(input);
+                         interp, true).contiguous();
+  const int layout = nhwc ? MC_NHWC : layout_of(input);
   check_map(input, sample_map, iw);
   TORCH_CHECK(weight.is_contiguous() && bias.is_contiguous(), "weight and bias must be contiguous");
   const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, OHt, OWt, H, W, K,
@@ -307,19 +310,20 @@ Tensor tconv_forward(const Tensor& input, const Tensor& sample_map, const OptTen
 
 std::vector<Tensor> tconv_backward(const Tensor& grad_output_in, const Tensor& sample_map,
                                    const OptTensor& iw, const Tensor& input, const Tensor& weight,
-                                   const Tensor& bias, int64_t K, int64_t interp) {
+                                   const Tensor& bias, int64_t K, int64_t interp,
+                                   bool nhwc = false) {
   const auto dev = need_cuda({&grad_output_in, &sample_map, opt(iw), &input, &weight, &bias});
   const int64_t B = input.size(0), Cin = input.size(1), H = input.size(2), W = input.size(3);
   const int64_t Cout = weight.size(1);
   const int64_t OHt = grad_output_in.size(2), OWt = grad_output_in.size(3);
-  if (via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cout, Cin, OHt, OWt, H,
-                                             W, K, 0, interp))) {
+  if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cout, Cin, OHt,
+                                                      OWt, H, W, K, 0, interp))) {
     auto g = tconv_backward(channels_last(grad_output_in), sample_map, c10::nullopt,
-                            channels_last(input), weight, bias, K, interp);
+                            channels_last(input), weight, bias, K, interp, true);
     g[0] = g[0].contiguous();
     return g;
   }
-  const int layout = layout_of(input);
+  const int layout = nhwc ? MC_NHWC : layout_of(input);
   const Tensor grad_output = as_layout(grad_output_in, layout);
   check_map(input, sample_map, iw);
   const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, OHt, OWt, H, W, K,

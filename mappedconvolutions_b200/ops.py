@@ -166,21 +166,22 @@ def _tensor_core_via_channels_last(input, interp_weights, make_desc):
     64 channels).  True if the call should be rerouted through channels-last copies."""
     if interp_weights is not None or input.dtype != torch.bfloat16 or input.dim() != 4:
         return False
-    if _layout(input) != _lib.MC_NCHW or input.is_contiguous(memory_format=torch.channels_last):
+    if _layout(input) != _lib.MC_NCHW:
         return False
     return lib().mc_conv_fwd_workspace_bytes(make_desc(_lib.MC_NHWC)) > 0
 
 
-def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, interpolation):
+def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, interpolation,
+                  _nhwc=False):
     dev = _need_cuda(input, sample_map, interp_weights, weight, bias)
-    if _tensor_core_via_channels_last(
+    if not _nhwc and _tensor_core_via_channels_last(
             input, interp_weights,
             lambda lay: _desc(input.dtype, lay, input.shape[0], input.shape[1], weight.shape[0],
                               input.shape[2], input.shape[3], sample_map.shape[0], sample_map.shape[1],
                               kernel_size, 0, interpolation)):
         return _conv_forward(_cl(input), sample_map, None, weight, bias, kernel_size,
-                             interpolation).contiguous()
-    layout = _layout(input)
+                             interpolation, _nhwc=True).contiguous()
+    layout = _lib.MC_NHWC if _nhwc else _layout(input)
     sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
     if not weight.is_contiguous() or not bias.is_contiguous():
         raise RuntimeError("weight and bias must be contiguous")
@@ -204,17 +205,17 @@ def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, 
 
 
 def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
-                   interpolation, need_input_grad=True):
+                   interpolation, need_input_grad=True, _nhwc=False):
     dev = _need_cuda(grad_output, sample_map, interp_weights, input, weight, bias)
-    if _tensor_core_via_channels_last(
+    if not _nhwc and _tensor_core_via_channels_last(
             input, interp_weights,
             lambda lay: _desc(input.dtype, lay, input.shape[0], input.shape[1], weight.shape[0],
                               input.shape[2], input.shape[3], sample_map.shape[0], sample_map.shape[1],
                               kernel_size, 0, interpolation)):
         g = _conv_backward(_cl(grad_output), sample_map, None, _cl(input), weight, bias, kernel_size,
-                           interpolation, need_input_grad)
+                           interpolation, need_input_grad, _nhwc=True)
         return [g[0].contiguous() if g[0] is not None else None, g[1], g[2]]
-    layout = _layout(input)
+    layout = _lib.MC_NHWC if _nhwc else _layout(input)
     grad_output = _as_layout(grad_output, layout)
     sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
     B, Cin, IH, IW = input.shape
@@ -288,16 +289,16 @@ def weighted_mapped_conv_backward(grad_output, sample_map, interp_weights, input
 # ------------------------------------------------------------------------------------------
 
 def _tconv_forward(input, sample_map, interp_weights, weight, bias, output_height, output_width,
-                   kernel_size, interpolation):
+                   kernel_size, interpolation, _nhwc=False):
     dev = _need_cuda(input, sample_map, interp_weights, weight, bias)
-    if _tensor_core_via_channels_last(
+    if not _nhwc and _tensor_core_via_channels_last(
             input, interp_weights,
             lambda lay: _desc(input.dtype, lay, input.shape[0], weight.shape[1], input.shape[1],
                               output_height, output_width, input.shape[2], input.shape[3],
                               kernel_size, 0, interpolation)):
         return _tconv_forward(_cl(input), sample_map, None, weight, bias, output_height, output_width,
-                              kernel_size, interpolation).contiguous()
-    layout = _layout(input)
+                              kernel_size, interpolation, _nhwc=True).contiguous()
+    layout = _lib.MC_NHWC if _nhwc else _layout(input)
     sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
     if not weight.is_contiguous() or not bias.is_contiguous():
         raise RuntimeError("weight and bias must be contiguous")
@@ -325,17 +326,17 @@ def _tconv_forward(input, sample_map, interp_weights, weight, bias, output_heigh
 
 
 def _tconv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
-                    interpolation):
+                    interpolation, _nhwc=False):
     dev = _need_cuda(grad_output, sample_map, interp_weights, input, weight, bias)
-    if _tensor_core_via_channels_last(
+    if not _nhwc and _tensor_core_via_channels_last(
             input, interp_weights,
             lambda lay: _desc(input.dtype, lay, input.shape[0], weight.shape[1], input.shape[1],
                               grad_output.shape[2], grad_output.shape[3], input.shape[2],
                               input.shape[3], kernel_size, 0, interpolation)):
         g = _tconv_backward(_cl(grad_output), sample_map, None, _cl(input), weight, bias, kernel_size,
-                            interpolation)
+                            interpolation, _nhwc=True)
         return [g[0].contiguous(), g[1], g[2]]
-    layout = _layout(input)
+    layout = _lib.MC_NHWC if _nhwc else _layout(input)
     grad_output = _as_layout(grad_output, layout)
     sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
     B, Cin, H, W = input.shape

@@ -153,6 +153,14 @@ def _device_status():
     # K * C_in <= 64: one slice per tile, built row-per-thread from the global tap table
     (1, 4, 128, 16, 32, 16, 32, 9),
     (3, 3, 64, 5, 50, 5, 50, 9),
+    # nearest maps of such layers read whole pixels (1, 3 or 4 channels) through the compact
+    # table: an odd element count (the last word straddles the end of the tensor), one channel,
+    # more taps than one pass of loads holds
+    (1, 3, 64, 1, 643, 1, 643, 7),
+    (2, 1, 64, 1, 333, 1, 333, 9),
+    (1, 1, 64, 8, 16, 8, 16, 33),
+    (1, 3, 64, 7, 9, 16, 16, 20),
+    (2, 4, 64, 1, 500, 1, 700, 16),
 ])
 @pytest.mark.parametrize("interp", [0, 1, 2])
 def test_bf16_tensor_core_conv_forward(shape, interp):
@@ -172,7 +180,9 @@ def test_bf16_tensor_core_conv_forward(shape, interp):
     xd = x.cuda().contiguous(memory_format=torch.channels_last)
     y = ops.mapped_conv_forward(xd, m.cuda(), w.cuda(), b.cuda(), K, interp)
     assert _device_status() == 0
-    assert y.dtype == torch.bfloat16 and y.is_contiguous(memory_format=torch.channels_last)
+    # (a single-channel input is contiguous in both layouts and counts as NCHW: so does its result)
+    assert y.dtype == torch.bfloat16
+    assert y.is_contiguous() if Cin == 1 else y.is_contiguous(memory_format=torch.channels_last)
     H.assert_close(y.float(), want, 2e-2, "tc fwd")
 
 
@@ -197,6 +207,10 @@ def test_bf16_tensor_core_conv_forward(shape, interp):
     (1, 20, 64, 9, 9, 9, 9, 5),
     (1, 4, 128, 16, 32, 16, 32, 9),
     (3, 3, 64, 5, 50, 5, 50, 9),
+    (1, 3, 64, 1, 643, 1, 643, 7),
+    (2, 1, 64, 1, 333, 1, 333, 9),
+    (1, 3, 64, 7, 9, 16, 16, 20),
+    (2, 4, 64, 1, 500, 1, 700, 16),
 ])
 @pytest.mark.parametrize("interp", [0, 1, 2])
 def test_bf16_tensor_core_conv_backward(shape, interp):
