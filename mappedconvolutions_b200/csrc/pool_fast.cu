@@ -339,8 +339,63 @@ __global__ void __launch_bounds__(256) inv_gather_cl_kernel(const InvGatherArgs 
   const int lane = (int)(gthread & (lpp - 1));
   if (q >= a.npix) return;
   const int beg = __ldg(a.off + q * a.K), end = __ldg(a.off + (q + 1) * a.K);
-  const T* g = (const T*)a.g;
-  T* out = (T*)a.out;
+  const T* __restrict__ g = (const T*)a.g;
+  T* __restrict__ out = (T*)a.out;
+  if (end - beg <= 2 && chunks == 1) {
+    // Lists of one or two entries (pooling maps; most pixels of a resample map): the entries stay
+    // in registers and four batch elements are in flight at once - one load per trip leaves the
+    // kernel waiting on latency.
+    constexpr int UB = 4;
+    const int n = end - beg;
+    const int2 e0 = n >= 1 ? __ldg(a.ent + beg) : make_int2(0, 0);
+    const int2 e1 = n >= 2 ? __ldg(a.ent + beg + 1) : make_int2(0, 0);
+    const float w0 = __int_as_float(e0.y), w1 = __int_as_float(e1.y);
+    const int c0 = lane * VN;
+    const long o0 = (long)e0.x * a.C + c0, o1 = (long)e1.x * a.C + c0;
+    const long img_in = a.ngrid * a.C, img_out = a.npix * a.C;
+    for (int b = blockIdx.y; b < a.B; b += UB * gridDim.y) {
+      uint4 r0[UB], r1[UB];
+#pragma unroll
+      for (int u = 0; u < UB; ++u) {
+        const int bb = b + u * gridDim.y;
+        r0[u] = r1[u] = make_uint4(0, 0, 0, 0);
+        if (bb < a.B) {
+          const T* src = g + bb * img_in;
+          if (n >= 1) r0[u] = __ldg(reinterpret_cast<const uint4*>(src + o0));
+          if (n >= 2) r1[u] = __ldg(reinterpret_cast<const uint4*>(src + o1));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UB; ++u) {
+        const int bb = b + u * gridDim.y;
+        if (bb >= a.B) break;
+        float v0[VN], v1[VN], acc[VN];
+        Vec16<T>::unpack(r0[u], v0);
+        Vec16<T>::unpack(r1[u], v1);
+#pragma unroll
+        for (int j = 0; j < VN; ++j) {
+          if (sizeof(T) == 2) {
+            acc[j] = fmaf(w1, v1[j], w0 * v0[j]);
+            if (AVG) acc[j] *= a.inv_k;
+          } else {
+            // the same operations in the same order as the general loop below
+            const float t0 = AVG ? div_by_const(v0[j], (float)a.K, a.inv_k) : v0[j];
+            acc[j] = __fadd_rn(0.f, __fmul_rn(w0, t0));
+            if (n >= 2) {
+              const float t1 = AVG ? div_by_const(v1[j], (float)a.K, a.inv_k) : v1[j];
+              acc[j] = __fadd_rn(acc[j], __fmul_rn(w1, t1));
+            }
+          }
+        }
+        if (n == 0) {
+#pragma unroll
+          for (int j = 0; j < VN; ++j) acc[j] = 0.f;
+        }
+        *reinterpret_cast<uint4*>(out + bb * img_out + q * a.C + c0) = Vec16<T>::pack(acc);
+      }
+    }
+    return;
+  }
   for (int b = blockIdx.y; b < a.B; b += gridDim.y) {
     for (int ch = 0; ch < chunks; ++ch) {
       const int c0 = (ch * lpp + lane) * VN;
@@ -355,9 +410,19 @@ __global__ void __launch_bounds__(256) inv_gather_cl_kernel(const InvGatherArgs 
         Vec16<T>::unpack(__ldg(reinterpret_cast<const uint4*>(src + (long)en.x * a.C)), v);
 #pragma unroll
         for (int j = 0; j < VN; ++j) {
-          const float t = AVG ? div_by_const(v[j], (float)a.K, a.inv_k) : v[j];
-          acc[j] = __fadd_rn(acc[j], __fmul_rn(w, t));
+          if (sizeof(T) == 2) {
+            // bf16: the reference has no such type to match bit for bit, and the kernel is bound
+            // by its instruction count - one fma per value, the division by K once at the end
+            acc[j] = fmaf(w, v[j], acc[j]);
+          } else {
+            const float t = AVG ? div_by_const(v[j], (float)a.K, a.inv_k) : v[j];
+            acc[j] = __fadd_rn(acc[j], __fmul_rn(w, t));
+          }
         }
+      }
+      if (sizeof(T) == 2 && AVG) {
+#pragma unroll
+        for (int j = 0; j < VN; ++j) acc[j] *= a.inv_k;
       }
       *reinterpret_cast<uint4*>(out + ((long)b * a.npix + q) * a.C + c0) = Vec16<T>::pack(acc);
     }

@@ -394,6 +394,22 @@ def test_bf16_pool_and_resample():
     gy = torch.randn(2, 8, 6, 7, generator=g).to(torch.bfloat16)
     u = ops.mapped_avg_unpool(gy.cuda(), m.cuda(), 9, 11, 4, 1)
     H.assert_close(u.float(), oracle.mapped_avg_unpool(gy.float(), m, 9, 11, 4, 1), 2e-2, "bf16 unpool")
+    # channels-last, nearest and bilinear: the vectorised gathers through the inverse map
+    cl = lambda t: t.cuda().contiguous(memory_format=torch.channels_last)
+    gy = torch.randn(3, 64, 6, 7, generator=g).to(torch.bfloat16)
+    img = torch.randn(3, 64, 9, 11, generator=g).to(torch.bfloat16)
+    for interp in (0, 1):
+        u = ops.mapped_avg_unpool(cl(gy), m.cuda(), 9, 11, 4, interp)
+        assert u.is_contiguous(memory_format=torch.channels_last)
+        H.assert_close(u.float(), oracle.mapped_avg_unpool(gy.float(), m, 9, 11, 4, interp), 2e-2,
+                       "bf16 unpool, channels-last")
+        m1 = m[:, :, :1].contiguous()
+        r = ops.resample_to_map(cl(gy), m1.cuda(), 9, 11, interp)
+        H.assert_close(r.float(), oracle.resample_to_map(gy.float(), m1, 9, 11, interp), 2e-2,
+                       "bf16 resample scatter, channels-last")
+        a = ops.mapped_avg_pool(cl(img), m.cuda(), 4, interp)
+        H.assert_close(a.float(), oracle.mapped_avg_pool(img.float(), m, 4, interp), 2e-2,
+                       "bf16 avg pool, channels-last")
 
 
 def test_empty_and_degenerate_shapes():
