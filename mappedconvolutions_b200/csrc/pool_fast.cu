@@ -97,8 +97,10 @@ __global__ void __launch_bounds__(256) sample_planes_kernel(const FastArgs a) {
   const long pl0 = (long)blockIdx.y * a.planes_per_block;
   long pl1 = pl0 + a.planes_per_block;
   if (pl1 > nplanes) pl1 = nplanes;
-  const T* x = (const T*)a.x;
-  T* y = (T*)a.y;
+  // (restrict: lets the loads of the next plane start before this plane's stores)
+  const T* __restrict__ x = (const T*)a.x;
+  T* __restrict__ y = (T*)a.y;
+  int64_t* __restrict__ idx = a.idx;
 #pragma unroll 2
   for (long pl = pl0; pl < pl1; ++pl) {
     const T* src = x + pl * a.npix_in;
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(256) sample_planes_kernel(const FastArgs a) {
     int best;
     const float r = combine<NT, NC, OP>(v, e, a.K, best);
     stv(y + pl * a.npix_out + p, r);
-    if (OP == FOP_MAX) a.idx[pl * a.npix_out + p] = best < 0 ? -1 : 2 * (p * NT + best);
+    if (OP == FOP_MAX) idx[pl * a.npix_out + p] = best < 0 ? -1 : 2 * (p * NT + best);
   }
 }
 
@@ -293,8 +295,46 @@ __global__ void __launch_bounds__(256) inv_gather_planes_kernel(const InvGatherA
   const long pl0 = (long)blockIdx.y * a.planes_per_block;
   long pl1 = pl0 + a.planes_per_block;
   if (pl1 > nplanes) pl1 = nplanes;
-  const T* g = (const T*)a.g;
-  T* out = (T*)a.out;
+  const T* __restrict__ g = (const T*)a.g;
+  T* __restrict__ out = (T*)a.out;
+  if (__all_sync(__activemask(), end - beg <= 2)) {
+    // Every list of the warp has at most two entries (pooling maps): eight planes per trip, all
+    // their loads issued before the first value is used.  The operations and their order are
+    // those of the general loop below.  (A warp with longer lists takes the general loop as a
+    // whole: running both paths side by side costs more than the batching gains.)
+    constexpr int UP = 8;
+    const int n = end - beg;
+    const int2 e0 = n >= 1 ? __ldg(a.ent + beg) : make_int2(0, 0);
+    const int2 e1 = n >= 2 ? __ldg(a.ent + beg + 1) : make_int2(0, 0);
+    const float w0 = __int_as_float(e0.y), w1 = __int_as_float(e1.y);
+    for (long pl = pl0; pl < pl1; pl += UP) {
+      float v0[UP], v1[UP];
+#pragma unroll
+      for (int u = 0; u < UP; ++u) {
+        v0[u] = v1[u] = 0.f;
+        if (pl + u < pl1) {
+          const T* src = g + (pl + u) * a.ngrid;
+          if (n >= 1) v0[u] = (float)ldv(src + e0.x);
+          if (n >= 2) v1[u] = (float)ldv(src + e1.x);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UP; ++u) {
+        if (pl + u >= pl1) break;
+        float acc = 0.f;
+        if (n >= 1) {
+          const float t = AVG ? div_by_const(v0[u], (float)a.K, a.inv_k) : v0[u];
+          acc = __fadd_rn(acc, __fmul_rn(w0, t));
+        }
+        if (n >= 2) {
+          const float t = AVG ? div_by_const(v1[u], (float)a.K, a.inv_k) : v1[u];
+          acc = __fadd_rn(acc, __fmul_rn(w1, t));
+        }
+        stv(out + (pl + u) * a.npix + q, acc);
+      }
+    }
+    return;
+  }
   // the common short lists stay in registers; longer ones are re-read per plane
   int2 e4[4];
 #pragma unroll
@@ -341,10 +381,10 @@ __global__ void __launch_bounds__(256) inv_gather_cl_kernel(const InvGatherArgs 
   const int beg = __ldg(a.off + q * a.K), end = __ldg(a.off + (q + 1) * a.K);
   const T* __restrict__ g = (const T*)a.g;
   T* __restrict__ out = (T*)a.out;
-  if (end - beg <= 2 && chunks == 1) {
-    // Lists of one or two entries (pooling maps; most pixels of a resample map): the entries stay
-    // in registers and four batch elements are in flight at once - one load per trip leaves the
-    // kernel waiting on latency.
+  if (chunks == 1 && __all_sync(__activemask(), end - beg <= 2)) {
+    // Every list of the warp has one or two entries (pooling maps): the entries stay in registers
+    // and four batch elements are in flight at once - one load per trip leaves the kernel waiting
+    // on latency.  (A warp with longer lists takes the general loop as a whole.)
     constexpr int UB = 4;
     const int n = end - beg;
     const int2 e0 = n >= 1 ? __ldg(a.ent + beg) : make_int2(0, 0);
