@@ -113,7 +113,8 @@ int mc_conv_dgrad(const mc_desc* d, const void* gy, const void* map, const void*
 size_t mc_conv_dgrad_workspace_bytes(const mc_desc* d);
 
 /* Tap table: the sample map decoded once - for every map entry the (up to four) source pixels and
- * interpolation weights, 32 bytes each.  Like the inverse map below it depends only on the map and
+ * interpolation weights, 32 bytes each (nearest maps: followed by a compact copy, one int per
+ * entry - the buffer is opaque, size it with mc_tapmap_bytes()).  Like the inverse map below it depends only on the map and
  * the image size, so a layer builds it once and passes it to every forward / weight-gradient call;
  * the tensor-core kernels then stream it with bulk copies instead of decoding the map again for
  * every batch.  mc_tapmap_bytes() is 0 when the descriptor has no tensor-core path.
