@@ -724,6 +724,16 @@ def run_profile_case(args):
         torch.cuda.synchronize()
         print("profile case pool batch %d done" % B)
         return
+    if args.profile_case == "resample":  # config 3: gather to the level-7 vertices and scatter back
+        from mappedconvolutions_b200.util import icosphere as ico
+        img = torch.rand(B, 3, 512, 1024, device=dev)
+        rm = ico.image_to_sphere_resample_map((512, 1024), 7).to(dev)
+        for _ in range(3):
+            v = ops.resample_from_map(img, rm, 1)
+            ops.resample_to_map(v, rm, 512, 1024, 1)
+        torch.cuda.synchronize()
+        print("profile case resample batch %d done" % B)
+        return
     bf = lambda *shape: torch.randn(*shape, device=dev).to(torch.bfloat16)
     x = bf(B, CIN, H, W).contiguous(memory_format=torch.channels_last)
     gy = bf(B, COUT, H, W).contiguous(memory_format=torch.channels_last)
@@ -747,7 +757,7 @@ def main():
     ap.add_argument("--workload", default="conv", choices=["conv", "resample", "pool", "knn", "encoder"],
                     help="conv (default) is the headline config; the others are the remaining configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", choices=["fwd", "bwd", "pool", "knn"],
+    ap.add_argument("--profile-case", choices=["fwd", "bwd", "pool", "knn", "resample"],
                     help="run three calls of the config-2 forward / backward at --batch and exit "
                          "(small case for profiler captures)")
     ap.add_argument("--batch", type=int, default=2, help="batch of --profile-case")

@@ -297,7 +297,9 @@ __global__ void __launch_bounds__(256) inv_gather_planes_kernel(const InvGatherA
   if (pl1 > nplanes) pl1 = nplanes;
   const T* __restrict__ g = (const T*)a.g;
   T* __restrict__ out = (T*)a.out;
-  if (__all_sync(__activemask(), end - beg <= 2)) {
+  // (Average unpooling only: the lists of a resample map are of mixed lengths, and the registers
+  // of this path would cost the general loop its occupancy.)
+  if (AVG && __all_sync(__activemask(), end - beg <= 2)) {
     // Every list of the warp has at most two entries (pooling maps): eight planes per trip, all
     // their loads issued before the first value is used.  The operations and their order are
     // those of the general loop below.  (A warp with longer lists takes the general loop as a
