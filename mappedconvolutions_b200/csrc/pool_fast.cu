@@ -343,6 +343,31 @@ __global__ void __launch_bounds__(256) inv_gather_planes_kernel(const InvGatherA
   for (int i = 0; i < 4; ++i) e4[i] = beg + i < end ? __ldg(a.ent + beg + i) : make_int2(0, 0);
   const int n4 = end - beg < 4 ? end - beg : 4;
   const bool longer = end - beg > 4;
+  if (!AVG && __all_sync(__activemask(), !longer)) {
+    // no list of the warp goes beyond the four entries held in registers: four planes per trip,
+    // their loads issued together (same operations and order as the loop below)
+    constexpr int UP = 4;
+    for (long pl = pl0; pl < pl1; pl += UP) {
+      float v[UP][4];
+#pragma unroll
+      for (int u = 0; u < UP; ++u) {
+        const T* src = g + (pl + u) * a.ngrid;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          v[u][i] = (i < n4 && pl + u < pl1) ? (float)ldv(src + e4[i].x) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < UP; ++u) {
+        if (pl + u >= pl1) break;
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (i < n4) acc = __fadd_rn(acc, __fmul_rn(__int_as_float(e4[i].y), v[u][i]));
+        stv(out + (pl + u) * a.npix + q, acc);
+      }
+    }
+    return;
+  }
   // four planes per trip: their (independent) loads are in flight together
 #pragma unroll 4
   for (long pl = pl0; pl < pl1; ++pl) {
