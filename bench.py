@@ -68,16 +68,22 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.n0 = index, None, [], 0
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
+            # nvidia-smi needs ~0.1 s before its first line: wait for it, so that the sampler is
+            # live when the timed region starts; the samples of the region are those after n0
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 1.5:
+                time.sleep(0.005)
+            self.n0 = len(self.lines)
         except OSError:
             self.proc = None
 
@@ -96,7 +102,10 @@ class ClockSampler:
         self.th.join(timeout=2)
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        # a region shorter than the sampling period: the last sample before it (the GPU is warm
+        # from the warm-up steps by then)
+        region = self.lines[self.n0:] or self.lines[-1:]
+        for ln in region:
             f = [s.strip() for s in ln.split(",")]
             if len(f) < 8:
                 continue
@@ -235,10 +244,10 @@ def run_ours(args):
 
     for _ in range(max(args.warmup, 3)):
         step()
-    barrier()
     sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
+    if sampler:  # (before the barrier: its start-up must not delay rank 0 inside the timed region)
         sampler.start()
+    barrier()
     n0 = L.mc_kernel_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -751,7 +760,7 @@ def run_profile_case(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="conv", choices=["conv", "resample", "pool", "knn", "encoder"],
