@@ -733,6 +733,21 @@ def run_profile_case(args):
         torch.cuda.synchronize()
         print("profile case pool batch %d done" % B)
         return
+    if args.profile_case == "first":  # config 5's first layer: 3 -> 64 channels on level-7 vertices
+        from mappedconvolutions_b200.util import icosphere as ico
+        n = ico.num_vertices(7)
+        cl = lambda t: t.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        x1 = cl(torch.randn(B, 3, 1, n, device=dev))
+        g1 = cl(torch.randn(B, 64, 1, n, device=dev))
+        w1 = (torch.randn(64, 3, 7, device=dev) * 0.1).to(torch.bfloat16)
+        b1 = torch.zeros(64, device=dev, dtype=torch.bfloat16)
+        km = ico.vertex_kernel_map(7).to(dev).contiguous()
+        for _ in range(3):
+            ops.mapped_conv_forward(x1, km, w1, b1, 7, 0)
+            ops.mapped_conv_backward(g1, km, x1, w1, b1, 7, 0, need_input_grad=False)
+        torch.cuda.synchronize()
+        print("profile case first batch %d done" % B)
+        return
     if args.profile_case == "resample":  # config 3: gather to the level-7 vertices and scatter back
         from mappedconvolutions_b200.util import icosphere as ico
         img = torch.rand(B, 3, 512, 1024, device=dev)
@@ -766,7 +781,7 @@ def main():
     ap.add_argument("--workload", default="conv", choices=["conv", "resample", "pool", "knn", "encoder"],
                     help="conv (default) is the headline config; the others are the remaining configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", choices=["fwd", "bwd", "pool", "knn", "resample"],
+    ap.add_argument("--profile-case", choices=["fwd", "bwd", "pool", "knn", "resample", "first"],
                     help="run three calls of the config-2 forward / backward at --batch and exit "
                          "(small case for profiler captures)")
     ap.add_argument("--batch", type=int, default=2, help="batch of --profile-case")
