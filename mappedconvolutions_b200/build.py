@@ -80,7 +80,10 @@ def build_torch_ext(force=False):
     hdrs = glob.glob(os.path.join(ROOT, "include", "*.h"))
     if not force and not _newer(out, [TORCH_EXT_SRC, LIB] + hdrs):
         return out
-    cxx = os.environ.get("CXX", "g++")
+    # The plain system compiler.  ($CXX is deliberately not consulted: a compiler wrapper that
+    # reorders the system include directories produced an extension whose error messages crashed
+    # while formatting integers; MC_CXX overrides.)
+    cxx = os.environ.get("MC_CXX", "g++")
     cuda_inc = os.path.join(os.path.dirname(os.path.dirname(NVCC)), "include")
     cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wno-deprecated-declarations",
            "-DTORCH_EXTENSION_NAME=" + TORCH_EXT_NAME, "-DTORCH_API_INCLUDE_EXTENSION_H",

@@ -43,7 +43,7 @@ int conv_tc_wgrad_launch(const mc_desc*, const void*, const void*, const void*, 
 }  // namespace mc
 
 namespace mc {
-unsigned long long g_launches = 0;
+std::atomic<unsigned long long> g_launches{0};
 }
 using namespace mc;
 
@@ -51,7 +51,7 @@ extern "C" {
 
 int mc_abi_version(void) { return 1; }
 
-uint64_t mc_kernel_launch_count(void) { return g_launches; }
+uint64_t mc_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* mc_strerror(int code) {
   switch (code) {

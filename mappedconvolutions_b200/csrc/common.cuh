@@ -14,6 +14,8 @@
 #include <float.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "mc_b200.h"
 
 namespace mc {
@@ -174,9 +176,9 @@ inline int grid_for(long n, int block, int max_blocks = 148 * 32) {
   return (int)g;
 }
 
-// Number of kernels this library has launched in this process (diagnostic, not thread-safe).
-extern unsigned long long g_launches;
-#define MC_COUNT(n) (mc::g_launches += (n))
+// Number of kernels this library has launched in this process (diagnostic).
+extern std::atomic<unsigned long long> g_launches;
+#define MC_COUNT(n) (mc::g_launches.fetch_add((n), std::memory_order_relaxed))
 
 #define MC_CHECK_LAUNCH()                                  \
   do {                                                     \

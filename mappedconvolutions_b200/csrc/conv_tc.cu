@@ -24,6 +24,11 @@
 // src/nn/cuda/mapped_convolution_layer.cu:39-70, :100-127, :155-190.
 #include <cub/device/device_scan.cuh>
 
+#include <atomic>
+#include <mutex>
+#include <set>
+#include <utility>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -48,13 +53,21 @@ struct Tiling {
   long npix;  // pixels per image of the tiled domain
   long mtot;  // batch * npix
   int W;      // width of the tiled domain
+  int B;      // batch
   int tiles, tile2d, tiles_x, tiles_per_img;
 };
+
+// 2-D tiles are numbered batch-innermost: tile = spatial tile * B + image.  The CTAs that run at the
+// same time then work on the same few spatial tiles of every image, so that a tile's slice of the
+// tap table comes from DRAM once and from L2 for the other B - 1 images.
+__host__ __device__ __forceinline__ int tile_img(const Tiling& t, int tile) { return tile % t.B; }
+__host__ __device__ __forceinline__ int tile_spatial(const Tiling& t, int tile) { return tile / t.B; }
 
 static bool make_tiling(Tiling& t, int B, int Hd, int Wd) {
   t.npix = (long)Hd * Wd;
   t.mtot = (long)B * t.npix;
   t.W = Wd;
+  t.B = B;
   t.tile2d = (Hd % 8 == 0 && Wd % 16 == 0) ? 1 : 0;  // 8 x 16 pixel tiles keep the footprint small
   t.tiles_x = Wd / 16;
   t.tiles_per_img = (Hd / 8) * (Wd / 16);
@@ -67,8 +80,8 @@ static bool make_tiling(Tiling& t, int B, int Hd, int Wd) {
 __device__ __forceinline__ void tile_pixel(const Tiling& t, int tile, int r, long& gp, int& img,
                                            long& p, bool& valid) {
   if (t.tile2d) {
-    img = tile / t.tiles_per_img;
-    const int tt = tile % t.tiles_per_img;
+    img = tile_img(t, tile);
+    const int tt = tile_spatial(t, tile);
     const int ty = tt / t.tiles_x, tx = tt % t.tiles_x;
     p = (long)(ty * 8 + (r >> 4)) * t.W + tx * 16 + (r & 15);
     gp = (long)img * t.npix + p;
@@ -170,8 +183,8 @@ __device__ __forceinline__ void decode_tile(const Source& s, const Tiling& t, in
   // per-tile constants (2-D tiles): image and the pixel of the tile's corner
   int img0 = 0, ty = 0, tx = 0;
   if (t.tile2d) {
-    img0 = tile / t.tiles_per_img;
-    const int tt = tile - img0 * t.tiles_per_img;
+    img0 = tile_img(t, tile);
+    const int tt = tile_spatial(t, tile);
     ty = tt / t.tiles_x;
     tx = tt - ty * t.tiles_x;
   }
@@ -399,8 +412,7 @@ __device__ __forceinline__ void loader_loop(const Source& s, const Tiling& t, ui
     if (!mbar_wait(tabbar0 + 16 + 8 * half, ph ^ 1, abort_flag, 0x72, 512)) return;
     const uint32_t dst0 = table0 + half * TILE_M * entb, bar = tabbar0 + 8 * half;
     if (t.tile2d) {
-      const int img = tile / t.tiles_per_img;
-      const int tt = tile - img * t.tiles_per_img;
+      const int tt = tile_spatial(t, tile);
       const int ty = tt / t.tiles_x, tx = tt - ty * t.tiles_x;
       mbar_expect_tx(bar, TILE_M * entb);
       for (int ry = 0; ry < 8; ++ry) {
@@ -456,7 +468,7 @@ __device__ __forceinline__ void producer_loop_map(const Source& s, const Tiling&
     // all-zero-weight entries that follow the two table halves
     const bf16 *s0, *s1;
     if (t.tile2d) {
-      s0 = s1 = srcl + (long)(tile / t.tiles_per_img) * s.spix * s.C;
+      s0 = s1 = srcl + (long)tile_img(t, tile) * s.spix * s.C;
     } else {
       const long g0 = (long)tile * TILE_M + r0, g1 = (long)tile * TILE_M + r1;
       const TapEnt* zero_ent = table + (size_t)2 * TILE_M * s.K;
@@ -555,7 +567,7 @@ __device__ __forceinline__ void producer_loop_packed(const Source& s, const Tili
     const TapEnt* t1 = tab + r1 * s.K;
     const bf16 *s0, *s1;
     if (t.tile2d) {
-      s0 = s1 = s.src + (long)(tile / t.tiles_per_img) * s.spix * C;
+      s0 = s1 = s.src + (long)tile_img(t, tile) * s.spix * C;
     } else {
       const long g0 = (long)tile * TILE_M + r0, g1 = (long)tile * TILE_M + r1;
       // rows past the end of the batch: entries of tap 0..K-1 with zero weights
@@ -930,7 +942,7 @@ __device__ __forceinline__ void producer_loop_copy(const Source& s, const Tiling
     const TapEnt* t1 = tab + r1 * s.K;
     const bf16 *s0, *s1;
     if (t.tile2d) {
-      s0 = s1 = srcl + (long)(tile / t.tiles_per_img) * s.spix * s.C;
+      s0 = s1 = srcl + (long)tile_img(t, tile) * s.spix * s.C;
     } else {
       const long g0 = (long)tile * TILE_M + r0, g1 = (long)tile * TILE_M + r1;
       const TapEnt* zero_ent = table + (size_t)2 * TILE_M * s.K;
@@ -1618,13 +1630,18 @@ __global__ void invtap_build_kernel(const int* __restrict__ off, const int2* __r
   }
 }
 
+constexpr int MAX_DEVICES = 64;
+
+// SM count of the current device (cached per device ordinal).
 static int sm_count() {
-  static int n = 0;
+  static std::atomic<int> cache[MAX_DEVICES];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 148;
+  int n = cache[dev].load(std::memory_order_relaxed);
   if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
+      return 148;  // not cached: asked again next time
+    cache[dev].store(n, std::memory_order_relaxed);
   }
   return n;
 }
@@ -1638,11 +1655,24 @@ static int pick_stages(size_t extra, int nfloat, int max_st, int min_st, bool ev
   return 0;
 }
 
-template <typename Kern>
-static bool allow_big_smem(Kern k) {
-  return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) ==
-         cudaSuccess;
+// Opts a kernel in to the full dynamic shared memory of the SM.  The attribute belongs to the
+// (device, kernel) pair, so it is set once per device the library is used on; a failure is not
+// remembered (the next call tries again).
+static bool allow_big_smem_ptr(const void* k) {
+  static std::mutex mu;
+  static std::set<std::pair<int, const void*>> done;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (done.count({dev, k})) return true;
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) !=
+      cudaSuccess)
+    return false;
+  done.insert({dev, k});
+  return true;
 }
+template <typename Kern>
+static bool allow_big_smem(Kern k) { return allow_big_smem_ptr(reinterpret_cast<const void*>(k)); }
 
 static bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
@@ -1722,19 +1752,16 @@ static int launch_gemm_n(const GemmArgs& a, const GemmPlan& p, bool pre, cudaStr
   const dim3 grid(gx, ny);
   if (p.wres) {
     if (pre) {
-      static bool attr = allow_big_smem(conv_gemm_tc_kernel<NOUT, CSR, true, true>);
-      if (!attr) return MC_ERR_LAUNCH;
+      if (!allow_big_smem(conv_gemm_tc_kernel<NOUT, CSR, true, true>)) return MC_ERR_LAUNCH;
       conv_gemm_tc_kernel<NOUT, CSR, true, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
     } else {
       if (CSR) return MC_ERR_UNSUPPORTED;
-      static bool attr = allow_big_smem(conv_gemm_tc_kernel<NOUT, false, false, true>);
-      if (!attr) return MC_ERR_LAUNCH;
+      if (!allow_big_smem(conv_gemm_tc_kernel<NOUT, false, false, true>)) return MC_ERR_LAUNCH;
       conv_gemm_tc_kernel<NOUT, false, false, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
     }
   } else {
     if (!pre) return MC_ERR_UNSUPPORTED;
-    static bool attr = allow_big_smem(conv_gemm_tc_kernel<NOUT, CSR, true, false>);
-    if (!attr) return MC_ERR_LAUNCH;
+    if (!allow_big_smem(conv_gemm_tc_kernel<NOUT, CSR, true, false>)) return MC_ERR_LAUNCH;
     conv_gemm_tc_kernel<NOUT, CSR, true, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   }
   MC_CHECK_LAUNCH();
@@ -1970,9 +1997,9 @@ static int launch_wgrad_n(const GemmArgs& a, const WgradPlan& p, bool pre, cudaS
   if (gx < 1) gx = 1;
   if (gx > a.t.tiles) gx = a.t.tiles;
   const dim3 grid(gx, p.groups, p.chunks);
-  static bool attr = allow_big_smem(conv_wgrad_tc_kernel<NOUT, false>) &&
-                     allow_big_smem(conv_wgrad_tc_kernel<NOUT, true>);
-  if (!attr) return MC_ERR_LAUNCH;
+  if (!allow_big_smem(conv_wgrad_tc_kernel<NOUT, false>) ||
+      !allow_big_smem(conv_wgrad_tc_kernel<NOUT, true>))
+    return MC_ERR_LAUNCH;
   if (pre) conv_wgrad_tc_kernel<NOUT, true><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   else conv_wgrad_tc_kernel<NOUT, false><<<grid, TC_THREADS, smem, st>>>(a), MC_COUNT(1);
   MC_CHECK_LAUNCH();

@@ -17,6 +17,7 @@
 #include <c10/cuda/CUDAStream.h>
 
 #include <list>
+#include <mutex>
 #include <tuple>
 #include <vector>
 
@@ -97,6 +98,34 @@ mc_desc make_desc(at::ScalarType dt, int layout, int64_t B, int64_t Cin, int64_t
 
 int64_t n_interp(const OptTensor& iw) { return iw.has_value() ? iw->size(-1) : 0; }
 
+// The C ABI takes raw pointers, so everything it would otherwise read past or misinterpret is
+// checked here: parameter and gradient dtypes equal to the input's (the reference raises through
+// weight.data<scalar_t>(), src/nn/cuda/mapped_convolution_layer.cu:57-65) and the shapes the
+// descriptor is built from.  w0 / w1: the weight's first two dimensions.
+void check_conv_args(const Tensor& input, const Tensor& sample_map, const Tensor& weight,
+                     const Tensor& bias, int64_t w0, int64_t w1, int64_t n_bias, int64_t K,
+                     const Tensor* grad_output = nullptr, at::IntArrayRef grad_shape = {}) {
+  TORCH_CHECK(input.dim() == 4, "input must be 4-D (B, C, H, W)");
+  TORCH_CHECK(sample_map.dim() >= 4 && sample_map.size(-1) == 2,
+              "sample_map must be (OH, OW, K, 2) or (OH, OW, K, P, 2)");
+  TORCH_CHECK(weight.scalar_type() == input.scalar_type(), "weight dtype ", weight.scalar_type(),
+              " does not match input dtype ", input.scalar_type());
+  TORCH_CHECK(bias.scalar_type() == input.scalar_type(), "bias dtype ", bias.scalar_type(),
+              " does not match input dtype ", input.scalar_type());
+  TORCH_CHECK(weight.dim() == 3 && weight.size(0) == w0 && weight.size(1) == w1 && weight.size(2) == K,
+              "weight must have shape (", w0, ", ", w1, ", ", K, "), got ", weight.sizes());
+  TORCH_CHECK(bias.numel() == n_bias, "bias must have ", n_bias, " elements, got ", bias.numel());
+  TORCH_CHECK(sample_map.size(2) == K, "sample_map.size(2) = ", sample_map.size(2),
+              " does not match kernel_size ", K);
+  TORCH_CHECK(weight.is_contiguous() && bias.is_contiguous(), "weight and bias must be contiguous");
+  if (grad_output) {
+    TORCH_CHECK(grad_output->scalar_type() == input.scalar_type(), "grad_output dtype ",
+                grad_output->scalar_type(), " does not match input dtype ", input.scalar_type());
+    TORCH_CHECK(grad_output->sizes() == grad_shape, "grad_output must have shape ", grad_shape,
+                ", got ", grad_output->sizes());
+  }
+}
+
 // Scratch buffer of at least n bytes (undefined tensor for n == 0).
 struct Scratch {
   Tensor t;
@@ -138,10 +167,19 @@ std::list<PlanEntry>& plan_cache() {
 }
 constexpr size_t PLAN_CACHE_SIZE = 8;
 
+std::mutex& plan_mutex() {
+  static std::mutex m;
+  return m;
+}
+
+// The cache is shared by all threads of the process (one lock around lookup, build and insert).
+// A plan is built on the caller's current stream, which is then synchronised once: later calls may
+// read the cached buffer from any stream without further ordering.
 template <typename Build>
 Tensor cached_plan(int kind, const mc_desc& d, const Tensor& map, Build build) {
   PlanKey key{kind, map.data_ptr(), (int64_t)map._version(), map.sizes().vec(), d.IH, d.IW, d.interp,
               (int)map.device().index()};
+  std::lock_guard<std::mutex> lock(plan_mutex());
   auto& c = plan_cache();
   for (auto it = c.begin(); it != c.end(); ++it) {
     if (it->key == key && !it->owner.expired() &&
@@ -151,6 +189,7 @@ Tensor cached_plan(int kind, const mc_desc& d, const Tensor& map, Build build) {
     }
   }
   Tensor buf = build();
+  c10::cuda::getCurrentCUDAStream().synchronize();
   c.push_front(PlanEntry{key, c10::weak_intrusive_ptr<c10::TensorImpl>(map.getIntrusivePtr()), buf});
   while (c.size() > PLAN_CACHE_SIZE) c.pop_back();
   return buf;
@@ -177,7 +216,10 @@ Tensor tap_map(const mc_desc& d, const Tensor& map) {
   });
 }
 
-void clear_plan_cache() { plan_cache().clear(); }
+void clear_plan_cache() {
+  std::lock_guard<std::mutex> lock(plan_mutex());
+  plan_cache().clear();
+}
 
 Tensor channels_last(const Tensor& t) { return t.contiguous(at::MemoryFormat::ChannelsLast); }
 
@@ -197,8 +239,9 @@ bool via_channels_last(const Tensor& input, const OptTensor& iw, mc_desc d_nhwc)
 Tensor conv_forward(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
                     const Tensor& weight, const Tensor& bias, int64_t K, int64_t interp,
                     bool nhwc = false) {
+  TORCH_CHECK(input.dim() == 4 && weight.dim() == 3, "input must be 4-D, weight 3-D");
+  check_conv_args(input, sample_map, weight, bias, weight.size(0), input.size(1), weight.size(0), K);
   const auto dev = need_cuda({&input, &sample_map, opt(iw), &weight, &bias});
-  TORCH_CHECK(input.dim() == 4 && sample_map.dim() >= 3, "input must be 4-D, the map (OH, OW, K, ..)");
   const int64_t B = input.size(0), Cin = input.size(1), IH = input.size(2), IW = input.size(3);
   const int64_t Cout = weight.size(0), OH = sample_map.size(0), OW = sample_map.size(1);
   if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH,
@@ -227,6 +270,11 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
                                   const OptTensor& iw, const Tensor& input, const Tensor& weight,
                                   const Tensor& bias, int64_t K, int64_t interp,
                                   bool need_input_grad, bool nhwc = false) {
+  TORCH_CHECK(input.dim() == 4 && weight.dim() == 3 && sample_map.dim() >= 4,
+              "input must be 4-D, weight 3-D, the map (OH, OW, K, ..)");
+  check_conv_args(input, sample_map, weight, bias, weight.size(0), input.size(1), weight.size(0), K,
+                  &grad_output_in,
+                  {input.size(0), weight.size(0), sample_map.size(0), sample_map.size(1)});
   const auto dev = need_cuda({&grad_output_in, &sample_map, opt(iw), &input, &weight, &bias});
   const int64_t B = input.size(0), Cin = input.size(1), IH = input.size(2), IW = input.size(3);
   const int64_t Cout = weight.size(0), OH = sample_map.size(0), OW = sample_map.size(1);
@@ -277,6 +325,10 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
 Tensor tconv_forward(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
                      const Tensor& weight, const Tensor& bias, int64_t OHt, int64_t OWt, int64_t K,
                      int64_t interp, bool nhwc = false) {
+  TORCH_CHECK(input.dim() == 4 && weight.dim() == 3, "input must be 4-D, weight 3-D");
+  check_conv_args(input, sample_map, weight, bias, input.size(1), weight.size(1), weight.size(1), K);
+  TORCH_CHECK(sample_map.size(0) == input.size(2) && sample_map.size(1) == input.size(3),
+              "the sample map of a transposed convolution has the size of the input");
   const auto dev = need_cuda({&input, &sample_map, opt(iw), &weight, &bias});
   const int64_t B = input.size(0), Cin = input.size(1), H = input.size(2), W = input.size(3);
   const int64_t Cout = weight.size(1);
@@ -312,6 +364,13 @@ std::vector<Tensor> tconv_backward(const Tensor& grad_output_in, const Tensor& s
                                    const OptTensor& iw, const Tensor& input, const Tensor& weight,
                                    const Tensor& bias, int64_t K, int64_t interp,
                                    bool nhwc = false) {
+  TORCH_CHECK(input.dim() == 4 && weight.dim() == 3 && grad_output_in.dim() == 4,
+              "input and grad_output must be 4-D, weight 3-D");
+  check_conv_args(input, sample_map, weight, bias, input.size(1), weight.size(1), weight.size(1), K,
+                  &grad_output_in,
+                  {input.size(0), weight.size(1), grad_output_in.size(2), grad_output_in.size(3)});
+  TORCH_CHECK(sample_map.size(0) == input.size(2) && sample_map.size(1) == input.size(3),
+              "the sample map of a transposed convolution has the size of the input");
   const auto dev = need_cuda({&grad_output_in, &sample_map, opt(iw), &input, &weight, &bias});
   const int64_t B = input.size(0), Cin = input.size(1), H = input.size(2), W = input.size(3);
   const int64_t Cout = weight.size(1);
@@ -387,6 +446,13 @@ std::vector<Tensor> max_pool(const Tensor& input, const Tensor& sample_map, cons
 
 Tensor max_unpool(const Tensor& grad_output_in, const Tensor& idx_mask, const Tensor& sample_map,
                   const OptTensor& iw, int64_t IH, int64_t IW, int64_t K, int64_t interp) {
+  TORCH_CHECK(idx_mask.scalar_type() == at::kLong, "idx_mask must be int64, got ", idx_mask.scalar_type());
+  TORCH_CHECK(idx_mask.sizes() == grad_output_in.sizes(), "idx_mask shape ", idx_mask.sizes(),
+              " does not match grad_output shape ", grad_output_in.sizes());
+  TORCH_CHECK(grad_output_in.dim() == 4 && sample_map.dim() >= 3 &&
+                  grad_output_in.size(2) == sample_map.size(0) &&
+                  grad_output_in.size(3) == sample_map.size(1),
+              "grad_output must live on the map grid");
   const auto dev = need_cuda({&grad_output_in, &idx_mask, &sample_map, opt(iw)});
   const int layout = idx_mask.dim() == 4 ? layout_of(idx_mask) : MC_NCHW;
   const Tensor grad_output = as_layout(grad_output_in, layout);
@@ -588,5 +654,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // KNNForward, include/util/layers/knn_layer.h:25-35 -> [idx (B,k,N) int64 1-based, dist]
   m.def("knn_forward", &knn_forward);
   m.def("clear_plan_cache", &clear_plan_cache);
+  // Synchronises the current stream and returns the device status word (0 = every kernel ran to
+  // completion; otherwise the code of the first bounded device-side wait that ran out, after which
+  // the kernel returned early and its output is invalid).  reset clears the word.
+  m.def("device_status", [](bool reset) { return mc_device_status(cur_stream(), reset ? 1 : 0); },
+        py::arg("reset") = true);
   m.def("abi_version", []() { return mc_abi_version(); });
 }

@@ -74,6 +74,38 @@ def _map_args(x, sample_map, interp_weights):
     return sample_map, interp_weights
 
 
+def _check_conv_args(input, sample_map, weight, bias, w0, w1, n_bias, kernel_size, grad_output=None,
+                     grad_shape=None):
+    """The C ABI takes raw pointers: parameter / gradient dtypes must equal the input's (the
+    reference raises through weight.data<scalar_t>(), src/nn/cuda/mapped_convolution_layer.cu:57-65)
+    and the shapes must be the ones the descriptor is built from."""
+    if input.dim() != 4:
+        raise RuntimeError("input must be 4-D (B, C, H, W)")
+    if sample_map.dim() < 4 or sample_map.shape[-1] != 2:
+        raise RuntimeError("sample_map must be (OH, OW, K, 2) or (OH, OW, K, P, 2)")
+    if weight.dtype != input.dtype:
+        raise RuntimeError("weight dtype %s does not match input dtype %s" % (weight.dtype, input.dtype))
+    if bias.dtype != input.dtype:
+        raise RuntimeError("bias dtype %s does not match input dtype %s" % (bias.dtype, input.dtype))
+    if tuple(weight.shape) != (w0, w1, kernel_size):
+        raise RuntimeError("weight must have shape (%d, %d, %d), got %s"
+                           % (w0, w1, kernel_size, tuple(weight.shape)))
+    if bias.numel() != n_bias:
+        raise RuntimeError("bias must have %d elements, got %d" % (n_bias, bias.numel()))
+    if sample_map.shape[2] != kernel_size:
+        raise RuntimeError("sample_map.size(2) = %d does not match kernel_size %d"
+                           % (sample_map.shape[2], kernel_size))
+    if not weight.is_contiguous() or not bias.is_contiguous():
+        raise RuntimeError("weight and bias must be contiguous")
+    if grad_output is not None:
+        if grad_output.dtype != input.dtype:
+            raise RuntimeError("grad_output dtype %s does not match input dtype %s"
+                               % (grad_output.dtype, input.dtype))
+        if tuple(grad_output.shape) != tuple(grad_shape):
+            raise RuntimeError("grad_output must have shape %s, got %s"
+                               % (tuple(grad_shape), tuple(grad_output.shape)))
+
+
 def _desc(x_dtype, layout, B, C_in, C_out, IH, IW, OH, OW, K, P, interp):
     if x_dtype not in _DT:
         raise RuntimeError("unsupported dtype %s (float32, float64, bfloat16)" % x_dtype)
@@ -173,6 +205,9 @@ def _tensor_core_via_channels_last(input, interp_weights, make_desc):
 
 def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, interpolation,
                   _nhwc=False):
+    _check_conv_args(input, sample_map, weight, bias, weight.shape[0] if weight.dim() else 0,
+                     input.shape[1] if input.dim() > 1 else 0, weight.shape[0] if weight.dim() else 0,
+                     kernel_size)
     dev = _need_cuda(input, sample_map, interp_weights, weight, bias)
     if not _nhwc and _tensor_core_via_channels_last(
             input, interp_weights,
@@ -206,6 +241,10 @@ def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, 
 
 def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
                    interpolation, need_input_grad=True, _nhwc=False):
+    _check_conv_args(input, sample_map, weight, bias, weight.shape[0] if weight.dim() else 0,
+                     input.shape[1] if input.dim() > 1 else 0, weight.shape[0] if weight.dim() else 0,
+                     kernel_size, grad_output,
+                     (input.shape[0], weight.shape[0], sample_map.shape[0], sample_map.shape[1]))
     dev = _need_cuda(grad_output, sample_map, interp_weights, input, weight, bias)
     if not _nhwc and _tensor_core_via_channels_last(
             input, interp_weights,
@@ -290,6 +329,11 @@ def weighted_mapped_conv_backward(grad_output, sample_map, interp_weights, input
 
 def _tconv_forward(input, sample_map, interp_weights, weight, bias, output_height, output_width,
                    kernel_size, interpolation, _nhwc=False):
+    _check_conv_args(input, sample_map, weight, bias, input.shape[1] if input.dim() > 1 else 0,
+                     weight.shape[1] if weight.dim() > 1 else 0,
+                     weight.shape[1] if weight.dim() > 1 else 0, kernel_size)
+    if tuple(sample_map.shape[:2]) != tuple(input.shape[2:]):
+        raise RuntimeError("the sample map of a transposed convolution has the size of the input")
     dev = _need_cuda(input, sample_map, interp_weights, weight, bias)
     if not _nhwc and _tensor_core_via_channels_last(
             input, interp_weights,
@@ -327,6 +371,14 @@ def _tconv_forward(input, sample_map, interp_weights, weight, bias, output_heigh
 
 def _tconv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
                     interpolation, _nhwc=False):
+    if grad_output.dim() != 4:
+        raise RuntimeError("grad_output must be 4-D")
+    _check_conv_args(input, sample_map, weight, bias, input.shape[1] if input.dim() > 1 else 0,
+                     weight.shape[1] if weight.dim() > 1 else 0,
+                     weight.shape[1] if weight.dim() > 1 else 0, kernel_size, grad_output,
+                     (input.shape[0], weight.shape[1], grad_output.shape[2], grad_output.shape[3]))
+    if tuple(sample_map.shape[:2]) != tuple(input.shape[2:]):
+        raise RuntimeError("the sample map of a transposed convolution has the size of the input")
     dev = _need_cuda(grad_output, sample_map, interp_weights, input, weight, bias)
     if not _nhwc and _tensor_core_via_channels_last(
             input, interp_weights,
@@ -437,6 +489,13 @@ def _max_pool(input, sample_map, interp_weights, kernel_size, interpolation):
 
 def _max_unpool(grad_output, idx_mask, sample_map, interp_weights, input_height, input_width,
                 kernel_size, interpolation):
+    if idx_mask.dtype != torch.int64:
+        raise RuntimeError("idx_mask must be int64, got %s" % idx_mask.dtype)
+    if tuple(idx_mask.shape) != tuple(grad_output.shape):
+        raise RuntimeError("idx_mask shape %s does not match grad_output shape %s"
+                           % (tuple(idx_mask.shape), tuple(grad_output.shape)))
+    if grad_output.dim() != 4 or tuple(grad_output.shape[2:]) != tuple(sample_map.shape[:2]):
+        raise RuntimeError("grad_output must live on the map grid")
     dev = _need_cuda(grad_output, idx_mask, sample_map, interp_weights)
     layout = _layout(idx_mask) if idx_mask.dim() == 4 else _lib.MC_NCHW
     grad_output = _as_layout(grad_output, layout)

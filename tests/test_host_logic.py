@@ -102,3 +102,63 @@ def test_compiled_extension_carries_the_reference_surface():
               if not n.startswith("_") and f.__module__ == ops.__name__ and n != "clear_inverse_map_cache"]
     assert len(public) >= 21 and all(hasattr(host.impl, n) for n in public)
     assert host.impl.abi_version() == 1
+
+
+def _both_bindings():
+    from mappedconvolutions_b200 import host, ops
+    return [ops] + ([host.impl] if host.COMPILED else [])
+
+
+@pytest.mark.parametrize("which", [0, 1])
+def test_bindings_refuse_mismatched_parameters(which):
+    """The C ABI takes raw pointers, so both host bindings check parameter / gradient dtypes and
+    shapes before anything reaches it (the reference raises through weight.data<scalar_t>(),
+    src/nn/cuda/mapped_convolution_layer.cu:57-65).  The checks come before the device check, so
+    they can be exercised with CPU tensors."""
+    b = _both_bindings()
+    if which >= len(b):
+        pytest.skip("compiled extension not built")
+    o = b[which]
+    x = torch.zeros(2, 4, 5, 6)
+    m = torch.zeros(5, 6, 3, 2)
+    w, bias = torch.zeros(7, 4, 3), torch.zeros(7)
+    gy = torch.zeros(2, 7, 5, 6)
+    bf = torch.bfloat16
+    # a well-formed CPU call gets as far as the device check
+    with pytest.raises(RuntimeError, match="CUDA only"):
+        o.mapped_conv_forward(x, m, w, bias, 3, 1)
+    with pytest.raises(RuntimeError, match="weight dtype"):
+        o.mapped_conv_forward(x.to(bf), m, w, bias, 3, 1)          # fp32 layer fed bf16 input
+    with pytest.raises(RuntimeError, match="weight dtype"):
+        o.mapped_conv_forward(x.double(), m.double(), w, bias, 3, 1)
+    with pytest.raises(RuntimeError, match="bias dtype"):
+        o.mapped_conv_forward(x, m, w, bias.double(), 3, 1)
+    with pytest.raises(RuntimeError, match="weight must have shape"):
+        o.mapped_conv_forward(x, m, torch.zeros(7, 5, 3), bias, 3, 1)  # C_in mismatch
+    with pytest.raises(RuntimeError, match="weight must have shape"):
+        o.mapped_conv_forward(x, m, torch.zeros(7, 4, 2), bias, 3, 1)  # K mismatch
+    with pytest.raises(RuntimeError, match="bias must have"):
+        o.mapped_conv_forward(x, m, w, torch.zeros(6), 3, 1)
+    with pytest.raises(RuntimeError, match="sample_map.size"):
+        o.mapped_conv_forward(x, torch.zeros(5, 6, 4, 2), torch.zeros(7, 4, 4), bias, 3, 1) \
+            if False else o.mapped_conv_forward(x, torch.zeros(5, 6, 4, 2), w, bias, 3, 1)
+    with pytest.raises(RuntimeError, match="grad_output dtype"):
+        o.mapped_conv_backward(gy.double(), m, x, w, bias, 3, 1)
+    with pytest.raises(RuntimeError, match="grad_output must have shape"):
+        o.mapped_conv_backward(torch.zeros(2, 7, 5, 5), m, x, w, bias, 3, 1)
+    # transposed layer: weight (C_in, C_out, K), map of the input's size
+    wt = torch.zeros(4, 7, 3)
+    with pytest.raises(RuntimeError, match="CUDA only"):
+        o.mapped_transposed_conv_forward(x, m, wt, bias, 9, 9, 3, 1)
+    with pytest.raises(RuntimeError, match="weight must have shape"):
+        o.mapped_transposed_conv_forward(x, m, w, bias, 9, 9, 3, 1)
+    with pytest.raises(RuntimeError, match="weight dtype"):
+        o.mapped_transposed_conv_backward(torch.zeros(2, 7, 9, 9), m, x, wt.double(), bias, 3, 1)
+    with pytest.raises(RuntimeError, match="size of the input"):
+        o.mapped_transposed_conv_forward(x, torch.zeros(4, 6, 3, 2), wt, bias, 9, 9, 3, 1)
+    # max unpooling: int64 offsets of grad_output's shape
+    g = torch.zeros(2, 4, 5, 6)
+    with pytest.raises(RuntimeError, match="idx_mask must be int64"):
+        o.mapped_max_unpool(g, torch.zeros(2, 4, 5, 6, dtype=torch.int32), m, 8, 8, 3, 0)
+    with pytest.raises(RuntimeError, match="idx_mask shape"):
+        o.mapped_max_unpool(g, torch.zeros(2, 4, 5, 5, dtype=torch.int64), m, 8, 8, 3, 0)
