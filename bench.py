@@ -44,7 +44,7 @@ BATCH = 8  # per GPU
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at batch 8, scaled from ncu captures of
-# the batch-2 case (profiles/conv_tc_kernels_config2_b2.md explains the scaling)
+# a batch-2 case (every term grows with the batch)
 DRAM_TRAFFIC_BYTES = {"conv_fwd": 2.21e9, "conv_dgrad": 2.25e9, "conv_wgrad": 2.30e9}
 
 
@@ -121,9 +121,30 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _map_builders():
+    """The pure-torch sample-map builders, loaded by file path: importing the product package would
+    load its CUDA libraries, which the CPU arm must not touch."""
+    import importlib.util
+    path = os.path.join(ROOT, "mappedconvolutions_b200", "util", "spherical_projections.py")
+    spec = importlib.util.spec_from_file_location("_bench_spherical_projections", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _all_host_threads():
+    """torchrun pins OMP_NUM_THREADS=1 for its workers; the CPU legs are meant to use every host
+    core this process may run on."""
+    import torch
+    ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(ncpu)
+    torch.set_num_threads(ncpu)
+    return ncpu
+
+
 def make_inputs(batch, seed):
     import torch
-    from mappedconvolutions_b200.util import get_projection_map
+    get_projection_map = _map_builders().get_projection_map
     g = torch.Generator().manual_seed(seed)
     bf = torch.bfloat16
     x = torch.randn(batch, CIN, H, W, generator=g).to(bf).contiguous(memory_format=torch.channels_last)
@@ -155,6 +176,7 @@ def cpu_step(O, x, gy, w, b, m):
 def cpu_baseline(reps=1, warm=0):
     """fp32 forward + backward of ONE batch element of the workload on the host cores."""
     import torch
+    _all_host_threads()
     O, kind = cpu_ops()
     x, gy, w, b, m = make_inputs(1, 1)
     x, gy, w, b = [t.float().contiguous() for t in (x, gy, w, b)]
@@ -175,11 +197,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    # torchrun pins OMP_NUM_THREADS=1 for its workers; the CPU arm is meant to use every host core
-    ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    os.environ["OMP_NUM_THREADS"] = str(ncpu)
     import torch
-    torch.set_num_threads(ncpu)
+    _all_host_threads()
     O, kind = cpu_ops()
     x, gy, w, b, m = make_inputs(1, 1)
     x, gy, w, b = [t.float().contiguous() for t in (x, gy, w, b)]
@@ -258,6 +277,9 @@ def run_ours(args):
     launches = L.mc_kernel_launch_count() - n0
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler else None
+    # a bounded device-side wait that ran out makes a kernel return early: such a run is no result
+    status = L.mc_device_status(torch.cuda.current_stream().cuda_stream, 1)
+    assert status == 0, "device status word raised during the timed region: %d" % status
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -397,7 +419,7 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e / e2e_steps},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "device_status": int(status),
             "roofline": roof, "cpu_baseline": cpu}))
     if world > 1:
         dist.destroy_process_group()

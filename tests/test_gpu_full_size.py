@@ -205,3 +205,61 @@ def test_config5_encoder_gradients_add_up_over_the_batch():
     b, _ = grads(_cl(x[32:]))
     for gw, ga, gb in zip(whole, a, b):
         H.assert_close(gw, ga + gb, 2e-2, "gradient over the batch")
+
+
+# Each layer of the config-5 encoder at its REAL size (one batch element, which the oracle finishes
+# in seconds): (C_in, C_out, mesh level).  7-tap one-ring maps, nearest, bf16 channels-last.
+ENCODER_LAYERS = [(3, 64, 7), (64, 128, 6), (128, 256, 5), (256, 256, 5)]
+
+
+@pytest.mark.parametrize("cin,cout,level", ENCODER_LAYERS)
+def test_config5_layer_against_oracle(cin, cout, level):
+    """Forward, input gradient, weight gradient and bias gradient of one encoder layer at its full
+    vertex count against the oracle (float32 on the bf16-rounded operands, tolerance 2e-2), and
+    element e of a batch-4 call bit-equal to the batch-1 call (no atomics in fwd / dgrad)."""
+    from mappedconvolutions_b200 import ops
+    from mappedconvolutions_b200.util import icosphere as ico
+    g = torch.Generator().manual_seed(50 + level + cin)
+    n, K, B = ico.num_vertices(level), 7, 4
+    bf = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)
+    x, gy = bf(B, cin, 1, n), bf(B, cout, 1, n)
+    w = (torch.randn(cout, cin, K, generator=g) / (cin * K) ** 0.5).to(torch.bfloat16)
+    b = bf(cout)
+    m = ico.vertex_kernel_map(level)
+    xd, gd, md = _cl(x.to(DEV)), _cl(gy.to(DEV)), m.to(DEV)
+    y = ops.mapped_conv_forward(xd, md, w.to(DEV), b.to(DEV), K, 0)
+    gx, gw, gb = ops.mapped_conv_backward(gd, md, xd, w.to(DEV), b.to(DEV), K, 0)
+    e = 2
+    y1 = ops.mapped_conv_forward(_cl(xd[e:e + 1]), md, w.to(DEV), b.to(DEV), K, 0)
+    g1 = ops.mapped_conv_backward(_cl(gd[e:e + 1]), md, _cl(xd[e:e + 1]), w.to(DEV), b.to(DEV), K, 0)
+    assert torch.equal(y1[0], y[e]) and torch.equal(g1[0][0], gx[e])
+    xc, gc = x[e:e + 1].float().contiguous(), gy[e:e + 1].float().contiguous()
+    want_y = oracle.mapped_conv_forward(xc, m, w.float(), b.float(), K, 0)
+    want_g = oracle.mapped_conv_backward(gc, m, xc, w.float(), b.float(), K, 0)
+    H.assert_close(y1.float(), want_y, 2e-2, "y vs oracle")
+    H.assert_close(g1[0].float(), want_g[0], 2e-2, "grad_x vs oracle")
+    H.assert_close(g1[1].float(), want_g[1], 2e-2, "grad_w vs oracle")
+    H.assert_close(g1[2].float(), want_g[2], 2e-2, "grad_b vs oracle")
+    # the batch-4 weight gradient is the sum of the per-element ones
+    acc = sum(ops.mapped_conv_backward(_cl(gd[i:i + 1]), md, _cl(xd[i:i + 1]), w.to(DEV), b.to(DEV),
+                                       K, 0)[1].float() for i in range(B))
+    H.assert_close(gw.float(), acc, 2e-2, "grad_w batch sum")
+
+
+@pytest.mark.parametrize("ch,level", [(64, 7), (128, 6)])
+def test_config5_pooling_against_oracle(ch, level):
+    """The two average-pooling steps of the encoder (level 7 -> 6 on 64 channels, 6 -> 5 on 128),
+    forward and unpooling, bf16 channels-last, one element against the oracle."""
+    from mappedconvolutions_b200 import ops
+    from mappedconvolutions_b200.util import icosphere as ico
+    g = torch.Generator().manual_seed(60 + level)
+    n_hi, n_lo = ico.num_vertices(level), ico.num_vertices(level - 1)
+    x = torch.randn(2, ch, 1, n_hi, generator=g).to(torch.bfloat16)
+    gy = torch.randn(2, ch, 1, n_lo, generator=g).to(torch.bfloat16)
+    m = ico.pooling_map(level)
+    y = ops.mapped_avg_pool(_cl(x.to(DEV)), m.to(DEV), 7, 0)
+    gx = ops.mapped_avg_unpool(_cl(gy.to(DEV)), m.to(DEV), 1, n_hi, 7, 0)
+    want_y = oracle.mapped_avg_pool(x[1:2].float().contiguous(), m, 7, 0)
+    want_gx = oracle.mapped_avg_unpool(gy[1:2].float().contiguous(), m, 1, n_hi, 7, 0)
+    H.assert_close(y[1:2].float(), want_y, 2e-2, "avg pool vs oracle")
+    H.assert_close(gx[1:2].float(), want_gx, 2e-2, "avg unpool vs oracle")
