@@ -433,6 +433,7 @@ def run_secondary(args):
     import torch
     from mappedconvolutions_b200 import _lib
     from mappedconvolutions_b200.host import impl as ops  # the PyTorch C++ extension
+    from mappedconvolutions_b200 import util as mutil
     from mappedconvolutions_b200.util import icosphere as ico
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
@@ -445,7 +446,7 @@ def run_secondary(args):
     if wl == "resample":
         # config 3: equirect 512x1024x3 fp32 image (U[0,1]), batch 16, <-> icosphere level-7 vertices
         img_h = torch.rand(16, 3, 512, 1024, generator=g)
-        m = ico.image_to_sphere_resample_map((512, 1024), 7)
+        m = mutil.image_to_sphere_resample_map((512, 1024), mutil.generate_icosphere(7))
         img, md = img_h.to(dev), m.to(dev)
         verts = ops.resample_from_map(img, md, 1)
 
@@ -512,8 +513,7 @@ def run_secondary(args):
                         kind=kind, sample="2 of 32 batch elements, avg + max pool, %.3f s" % dt)
     else:
         # config 4b: k = 9 nearest neighbours among the 163 842 unit-sphere vertices of level 7
-        v, _ = ico.generate_icosphere(7)
-        p_h = torch.from_numpy(v).float().t().contiguous().unsqueeze(0)
+        p_h = mutil.generate_icosphere(7).get_vertices().t().contiguous().unsqueeze(0)
         p = p_h.to(dev)
         n = p.shape[2]
 
@@ -605,6 +605,7 @@ ENC_BATCH = 64
 
 def encoder_flops(batch):
     """fwd + dgrad + wgrad GEMM flops of the four convolutions (the first has no dgrad)."""
+    from mappedconvolutions_b200 import util as mutil
     from mappedconvolutions_b200.util import icosphere as ico
     tot = 0.0
     for i in range(4):
@@ -617,6 +618,7 @@ def run_encoder(args):
     import torch
     import torch.distributed as dist
     from mappedconvolutions_b200 import _lib, nn as mnn, dist as mdist
+    from mappedconvolutions_b200 import util as mutil
     from mappedconvolutions_b200.util import icosphere as ico
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
@@ -736,15 +738,16 @@ def run_profile_case(args):
     torch.manual_seed(0)
     B = args.batch
     if args.profile_case == "knn":  # config 4's k-NN on the 40 962 vertices of level 6
+        from mappedconvolutions_b200 import util as mutil
         from mappedconvolutions_b200.util import icosphere as ico
-        v, _ = ico.generate_icosphere(6)
-        p = torch.from_numpy(v).float().t().contiguous().unsqueeze(0).to(dev)
+        p = mutil.generate_icosphere(6).get_vertices().t().contiguous().unsqueeze(0).to(dev)
         for _ in range(3):
             ops.knn_forward(p, p, 9)
         torch.cuda.synchronize()
         print("profile case knn done")
         return
     if args.profile_case == "pool":  # config 4 at a reduced batch: avg pool, max pool, avg unpool
+        from mappedconvolutions_b200 import util as mutil
         from mappedconvolutions_b200.util import icosphere as ico
         x = torch.randn(B, 128, 1, ico.num_vertices(7), device=dev)
         pm = ico.pooling_map(7).to(dev)
@@ -756,6 +759,7 @@ def run_profile_case(args):
         print("profile case pool batch %d done" % B)
         return
     if args.profile_case == "first":  # config 5's first layer: 3 -> 64 channels on level-7 vertices
+        from mappedconvolutions_b200 import util as mutil
         from mappedconvolutions_b200.util import icosphere as ico
         n = ico.num_vertices(7)
         cl = lambda t: t.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
@@ -771,9 +775,10 @@ def run_profile_case(args):
         print("profile case first batch %d done" % B)
         return
     if args.profile_case == "resample":  # config 3: gather to the level-7 vertices and scatter back
+        from mappedconvolutions_b200 import util as mutil
         from mappedconvolutions_b200.util import icosphere as ico
         img = torch.rand(B, 3, 512, 1024, device=dev)
-        rm = ico.image_to_sphere_resample_map((512, 1024), 7).to(dev)
+        rm = mutil.image_to_sphere_resample_map((512, 1024), mutil.generate_icosphere(7)).to(dev)
         for _ in range(3):
             v = ops.resample_from_map(img, rm, 1)
             ops.resample_to_map(v, rm, 512, 1024, 1)
@@ -784,7 +789,7 @@ def run_profile_case(args):
     x = bf(B, CIN, H, W).contiguous(memory_format=torch.channels_last)
     gy = bf(B, COUT, H, W).contiguous(memory_format=torch.channels_last)
     w, b = bf(COUT, CIN, K), bf(COUT)
-    m = get_projection_map((H, W), (3, 3)).to(dev)
+    m = get_projection_map((H, W), (3, 3), "gnomonic").to(dev)
     for _ in range(3):
         if args.profile_case == "fwd":
             ops.mapped_conv_forward(x, m, w, b, K, 1)

@@ -220,6 +220,21 @@ int mc_resample_scatter(const mc_desc* d, const void* x, const void* map, const 
 int mc_knn(const float* ref, const float* query, int32_t B, int32_t D, int32_t M, int32_t N,
            int32_t k, int64_t* idx, float* dist, void* stream);
 
+/* ---- point location on the icosphere hierarchy ------------------------------------------------
+ * samples (n, 2) float (lon, lat) radians.  Levels 0..order of the mesh hierarchy are given as host
+ * arrays of DEVICE pointers: vertices[l] (V_l, 3) float, face_vertices[l] (F_l, 3) int32 (the
+ * vertices of every face in its half-edge walk order), face_adjacent[l] (F_l, 3) int32 (the faces
+ * across the three half-edges), num_faces[l] = F_l; children of face f of level l are faces
+ * 4 f .. 4 f + 3 of level l + 1.  Outputs: face_idx (n) int64 face of level `order` hit by the ray
+ * of every sample (-1: not found), vertex_idx (n, 3) int64 its vertices (walk vertices 2, 1, 0),
+ * weights (n, 3) float their barycentric weights (one-hot of the largest when nearest != 0).
+ * Replaces Sphere::getPlanarConvolutionOperatorFromSamples, src/util/cpp/sphere.cpp:1116-1270
+ * (search :1007-1053, face test :1055-1105), a host OpenMP loop in the reference.  order <= 11. */
+int mc_sphere_locate(const float* samples, int64_t n, int32_t order, const float* const* vertices,
+                     const int32_t* const* face_vertices, const int32_t* const* face_adjacent,
+                     const int32_t* num_faces, int32_t nearest, int64_t* face_idx,
+                     int64_t* vertex_idx, float* weights, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

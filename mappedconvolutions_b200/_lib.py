@@ -66,6 +66,9 @@ SIGNATURES = {
     "mc_resample_gather": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp]),
     "mc_resample_scatter": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_knn": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "mc_sphere_locate": (ctypes.c_int, [_vp, ctypes.c_int64, _i32, ctypes.POINTER(_vp),
+                                        ctypes.POINTER(_vp), ctypes.POINTER(_vp),
+                                        ctypes.POINTER(_i32), _i32, _vp, _vp, _vp, _vp]),
 }
 
 

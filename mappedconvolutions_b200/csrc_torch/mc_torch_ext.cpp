@@ -223,6 +223,14 @@ void clear_plan_cache() {
 
 Tensor channels_last(const Tensor& t) { return t.contiguous(at::MemoryFormat::ChannelsLast); }
 
+// The tensor-core kernels read rows with 16-byte vector loads and bulk copies.  A view into a larger
+// tensor (a batch slice, a map slice) can start on any element boundary: such a tensor is copied
+// into a fresh allocation, which the caching allocator aligns to 512 bytes.
+Tensor aligned16(const Tensor& t) {
+  if ((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0) return t;
+  return t.clone(at::MemoryFormat::Preserve);
+}
+
 // bfloat16 tensors in the reference's NCHW layout: the tensor-core kernels want channels-last, and
 // two extra layout passes cost far less than the generic kernels.  (A single-channel tensor is
 // contiguous in both layouts at once and counts as NCHW: it is rerouted too, at no cost, and the
@@ -236,9 +244,10 @@ bool via_channels_last(const Tensor& input, const OptTensor& iw, mc_desc d_nhwc)
 
 // ---- convolution ---------------------------------------------------------------------------------------
 
-Tensor conv_forward(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
+Tensor conv_forward(const Tensor& input_in, const Tensor& sample_map_in, const OptTensor& iw,
                     const Tensor& weight, const Tensor& bias, int64_t K, int64_t interp,
                     bool nhwc = false) {
+  const Tensor input = aligned16(input_in), sample_map = aligned16(sample_map_in);
   TORCH_CHECK(input.dim() == 4 && weight.dim() == 3, "input must be 4-D, weight 3-D");
   check_conv_args(input, sample_map, weight, bias, weight.size(0), input.size(1), weight.size(0), K);
   const auto dev = need_cuda({&input, &sample_map, opt(iw), &weight, &bias});
@@ -266,10 +275,11 @@ Tensor conv_forward(const Tensor& input, const Tensor& sample_map, const OptTens
   return y;
 }
 
-std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sample_map,
-                                  const OptTensor& iw, const Tensor& input, const Tensor& weight,
+std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sample_map_in,
+                                  const OptTensor& iw, const Tensor& input_in, const Tensor& weight,
                                   const Tensor& bias, int64_t K, int64_t interp,
                                   bool need_input_grad, bool nhwc = false) {
+  const Tensor input = aligned16(input_in), sample_map = aligned16(sample_map_in);
   TORCH_CHECK(input.dim() == 4 && weight.dim() == 3 && sample_map.dim() >= 4,
               "input must be 4-D, weight 3-D, the map (OH, OW, K, ..)");
   check_conv_args(input, sample_map, weight, bias, weight.size(0), input.size(1), weight.size(0), K,
@@ -286,7 +296,7 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
     return g;
   }
   const int layout = nhwc ? MC_NHWC : layout_of(input);
-  const Tensor grad_output = as_layout(grad_output_in, layout);
+  const Tensor grad_output = aligned16(as_layout(grad_output_in, layout));
   check_map(input, sample_map, iw);
   const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, IH, IW, OH, OW, K,
                               n_interp(iw), interp);
@@ -322,9 +332,10 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
 
 // ---- transposed convolution ------------------------------------------------------------------------------
 
-Tensor tconv_forward(const Tensor& input, const Tensor& sample_map, const OptTensor& iw,
+Tensor tconv_forward(const Tensor& input_in, const Tensor& sample_map_in, const OptTensor& iw,
                      const Tensor& weight, const Tensor& bias, int64_t OHt, int64_t OWt, int64_t K,
                      int64_t interp, bool nhwc = false) {
+  const Tensor input = aligned16(input_in), sample_map = aligned16(sample_map_in);
   TORCH_CHECK(input.dim() == 4 && weight.dim() == 3, "input must be 4-D, weight 3-D");
   check_conv_args(input, sample_map, weight, bias, input.size(1), weight.size(1), weight.size(1), K);
   TORCH_CHECK(sample_map.size(0) == input.size(2) && sample_map.size(1) == input.size(3),
@@ -360,10 +371,11 @@ Tensor tconv_forward(const Tensor& input, const Tensor& sample_map, const OptTen
   return y;
 }
 
-std::vector<Tensor> tconv_backward(const Tensor& grad_output_in, const Tensor& sample_map,
-                                   const OptTensor& iw, const Tensor& input, const Tensor& weight,
+std::vector<Tensor> tconv_backward(const Tensor& grad_output_in, const Tensor& sample_map_in,
+                                   const OptTensor& iw, const Tensor& input_in, const Tensor& weight,
                                    const Tensor& bias, int64_t K, int64_t interp,
                                    bool nhwc = false) {
+  const Tensor input = aligned16(input_in), sample_map = aligned16(sample_map_in);
   TORCH_CHECK(input.dim() == 4 && weight.dim() == 3 && grad_output_in.dim() == 4,
               "input and grad_output must be 4-D, weight 3-D");
   check_conv_args(input, sample_map, weight, bias, input.size(1), weight.size(1), weight.size(1), K,
@@ -383,7 +395,7 @@ std::vector<Tensor> tconv_backward(const Tensor& grad_output_in, const Tensor& s
     return g;
   }
   const int layout = nhwc ? MC_NHWC : layout_of(input);
-  const Tensor grad_output = as_layout(grad_output_in, layout);
+  const Tensor grad_output = aligned16(as_layout(grad_output_in, layout));
   check_map(input, sample_map, iw);
   const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, OHt, OWt, H, W, K,
                               n_interp(iw), interp);

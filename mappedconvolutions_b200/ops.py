@@ -192,6 +192,12 @@ def _cl(t):
     return t.contiguous(memory_format=torch.channels_last)
 
 
+def _a16(t):
+    """The tensor-core kernels read rows with 16-byte vector loads: a view that starts off a 16-byte
+    boundary (a batch slice, say) is copied into a fresh, aligned allocation."""
+    return t if t is None or t.data_ptr() % 16 == 0 else t.clone(memory_format=torch.preserve_format)
+
+
 def _tensor_core_via_channels_last(input, interp_weights, make_desc):
     """bfloat16 tensors in the reference's NCHW layout: the tensor-core kernels want channels-last,
     and two extra layout passes cost far less than the generic kernels (a factor of ten and more at
@@ -205,6 +211,7 @@ def _tensor_core_via_channels_last(input, interp_weights, make_desc):
 
 def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, interpolation,
                   _nhwc=False):
+    input, sample_map = _a16(input), _a16(sample_map)
     _check_conv_args(input, sample_map, weight, bias, weight.shape[0] if weight.dim() else 0,
                      input.shape[1] if input.dim() > 1 else 0, weight.shape[0] if weight.dim() else 0,
                      kernel_size)
@@ -241,6 +248,7 @@ def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, 
 
 def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
                    interpolation, need_input_grad=True, _nhwc=False):
+    input, sample_map = _a16(input), _a16(sample_map)
     _check_conv_args(input, sample_map, weight, bias, weight.shape[0] if weight.dim() else 0,
                      input.shape[1] if input.dim() > 1 else 0, weight.shape[0] if weight.dim() else 0,
                      kernel_size, grad_output,
@@ -255,7 +263,7 @@ def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias,
                            interpolation, need_input_grad, _nhwc=True)
         return [g[0].contiguous() if g[0] is not None else None, g[1], g[2]]
     layout = _lib.MC_NHWC if _nhwc else _layout(input)
-    grad_output = _as_layout(grad_output, layout)
+    grad_output = _a16(_as_layout(grad_output, layout))
     sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
     B, Cin, IH, IW = input.shape
     Cout = weight.shape[0]
@@ -329,6 +337,7 @@ def weighted_mapped_conv_backward(grad_output, sample_map, interp_weights, input
 
 def _tconv_forward(input, sample_map, interp_weights, weight, bias, output_height, output_width,
                    kernel_size, interpolation, _nhwc=False):
+    input, sample_map = _a16(input), _a16(sample_map)
     _check_conv_args(input, sample_map, weight, bias, input.shape[1] if input.dim() > 1 else 0,
                      weight.shape[1] if weight.dim() > 1 else 0,
                      weight.shape[1] if weight.dim() > 1 else 0, kernel_size)
@@ -371,6 +380,7 @@ def _tconv_forward(input, sample_map, interp_weights, weight, bias, output_heigh
 
 def _tconv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
                     interpolation, _nhwc=False):
+    input, sample_map = _a16(input), _a16(sample_map)
     if grad_output.dim() != 4:
         raise RuntimeError("grad_output must be 4-D")
     _check_conv_args(input, sample_map, weight, bias, input.shape[1] if input.dim() > 1 else 0,
@@ -389,7 +399,7 @@ def _tconv_backward(grad_output, sample_map, interp_weights, input, weight, bias
                             interpolation, _nhwc=True)
         return [g[0].contiguous(), g[1], g[2]]
     layout = _lib.MC_NHWC if _nhwc else _layout(input)
-    grad_output = _as_layout(grad_output, layout)
+    grad_output = _a16(_as_layout(grad_output, layout))
     sample_map, interp_weights = _map_args(input, sample_map, interp_weights)
     B, Cin, H, W = input.shape
     Cout = weight.shape[1]

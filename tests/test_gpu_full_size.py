@@ -49,7 +49,7 @@ def config2():
     bf = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)
     x, gy = _cl(bf(B, C, Hh, Ww).to(DEV)), _cl(bf(B, C, Hh, Ww).to(DEV))
     w, b = bf(C, C, K).to(DEV), bf(C).to(DEV)
-    m = get_projection_map((Hh, Ww), (3, 3)).to(DEV)
+    m = get_projection_map((Hh, Ww), (3, 3), "gnomonic").contiguous().to(DEV)
     return dict(x=x, gy=gy, w=w, b=b, m=m, K=K)
 
 
@@ -106,7 +106,8 @@ def test_config3_resample_adjoint_and_oracle():
     from mappedconvolutions_b200.util import icosphere as ico
     g = torch.Generator().manual_seed(3)
     img = torch.rand(16, 3, 512, 1024, generator=g)
-    m = ico.image_to_sphere_resample_map((512, 1024), 7)
+    from mappedconvolutions_b200 import util as mutil
+    m = mutil.image_to_sphere_resample_map((512, 1024), mutil.generate_icosphere(7))
     v = torch.rand(16, 3, m.shape[0], m.shape[1], generator=g)
     imgd, md, vd = img.to(DEV), m.to(DEV), v.to(DEV)
     gathered = ops.resample_from_map(imgd, md, 1)
@@ -154,8 +155,8 @@ def test_config4_knn_properties_at_full_size():
     """k = 9 nearest neighbours among the 163 842 level-7 vertices."""
     from mappedconvolutions_b200 import ops
     from mappedconvolutions_b200.util import icosphere as ico
-    v, _ = ico.generate_icosphere(7)
-    p = torch.from_numpy(v).float().t().contiguous().unsqueeze(0).to(DEV)   # (1, 3, N)
+    from mappedconvolutions_b200 import util as mutil
+    p = mutil.generate_icosphere(7).get_vertices().t().contiguous().unsqueeze(0).to(DEV)   # (1, 3, N)
     n = p.shape[2]
     idx, dist = ops.knn_forward(p, p, 9)
     idx, dist = idx[0], dist[0]                                             # (9, N)
@@ -232,7 +233,11 @@ def test_config5_layer_against_oracle(cin, cout, level):
     e = 2
     y1 = ops.mapped_conv_forward(_cl(xd[e:e + 1]), md, w.to(DEV), b.to(DEV), K, 0)
     g1 = ops.mapped_conv_backward(_cl(gd[e:e + 1]), md, _cl(xd[e:e + 1]), w.to(DEV), b.to(DEV), K, 0)
-    assert torch.equal(y1[0], y[e]) and torch.equal(g1[0][0], gx[e])
+    assert torch.equal(y1[0], y[e])
+    if cin % 64 == 0:   # gather-form input gradient: no atomics, bit for bit
+        assert torch.equal(g1[0][0], gx[e])
+    else:               # 3-channel first layer: generic input gradient with atomic adds
+        H.assert_close(g1[0][0].float(), gx[e].float(), 2e-2, "grad_x batch independence")
     xc, gc = x[e:e + 1].float().contiguous(), gy[e:e + 1].float().contiguous()
     want_y = oracle.mapped_conv_forward(xc, m, w.float(), b.float(), K, 0)
     want_g = oracle.mapped_conv_backward(gc, m, xc, w.float(), b.float(), K, 0)
