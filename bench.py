@@ -406,6 +406,22 @@ def run_ours(args):
         if not args.no_cpu:
             cpu, _ = cpu_baseline()
 
+    # ---- the other configurations of the path, in the same JSON line --------------------------
+    # config 5 (encoder training step, the fixed batch of 64 split over the ranks: strong scaling) at
+    # every N; configs 3 / 4 (resample, pooling, k-NN: no exchange step, "replicas only") on one GPU.
+    # Each timed region lasts at least a second so that the clock sampler sees it.
+    secondary = []
+    if not args.no_secondary:
+        del x, gy, xp, gyp, outs
+        torch.cuda.empty_cache()
+        enc = encoder_record(10, 3, min_seconds=1.0)
+        if rank == 0:
+            secondary.append(enc)
+            if world == 1:
+                for wl in ("resample", "pool", "knn"):
+                    torch.cuda.empty_cache()
+                    secondary.append(secondary_record(wl, 10, 3, args.no_cpu, min_seconds=1.0))
+
     if rank == 0:
         print(json.dumps({
             "metric": "mapped-conv fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
@@ -420,7 +436,7 @@ def run_ours(args):
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e / e2e_steps},
             "gpu_launches": int(launches), "device_status": int(status),
-            "roofline": roof, "cpu_baseline": cpu}))
+            "roofline": roof, "cpu_baseline": cpu, "secondary": secondary}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -429,7 +445,10 @@ def run_ours(args):
 # secondary workloads (--workload resample | pool | knn): the other configs of the path, same
 # timing rules, one JSON line each.  The default run (conv) is the headline line.
 # ---------------------------------------------------------------------------------------------
-def run_secondary(args):
+def secondary_record(wl, steps, warmup, no_cpu, min_seconds=0.0):
+    """One record (a dict with the keys of the headline line) for a secondary workload: 'resample'
+    (config 3), 'pool' (config 4) or 'knn' (config 4).  The timed region runs `steps` steps, or as
+    many more as it takes to last `min_seconds`, so that the clock sampler sees it."""
     import torch
     from mappedconvolutions_b200 import _lib
     from mappedconvolutions_b200.host import impl as ops  # the PyTorch C++ extension
@@ -441,7 +460,6 @@ def run_secondary(args):
     torch.cuda.set_device(dev)
     L = _lib.lib()
     g = torch.Generator().manual_seed(0)
-    wl = args.workload
     cpu = None
     if wl == "resample":
         # config 3: equirect 512x1024x3 fp32 image (U[0,1]), batch 16, <-> icosphere level-7 vertices
@@ -551,17 +569,20 @@ def run_secondary(args):
         torch.cuda.synchronize()
         return a.elapsed_time(c) / n
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
+    if min_seconds > 0:
+        steps = max(steps, int(min_seconds * 1e3 / max(timed(step, 3), 1e-3)) + 1)
     sampler = ClockSampler(dev.index)
     sampler.start()
     n0 = L.mc_kernel_launch_count()
-    ms = timed(step, args.steps)
+    ms = timed(step, steps)
     launches = L.mc_kernel_launch_count() - n0
     clocks = sampler.stop()
+    status = L.mc_device_status(torch.cuda.current_stream().cuda_stream, 1)
     for _ in range(2):
         e2e_step()
-    ms_e = timed(e2e_step, max(2, min(args.steps, 5)))
+    ms_e = timed(e2e_step, max(2, min(steps, 5)))
     times = {}
     for k, (fn, _) in fam.items():
         fn()
@@ -579,17 +600,23 @@ def run_secondary(args):
                 "frac": ach / pk["hbm"], "traffic": None, "peak_source": pk["source"] + " copy bandwidth",
                 "ms_per_launch": {k: round(v, 4) for k, v in times.items()},
                 "gbs": {k: round(fam[k][1] / (v * 1e-3) / 1e9, 1) for k, v in times.items()}}
-    if not args.no_cpu:
+    if not no_cpu:
+        _all_host_threads()
         cpu = cpu_fn()
     e2e_frac = {"resample": 1.0, "pool": 4.0 / 32.0, "knn": 1.0}[wl]
-    print(json.dumps({
+    return {
         "metric": metric, "value": algo_bytes / (ms * 1e-3) / scale, "unit": unit, "n_gpus": 1,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": workload}, "clocks": clocks,
         "e2e": {"value": algo_bytes * e2e_frac / (ms_e * 1e-3) / scale, "unit": unit,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e},
-        "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu}))
+        "gpu_launches": int(launches), "device_status": int(status), "roofline": roof,
+        "cpu_baseline": cpu}
+
+
+def run_secondary(args):
+    print(json.dumps(secondary_record(args.workload, args.steps, args.warmup, args.no_cpu)))
 
 
 # ---------------------------------------------------------------------------------------------
@@ -614,20 +641,17 @@ def encoder_flops(batch):
     return tot
 
 
-def run_encoder(args):
+def encoder_record(steps, warmup, min_seconds=0.0):
+    """The config-5 record (a dict; None on ranks other than 0).  Uses the process group the caller
+    has set up; the fixed batch of 64 is split over the ranks."""
     import torch
     import torch.distributed as dist
     from mappedconvolutions_b200 import _lib, nn as mnn, dist as mdist
-    from mappedconvolutions_b200 import util as mutil
     from mappedconvolutions_b200.util import icosphere as ico
 
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     L = _lib.lib()
     lo, hi = mdist.shard_batch(ENC_BATCH, rank, world)
     nb = hi - lo
@@ -681,13 +705,15 @@ def run_encoder(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step(x)
+    if min_seconds > 0:  # (the same count on every rank: timed() takes the max over ranks)
+        steps = max(steps, int(min_seconds * 1e3 / max(timed(lambda: step(x), 3) / 3, 1e-3)) + 1)
     sampler = ClockSampler(dev.index) if rank == 0 else None
     if sampler:
         sampler.start()
     n0 = L.mc_kernel_launch_count()
-    ms = timed(lambda: step(x), args.steps) / args.steps
+    ms = timed(lambda: step(x), steps) / steps
     launches = L.mc_kernel_launch_count() - n0
     clocks = sampler.stop() if sampler else None
     loss_h = torch.empty(1, dtype=torch.float32).pin_memory()
@@ -697,16 +723,17 @@ def run_encoder(args):
         loss_h.copy_(step(xd).detach().reshape(1), non_blocking=True)
     for _ in range(2):
         e2e_step()
-    ne = max(2, min(args.steps, 5))
+    ne = max(2, min(steps, 5))
     ms_e = timed(e2e_step, ne) / ne
     status = L.mc_device_status(torch.cuda.current_stream().cuda_stream, 1)
     fl = encoder_flops(ENC_BATCH)
+    rec = None
     if rank == 0:
         pk = peaks()
         val = fl / (ms * 1e-3) / 1e12
-        print(json.dumps({
+        rec = ({
             "metric": "mapped-conv fwd+bwd TFLOP/s (encoder step)", "value": val, "unit": "TFLOP/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "n_gpus": world, "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "config5: icosphere level-7 encoder training step, batch 64 in all, "
@@ -722,7 +749,22 @@ def run_encoder(args):
             "roofline": {"bound": "tensor", "achieved": val / world, "peak": pk["bf16_sustained"],
                          "unit": "TFLOP/s", "frac": val / world / pk["bf16_sustained"],
                          "traffic": None, "note": "whole step (conv kernels, ReLU, pooling, update) per GPU against the bf16 GEMM peak"},
-            "cpu_baseline": None}))
+            "cpu_baseline": None})
+    return rec
+
+
+def run_encoder(args):
+    import torch
+    import torch.distributed as dist
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rec = encoder_record(args.steps, args.warmup)
+    if rec is not None:
+        print(json.dumps(rec))
     if world > 1:
         dist.destroy_process_group()
 
@@ -808,6 +850,8 @@ def main():
     ap.add_argument("--workload", default="conv", choices=["conv", "resample", "pool", "knn", "encoder"],
                     help="conv (default) is the headline config; the others are the remaining configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="headline workload only: skip the records of configs 3, 4 and 5")
     ap.add_argument("--profile-case", choices=["fwd", "bwd", "pool", "knn", "resample", "first"],
                     help="run three calls of the config-2 forward / backward at --batch and exit "
                          "(small case for profiler captures)")

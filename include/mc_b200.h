@@ -67,6 +67,13 @@ uint64_t mc_kernel_launch_count(void);
  * reset != 0 clears the word.  No counterpart in the reference (its kernels have no waits). */
 int mc_device_status(void* stream, int reset);
 
+/* Self-test of the bounded device-side waits: launches a one-warp kernel that waits about a
+ * millisecond on a barrier nobody arrives at.  The wait gives up, the kernel returns, and
+ * mc_device_status() then reports 0x7F1; observed_dev (one int32 in device memory, may be NULL)
+ * receives 2 (the block's abort flag was raised and the wait reported failure).  Nothing faults or
+ * hangs.  No counterpart in the reference. */
+int mc_selftest_wait_expiry(int32_t* observed_dev, void* stream);
+
 /* ---- mapped convolution ---------------------------------------------------------------
  * weight (C_out, C_in, K) and bias (C_out) in `dtype`, contiguous. */
 
@@ -145,6 +152,41 @@ int mc_conv_dgrad_inv_supported(const mc_desc* d);
 size_t mc_conv_dgrad_inv_workspace_bytes(const mc_desc* d);
 int mc_conv_dgrad_inv(const mc_desc* d, const void* gy, const void* inv, const void* w,
                       const void* bias_out, void* gx, void* ws, size_t ws_bytes, void* stream);
+
+/* Row plans: sample maps that are translation invariant along image rows,
+ *     map[r, x, k] = (x + cx[r, k], cy[r, k])      (x possibly wrapped into [0, W)),
+ * which is what spherical kernels on equirectangular images produce (gnomonic, equirectangular and
+ * plain grids).  For such maps the bilinear weights of a tap are constants of the row; they are
+ * folded into per-row effective weight matrices, and the convolution runs on plain shifted windows
+ * of source rows - no interpolation in the data path.  Same results as mc_conv_fwd / mc_conv_dgrad /
+ * mc_conv_wgrad within the bf16 tolerance; same reference drivers
+ * (src/nn/cuda/mapped_convolution_layer.cu:16-73, :75-132, :134-193).
+ *
+ * Building a plan takes three steps, none of which allocates:
+ *   1. mc_rowplan_analyse writes (OH, K, 3) doubles (cx, cy, kind) to DEVICE memory
+ *      (mc_rowplan_analysis_bytes; 0 = this descriptor has no row-plan kernels: they take MC_BF16,
+ *      MC_NHWC, P == 0, bilinear / bispherical, C_in == C_out == 64, OW == IW, OW % 512 == 0);
+ *   2. if no kind is 0 the caller copies them and the sample map to the host, and
+ *      mc_rowplan_assemble (pure host code) writes the plan as int32s into a host buffer.  It decodes
+ *      every map entry exactly as mc_conv_fwd does and lists the few pixels that deviate from their
+ *      row's nominal behaviour (the seam of wrapped maps, positions within rounding of an integer)
+ *      as corrections that the kernels apply, so results agree with mc_conv_fwd pixel for pixel.
+ *      It returns the number of int32s the plan needs (call with capacity 0 to size the buffer) or 0
+ *      if the map is not row invariant;
+ *   3. the caller keeps the host copy and uploads a copy to the device (16-byte aligned).
+ * A plan depends only on the map and the image sizes, like the tap table and the inverse map.
+ * dir: 0 = forward, 1 = input gradient.  ws holds the effective weights of the call. */
+size_t mc_rowplan_analysis_bytes(const mc_desc* d);
+int mc_rowplan_analyse(const mc_desc* d, const void* map, void* analysis, void* stream);
+int64_t mc_rowplan_assemble(const mc_desc* d, const double* analysis_host, const float* map_host,
+                            int32_t* plan_host, int64_t capacity);
+size_t mc_conv_rowplan_workspace_bytes(const mc_desc* d, const void* plan_host, int32_t dir);
+int mc_conv_fwd_rowplan(const mc_desc* d, const void* x, const void* plan_host, const void* plan_dev,
+                        const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
+                        void* stream);
+int mc_conv_dgrad_rowplan(const mc_desc* d, const void* gy, const void* plan_host,
+                          const void* plan_dev, const void* w, const void* bias_out, void* gx,
+                          void* ws, size_t ws_bytes, void* stream);
 
 /* gw(C_out,C_in,K) = sum_b gy_b . im2col_map(x_b)^T and gb(C_out) = sum_{b,h,w} gy.
  * gw and gb are written in the accumulation type: double for MC_F64, float otherwise

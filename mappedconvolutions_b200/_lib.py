@@ -33,6 +33,7 @@ SIGNATURES = {
     "mc_abi_version": (ctypes.c_int, []),
     "mc_kernel_launch_count": (ctypes.c_uint64, []),
     "mc_device_status": (ctypes.c_int, [_vp, ctypes.c_int]),
+    "mc_selftest_wait_expiry": (ctypes.c_int, [_vp, _vp]),
     "mc_conv_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_fwd_workspace_bytes": (_sz, [_dp]),
     "mc_conv_fwd_static_scratch_limit": (_sz, []),
@@ -49,6 +50,12 @@ SIGNATURES = {
     "mc_conv_dgrad_inv_supported": (ctypes.c_int, [_dp]),
     "mc_conv_dgrad_inv_workspace_bytes": (_sz, [_dp]),
     "mc_conv_dgrad_inv": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "mc_rowplan_analysis_bytes": (_sz, [_dp]),
+    "mc_rowplan_analyse": (ctypes.c_int, [_dp, _vp, _vp, _vp]),
+    "mc_rowplan_assemble": (ctypes.c_int64, [_dp, _vp, _vp, _vp, ctypes.c_int64]),
+    "mc_conv_rowplan_workspace_bytes": (_sz, [_dp, _vp, _i32]),
+    "mc_conv_fwd_rowplan": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "mc_conv_dgrad_rowplan": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_wgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_wgrad_workspace_bytes": (_sz, [_dp]),
     "mc_tconv_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

@@ -40,6 +40,13 @@ bool conv_tc_wgrad_supported(const mc_desc*);
 size_t conv_tc_wgrad_ws(const mc_desc*);
 int conv_tc_wgrad_launch(const mc_desc*, const void*, const void*, const void*, void*, void*, void*,
                          size_t, cudaStream_t);
+bool conv_rowinv_shape_ok(const mc_desc*);
+size_t rowinv_analysis_bytes(const mc_desc*);
+int rowinv_analyse_launch(const mc_desc*, const void*, void*, cudaStream_t);
+long rowinv_assemble_host(const mc_desc*, const double*, const float*, int*, long);
+size_t rowinv_ws_bytes(const mc_desc*, const void*, int);
+int rowinv_conv_launch(const mc_desc*, int, const void*, const void*, const void*, const void*,
+                       const void*, void*, void*, size_t, cudaStream_t);
 }  // namespace mc
 
 namespace mc {
@@ -178,6 +185,46 @@ int mc_conv_dgrad_inv(const mc_desc* d, const void* gy, const void* inv, const v
   if (!gy || !inv || !w || !gx) return MC_ERR_BAD_ARG;
   if (!conv_tc_dgrad_supported(d)) return MC_ERR_UNSUPPORTED;
   return conv_tc_dgrad_launch(d, gy, inv, w, bias_out, gx, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+// ---- row-invariant maps --------------------------------------------------------------------------
+
+size_t mc_rowplan_analysis_bytes(const mc_desc* d) {
+  if (!d || check_conv_desc_public(d) || !conv_rowinv_shape_ok(d)) return 0;
+  return rowinv_analysis_bytes(d);
+}
+int mc_rowplan_analyse(const mc_desc* d, const void* map, void* analysis, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!map || !analysis) return MC_ERR_BAD_ARG;
+  if (!conv_rowinv_shape_ok(d)) return MC_ERR_UNSUPPORTED;
+  return rowinv_analyse_launch(d, map, analysis, (cudaStream_t)stream);
+}
+int64_t mc_rowplan_assemble(const mc_desc* d, const double* analysis_host, const float* map_host,
+                            int32_t* plan_host, int64_t capacity) {
+  if (!d || check_conv_desc_public(d) || !analysis_host || !map_host) return 0;
+  return rowinv_assemble_host(d, analysis_host, map_host, plan_host, capacity);
+}
+size_t mc_conv_rowplan_workspace_bytes(const mc_desc* d, const void* plan_host, int32_t dir) {
+  if (!d || check_conv_desc_public(d) || !plan_host || dir < 0 || dir > 1) return 0;
+  return rowinv_ws_bytes(d, plan_host, dir);
+}
+int mc_conv_fwd_rowplan(const mc_desc* d, const void* x, const void* plan_host, const void* plan_dev,
+                        const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
+                        void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!x || !plan_host || !plan_dev || !w || !y) return MC_ERR_BAD_ARG;
+  return rowinv_conv_launch(d, 0, x, plan_host, plan_dev, w, bias, y, ws, ws_bytes, (cudaStream_t)stream);
+}
+int mc_conv_dgrad_rowplan(const mc_desc* d, const void* gy, const void* plan_host,
+                          const void* plan_dev, const void* w, const void* bias_out, void* gx,
+                          void* ws, size_t ws_bytes, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!gy || !plan_host || !plan_dev || !w || !gx) return MC_ERR_BAD_ARG;
+  return rowinv_conv_launch(d, 1, gy, plan_host, plan_dev, w, bias_out, gx, ws, ws_bytes,
+                            (cudaStream_t)stream);
 }
 
 int mc_conv_dgrad(const mc_desc* d, const void* gy, const void* map, const void* iw, const void* w,

@@ -1,0 +1,818 @@
+// Mapped convolution for sample maps that are translation invariant along image rows - the maps
+// of spherical kernels on equirectangular images (gnomonic, equirectangular, plain grids):
+//
+//     map[r, x, k] = (x + cx[r, k], cy[r, k])            x positions possibly wrapped into [0, W)
+//
+// Along a row every tap keeps its fractional position, so its bilinear weights are constants of
+// the row and the interpolation can be folded into the weights once per call:
+//
+//     y[r, x, :] = sum over the row's slots (sy, dx) of  E[r, (sy, dx)] . X[sy, x + dx, :]
+//     E[r, (sy, dx)] = sum over the (tap k, corner c) that read (sy, x + dx) of  w[r, k, c] * W[:, :, k]
+//
+// No interpolation is left in the data path.  The operand of the GEMM is a plain run of source
+// pixels: a WINDOW of 128 * T + span consecutive pixels of source row sy is copied once into
+// shared memory (cp.async, 128-byte swizzle) and serves every slot of that source row and every
+// one of the T 128-pixel tiles of the unit - a slot only moves the START ADDRESS of the tcgen05
+// operand by dx rows.  The reference interpolates every tap of every pixel
+// (include/nn/common/mapped_im2col.h:12-42) and multiplies a K-times inflated column buffer
+// (src/nn/cuda/mapped_convolution_layer.cu:39-70).
+//
+//   forward          result rows = rows of the map grid, source = x, E = sum w W_k
+//   input gradient   result rows = rows of the sampled image, source = grad_output, the plan
+//                    transposed (slot (r, -dx) for every forward slot (sy, dx) of row r) and E^T
+//   weight gradient  per slot gE = sum over pixels of gy (x) X-window (conv_rowinv_wgrad kernel),
+//                    then gw_k = sum over slots of w * gE
+//
+// A row's plan is the NOMINAL behaviour of its taps.  A few pixels deviate from it: a bilinear map
+// whose positions are wrapped into [0, W) has, per tap and row, one pixel whose left corner is
+// column W - 1 and whose right corner (column W) does not exist and reads as zero
+// (include/core/interpolation.h:125-154), where a wrapped window reads column 0; and where a
+// position sits within rounding of an integer the float32 map entry of single pixels can fall on
+// the other side of it (or on W itself).  The planner therefore decodes EVERY map entry exactly as
+// the general kernels do, compares it with the row's nominal corners and emits a list of
+// corrections (result pixel, source pixel, tap, weight difference) for the pixels that differ by
+// more than 1e-3 in a weight; the fix-up kernels below apply them after the main kernels.
+//
+// This header is part of conv_tc.cu's translation unit (one device status word, shared helpers).
+#pragma once
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+namespace mc {
+namespace tc {
+
+constexpr int RI_SPAN = 32;  // shifts 0..RI_SPAN of one source row share a window
+constexpr int RI_MAX_WIN_PER_ROW = 64;
+constexpr int RI_MAX_SLOT_PER_ROW = 128;
+constexpr double RI_TOL = 1e-3;  // pixels: largest deviation from exact translation invariance
+constexpr int RI_MODE_CLIP = 0, RI_MODE_WRAP = 1;
+constexpr int RI_PLAN_MAGIC = 0x52495031;
+
+// ---- plan layout (a flat int32 buffer, identical on host and device) -------------------------------
+struct RiDir {
+  int rows, nwin, nslot, ncon, nskip, ngroup;
+  int max_win_per_row, max_slot_per_row;
+  // int offsets from the start of the plan
+  int off_row;    // (rows + 1) first window of every result row
+  int off_win;    // nwin x 4: source row, dx0 (first shift), first slot, nslots | span << 8 | mode << 16
+  int off_slot;   // nslot: shift inside the window
+  int off_coff;   // (nslot + 1) contributions of every slot
+  int off_ctap;   // ncon taps
+  int off_cw;     // ncon weights (float bits)
+  int off_skip;   // nskip x 6 corrections: result row, result column, source row, source column, tap,
+                  // weight difference (float bits; exact minus nominal)
+  int off_group;  // (ngroup + 1): runs of corrections that apply to the same result pixel
+};
+struct RiHeader {
+  int magic, total_ints;
+  int OH, OW, IH, IW, K, interp;
+  RiDir dir[2];  // 0: forward (result = map grid), 1: adjoint (result = sampled image)
+};
+
+// ---- analysis: is the map row invariant? --------------------------------------------------------------
+// One block per row of the map grid.  out[(r * K + k) * 3 + {0, 1, 2}] = cx, cy, kind; kind is a
+// bit mask: 1 = the x positions are x + cx as they stand, 2 = they are (x + cx) wrapped into [0, W)
+// (a tap can be both, e.g. the centre tap of a kernel); 0 = not invariant.
+__global__ void rowinv_analyse_kernel(const float* __restrict__ map, int OH, int OW, int K, int IW,
+                                      double* __restrict__ out) {
+  const int r = blockIdx.x;
+  __shared__ double s_sum[2][32];
+  __shared__ int s_bad[3][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int k = 0; k < K; ++k) {
+    const float2 mref = __ldg(reinterpret_cast<const float2*>(map) + ((long)r * OW + OW / 2) * K + k);
+    const double ref = (double)mref.x - (double)(OW / 2), cy0 = (double)mref.y;
+    double sum_d = 0.0, sum_y = 0.0;
+    int bad_plain = 0, bad_wrap = 0, bad_y = 0;
+    for (int x = threadIdx.x; x < OW; x += blockDim.x) {
+      const float2 m = __ldg(reinterpret_cast<const float2*>(map) + ((long)r * OW + x) * K + k);
+      const double d = (double)m.x - (double)x - ref;
+      if (!(fabs(d) <= RI_TOL)) bad_plain = 1;
+      double dw = fmod(d + IW * 0.5, (double)IW);
+      if (dw < 0) dw += IW;
+      dw -= IW * 0.5;
+      if (!(fabs(dw) <= RI_TOL) || !(m.x >= 0.f && m.x < (float)IW)) bad_wrap = 1;
+      if (!(fabs((double)m.y - cy0) <= RI_TOL)) bad_y = 1;
+      sum_d += isfinite(dw) ? dw : 0.0;
+      sum_y += isfinite(m.y) ? (double)m.y : 0.0;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      sum_d += __shfl_xor_sync(0xffffffffu, sum_d, o);
+      sum_y += __shfl_xor_sync(0xffffffffu, sum_y, o);
+      bad_plain |= __shfl_xor_sync(0xffffffffu, bad_plain, o);
+      bad_wrap |= __shfl_xor_sync(0xffffffffu, bad_wrap, o);
+      bad_y |= __shfl_xor_sync(0xffffffffu, bad_y, o);
+    }
+    __syncthreads();
+    if (lane == 0) {
+      s_sum[0][warp] = sum_d; s_sum[1][warp] = sum_y;
+      s_bad[0][warp] = bad_plain; s_bad[1][warp] = bad_wrap; s_bad[2][warp] = bad_y;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double sd = 0, sy = 0;
+      int bp = 0, bw = 0, by = 0;
+      for (int i = 0; i < nwarp; ++i) {
+        sd += s_sum[0][i]; sy += s_sum[1][i];
+        bp |= s_bad[0][i]; bw |= s_bad[1][i]; by |= s_bad[2][i];
+      }
+      int kind = 0;
+      if (!by) kind = (!bp ? 1 : 0) | ((!bw && OW == IW) ? 2 : 0);
+      double* o = out + ((long)r * K + k) * 3;
+      o[0] = ref + sd / OW;
+      o[1] = sy / OW;
+      o[2] = (double)kind;
+    }
+  }
+}
+
+// ---- host-side planner ------------------------------------------------------------------------------------
+struct RiCon {  // one (tap, corner) contribution
+  int res_row, src_row, dx, mode, tap;
+  float w;
+};
+
+struct RiFix {  // one correction: result pixel += dw * W_tap . source pixel
+  int res_row, res_col, src_row, src_col, tap;
+  float dw;
+};
+
+static void ri_emit_dir(std::vector<RiCon>& cons, std::vector<RiFix>& fixes, int rows,
+                        std::vector<int>& plan, RiDir& d, bool& ok) {
+  std::stable_sort(cons.begin(), cons.end(), [](const RiCon& a, const RiCon& b) {
+    if (a.res_row != b.res_row) return a.res_row < b.res_row;
+    if (a.mode != b.mode) return a.mode < b.mode;
+    if (a.src_row != b.src_row) return a.src_row < b.src_row;
+    if (a.dx != b.dx) return a.dx < b.dx;
+    return a.tap < b.tap;
+  });
+  std::vector<int> row_off(rows + 1, 0), win, slot, coff, ctap, cw;
+  int max_w = 0, max_s = 0;
+  size_t i = 0;
+  for (int r = 0; r < rows; ++r) {
+    row_off[r] = (int)win.size() / 4;
+    const int slot0 = (int)slot.size();
+    while (i < cons.size() && cons[i].res_row == r) {
+      // a new slot; a new window if the source row / mode changes or the shift leaves the span
+      const RiCon& c = cons[i];
+      bool new_win = win.size() / 4 == (size_t)row_off[r];
+      if (!new_win) {
+        const int* w = &win[win.size() - 4];
+        new_win = w[0] != c.src_row || (w[3] >> 16) != c.mode || c.dx - w[1] > RI_SPAN;
+      }
+      if (new_win) {
+        win.push_back(c.src_row); win.push_back(c.dx); win.push_back((int)slot.size());
+        win.push_back(c.mode << 16);
+      }
+      int* w = &win[win.size() - 4];
+      slot.push_back(c.dx - w[1]);
+      w[3] = (w[3] & 0xFFFF0000) | ((c.dx - w[1]) << 8) | (((w[3] & 0xFF) + 1) & 0xFF);
+      coff.push_back((int)ctap.size());
+      size_t j = i;
+      while (j < cons.size() && cons[j].res_row == r && cons[j].mode == c.mode &&
+             cons[j].src_row == c.src_row && cons[j].dx == c.dx) {
+        ctap.push_back(cons[j].tap);
+        int bits;
+        std::memcpy(&bits, &cons[j].w, 4);
+        cw.push_back(bits);
+        ++j;
+      }
+      i = j;
+    }
+    max_w = std::max(max_w, (int)win.size() / 4 - row_off[r]);
+    max_s = std::max(max_s, (int)slot.size() - slot0);
+  }
+  row_off[rows] = (int)win.size() / 4;
+  coff.push_back((int)ctap.size());
+  if (max_w > RI_MAX_WIN_PER_ROW || max_s > RI_MAX_SLOT_PER_ROW) ok = false;
+  // corrections, grouped by the result pixel they apply to
+  std::stable_sort(fixes.begin(), fixes.end(), [](const RiFix& a, const RiFix& b) {
+    if (a.res_row != b.res_row) return a.res_row < b.res_row;
+    return a.res_col < b.res_col;
+  });
+  std::vector<int> skip, group;
+  for (size_t e = 0; e < fixes.size(); ++e) {
+    const RiFix& f = fixes[e];
+    if (e == 0 || f.res_row != fixes[e - 1].res_row || f.res_col != fixes[e - 1].res_col)
+      group.push_back((int)e);
+    int bits;
+    std::memcpy(&bits, &f.dw, 4);
+    const int ent[6] = {f.res_row, f.res_col, f.src_row, f.src_col, f.tap, bits};
+    skip.insert(skip.end(), ent, ent + 6);
+  }
+  group.push_back((int)fixes.size());
+  d.rows = rows; d.nwin = (int)win.size() / 4; d.nslot = (int)slot.size(); d.ncon = (int)ctap.size();
+  d.nskip = (int)fixes.size(); d.ngroup = (int)group.size() - 1;
+  d.max_win_per_row = max_w; d.max_slot_per_row = max_s;
+  auto put = [&plan](const std::vector<int>& v) {
+    const int off = (int)plan.size();
+    plan.insert(plan.end(), v.begin(), v.end());
+    while (plan.size() % 4) plan.push_back(0);  // every array starts on a 16-byte boundary
+    return off;
+  };
+  d.off_row = put(row_off); d.off_win = put(win); d.off_slot = put(slot); d.off_coff = put(coff);
+  d.off_ctap = put(ctap); d.off_cw = put(cw); d.off_skip = put(skip); d.off_group = put(group);
+}
+
+// One decoded map entry on the host: the (up to four) source pixels and weights the general kernels
+// use for it (common.cuh decode_tap; include/core/interpolation.h:125-154, :183-210).
+struct RiCorner {
+  int row, col;
+  float w;
+};
+static int ri_decode_exact(float x, float y, int H, int W, int interp, RiCorner (&out)[4]) {
+  const float xf = floorf(x), yf = floorf(y);
+  if (!std::isfinite(xf) || !std::isfinite(yf)) return 0;
+  const float Bx = (xf + 1.f) - x, Cx = x - xf, Ay = (yf + 1.f) - y, Dy = y - yf;
+  const float w4[4] = {Ay * Bx, Ay * Cx, Dy * Bx, Dy * Cx};
+  int n = 0;
+  for (int c = 0; c < 4; ++c) {
+    const int oy = c >> 1, ox = c & 1;
+    const double ry = (double)yf + oy, rx = (double)xf + ox;
+    if (ry < 0 || ry > H - 1 || w4[c] == 0.f) continue;
+    long col;
+    if (interp == 1) {
+      if (rx < 0 || rx > W - 1) continue;
+      col = (long)rx;
+    } else {
+      if (!(fabs(rx) < 1e18)) continue;
+      col = (((long)rx % W) + W) % W;
+    }
+    out[n].row = (int)ry; out[n].col = (int)col; out[n].w = w4[c];
+    ++n;
+  }
+  return n;
+}
+
+// analysis: (OH, K, 3) doubles from rowinv_analyse_kernel; map: the (OH, OW, K, 2) sample map; both
+// on the host.  Returns the plan as int32s (empty if the map does not qualify).
+static std::vector<int> rowinv_assemble(const mc_desc* d, const double* analysis, const float* map) {
+  const int OH = d->OH, OW = d->OW, IH = d->IH, IW = d->IW, K = d->K;
+  std::vector<RiCon> fwd, adj;
+  std::vector<RiFix> ffix, afix;
+  // One addressing mode for the whole map where possible (windows are shared by the taps of a source
+  // row only if they agree on it): wrap if some tap needs it, clip otherwise.  Single pixels where
+  // the two differ are caught by the per-pixel comparison below.
+  bool prefer_wrap = d->interp == 2;
+  for (long i = 0; i < (long)OH * K; ++i) prefer_wrap |= (int)analysis[i * 3 + 2] == 2;
+  for (int r = 0; r < OH; ++r) {
+    for (int k = 0; k < K; ++k) {
+      const double* a = analysis + ((long)r * K + k) * 3;
+      const int kind = (int)a[2];
+      if (kind == 0 || !std::isfinite(a[0]) || !std::isfinite(a[1]) || fabs(a[0]) > 1e7 ||
+          fabs(a[1]) > 1e7)
+        return {};
+      // nominal corner weights in float32, from the row's position, with the reference's formulas
+      // (include/core/interpolation.h:17-33: A = y2 - y, B = x2 - x, C = x - x1, D = y - y1)
+      const float px = (float)a[0], py = (float)a[1];
+      const float xf = floorf(px), yf = floorf(py);
+      const float Bx = (xf + 1.f) - px, Cx = px - xf, Ay = (yf + 1.f) - py, Dy = py - yf;
+      const float w4[4] = {Ay * Bx, Ay * Cx, Dy * Bx, Dy * Cx};
+      const int mode = (d->interp == 2 || kind == 2 || (prefer_wrap && (kind & 2))) ? RI_MODE_WRAP
+                                                                                     : RI_MODE_CLIP;
+      RiCorner nom[4];  // col holds dx here
+      int nn = 0;
+      for (int c = 0; c < 4; ++c) {
+        const int oy = c >> 1, ox = c & 1;
+        const int sy = (int)yf + oy;
+        if (sy < 0 || sy > IH - 1 || w4[c] == 0.f) continue;
+        RiCon con;
+        con.res_row = r; con.src_row = sy; con.dx = (int)xf + ox; con.mode = mode; con.tap = k;
+        con.w = w4[c];
+        fwd.push_back(con);
+        RiCon t = con;
+        t.res_row = sy; t.src_row = r; t.dx = -con.dx;
+        adj.push_back(t);
+        nom[nn].row = sy; nom[nn].col = con.dx; nom[nn].w = w4[c];
+        ++nn;
+      }
+      // every pixel of the row against the nominal corners
+      for (int x = 0; x < OW; ++x) {
+        const float* m = map + (((long)r * OW + x) * K + k) * 2;
+        RiCorner ex[4];
+        const int ne = ri_decode_exact(m[0], m[1], IH, IW, d->interp, ex);
+        RiCorner diff[8];
+        int nd = 0;
+        float worst = 0.f;
+        for (int i = 0; i < ne; ++i) diff[nd++] = ex[i];
+        for (int i = 0; i < nn; ++i) {
+          long col = (long)x + nom[i].col;
+          if (mode == RI_MODE_WRAP) col = ((col % IW) + IW) % IW;
+          else if (col < 0 || col > IW - 1) continue;
+          int j = 0;
+          while (j < nd && !(diff[j].row == nom[i].row && diff[j].col == (int)col)) ++j;
+          if (j == nd) { diff[nd].row = nom[i].row; diff[nd].col = (int)col; diff[nd].w = 0.f; ++nd; }
+          diff[j].w -= nom[i].w;
+        }
+        for (int i = 0; i < nd; ++i) worst = std::max(worst, fabsf(diff[i].w));
+        if (!(worst > 1e-3f)) continue;
+        for (int i = 0; i < nd; ++i) {
+          if (diff[i].w == 0.f) continue;
+          ffix.push_back({r, x, diff[i].row, diff[i].col, k, diff[i].w});
+          afix.push_back({diff[i].row, diff[i].col, r, x, k, diff[i].w});
+        }
+      }
+    }
+  }
+  if (ffix.size() > (size_t)OH * 64) return {};  // more than a fringe: not what this path is for
+  RiHeader h;
+  std::memset(&h, 0, sizeof(h));
+  h.magic = RI_PLAN_MAGIC;
+  h.OH = OH; h.OW = OW; h.IH = IH; h.IW = IW; h.K = K; h.interp = d->interp;
+  std::vector<int> plan((sizeof(RiHeader) + 3) / 4, 0);
+  while (plan.size() % 4) plan.push_back(0);
+  bool ok = true;
+  ri_emit_dir(fwd, ffix, OH, plan, h.dir[0], ok);
+  ri_emit_dir(adj, afix, IH, plan, h.dir[1], ok);
+  if (!ok) return {};
+  h.total_ints = (int)plan.size();
+  std::memcpy(plan.data(), &h, sizeof(h));
+  return plan;
+}
+
+// ---- effective weights -------------------------------------------------------------------------------
+// Wk[k][n][c]: the layer's weights with the tap outermost, n = result channel, c = source channel
+// (transpose = 0: W[n, c, k]; transpose = 1: W[c, n, k]), so that the kernels below read whole
+// 128-byte rows.
+__global__ void rowinv_wk_kernel(const bf16* __restrict__ w, bf16* __restrict__ wk, int NR, int K,
+                                 int Cin, int transpose) {
+  const int total = K * NR * 64;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int c = i & 63, n = (i >> 6) % NR, k = i / (64 * NR);
+    const int co = transpose ? c : n, ci = transpose ? n : c;
+    wk[i] = w[((long)co * Cin + ci) * K + k];
+  }
+}
+
+// E[slot] = sum over the slot's contributions of weight * Wk[tap], in the shared-memory image of a
+// K-major MMA operand: NR rows (result channels) of 64 source channels, 128 bytes each, 16-byte
+// chunks XOR-swizzled by (row & 7).  One thread per 16-byte chunk.
+__global__ void __launch_bounds__(256) rowinv_weights_kernel(const bf16* __restrict__ wk,
+                                                             const int* __restrict__ plan, RiDir d,
+                                                             uint4* __restrict__ E, int NR) {
+  const int s = blockIdx.x;
+  const int b0 = __ldg(plan + d.off_coff + s), b1 = __ldg(plan + d.off_coff + s + 1);
+  for (int i = threadIdx.x; i < NR * 8; i += 256) {
+    const int n = i >> 3, ch = i & 7;
+    float2 acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = make_float2(0.f, 0.f);
+    for (int e = b0; e < b1; ++e) {
+      const float we = __int_as_float(__ldg(plan + d.off_cw + e));
+      const uint4 v = ldg16(wk + ((long)__ldg(plan + d.off_ctap + e) * NR + n) * 64 + ch * 8);
+      const float2 w2 = make_float2(we, we);
+      ffma2_bf16x2(acc[0], w2, v.x);
+      ffma2_bf16x2(acc[1], w2, v.y);
+      ffma2_bf16x2(acc[2], w2, v.z);
+      ffma2_bf16x2(acc[3], w2, v.w);
+    }
+    E[(size_t)s * NR * 8 + n * 8 + (ch ^ (n & 7))] = pack_row(acc);
+  }
+}
+
+// ---- main kernel: forward / input gradient ---------------------------------------------------------
+struct RowInvArgs {
+  const bf16* src;   // (B, SH, SW, 64) channels-last
+  bf16* out;         // (B, RH, RW, NOUT)
+  const bf16* bias;  // NOUT or null
+  const int* plan;
+  RiDir d;
+  const uint4* E;  // [slot][NOUT x 128 B]
+  int B, SH, SW, RH, RW;
+  int tpu;         // 128-pixel tiles per unit
+  int upr;         // units per (row, image): RW / (128 * tpu)
+  long units;      // RH * B * upr
+  int dbg;
+};
+
+__device__ __forceinline__ void ri_unit(const RowInvArgs& a, long u, int& r, int& b, int& x0) {
+  const int per_row = a.B * a.upr;
+  r = (int)(u / per_row);
+  const int rem = (int)(u - (long)r * per_row);
+  b = rem / a.upr;
+  x0 = (rem - b * a.upr) * a.tpu * TILE_M;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+constexpr int RI_WIN_STAGES = 2;
+
+template <int NOUT>
+struct RiCfg {
+  static constexpr int TPU = 256 / NOUT;                              // tiles per unit (TMEM: 2 x TPU x NOUT = 512)
+  static constexpr uint32_t WIN_ROWS = TPU * TILE_M + RI_SPAN;
+  static constexpr uint32_t WIN_BYTES = ((WIN_ROWS * 128 + 1023) / 1024) * 1024;
+  static constexpr uint32_t E_BYTES = NOUT * 128;
+  static constexpr int NE = NOUT == 64 ? 6 : (NOUT == 128 ? 4 : 2);  // E stages
+  static constexpr int NBAR = 2 * RI_WIN_STAGES + 2 * NE + 5;
+  static constexpr size_t SMEM = 1024 + (size_t)RI_WIN_STAGES * WIN_BYTES + (size_t)NE * E_BYTES +
+                                 EPI_STAGING_BYTES + NOUT * 4 + NBAR * 8 + 48 +
+                                 (RI_MAX_WIN_PER_ROW * 16 + RI_MAX_SLOT_PER_ROW * 4);
+};
+
+template <int NOUT>
+__global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const RowInvArgs a) {
+  using Cfg = RiCfg<NOUT>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t win0 = smem_u32(sm);
+  const uint32_t e0 = win0 + RI_WIN_STAGES * Cfg::WIN_BYTES;
+  const uint32_t stg0 = e0 + Cfg::NE * Cfg::E_BYTES;
+  uint8_t* tail = sm + RI_WIN_STAGES * Cfg::WIN_BYTES + Cfg::NE * Cfg::E_BYTES + EPI_STAGING_BYTES;
+  float* bias_s = (float*)tail;
+  uint64_t* bars = (uint64_t*)(bias_s + NOUT);
+  uint32_t* misc = (uint32_t*)(bars + Cfg::NBAR);
+  volatile int* abort_flag = (volatile int*)(misc + 1);
+  int4* s_win = (int4*)(((uintptr_t)(misc + 4) + 15) & ~(uintptr_t)15);  // the MMA warp's copy of the row's windows
+  int* s_shift = (int*)(s_win + RI_MAX_WIN_PER_ROW);     // and slot shifts
+  const uint32_t bar0 = smem_u32(bars);
+  auto wfull = [&](int s) { return bar0 + 8u * s; };
+  auto wempty = [&](int s) { return bar0 + 8u * (RI_WIN_STAGES + s); };
+  auto efull = [&](int s) { return bar0 + 8u * (2 * RI_WIN_STAGES + s); };
+  auto eempty = [&](int s) { return bar0 + 8u * (2 * RI_WIN_STAGES + Cfg::NE + s); };
+  auto tfull = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + i); };
+  auto tempty = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 2 + i); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 512;
+  const int* plan = a.plan;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < RI_WIN_STAGES; ++s) { mbar_init(wfull(s), N_PRODUCER_WARPS / RI_WIN_STAGES); mbar_init(wempty(s), 1); }
+    for (int s = 0; s < Cfg::NE; ++s) { mbar_init(efull(s), 1); mbar_init(eempty(s), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(tfull(i), 1); mbar_init(tempty(i), N_EPI_WARPS); }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  for (int i = threadIdx.x; i < NOUT; i += TC_THREADS)
+    bias_s[i] = a.bias ? __bfloat162float(a.bias[i]) : 0.f;
+  if (warp == 0) tmem_alloc(smem_u32(misc), TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *misc;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    // All lanes fetch the row's window and slot records into the warp's strip of shared memory
+    // (one round of independent loads); lane 0 then issues from there.
+    constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 0, 0);
+    uint32_t it = 0, nw = 0, se = 0, pe = 0;
+    int ok = 1;
+    for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x, ++it) {
+      int r, b, x0;
+      ri_unit(a, u, r, b, x0);
+      const int w0 = __ldg(plan + a.d.off_row + r), w1 = __ldg(plan + a.d.off_row + r + 1);
+      __syncwarp();
+      for (int i = lane; i < w1 - w0; i += 32)
+        s_win[i] = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w0 + i);
+      __syncwarp();
+      int ns = 0, sfirst = 0;
+      if (w1 > w0) {
+        sfirst = s_win[0].z;
+        ns = s_win[w1 - w0 - 1].z + (s_win[w1 - w0 - 1].w & 0xFF) - sfirst;
+      }
+      for (int i = lane; i < ns; i += 32) s_shift[i] = __ldg(plan + a.d.off_slot + sfirst + i);
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t acc = it & 1, aph = (it >> 1) & 1;
+        ok = mbar_wait(tempty(acc), aph ^ 1, abort_flag, 0x81) ? 1 : 0;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * (Cfg::TPU * NOUT);
+        int si = 0;
+        for (int w = 0; w < w1 - w0 && ok; ++w, ++nw) {
+          const uint32_t ws = nw % RI_WIN_STAGES, wph = (nw / RI_WIN_STAGES) & 1;
+          ok = mbar_wait(wfull(ws), wph, abort_flag, 0x82) ? 1 : 0;
+          const int nsl = s_win[w].w & 0xFF;
+          for (int s = 0; s < nsl && ok; ++s, ++si) {
+            ok = mbar_wait(efull(se), pe, abort_flag, 0x83) ? 1 : 0;
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint64_t bdesc = make_desc_sw128(e0 + se * Cfg::E_BYTES, 16, 1024);
+            const uint32_t abase = win0 + ws * Cfg::WIN_BYTES + (uint32_t)s_shift[si] * 128u;
+#pragma unroll
+            for (int t = 0; t < Cfg::TPU; ++t) {
+              const uint64_t adesc = make_desc_sw128(abase + t * (TILE_M * 128), 16, 1024);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (!(a.dbg & 2)) mma_bf16_ss(tmem_d + t * NOUT, adesc + 2 * j, bdesc + 2 * j, idesc, (si | j) != 0);
+            }
+            mma_commit(eempty(se));
+            if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; }
+          }
+          if (ok) mma_commit(wempty(ws));
+        }
+        if (ok) mma_commit(tfull(acc));
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    if (lane == 0) {
+      mma_commit(drain_bar);
+      mbar_wait(drain_bar, 0, abort_flag, 0x84);
+    }
+    __syncwarp();
+  } else if (warp <= N_EPI_WARPS) {
+    // ------------------------------------------------------------------ epilogue
+    // (the same accumulator read-out as conv_gemm_tc_kernel: TMEM -> registers -> + bias -> bf16 ->
+    // a 32 x 64-byte block turned around in shared memory -> stores of 8 rows x 64 bytes)
+    const int q = warp & 3;
+    const uint32_t stg = stg0 + (uint32_t)(warp - 1) * 2048u;
+    const uint32_t wr_row = stg + lane * 64, wr_x = (lane >> 1) & 3;
+    uint32_t rd_addr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = 8 * i + (lane >> 2);
+      rd_addr[i] = stg + row * 64 + (((lane & 3) ^ ((row >> 1) & 3)) << 4);
+    }
+    uint32_t it = 0;
+    for (long u = blockIdx.x; u < a.units; u += gridDim.x, ++it) {
+      int r, b, x0;
+      ri_unit(a, u, r, b, x0);
+      const uint32_t acc = it & 1, aph = (it >> 1) & 1;
+      const bool empty_row = __ldg(plan + a.d.off_row + r) == __ldg(plan + a.d.off_row + r + 1);
+      if (!mbar_wait(tfull(acc), aph, abort_flag, 0x85, 512)) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int t = 0; t < Cfg::TPU; ++t) {
+        bf16* orow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const long gp = ((long)b * a.RH + r) * a.RW + x0 + t * TILE_M + q * 32 + 8 * i + (lane >> 2);
+          orow[i] = a.out + gp * NOUT + (lane & 3) * 8;
+        }
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * (Cfg::TPU * NOUT) + t * NOUT;
+#pragma unroll
+        for (int cc = 0; cc < NOUT / 32; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + cc * 32, v);
+          tmem_ld_wait();
+          if (t == Cfg::TPU - 1 && cc == NOUT / 32 - 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty(acc));
+          }
+          if (empty_row) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            const float* bs = bias_s + cc * 32 + j * 8;
+            o.x = pack_bf16x2(__uint_as_float(v[j * 8 + 0]) + bs[0], __uint_as_float(v[j * 8 + 1]) + bs[1]);
+            o.y = pack_bf16x2(__uint_as_float(v[j * 8 + 2]) + bs[2], __uint_as_float(v[j * 8 + 3]) + bs[3]);
+            o.z = pack_bf16x2(__uint_as_float(v[j * 8 + 4]) + bs[4], __uint_as_float(v[j * 8 + 5]) + bs[5]);
+            o.w = pack_bf16x2(__uint_as_float(v[j * 8 + 6]) + bs[6], __uint_as_float(v[j * 8 + 7]) + bs[7]);
+            sts16(wr_row + ((j ^ wr_x) << 4), o);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
+                         : "r"(rd_addr[i]));
+            *reinterpret_cast<uint4*>(orow[i] + cc * 32) = o;
+          }
+          __syncwarp();
+        }
+      }
+    }
+  } else if (warp == FIRST_DEC_WARP) {
+    // ------------------------------------------------------------------ E streamer
+    if (lane == 0) {
+      uint32_t se = 0, pe = 0;
+      bool ok = true;
+      for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x) {
+        int r, b, x0;
+        ri_unit(a, u, r, b, x0);
+        const int w0 = __ldg(plan + a.d.off_row + r), w1 = __ldg(plan + a.d.off_row + r + 1);
+        if (w1 == w0) continue;
+        const int4 wa = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w0);
+        const int4 wb = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w1 - 1);
+        const int s0 = wa.z, s1 = wb.z + (wb.w & 0xFF);
+        for (int s = s0; s < s1; ++s) {
+          ok = mbar_wait(eempty(se), pe ^ 1, abort_flag, 0x86, 256);
+          if (!ok) break;
+          mbar_expect_tx(efull(se), Cfg::E_BYTES);
+          bulk_g2s(e0 + se * Cfg::E_BYTES, a.E + (size_t)((a.dbg & 4) ? 0 : s) * (Cfg::E_BYTES / 16), Cfg::E_BYTES, efull(se));
+          if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; }
+        }
+      }
+    }
+  } else if (warp >= FIRST_PROD_WARP) {
+    // ------------------------------------------------------------------ window loaders
+    // Two teams of eight warps; team t copies the windows t, t + 2, ... of the CTA's window sequence
+    // into stage t, so that two windows are in flight at any time: a team sends the arrival for its
+    // window once the copies have landed and then waits for its stage to come free again, while the
+    // other team's copies are under way.
+    constexpr int TEAM_WARPS = N_PRODUCER_WARPS / RI_WIN_STAGES;
+    const int team = (warp - FIRST_PROD_WARP) / TEAM_WARPS;
+    const int ptid = ((warp - FIRST_PROD_WARP) % TEAM_WARPS) * 32 + lane;
+    constexpr int NPT = TEAM_WARPS * 32;
+    uint32_t nw = 0;   // windows of this CTA so far (both teams count all of them)
+    uint32_t mine = 0; // windows this team has copied
+    bool ok = true;
+    for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x) {
+      int r, b, x0;
+      ri_unit(a, u, r, b, x0);
+      const int w0 = __ldg(plan + a.d.off_row + r), w1 = __ldg(plan + a.d.off_row + r + 1);
+      for (int w = w0; w < w1; ++w, ++nw) {
+        if ((int)(nw % RI_WIN_STAGES) != team) continue;
+        const int4 wr = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w);
+        const uint32_t ws = team, wph = mine & 1;
+        int okw = 1;
+        if (lane == 0) okw = mbar_wait(wempty(ws), wph ^ 1, abort_flag, 0x87) ? 1 : 0;
+        okw = __shfl_sync(0xffffffffu, okw, 0);
+        if (!okw) { ok = false; break; }
+        const int span = (wr.w >> 8) & 0xFF, mode = wr.w >> 16;
+        const int nch = (Cfg::TPU * TILE_M + span) * 8;
+        const bf16* rowp = a.src + ((long)b * a.SH + wr.x) * a.SW * 64;
+        const uint32_t sbase = win0 + ws * Cfg::WIN_BYTES;
+        int sx0 = x0 + wr.y;
+        if (mode == RI_MODE_WRAP) { sx0 %= a.SW; if (sx0 < 0) sx0 += a.SW; }
+        for (int c = ptid; c < nch; c += NPT) {
+          const int j = c >> 3, lg = c & 7;
+          int sx = sx0 + j;
+          bool valid = true;
+          if (mode == RI_MODE_WRAP) sx %= a.SW;
+          else { valid = sx >= 0 && sx < a.SW; if (!valid) sx = 0; }
+          if (!(a.dbg & 1)) cp_async16(sbase + j * 128 + ((lg ^ (j & 7)) << 4), rowp + (long)sx * 64 + lg * 8, valid ? 16u : 0u);
+        }
+        cp_async_commit();
+        cp_async_wait_all();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(wfull(ws));
+        ++mine;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- fix-up kernel: the planner's corrections for the pixels that deviate from their row's plan --------
+// One block per group of corrections that share a result pixel; thread = result channel.
+// forward : y[b, row, col, n]   += sum_e dw_e sum_c W[n, c, k_e]  x[b, srow_e, scol_e, c]
+// adjoint : gx[b, row, col, n]  += sum_e dw_e sum_c W[c, n, k_e] gy[b, srow_e, scol_e, c]
+constexpr int FIX_LANES = 4;  // corrections of a group worked on at the same time
+__global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
+    const bf16* __restrict__ src, bf16* __restrict__ res, const bf16* __restrict__ wk,
+    const int* __restrict__ plan, RiDir d, int SH, int SW, int RH, int RW, int NR) {
+  const int g = blockIdx.x, b = blockIdx.y;
+  const int e0 = __ldg(plan + d.off_group + g), e1 = __ldg(plan + d.off_group + g + 1);
+  if (e0 >= e1) return;
+  const int row = __ldg(plan + d.off_skip + 6 * e0), col = __ldg(plan + d.off_skip + 6 * e0 + 1);
+  __shared__ float xs[FIX_LANES][64];
+  __shared__ float total[64];
+  const int n = threadIdx.x, y = threadIdx.y;  // NR == 64 == blockDim.x
+  if (y == 0) total[n] = 0.f;
+  float acc = 0.f;
+  for (int eb = e0; eb < e1; eb += FIX_LANES) {
+    const int e = eb + y;
+    const bool on = e < e1;
+    int k = 0;
+    float we = 0.f;
+    if (on) {
+      const int* ent = plan + d.off_skip + 6 * e;
+      const int srow = __ldg(ent + 2), scol = __ldg(ent + 3);
+      k = __ldg(ent + 4);
+      we = __int_as_float(__ldg(ent + 5));
+      xs[y][n] = __bfloat162float(src[(((long)b * SH + srow) * SW + scol) * 64 + n]);
+    }
+    __syncthreads();
+    if (on) {
+      const uint4* wr = reinterpret_cast<const uint4*>(wk + ((long)k * NR + n) * 64);
+      float part = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const uint4 v = __ldg(wr + q);
+        const uint32_t p4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          part = fmaf(__uint_as_float(p4[t] << 16), xs[y][q * 8 + 2 * t], part);
+          part = fmaf(__uint_as_float(p4[t] & 0xFFFF0000u), xs[y][q * 8 + 2 * t + 1], part);
+        }
+      }
+      acc = fmaf(we, part, acc);
+    }
+    __syncthreads();
+  }
+  atomicAdd(&total[n], acc);
+  __syncthreads();
+  if (y == 0) {
+    bf16* rp = res + (((long)b * RH + row) * RW + col) * NR + n;
+    *rp = __float2bfloat16_rn(__bfloat162float(*rp) + total[n]);
+  }
+}
+
+static size_t rowinv_e_bytes(const RiDir& d, int NR) { return (size_t)d.nslot * NR * 128; }
+
+template <int NOUT>
+static int rowinv_launch_n(const RowInvArgs& a, cudaStream_t st) {
+  using Cfg = RiCfg<NOUT>;
+  static_assert(Cfg::SMEM <= SMEM_LIMIT, "row-invariant kernel does not fit shared memory");
+  if (!allow_big_smem(conv_rowinv_tc_kernel<NOUT>)) return MC_ERR_LAUNCH;
+  const long g = a.units < sm_count() ? a.units : sm_count();
+  conv_rowinv_tc_kernel<NOUT><<<(int)g, TC_THREADS, Cfg::SMEM, st>>>(a), MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
+
+}  // namespace tc
+
+using namespace tc;
+
+// Shapes the row-invariant kernels take (the map itself is judged by the planner).
+bool conv_rowinv_shape_ok(const mc_desc* d) {
+  return d->dtype == MC_BF16 && d->layout == MC_NHWC && d->P == 0 && (d->interp == 1 || d->interp == 2) &&
+         d->C_in == 64 && d->C_out == 64 && d->OW == d->IW && d->OW % TILE_M == 0 &&
+         (d->OW / TILE_M) % RiCfg<64>::TPU == 0 && d->K <= 64 &&
+         (long)d->B * std::max(d->OH, d->IH) * d->OW < (1L << 30);
+}
+
+size_t rowinv_analysis_bytes(const mc_desc* d) { return (size_t)d->OH * d->K * 3 * sizeof(double); }
+
+int rowinv_analyse_launch(const mc_desc* d, const void* map, void* out, cudaStream_t st) {
+  if (!aligned16(map) || !aligned16(out)) return MC_ERR_BAD_ARG;
+  rowinv_analyse_kernel<<<d->OH, 256, 0, st>>>((const float*)map, d->OH, d->OW, d->K, d->IW,
+                                               (double*)out), MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
+
+// -> number of int32s of the plan (0: the map does not qualify); copies at most cap ints to out
+long rowinv_assemble_host(const mc_desc* d, const double* analysis, const float* map, int* out,
+                          long cap) {
+  if (!conv_rowinv_shape_ok(d)) return 0;
+  const std::vector<int> plan = rowinv_assemble(d, analysis, map);
+  if (plan.empty()) return 0;
+  if (out && cap >= (long)plan.size()) std::memcpy(out, plan.data(), plan.size() * sizeof(int));
+  return (long)plan.size();
+}
+
+static bool rowinv_plan_matches(const mc_desc* d, const RiHeader* h) {
+  return h && h->magic == RI_PLAN_MAGIC && h->OH == d->OH && h->OW == d->OW && h->IH == d->IH &&
+         h->IW == d->IW && h->K == d->K && h->interp == d->interp;
+}
+
+// workspace of a call: the effective weights of every slot, then the tap-major weight copy
+static size_t rowinv_wk_offset(const RiDir& D, int NR) { return (rowinv_e_bytes(D, NR) + 255) & ~(size_t)255; }
+size_t rowinv_ws_bytes(const mc_desc* d, const void* plan_host, int dir) {
+  const RiHeader* h = (const RiHeader*)plan_host;
+  if (!rowinv_plan_matches(d, h)) return 0;
+  return rowinv_wk_offset(h->dir[dir], 64) + (size_t)d->K * 64 * 64 * sizeof(bf16);
+}
+
+// dir 0: y = conv(x); dir 1: gx = conv^T(gy).  `src` is the tensor that is gathered from.
+int rowinv_conv_launch(const mc_desc* d, int dir, const void* src, const void* plan_host,
+                       const void* plan_dev, const void* w, const void* bias, void* res, void* ws,
+                       size_t ws_bytes, cudaStream_t st) {
+  if (!conv_rowinv_shape_ok(d)) return MC_ERR_UNSUPPORTED;
+  const RiHeader* h = (const RiHeader*)plan_host;
+  if (!rowinv_plan_matches(d, h)) return MC_ERR_BAD_ARG;
+  const RiDir& D = h->dir[dir];
+  if (!ws || ws_bytes < rowinv_ws_bytes(d, plan_host, dir)) return MC_ERR_WORKSPACE;
+  if (!aligned16(src) || !aligned16(res) || !aligned16(ws) || !aligned16(plan_dev)) return MC_ERR_BAD_ARG;
+  const int* plan = (const int*)plan_dev;
+  bf16* wk = (bf16*)((uint8_t*)ws + rowinv_wk_offset(D, 64));
+  rowinv_wk_kernel<<<grid_for((long)d->K * 64 * 64, 256), 256, 0, st>>>((const bf16*)w, wk, 64, d->K,
+                                                                         d->C_in, dir), MC_COUNT(1);
+  if (D.nslot > 0)
+    rowinv_weights_kernel<<<D.nslot, 256, 0, st>>>(wk, plan, D, (uint4*)ws, 64), MC_COUNT(1);
+  RowInvArgs a;
+  a.src = (const bf16*)src; a.out = (bf16*)res; a.bias = (const bf16*)bias;
+  a.plan = plan; a.d = D; a.E = (const uint4*)ws;
+  a.B = d->B;
+  if (dir == 0) { a.SH = d->IH; a.SW = d->IW; a.RH = d->OH; a.RW = d->OW; }
+  else { a.SH = d->OH; a.SW = d->OW; a.RH = d->IH; a.RW = d->IW; }
+  a.tpu = RiCfg<64>::TPU;
+  a.upr = a.RW / (TILE_M * a.tpu);
+  a.units = (long)a.RH * a.B * a.upr;
+  a.dbg = getenv("MC_RI_DBG") ? atoi(getenv("MC_RI_DBG")) : 0;
+  int rc = rowinv_launch_n<64>(a, st);
+  if (rc) return rc;
+  if (D.ngroup > 0) {
+    rowinv_fix_kernel<<<dim3(D.ngroup, d->B), dim3(64, FIX_LANES), 0, st>>>((const bf16*)src, (bf16*)res, wk, plan, D,
+                                                           a.SH, a.SW, a.RH, a.RW, 64), MC_COUNT(1);
+    MC_CHECK_LAUNCH();
+  }
+  return MC_OK;
+}
+
+}  // namespace mc

@@ -2086,6 +2086,33 @@ extern "C" int mc_conv_fwd_static_scratch(const mc_desc* d, const void* x, const
                             (cudaStream_t)stream);
 }
 
+// ---- self-test of the bounded waits ---------------------------------------------------------------
+// One warp waits, with a limit of about a millisecond, on an mbarrier that nobody ever arrives at.
+// The wait must give up, raise the block's abort flag and the device status word, and the kernel
+// must return: the same path a tensor-core kernel takes if one of its roles stops answering.
+constexpr int SELFTEST_STATUS = 0x7F1;
+__global__ void wait_expiry_selftest_kernel(long long limit_cycles, int* observed) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(tc::smem_u32(&bar), 1);
+    abort_flag = 0;
+    tc::fence_barrier_init();
+  }
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = tc::mbar_wait(tc::smem_u32(&bar), 0, &abort_flag, SELFTEST_STATUS, 64, limit_cycles);
+  __syncthreads();
+  // the other lanes see the abort flag, as the roles of a real kernel do
+  if (threadIdx.x == 1 && observed) *observed = (abort_flag ? 2 : 0) | (ok ? 1 : 0);
+}
+
+extern "C" int mc_selftest_wait_expiry(int32_t* observed_dev, void* stream) {
+  wait_expiry_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(2000000LL, observed_dev), MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
+
 int device_status_read(cudaStream_t st, int reset) {
   int v = 0;
   if (cudaStreamSynchronize(st) != cudaSuccess) return MC_ERR_LAUNCH;
@@ -2098,3 +2125,5 @@ int device_status_read(cudaStream_t st, int reset) {
 }
 
 }  // namespace mc
+
+#include "conv_rowinv.cuh"

@@ -58,7 +58,8 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t par
 // of the device.
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int code, unsigned sleep_ns = 64) {
+                                          int code, unsigned sleep_ns = 64,
+                                          long long limit_cycles = WAIT_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   // Not ready: back off between polls.  Polling hammers the shared-memory pipe that the producer
   // warps need; every waiting role sleeps a little instead (the ring buffers absorb the latency).
@@ -69,7 +70,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if (ns < sleep_ns) ns *= 2;
     if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
+    if (clock64() - t0 > limit_cycles) break;
   }
   *abort_flag = 1;
   atomicCAS(&g_status, 0, code);

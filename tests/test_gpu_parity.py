@@ -461,3 +461,57 @@ def test_knn_self_match_is_first_and_one_based():
     assert torch.equal(idx[0, 0], torch.arange(1, 501, device="cuda"))
     assert torch.count_nonzero(dist[0, 0]) == 0
     assert (dist[0, 1:] >= dist[0, :-1]).all()
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_library_stays_usable(op_binding):
+    """The tensor-core kernels never wait without a limit: a wait that runs out raises the block's
+    abort flag and the device status word and the kernel returns.  mc_selftest_wait_expiry drives
+    that path on purpose with a one-warp kernel waiting a millisecond on a barrier nobody arrives
+    at; afterwards mc_device_status reports the code once, and ordinary calls work as before."""
+    from mappedconvolutions_b200 import _lib, ops
+    L = _lib.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    assert L.mc_device_status(st, 1) == 0
+    seen = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.check(L.mc_selftest_wait_expiry(seen.data_ptr(), st))
+    assert L.mc_device_status(st, 1) == 0x7F1        # raised by the wait; the read clears it
+    assert seen.item() == 2                           # abort flag set, the wait returned false
+    assert L.mc_device_status(st, 0) == 0
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(1, 64, 8, 16, generator=g).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    m = (torch.rand(8, 16, 4, 2, generator=g) * torch.tensor([15., 7.])).cuda()
+    w, b = torch.randn(64, 64, 4, generator=g).to(torch.bfloat16).cuda(), torch.zeros(64, dtype=torch.bfloat16).cuda()
+    y = ops.mapped_conv_forward(x, m, w, b, 4, 1)
+    want = oracle.mapped_conv_forward(x.float().cpu().contiguous(), m.cpu(), w.float().cpu(), b.float().cpu(), 4, 1)
+    H.assert_close(y.float(), want, 2e-2, "forward after the self-test")
+    assert L.mc_device_status(st, 1) == 0
+
+
+def test_non_finite_input_next_to_a_tap_that_reads_nothing(op_binding):
+    """Documented deviation of the bf16 tensor-core kernels: their tap records always point at real
+    pixels (a corner that contributes nothing gets weight 0 and the address of a pixel the tap reads
+    anyway, a tap that reads nothing at all the address of pixel 0), so that the gather needs no
+    predicates.  The reference skips such corners (include/core/interpolation.h:125-154).  With
+    finite inputs the two agree; a NaN in pixel 0 of an image reaches, through 0 * NaN, exactly the
+    outputs that have a tap lying completely outside the image - and no others."""
+    from mappedconvolutions_b200 import ops
+    g = torch.Generator().manual_seed(10)
+    Hh, Ww, K = 8, 16, 4
+    x = torch.randn(1, 64, Hh, Ww, generator=g).to(torch.bfloat16)
+    m = torch.rand(Hh, Ww, K, 2, generator=g) * torch.tensor([Ww - 2.0, Hh - 2.0]) + 0.5   # all inside
+    outside = torch.zeros(Hh, Ww, dtype=torch.bool)
+    outside[2, 3] = outside[5, 9] = True
+    m[outside, 1, :] = torch.tensor([-7.5, -3.25])          # tap 1 of two pixels reads nothing
+    reads_pixel0 = ((m[..., 0] < 1) & (m[..., 1] < 1)).any(-1)
+    assert not reads_pixel0.any()
+    w, b = torch.randn(64, 64, K, generator=g).to(torch.bfloat16), torch.zeros(64, dtype=torch.bfloat16)
+    cl = lambda t: t.cuda().contiguous(memory_format=torch.channels_last)
+    clean = ops.mapped_conv_forward(cl(x), m.cuda(), w.cuda(), b.cuda(), K, 1)
+    want = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, 1)
+    H.assert_close(clean.float(), want, 2e-2, "finite input")
+    xn = x.clone()
+    xn[0, :, 0, 0] = float("nan")
+    y = ops.mapped_conv_forward(cl(xn), m.cuda(), w.cuda(), b.cuda(), K, 1)
+    nan_at = torch.isnan(y.float()).any(1)[0].cpu()
+    assert torch.equal(nan_at, outside)
+    assert torch.equal(y[0][:, ~outside.cuda()], clean[0][:, ~outside.cuda()])

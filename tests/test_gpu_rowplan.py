@@ -1,0 +1,100 @@
+"""Row-plan convolution kernels (maps that are translation invariant along image rows) through the
+C ABI, against the oracle (float32 on the bf16-rounded operands, tolerance 2e-2) and against the
+general tensor-core kernels of the same library."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+from oracle import oracle
+from test_rowplan_host import gnomonic_like_map
+
+pytestmark = pytest.mark.gpu
+
+
+def build_plan(d, m_dev):
+    """analysis on the device -> host assembly -> (host plan, device plan) or None"""
+    from mappedconvolutions_b200 import _lib
+    L = _lib.lib()
+    n = L.mc_rowplan_analysis_bytes(d)
+    if n == 0:
+        return None
+    ana = torch.empty(n // 8, dtype=torch.float64, device=m_dev.device)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(L.mc_rowplan_analyse(d, m_dev.data_ptr(), ana.data_ptr(), st))
+    ana_h = np.ascontiguousarray(ana.cpu().numpy())
+    if (ana_h.reshape(-1, 3)[:, 2] == 0).any():
+        return None
+    map_h = np.ascontiguousarray(m_dev.cpu().numpy())
+    need = L.mc_rowplan_assemble(d, ana_h.ctypes.data, map_h.ctypes.data, None, 0)
+    if need == 0:
+        return None
+    plan_h = np.zeros(need, dtype=np.int32)
+    assert L.mc_rowplan_assemble(d, ana_h.ctypes.data, map_h.ctypes.data, plan_h.ctypes.data, need) == need
+    return plan_h, torch.from_numpy(plan_h).to(m_dev.device)
+
+
+def run(d, direction, src, plan, w, bias, res_shape):
+    from mappedconvolutions_b200 import _lib
+    L = _lib.lib()
+    plan_h, plan_d = plan
+    nws = L.mc_conv_rowplan_workspace_bytes(d, plan_h.ctypes.data, direction)
+    ws = torch.empty(max(nws, 16), dtype=torch.uint8, device=src.device)
+    res = torch.empty(res_shape, dtype=torch.bfloat16, device=src.device).contiguous(
+        memory_format=torch.channels_last)
+    fn = L.mc_conv_fwd_rowplan if direction == 0 else L.mc_conv_dgrad_rowplan
+    _lib.check(fn(d, src.data_ptr(), plan_h.ctypes.data, plan_d.data_ptr(), w.data_ptr(),
+                  None if bias is None else bias.data_ptr(), res.data_ptr(), ws.data_ptr(), nws,
+                  torch.cuda.current_stream().cuda_stream))
+    assert L.mc_device_status(torch.cuda.current_stream().cuda_stream, 1) == 0
+    return res
+
+
+def cl(t):
+    return t.contiguous(memory_format=torch.channels_last)
+
+
+@pytest.mark.parametrize("wrapped,interp,Hh,Ww,B", [(True, 1, 12, 512, 2), (False, 1, 9, 512, 3),
+                                                  (True, 2, 7, 1024, 1), (False, 2, 5, 512, 2)])
+def test_rowplan_forward_and_input_gradient(wrapped, interp, Hh, Ww, B):
+    from mappedconvolutions_b200 import _lib
+    C, K = 64, 9
+    m = gnomonic_like_map(Hh, Ww, wrapped, seed=Hh)
+    d = _lib.McDesc(B, C, C, Hh, Ww, Hh, Ww, K, 0, interp, _lib.MC_BF16, _lib.MC_NHWC)
+    plan = build_plan(d, m.cuda())
+    assert plan is not None
+    g = torch.Generator().manual_seed(3)
+    bf = torch.bfloat16
+    x, gy = torch.randn(B, C, Hh, Ww, generator=g).to(bf), torch.randn(B, C, Hh, Ww, generator=g).to(bf)
+    w, b = torch.randn(C, C, K, generator=g).to(bf), torch.randn(C, generator=g).to(bf)
+    y = run(d, 0, cl(x.cuda()), plan, w.cuda(), b.cuda(), (B, C, Hh, Ww))
+    gx = run(d, 1, cl(gy.cuda()), plan, w.cuda(), None, (B, C, Hh, Ww))
+    want_y = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, interp)
+    want_gx = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, interp)[0]
+    H.assert_close(y.float(), want_y, 2e-2, "row-plan forward vs oracle")
+    H.assert_close(gx.float(), want_gx, 2e-2, "row-plan input gradient vs oracle")
+
+
+def test_rowplan_on_the_gnomonic_map_matches_the_general_kernels():
+    """The benchmark's gnomonic 3 x 3 map (all latitudes, poles included) on a 64 x 512 image."""
+    from mappedconvolutions_b200 import _lib, ops
+    from mappedconvolutions_b200.util import get_projection_map
+    Hh, Ww, C, K, B = 64, 512, 64, 9, 2
+    m = get_projection_map((Hh, Ww), (3, 3), "gnomonic").contiguous()
+    d = _lib.McDesc(B, C, C, Hh, Ww, Hh, Ww, K, 0, 1, _lib.MC_BF16, _lib.MC_NHWC)
+    plan = build_plan(d, m.cuda())
+    assert plan is not None
+    g = torch.Generator().manual_seed(4)
+    bf = torch.bfloat16
+    x, gy = torch.randn(B, C, Hh, Ww, generator=g).to(bf), torch.randn(B, C, Hh, Ww, generator=g).to(bf)
+    w, b = torch.randn(C, C, K, generator=g).to(bf), torch.randn(C, generator=g).to(bf)
+    y = run(d, 0, cl(x.cuda()), plan, w.cuda(), b.cuda(), (B, C, Hh, Ww))
+    gx = run(d, 1, cl(gy.cuda()), plan, w.cuda(), None, (B, C, Hh, Ww))
+    want_y = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, 1)
+    want_gx = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, 1)[0]
+    H.assert_close(y.float(), want_y, 2e-2, "forward vs oracle")
+    H.assert_close(gx.float(), want_gx, 2e-2, "input gradient vs oracle")
+    y2 = ops.mapped_conv_forward(cl(x.cuda()), m.cuda(), w.cuda(), b.cuda(), K, 1)
+    H.assert_close(y.float(), y2.float(), 2e-2, "forward vs the general kernel")

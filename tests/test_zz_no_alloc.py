@@ -73,3 +73,38 @@ def test_static_scratch_rejects_what_does_not_fit():
     d2 = _lib.McDesc(1, 64, 40, 8, 16, 8, 16, 3, 0, 1, _lib.MC_BF16, _lib.MC_NHWC)  # C_out % 64 != 0
     assert lib.mc_conv_fwd_static_scratch(d2, x.data_ptr(), m.data_ptr(), w.data_ptr(),
                                           b.data_ptr(), y.data_ptr(), st) == -2
+
+
+def test_static_scratch_call_leaves_device_memory_untouched():
+    """What the entry point is for: no device memory is obtained or released by the call.  After a
+    first call (which looks the array's address up) the free memory of the device and the caching
+    allocator's reservation are the same before and after further calls, and two calls queued back
+    to back on one stream with different weights both give their own result."""
+    from mappedconvolutions_b200 import _lib
+    lib = _lib.lib()
+    x, w1, b1, m, full = _case(5, 2, 64, 16, 32, 16, 32, 9, 1)
+    _, w2, b2, _, _ = _case(6, 2, 64, 16, 32, 16, 32, 9, 1)
+    d = _lib.McDesc(*full, _lib.MC_BF16, _lib.MC_NHWC)
+    st = torch.cuda.current_stream().cuda_stream
+    mk = lambda: torch.empty((2, 64, 16, 32), dtype=torch.bfloat16, device="cuda",
+                             memory_format=torch.channels_last)
+    y1, y2, r1, r2 = mk(), mk(), mk(), mk()
+    n = lib.mc_conv_fwd_workspace_bytes(d)
+    ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+    for w, b, r in ((w1, b1, r1), (w2, b2, r2)):
+        _lib.check(lib.mc_conv_fwd(d, x.data_ptr(), m.data_ptr(), None, w.data_ptr(), b.data_ptr(),
+                                   r.data_ptr(), ws.data_ptr(), n, st))
+    _lib.check(lib.mc_conv_fwd_static_scratch(d, x.data_ptr(), m.data_ptr(), w1.data_ptr(),
+                                              b1.data_ptr(), y1.data_ptr(), st))   # set-up call
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    reserved0 = torch.cuda.memory_reserved()
+    for _ in range(3):
+        _lib.check(lib.mc_conv_fwd_static_scratch(d, x.data_ptr(), m.data_ptr(), w1.data_ptr(),
+                                                  b1.data_ptr(), y1.data_ptr(), st))
+        _lib.check(lib.mc_conv_fwd_static_scratch(d, x.data_ptr(), m.data_ptr(), w2.data_ptr(),
+                                                  b2.data_ptr(), y2.data_ptr(), st))
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0 and torch.cuda.memory_reserved() == reserved0
+    assert torch.equal(y1, r1) and torch.equal(y2, r2) and not torch.equal(y1, y2)
