@@ -124,12 +124,14 @@ class ClockSampler:
 def _map_builders():
     """The pure-torch sample-map builders, loaded by file path: importing the product package would
     load its CUDA libraries, which the CPU arm must not touch."""
-    import importlib.util
-    path = os.path.join(ROOT, "mappedconvolutions_b200", "util", "spherical_projections.py")
-    spec = importlib.util.spec_from_file_location("_bench_spherical_projections", path)
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    return mod
+    import importlib
+    import types
+    name = "_bench_map_builders"
+    if name not in sys.modules:  # the util directory as a package of its own, without its __init__
+        pkg = types.ModuleType(name)
+        pkg.__path__ = [os.path.join(ROOT, "mappedconvolutions_b200", "util")]
+        sys.modules[name] = pkg
+    return importlib.import_module(name + ".spherical_projections")
 
 
 def _all_host_threads():
@@ -370,27 +372,11 @@ def run_ours(args):
             torch.cuda.synchronize()
             return a.elapsed_time(c) / n
 
-        d = _lib.McDesc(BATCH, CIN, COUT, H, W, H, W, K, 0, 1, _lib.MC_BF16, _lib.MC_NHWC)
-        st = torch.cuda.current_stream().cuda_stream
-        y = torch.empty_like(gy)
-        gx = torch.empty_like(x)
-        gw = torch.empty(COUT, CIN, K, dtype=torch.float32, device=dev)
-        gb = torch.empty(COUT, dtype=torch.float32, device=dev)
-        nws = max(L.mc_conv_dgrad_workspace_bytes(d), L.mc_conv_wgrad_workspace_bytes(d),
-                  L.mc_conv_fwd_workspace_bytes(d), L.mc_conv_dgrad_inv_workspace_bytes(d), 16)
-        ws = torch.empty(nws, dtype=torch.uint8, device=dev)
-        if L.mc_conv_dgrad_inv_supported(d):
-            inv = ops._inverse_map(d, m)
-            dgrad = lambda: _lib.check(L.mc_conv_dgrad_inv(d, gy.data_ptr(), inv.data_ptr(), w.data_ptr(), None, gx.data_ptr(), ws.data_ptr(), nws, st))
-        else:
-            dgrad = lambda: _lib.check(L.mc_conv_dgrad(d, gy.data_ptr(), m.data_ptr(), None, w.data_ptr(), None, gx.data_ptr(), ws.data_ptr(), nws, st))
-        tab = ops._tap_map(d, m)
-        if tab is not None:
-            fwd = lambda: _lib.check(L.mc_conv_fwd_tap(d, x.data_ptr(), tab.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), ws.data_ptr(), nws, st))
-            wgrad = lambda: _lib.check(L.mc_conv_wgrad_tap(d, gy.data_ptr(), x.data_ptr(), tab.data_ptr(), gw.data_ptr(), gb.data_ptr(), st))
-        else:
-            fwd = lambda: _lib.check(L.mc_conv_fwd(d, x.data_ptr(), m.data_ptr(), None, w.data_ptr(), b.data_ptr(), y.data_ptr(), ws.data_ptr(), nws, st))
-            wgrad = lambda: _lib.check(L.mc_conv_wgrad(d, gy.data_ptr(), x.data_ptr(), m.data_ptr(), None, gw.data_ptr(), gb.data_ptr(), ws.data_ptr(), nws, st))
+        # each family through the extension, as the step runs it: forward; input gradient only;
+        # weight + bias gradient only (each includes its few microseconds of helper kernels)
+        fwd = lambda: host_ops.mapped_conv_forward(x, m, w, b, K, 1)
+        dgrad = lambda: host_ops.mapped_conv_backward(gy, m, x, w, b, K, 1, True, False)
+        wgrad = lambda: host_ops.mapped_conv_backward(gy, m, x, w, b, K, 1, False, True)
         fam = {"conv_fwd": fwd, "conv_dgrad": dgrad, "conv_wgrad": wgrad}
         times = {k: timed(f) for k, f in fam.items()}
         top = max(times, key=times.get)

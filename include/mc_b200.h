@@ -53,10 +53,18 @@ typedef struct mc_desc {
   int32_t interp;
   int32_t dtype;  /* MC_F32 / MC_F64 / MC_BF16 */
   int32_t layout; /* MC_NCHW / MC_NHWC, applies to every activation tensor of the call */
+  int32_t flags;  /* MC_FLAG_* bits, 0 = the reference's behaviour */
 } mc_desc;
 
+/* mc_conv_fwd / mc_conv_fwd_tap / mc_tconv_fwd: y = max(0, W . im2col(x) + bias), the activation
+ * applied in the kernel's epilogue (the reference leaves ReLU to a separate element-wise pass over
+ * y).  Its gradient is taken before the backward entry points: gz = gy where y > 0, else 0.
+ * Entry points that do not produce a layer output ignore the flag; the row-plan kernels refuse it
+ * (MC_ERR_UNSUPPORTED). */
+enum { MC_FLAG_RELU = 1 };
+
 const char* mc_strerror(int code);
-/* ABI version, bumped on any signature change. */
+/* ABI version, bumped on any change of a signature or of mc_desc (2: mc_desc.flags, row plans). */
 int mc_abi_version(void);
 /* Diagnostic: kernels launched by this library so far in this process (no counterpart in the
  * reference; used by the benchmark to report its launch count). */
@@ -187,6 +195,12 @@ int mc_conv_fwd_rowplan(const mc_desc* d, const void* x, const void* plan_host, 
 int mc_conv_dgrad_rowplan(const mc_desc* d, const void* gy, const void* plan_host,
                           const void* plan_dev, const void* w, const void* bias_out, void* gx,
                           void* ws, size_t ws_bytes, void* stream);
+/* Weight and bias gradient (float32, fully overwritten; gb may be NULL) from the same plan; ws holds
+ * one 64 x 64 float32 partial sum per slot and batch part. */
+size_t mc_conv_wgrad_rowplan_workspace_bytes(const mc_desc* d, const void* plan_host);
+int mc_conv_wgrad_rowplan(const mc_desc* d, const void* gy, const void* x, const void* plan_host,
+                          const void* plan_dev, void* gw, void* gb, void* ws, size_t ws_bytes,
+                          void* stream);
 
 /* gw(C_out,C_in,K) = sum_b gy_b . im2col_map(x_b)^T and gb(C_out) = sum_{b,h,w} gy.
  * gw and gb are written in the accumulation type: double for MC_F64, float otherwise

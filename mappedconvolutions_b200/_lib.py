@@ -11,11 +11,13 @@ LIB_PATH = os.path.join(_PKG, "lib", "libmc_b200.so")
 
 MC_F32, MC_F64, MC_BF16 = 0, 1, 2
 MC_NCHW, MC_NHWC = 0, 1
+MC_FLAG_RELU = 1
 
 
 class McDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in
-                ("B", "C_in", "C_out", "IH", "IW", "OH", "OW", "K", "P", "interp", "dtype", "layout")]
+                ("B", "C_in", "C_out", "IH", "IW", "OH", "OW", "K", "P", "interp", "dtype", "layout",
+                 "flags")]
 
 
 class McError(RuntimeError):
@@ -56,6 +58,8 @@ SIGNATURES = {
     "mc_conv_rowplan_workspace_bytes": (_sz, [_dp, _vp, _i32]),
     "mc_conv_fwd_rowplan": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_dgrad_rowplan": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "mc_conv_wgrad_rowplan_workspace_bytes": (_sz, [_dp, _vp]),
+    "mc_conv_wgrad_rowplan": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_wgrad": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mc_conv_wgrad_workspace_bytes": (_sz, [_dp]),
     "mc_tconv_fwd": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

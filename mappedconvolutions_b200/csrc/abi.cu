@@ -47,6 +47,9 @@ long rowinv_assemble_host(const mc_desc*, const double*, const float*, int*, lon
 size_t rowinv_ws_bytes(const mc_desc*, const void*, int);
 int rowinv_conv_launch(const mc_desc*, int, const void*, const void*, const void*, const void*,
                        const void*, void*, void*, size_t, cudaStream_t);
+size_t rowinv_wgrad_ws_bytes(const mc_desc*, const void*);
+int rowinv_wgrad_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
+                        void*, void*, size_t, cudaStream_t);
 }  // namespace mc
 
 namespace mc {
@@ -56,7 +59,7 @@ using namespace mc;
 
 extern "C" {
 
-int mc_abi_version(void) { return 1; }
+int mc_abi_version(void) { return 2; }
 
 uint64_t mc_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -225,6 +228,19 @@ int mc_conv_dgrad_rowplan(const mc_desc* d, const void* gy, const void* plan_hos
   if (!gy || !plan_host || !plan_dev || !w || !gx) return MC_ERR_BAD_ARG;
   return rowinv_conv_launch(d, 1, gy, plan_host, plan_dev, w, bias_out, gx, ws, ws_bytes,
                             (cudaStream_t)stream);
+}
+
+size_t mc_conv_wgrad_rowplan_workspace_bytes(const mc_desc* d, const void* plan_host) {
+  if (!d || check_conv_desc_public(d) || !plan_host) return 0;
+  return rowinv_wgrad_ws_bytes(d, plan_host);
+}
+int mc_conv_wgrad_rowplan(const mc_desc* d, const void* gy, const void* x, const void* plan_host,
+                          const void* plan_dev, void* gw, void* gb, void* ws, size_t ws_bytes,
+                          void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!gy || !x || !plan_host || !plan_dev || !gw) return MC_ERR_BAD_ARG;
+  return rowinv_wgrad_launch(d, gy, x, plan_host, plan_dev, gw, gb, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 int mc_conv_dgrad(const mc_desc* d, const void* gy, const void* map, const void* iw, const void* w,

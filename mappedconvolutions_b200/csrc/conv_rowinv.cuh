@@ -49,7 +49,8 @@ constexpr int RI_MAX_WIN_PER_ROW = 64;
 constexpr int RI_MAX_SLOT_PER_ROW = 128;
 constexpr double RI_TOL = 1e-3;  // pixels: largest deviation from exact translation invariance
 constexpr int RI_MODE_CLIP = 0, RI_MODE_WRAP = 1;
-constexpr int RI_PLAN_MAGIC = 0x52495031;
+constexpr int RI_PLAN_MAGIC = 0x52495032;
+constexpr int RI_WG_PAIRS = 8;  // M = 128 accumulators (two slots each) a weight-gradient unit holds
 
 // ---- plan layout (a flat int32 buffer, identical on host and device) -------------------------------
 struct RiDir {
@@ -65,6 +66,8 @@ struct RiDir {
   int off_skip;   // nskip x 6 corrections: result row, result column, source row, source column, tap,
                   // weight difference (float bits; exact minus nominal)
   int off_group;  // (ngroup + 1): runs of corrections that apply to the same result pixel
+  int nwgunit;    // weight-gradient work units: runs of windows of a row whose slot pairs fit TMEM
+  int off_wgunit; // nwgunit x 4: row, first window, windows, first slot
 };
 struct RiHeader {
   int magic, total_ints;
@@ -215,6 +218,27 @@ static void ri_emit_dir(std::vector<RiCon>& cons, std::vector<RiFix>& fixes, int
   };
   d.off_row = put(row_off); d.off_win = put(win); d.off_slot = put(slot); d.off_coff = put(coff);
   d.off_ctap = put(ctap); d.off_cw = put(cw); d.off_skip = put(skip); d.off_group = put(group);
+  // weight-gradient units: consecutive windows of a row, as many as give at most RI_WG_PAIRS pairs
+  // of slots (the slots of a window are paired up; an odd one out is paired with itself)
+  std::vector<int> wg;
+  for (int r = 0; r < rows; ++r) {
+    int w = row_off[r];
+    while (w < row_off[r + 1]) {
+      int pairs = 0, w1 = w;
+      while (w1 < row_off[r + 1]) {
+        const int p = ((win[4 * w1 + 3] & 0xFF) + 1) / 2;
+        if (w1 > w && pairs + p > RI_WG_PAIRS) break;
+        pairs += p;
+        ++w1;
+      }
+      if (pairs > RI_WG_PAIRS) ok = false;  // a single window with more than 16 slots
+      const int rec[4] = {r, w, w1 - w, win[4 * w + 2]};
+      wg.insert(wg.end(), rec, rec + 4);
+      w = w1;
+    }
+  }
+  d.nwgunit = (int)wg.size() / 4;
+  d.off_wgunit = put(wg);
 }
 
 // One decoded map entry on the host: the (up to four) source pixels and weights the general kernels
@@ -404,6 +428,8 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 constexpr int RI_WIN_STAGES = 2;
+static __device__ long long g_ri_prof[16];
+#define RI_T(var) const long long var = clock64()
 
 template <int NOUT>
 struct RiCfg {
@@ -468,9 +494,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
     constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 0, 0);
     uint32_t it = 0, nw = 0, se = 0, pe = 0;
     int ok = 1;
+    long long p_plan = 0, p_temp = 0, p_wf = 0, p_ef = 0, p_iss = 0, p_tot = clock64();
     for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x, ++it) {
       int r, b, x0;
       ri_unit(a, u, r, b, x0);
+      RI_T(t_a);
       const int w0 = __ldg(plan + a.d.off_row + r), w1 = __ldg(plan + a.d.off_row + r + 1);
       __syncwarp();
       for (int i = lane; i < w1 - w0; i += 32)
@@ -484,17 +512,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
       for (int i = lane; i < ns; i += 32) s_shift[i] = __ldg(plan + a.d.off_slot + sfirst + i);
       __syncwarp();
       if (lane == 0) {
+        RI_T(t_b); p_plan += t_b - t_a;
         const uint32_t acc = it & 1, aph = (it >> 1) & 1;
-        ok = mbar_wait(tempty(acc), aph ^ 1, abort_flag, 0x81) ? 1 : 0;
+        ok = mbar_wait_spin(tempty(acc), aph ^ 1, abort_flag, 0x81) ? 1 : 0;
         tc_fence_after_sync();
+        RI_T(t_c); p_temp += t_c - t_b;
         const uint32_t tmem_d = tmem_base + acc * (Cfg::TPU * NOUT);
         int si = 0;
         for (int w = 0; w < w1 - w0 && ok; ++w, ++nw) {
           const uint32_t ws = nw % RI_WIN_STAGES, wph = (nw / RI_WIN_STAGES) & 1;
-          ok = mbar_wait(wfull(ws), wph, abort_flag, 0x82) ? 1 : 0;
+          RI_T(t_d);
+          ok = mbar_wait_spin(wfull(ws), wph, abort_flag, 0x82) ? 1 : 0;
+          RI_T(t_e); p_wf += t_e - t_d;
           const int nsl = s_win[w].w & 0xFF;
           for (int s = 0; s < nsl && ok; ++s, ++si) {
-            ok = mbar_wait(efull(se), pe, abort_flag, 0x83) ? 1 : 0;
+            RI_T(t_f);
+            ok = mbar_wait_spin(efull(se), pe, abort_flag, 0x83) ? 1 : 0;
+            RI_T(t_g); p_ef += t_g - t_f;
             if (!ok) break;
             tc_fence_after_sync();
             const uint64_t bdesc = make_desc_sw128(e0 + se * Cfg::E_BYTES, 16, 1024);
@@ -508,6 +542,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
             }
             mma_commit(eempty(se));
             if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; }
+            p_iss += clock64() - t_g;
           }
           if (ok) mma_commit(wempty(ws));
         }
@@ -517,7 +552,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
     }
     if (lane == 0) {
       mma_commit(drain_bar);
-      mbar_wait(drain_bar, 0, abort_flag, 0x84);
+      mbar_wait_spin(drain_bar, 0, abort_flag, 0x84);
+      if (blockIdx.x == 0) {
+        g_ri_prof[0] = clock64() - p_tot; g_ri_prof[1] = p_plan; g_ri_prof[2] = p_temp;
+        g_ri_prof[3] = p_wf; g_ri_prof[4] = p_ef; g_ri_prof[5] = p_iss; g_ri_prof[6] = it;
+      }
     }
     __syncwarp();
   } else if (warp <= N_EPI_WARPS) {
@@ -539,7 +578,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
       ri_unit(a, u, r, b, x0);
       const uint32_t acc = it & 1, aph = (it >> 1) & 1;
       const bool empty_row = __ldg(plan + a.d.off_row + r) == __ldg(plan + a.d.off_row + r + 1);
-      if (!mbar_wait(tfull(acc), aph, abort_flag, 0x85, 512)) break;
+      {
+        int okt = 1;
+        if (lane == 0) okt = mbar_wait_spin(tfull(acc), aph, abort_flag, 0x85) ? 1 : 0;
+        okt = __shfl_sync(0xffffffffu, okt, 0);
+        if (!okt) break;
+      }
       tc_fence_after_sync();
 #pragma unroll
       for (int t = 0; t < Cfg::TPU; ++t) {
@@ -564,6 +608,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0u;
           }
+          if (a.dbg & 16) continue;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 o;
@@ -601,10 +646,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
         const int4 wb = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w1 - 1);
         const int s0 = wa.z, s1 = wb.z + (wb.w & 0xFF);
         for (int s = s0; s < s1; ++s) {
-          ok = mbar_wait(eempty(se), pe ^ 1, abort_flag, 0x86, 256);
+          ok = mbar_wait_spin(eempty(se), pe ^ 1, abort_flag, 0x86);
           if (!ok) break;
+          if (a.dbg & 8) { mbar_arrive(efull(se)); } else {
           mbar_expect_tx(efull(se), Cfg::E_BYTES);
           bulk_g2s(e0 + se * Cfg::E_BYTES, a.E + (size_t)((a.dbg & 4) ? 0 : s) * (Cfg::E_BYTES / 16), Cfg::E_BYTES, efull(se));
+          }
           if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; }
         }
       }
@@ -631,22 +678,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
         const int4 wr = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w);
         const uint32_t ws = team, wph = mine & 1;
         int okw = 1;
-        if (lane == 0) okw = mbar_wait(wempty(ws), wph ^ 1, abort_flag, 0x87) ? 1 : 0;
+        if (lane == 0) okw = mbar_wait_spin(wempty(ws), wph ^ 1, abort_flag, 0x87) ? 1 : 0;
         okw = __shfl_sync(0xffffffffu, okw, 0);
         if (!okw) { ok = false; break; }
         const int span = (wr.w >> 8) & 0xFF, mode = wr.w >> 16;
-        const int nch = (Cfg::TPU * TILE_M + span) * 8;
         const bf16* rowp = a.src + ((long)b * a.SH + wr.x) * a.SW * 64;
         const uint32_t sbase = win0 + ws * Cfg::WIN_BYTES;
-        int sx0 = x0 + wr.y;
-        if (mode == RI_MODE_WRAP) { sx0 %= a.SW; if (sx0 < 0) sx0 += a.SW; }
-        for (int c = ptid; c < nch; c += NPT) {
-          const int j = c >> 3, lg = c & 7;
-          int sx = sx0 + j;
+        // thread -> 16-byte chunk lg of rows j0, j0 + NPT / 8, ...; the source column advances with
+        // the row and is wrapped (or clipped) by one compare per step instead of a division
+        const int lg = ptid & 7, j0 = ptid >> 3;
+        constexpr int JSTEP = NPT / 8;
+        int sx = x0 + wr.y + j0;
+        if (mode == RI_MODE_WRAP) { sx %= a.SW; if (sx < 0) sx += a.SW; }
+        const int nrows = Cfg::TPU * TILE_M + span;
+        const bf16* colp = rowp + lg * 8;
+        uint32_t dst = sbase + j0 * 128;
+        for (int j = j0; j < nrows; j += JSTEP) {
           bool valid = true;
-          if (mode == RI_MODE_WRAP) sx %= a.SW;
-          else { valid = sx >= 0 && sx < a.SW; if (!valid) sx = 0; }
-          if (!(a.dbg & 1)) cp_async16(sbase + j * 128 + ((lg ^ (j & 7)) << 4), rowp + (long)sx * 64 + lg * 8, valid ? 16u : 0u);
+          int scol = sx;
+          if (mode != RI_MODE_WRAP) { valid = sx >= 0 && sx < a.SW; if (!valid) scol = 0; }
+          if (!(a.dbg & 1)) cp_async16(dst + ((lg ^ (j & 7)) << 4), colp + (long)scol * 64, valid ? 16u : 0u);
+          dst += JSTEP * 128;
+          sx += JSTEP;
+          if (mode == RI_MODE_WRAP) { while (sx >= a.SW) sx -= a.SW; }
         }
         cp_async_commit();
         cp_async_wait_all();
@@ -721,6 +775,336 @@ __global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
   }
 }
 
+
+// ---- weight gradient -------------------------------------------------------------------------------
+// Per slot s = (row r, source row sy, shift dx):  gE[s][ci][co] = sum_{b, x} X[b, sy, x + dx, ci] gy[b, r, x, co],
+// then gw[co, ci, k] = sum_s sum_{contributions (k, w) of s} w gE[s][ci][co]  (rowinv_wgrad_reduce_kernel).
+// The X window [pixel][ci] is the MN-major A operand (M = ci); two slots of a window make one M = 128
+// operand whose second half starts (shift_B - shift_A) rows after the first (the descriptor's
+// leading byte offset); the gy chunk [pixel][co] is the MN-major B operand; the reduction runs
+// over pixels, 16 per MMA.  A unit (a run of windows of one row with at most RI_WG_PAIRS pairs, for
+// one part of the batch) keeps its pairs' accumulators in tensor memory while it streams the row of
+// every image in chunks of 256 pixels.
+constexpr int WG_TILES = 2;                                         // 128-pixel tiles per chunk
+constexpr uint32_t WG_WIN_ROWS = WG_TILES * TILE_M + RI_SPAN;
+constexpr uint32_t WG_WIN_BYTES = ((WG_WIN_ROWS * 128 + 1023) / 1024) * 1024;  // 36 864
+constexpr uint32_t WG_GY_BYTES = WG_TILES * TILE_M * 128;           // 32 768
+constexpr int WG_NW = 4, WG_NG = 2;                                 // window / gy stages
+constexpr int WG_NBAR = 2 * WG_NW + 2 * WG_NG + 3;
+constexpr size_t WG_SMEM = 1024 + (size_t)WG_NW * WG_WIN_BYTES + (size_t)WG_NG * WG_GY_BYTES +
+                           WG_NBAR * 8 + 64 + (RI_MAX_WIN_PER_ROW * 16 + RI_MAX_SLOT_PER_ROW * 4);
+
+struct RowInvWgArgs {
+  const bf16* x;    // (B, SH, SW, 64)
+  const bf16* gy;   // (B, RH, RW, 64)
+  float* gE;        // [bsplit][nslot][64 ci][64 co]
+  const int* plan;
+  RiDir d;
+  int B, SH, SW, RH, RW;
+  int bsplit;       // parts the batch is cut into (a unit works on one)
+  long units;       // nwgunit * bsplit
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const RowInvWgArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t win0 = smem_u32(sm);
+  const uint32_t gy0 = win0 + WG_NW * WG_WIN_BYTES;
+  uint64_t* bars = (uint64_t*)(sm + WG_NW * WG_WIN_BYTES + WG_NG * WG_GY_BYTES);
+  uint32_t* misc = (uint32_t*)(bars + WG_NBAR);
+  volatile int* abort_flag = (volatile int*)(misc + 1);
+  int4* s_win = (int4*)(((uintptr_t)(misc + 4) + 15) & ~(uintptr_t)15);
+  int* s_shift = (int*)(s_win + RI_MAX_WIN_PER_ROW);
+  const uint32_t bar0 = smem_u32(bars);
+  auto wfull = [&](int s) { return bar0 + 8u * s; };
+  auto wempty = [&](int s) { return bar0 + 8u * (WG_NW + s); };
+  auto gfull = [&](int s) { return bar0 + 8u * (2 * WG_NW + s); };
+  auto gempty = [&](int s) { return bar0 + 8u * (2 * WG_NW + WG_NG + s); };
+  const uint32_t accfull = bar0 + 8u * (2 * WG_NW + 2 * WG_NG);
+  const uint32_t accempty = accfull + 8u, drain_bar = accfull + 16u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr int TEAMS = 2, TEAM_WARPS = N_PRODUCER_WARPS / TEAMS;
+  const int* plan = a.plan;
+  const int nchunk = a.RW / (WG_TILES * TILE_M);
+  const int bper = (a.B + a.bsplit - 1) / a.bsplit;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < WG_NW; ++s) { mbar_init(wfull(s), TEAM_WARPS); mbar_init(wempty(s), 1); }
+    for (int s = 0; s < WG_NG; ++s) { mbar_init(gfull(s), TEAM_WARPS); mbar_init(gempty(s), 1); }
+    mbar_init(accfull, 1);
+    mbar_init(accempty, N_EPI_WARPS);
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) tmem_alloc(smem_u32(misc), TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *misc;
+
+  // unit u -> (unit record, batch part)
+  auto unit_rec = [&](long u, int& part) {
+    const int ui = (int)(u / a.bsplit);
+    part = (int)(u - (long)ui * a.bsplit);
+    return __ldg(reinterpret_cast<const int4*>(plan + a.d.off_wgunit) + ui);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc_bf16(TILE_M, 64, 1, 1);
+    uint32_t it = 0, nw = 0, ng = 0;
+    int ok = 1;
+    for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x, ++it) {
+      int part;
+      const int4 ur = unit_rec(u, part);
+      __syncwarp();
+      for (int i = lane; i < ur.z; i += 32)
+        s_win[i] = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + ur.y + i);
+      __syncwarp();
+      const int ns = s_win[ur.z - 1].z + (s_win[ur.z - 1].w & 0xFF) - ur.w;
+      for (int i = lane; i < ns; i += 32) s_shift[i] = __ldg(plan + a.d.off_slot + ur.w + i);
+      __syncwarp();
+      if (lane == 0) {
+        ok = mbar_wait(accempty, (it & 1) ^ 1, abort_flag, 0x91) ? 1 : 0;
+        tc_fence_after_sync();
+        const int b0 = part * bper, b1 = min(a.B, b0 + bper);
+        bool first = true;
+        for (int b = b0; b < b1 && ok; ++b) {
+          for (int ch = 0; ch < nchunk && ok; ++ch, ++ng) {
+            const uint32_t gs = ng % WG_NG, gph = (ng / WG_NG) & 1;
+            ok = mbar_wait(gfull(gs), gph, abort_flag, 0x92) ? 1 : 0;
+            int si = 0, pair = 0;
+            for (int w = 0; w < ur.z && ok; ++w, ++nw) {
+              const uint32_t ws = nw % WG_NW, wph = (nw / WG_NW) & 1;
+              ok = mbar_wait(wfull(ws), wph, abort_flag, 0x93) ? 1 : 0;
+              if (!ok) break;
+              tc_fence_after_sync();
+              const int nsl = s_win[w].w & 0xFF;
+              for (int s = 0; s < nsl; s += 2, ++pair) {
+                const int shA = s_shift[si + s], shB = s + 1 < nsl ? s_shift[si + s + 1] : shA;
+                const uint32_t abase = win0 + ws * WG_WIN_BYTES + (uint32_t)shA * 128u;
+                const uint64_t adesc = make_desc_sw128(abase, (uint32_t)(shB - shA) * 128u, 1024);
+                const uint64_t bdesc = make_desc_sw128(gy0 + gs * WG_GY_BYTES, STAGE_BYTES, 1024);
+#pragma unroll
+                for (int kk = 0; kk < WG_TILES * TILE_M / 16; ++kk)  // 16 pixels per MMA: +2048 bytes
+                  mma_bf16_ss(tmem_base + pair * 64, adesc + 128 * kk, bdesc + 128 * kk, idesc,
+                              !(first && kk == 0));
+              }
+              si += nsl;
+              mma_commit(wempty(ws));
+            }
+            first = false;
+            if (ok) mma_commit(gempty(gs));
+          }
+        }
+        if (ok) mma_commit(accfull);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    if (lane == 0) {
+      mma_commit(drain_bar);
+      mbar_wait(drain_bar, 0, abort_flag, 0x94);
+      if (blockIdx.x == 0) { g_ri_prof[0] = it; g_ri_prof[1] = nw; g_ri_prof[2] = ng; g_ri_prof[3] = ok; }
+    }
+    __syncwarp();
+  } else if (warp <= N_EPI_WARPS) {
+    // ------------------------------------------------------------------ epilogue: accumulators -> gE
+    const int q = warp & 3;
+    uint32_t it = 0;
+    for (long u = blockIdx.x; u < a.units; u += gridDim.x, ++it) {
+      int part;
+      const int4 ur = unit_rec(u, part);
+      int okt = 1;
+      if (lane == 0) okt = mbar_wait(accfull, it & 1, abort_flag, 0x95) ? 1 : 0;
+      okt = __shfl_sync(0xffffffffu, okt, 0);
+      if (!okt) { if (blockIdx.x == 0 && lane == 0 && q == 0) g_ri_prof[4] = it; break; }
+      tc_fence_after_sync();
+      float* out = a.gE + (size_t)part * a.d.nslot * 4096;
+      int pair = 0;
+      for (int w = 0; w < ur.z; ++w) {
+        const int4 wr = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + ur.y + w);
+        const int nsl = wr.w & 0xFF;
+        for (int s = 0; s < nsl; s += 2, ++pair) {
+          // lanes 0-63 of the accumulator: slot s (row = ci); lanes 64-127: slot s + 1
+          const int slot = wr.z + s + (q >> 1);
+          const bool live = (q >> 1) == 0 || s + 1 < nsl;
+          const int ci = (q & 1) * 32 + lane;
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + pair * 64 + cc * 32, v);
+            tmem_ld_wait();
+            if (live) {
+              float4* dst = reinterpret_cast<float4*>(out + ((size_t)slot * 64 + ci) * 64 + cc * 32);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                     __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(accempty);
+    }
+  } else if (warp >= FIRST_PROD_WARP) {
+    // ------------------------------------------------------------------ loaders
+    // Items in the order the MMA thread consumes them: per (image, chunk) the gy chunk, then the
+    // unit's windows.  Two teams of eight warps work side by side, so two copies are in flight.  A
+    // ring stage is always filled by the same team (stage index modulo 2): a team waits for its
+    // stages in order, so it can never be more than one phase ahead of the consumer - which is what a
+    // parity wait needs to be unambiguous.
+    const int team = (warp - FIRST_PROD_WARP) / TEAM_WARPS;
+    const int ptid = ((warp - FIRST_PROD_WARP) % TEAM_WARPS) * 32 + lane;
+    constexpr int NPT = TEAM_WARPS * 32, JSTEP = NPT / 8;
+    const int lg = ptid & 7, j0 = ptid >> 3;
+    uint32_t nw = 0, ng = 0;
+    bool ok = true;
+    auto finish = [&](uint32_t bar) {
+      cp_async_commit();
+      cp_async_wait_all();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
+    };
+    auto wait_empty = [&](uint32_t bar, uint32_t parity, int code) {
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait(bar, parity, abort_flag, code) ? 1 : 0;
+      return __shfl_sync(0xffffffffu, okw, 0) != 0;
+    };
+    for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x) {
+      int part;
+      const int4 ur = unit_rec(u, part);
+      const int b0 = part * bper, b1 = min(a.B, b0 + bper);
+      for (int b = b0; b < b1 && ok; ++b) {
+        for (int ch = 0; ch < nchunk && ok; ++ch) {
+          const int x0 = ch * WG_TILES * TILE_M;
+          if ((int)(ng % TEAMS) == team) {  // the gy chunk
+            const uint32_t gs = ng % WG_NG, gph = (ng / WG_NG) & 1;
+            if (!wait_empty(gempty(gs), gph ^ 1, 0x96)) { ok = false; break; }
+            const bf16* gp = a.gy + (((long)b * a.RH + ur.x) * a.RW + x0) * 64 + lg * 8;
+            const uint32_t dst = gy0 + gs * WG_GY_BYTES;
+            for (int j = j0; j < WG_TILES * TILE_M; j += JSTEP)
+              cp_async16(dst + j * 128 + ((lg ^ (j & 7)) << 4), gp + (long)j * 64, 16u);
+            finish(gfull(gs));
+          }
+          ++ng;
+          for (int w = 0; w < ur.z; ++w, ++nw) {
+            if ((int)(nw % TEAMS) != team) continue;
+            const int4 wr = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + ur.y + w);
+            const uint32_t ws = nw % WG_NW, wph = (nw / WG_NW) & 1;
+            if (!wait_empty(wempty(ws), wph ^ 1, 0x97)) {
+              ok = false; break; }
+            const int span = (wr.w >> 8) & 0xFF, mode = wr.w >> 16;
+            const bf16* colp = a.x + ((long)b * a.SH + wr.x) * a.SW * 64 + lg * 8;
+            int sx = x0 + wr.y + j0;
+            if (mode == RI_MODE_WRAP) { sx %= a.SW; if (sx < 0) sx += a.SW; }
+            const int nrows = WG_TILES * TILE_M + span;
+            uint32_t dst = win0 + ws * WG_WIN_BYTES + j0 * 128;
+            for (int j = j0; j < nrows; j += JSTEP) {
+              bool valid = true;
+              int scol = sx;
+              if (mode != RI_MODE_WRAP) { valid = sx >= 0 && sx < a.SW; if (!valid) scol = 0; }
+              cp_async16(dst + ((lg ^ (j & 7)) << 4), colp + (long)scol * 64, valid ? 16u : 0u);
+              dst += JSTEP * 128;
+              sx += JSTEP;
+              if (mode == RI_MODE_WRAP) { while (sx >= a.SW) sx -= a.SW; }
+            }
+            finish(wfull(ws));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// gw[co, ci, k] += sum over the slots of a chunk of rows of sum over the slot's contributions with
+// tap k of weight * (sum over batch parts of gE[slot][ci][co]).  Thread = one (ci, co) element;
+// blockIdx.y = chunk of slots.  gw is float32 and zero before the first block adds to it.
+constexpr int WGR_TAPS = 16;
+__global__ void __launch_bounds__(256) rowinv_wgrad_reduce_kernel(const float* __restrict__ gE,
+                                                                  const int* __restrict__ plan, RiDir d,
+                                                                  int bsplit, int K, int Cin,
+                                                                  float* __restrict__ gw) {
+  const int e = blockIdx.x * 256 + threadIdx.x;  // ci * 64 + co
+  const int ci = e >> 6, co = e & 63;
+  const int per = (d.nslot + gridDim.y - 1) / gridDim.y;
+  const int s0 = blockIdx.y * per, s1 = min(d.nslot, s0 + per);
+  for (int k0 = 0; k0 < K; k0 += WGR_TAPS) {
+    float acc[WGR_TAPS];
+#pragma unroll
+    for (int i = 0; i < WGR_TAPS; ++i) acc[i] = 0.f;
+    for (int s = s0; s < s1; ++s) {
+      float v = 0.f;
+      for (int p = 0; p < bsplit; ++p) v += __ldg(gE + ((size_t)p * d.nslot + s) * 4096 + e);
+      const int c0 = __ldg(plan + d.off_coff + s), c1 = __ldg(plan + d.off_coff + s + 1);
+      for (int c = c0; c < c1; ++c) {
+        const int k = __ldg(plan + d.off_ctap + c) - k0;
+        const float wv = __int_as_float(__ldg(plan + d.off_cw + c)) * v;
+#pragma unroll
+        for (int i = 0; i < WGR_TAPS; ++i)
+          if (i == k) acc[i] += wv;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < WGR_TAPS; ++i)
+      if (k0 + i < K && acc[i] != 0.f) atomicAdd(gw + ((long)co * Cin + ci) * K + k0 + i, acc[i]);
+  }
+}
+
+// The planner's corrections in the weight gradient:
+// gw[co, ci, k] += sum_b dw gy[b, row, col, co] x[b, srow, scol, ci] for every correction with tap k.
+// blockIdx.x = tap, blockIdx.y = chunk of corrections; thread = co x 4 groups of 16 ci.
+__global__ void __launch_bounds__(256) rowinv_wgrad_fix_kernel(const bf16* __restrict__ x,
+                                                               const bf16* __restrict__ gy,
+                                                               const int* __restrict__ plan, RiDir d,
+                                                               int B, int SH, int SW, int RH, int RW,
+                                                               int K, int Cin, float* __restrict__ gw) {
+  const int k = blockIdx.x;
+  const int per = (d.nskip + gridDim.y - 1) / gridDim.y;
+  const int e0 = blockIdx.y * per, e1 = min(d.nskip, e0 + per);
+  const int co = threadIdx.x & 63, cg = threadIdx.x >> 6;
+  float acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+  bool any = false;
+  for (int e = e0; e < e1; ++e) {
+    const int* ent = plan + d.off_skip + 6 * e;
+    if (__ldg(ent + 4) != k) continue;
+    any = true;
+    const int row = __ldg(ent), col = __ldg(ent + 1), srow = __ldg(ent + 2), scol = __ldg(ent + 3);
+    const float dw = __int_as_float(__ldg(ent + 5));
+    for (int b = 0; b < B; ++b) {
+      const float g = dw * __bfloat162float(gy[(((long)b * RH + row) * RW + col) * 64 + co]);
+      const uint4* xp = reinterpret_cast<const uint4*>(x + (((long)b * SH + srow) * SW + scol) * 64 + cg * 16);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint4 v = __ldg(xp + h);
+        const uint32_t p4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          acc[h * 8 + 2 * t] = fmaf(g, __uint_as_float(p4[t] << 16), acc[h * 8 + 2 * t]);
+          acc[h * 8 + 2 * t + 1] = fmaf(g, __uint_as_float(p4[t] & 0xFFFF0000u), acc[h * 8 + 2 * t + 1]);
+        }
+      }
+    }
+  }
+  if (!any) return;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    atomicAdd(gw + ((long)co * Cin + cg * 16 + i) * K + k, acc[i]);
+}
+
 static size_t rowinv_e_bytes(const RiDir& d, int NR) { return (size_t)d.nslot * NR * 128; }
 
 template <int NOUT>
@@ -756,6 +1140,14 @@ int rowinv_analyse_launch(const mc_desc* d, const void* map, void* out, cudaStre
   return MC_OK;
 }
 
+extern "C" int mc_debug_ri_prof(long long* out) {
+  unsigned m = 0;
+  cudaMemcpyFromSymbol(&m, tc::g_status_mask, sizeof(m));
+  const int rc = cudaMemcpyFromSymbol(out, tc::g_ri_prof, sizeof(long long) * 16) == cudaSuccess ? 0 : -4;
+  out[15] = m;
+  return rc;
+}
+
 // -> number of int32s of the plan (0: the map does not qualify); copies at most cap ints to out
 long rowinv_assemble_host(const mc_desc* d, const double* analysis, const float* map, int* out,
                           long cap) {
@@ -783,7 +1175,7 @@ size_t rowinv_ws_bytes(const mc_desc* d, const void* plan_host, int dir) {
 int rowinv_conv_launch(const mc_desc* d, int dir, const void* src, const void* plan_host,
                        const void* plan_dev, const void* w, const void* bias, void* res, void* ws,
                        size_t ws_bytes, cudaStream_t st) {
-  if (!conv_rowinv_shape_ok(d)) return MC_ERR_UNSUPPORTED;
+  if (!conv_rowinv_shape_ok(d) || (d->flags & MC_FLAG_RELU)) return MC_ERR_UNSUPPORTED;
   const RiHeader* h = (const RiHeader*)plan_host;
   if (!rowinv_plan_matches(d, h)) return MC_ERR_BAD_ARG;
   const RiDir& D = h->dir[dir];
@@ -812,6 +1204,53 @@ int rowinv_conv_launch(const mc_desc* d, int dir, const void* src, const void* p
                                                            a.SH, a.SW, a.RH, a.RW, 64), MC_COUNT(1);
     MC_CHECK_LAUNCH();
   }
+  return MC_OK;
+}
+
+
+int bias_grad_launch(const mc_desc*, const void*, void*, cudaStream_t);
+
+static int rowinv_bsplit(const mc_desc* d) { return d->B >= 2 ? 2 : 1; }
+
+size_t rowinv_wgrad_ws_bytes(const mc_desc* d, const void* plan_host) {
+  const RiHeader* h = (const RiHeader*)plan_host;
+  if (!rowinv_plan_matches(d, h)) return 0;
+  return (size_t)rowinv_bsplit(d) * h->dir[0].nslot * 4096 * sizeof(float);
+}
+
+// gw (C_out, C_in, K) float32 and gb (C_out) float32 (may be null), fully overwritten.
+int rowinv_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const void* plan_host,
+                        const void* plan_dev, void* gw, void* gb, void* ws, size_t ws_bytes,
+                        cudaStream_t st) {
+  if (!conv_rowinv_shape_ok(d)) return MC_ERR_UNSUPPORTED;
+  const RiHeader* h = (const RiHeader*)plan_host;
+  if (!rowinv_plan_matches(d, h)) return MC_ERR_BAD_ARG;
+  const RiDir& D = h->dir[0];
+  if (!ws || ws_bytes < rowinv_wgrad_ws_bytes(d, plan_host)) return MC_ERR_WORKSPACE;
+  if (!aligned16(gy) || !aligned16(x) || !aligned16(ws) || !aligned16(plan_dev)) return MC_ERR_BAD_ARG;
+  if (d->OW % (WG_TILES * TILE_M) != 0) return MC_ERR_UNSUPPORTED;
+  const int* plan = (const int*)plan_dev;
+  if (cudaMemsetAsync(gw, 0, (size_t)d->C_out * d->C_in * d->K * sizeof(float), st) != cudaSuccess)
+    return MC_ERR_LAUNCH;
+  if (D.nwgunit > 0) {
+    RowInvWgArgs a;
+    a.x = (const bf16*)x; a.gy = (const bf16*)gy; a.gE = (float*)ws; a.plan = plan; a.d = D;
+    a.B = d->B; a.SH = d->IH; a.SW = d->IW; a.RH = d->OH; a.RW = d->OW;
+    a.bsplit = rowinv_bsplit(d);
+    a.units = (long)D.nwgunit * a.bsplit;
+    if (!allow_big_smem(conv_rowinv_wgrad_kernel)) return MC_ERR_LAUNCH;
+    const long g = a.units < sm_count() ? a.units : sm_count();
+    conv_rowinv_wgrad_kernel<<<(int)g, TC_THREADS, WG_SMEM, st>>>(a), MC_COUNT(1);
+    MC_CHECK_LAUNCH();
+    rowinv_wgrad_reduce_kernel<<<dim3(16, 64), 256, 0, st>>>((const float*)ws, plan, D, a.bsplit, d->K,
+                                                             d->C_in, (float*)gw), MC_COUNT(1);
+  }
+  if (D.nskip > 0)
+    rowinv_wgrad_fix_kernel<<<dim3(d->K, 32), 256, 0, st>>>((const bf16*)x, (const bf16*)gy, plan, D,
+                                                            d->B, d->IH, d->IW, d->OH, d->OW, d->K,
+                                                            d->C_in, (float*)gw), MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  if (gb) return bias_grad_launch(d, gy, gb, st);
   return MC_OK;
 }
 

@@ -20,6 +20,7 @@ struct ConvArgs {
   const void* iw;
   const void* w;     // (Cout, Cin*K)
   const void* bias;  // fwd: (Cout)
+  int relu;          // fwd: clamp the result at zero after the bias
   void* out;         // fwd: y in T; dgrad: accumulation buffer in CT; wgrad: gw in CT
   int B, Cin, Cout, IH, IW, K, P, interp, layout;
   long npix_img, npix_grid;
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(256) conv_fwd_simt(ConvArgs a) {
     if (co < a.Cout) {
       CT v = acc[j];
       if (a.bias) v += (CT)ldv((const T*)a.bias + co);
+      if (a.relu && v < CT(0)) v = CT(0);
       stv(y + b * ys.b + co * ys.c + p * ys.p, v);
     }
   }
@@ -364,6 +366,7 @@ static int check_conv_desc(const mc_desc* d) {
 static ConvArgs make_args(const mc_desc* d) {
   ConvArgs a;
   a.x = a.gy = a.map = a.iw = a.w = a.bias = nullptr;
+  a.relu = 0;
   a.out = nullptr;
   a.B = d->B; a.Cin = d->C_in; a.Cout = d->C_out; a.IH = d->IH; a.IW = d->IW; a.K = d->K;
   a.P = d->P; a.interp = d->interp; a.layout = d->layout;
@@ -378,6 +381,7 @@ int conv_fwd_simt_launch(const mc_desc* d, const void* x, const void* map, const
                          const void* w, const void* bias, void* y, cudaStream_t st) {
   ConvArgs a = make_args(d);
   a.x = x; a.map = map; a.iw = d->P ? iw : nullptr; a.w = w; a.bias = bias; a.out = y;
+  a.relu = (d->flags & MC_FLAG_RELU) ? 1 : 0;
   const long total_pix = (long)d->B * a.npix_grid;
   dim3 grid((unsigned)((total_pix + TP - 1) / TP), (unsigned)((d->C_out + TCO - 1) / TCO));
   if (d->dtype == MC_F32) conv_fwd_simt<float><<<grid, 256, 0, st>>>(a), MC_COUNT(1);

@@ -149,6 +149,7 @@ struct GemmArgs {
   int ncol;           // channels of y / gy rows (a CTA works on a chunk of NOUT of them)
   int full_cnt;       // producer warps that arrive on a stage's "full" barrier
   int mtpg;           // wgrad: M = 128 gradient tiles per CTA (blockIdx.y picks the group)
+  int relu;           // fwd: y = max(0, .) after the bias
 };
 
 __device__ __forceinline__ void blend4(const uint4& v, float w, float (&acc)[8]) {
@@ -409,7 +410,7 @@ __device__ __forceinline__ void loader_loop(const Source& s, const Tiling& t, ui
   uint32_t it = 0;
   for (int tile = blockIdx.x; tile < t.tiles; tile += gridDim.x, ++it) {
     const uint32_t half = it & 1, ph = (it >> 1) & 1;
-    if (!mbar_wait(tabbar0 + 16 + 8 * half, ph ^ 1, abort_flag, 0x72, 512)) return;
+    if (!mbar_wait(tabbar0 + 16 + 8 * half, ph ^ 1, abort_flag, 0x72)) return;
     const uint32_t dst0 = table0 + half * TILE_M * entb, bar = tabbar0 + 8 * half;
     if (t.tile2d) {
       const int tt = tile_spatial(t, tile);
@@ -1161,7 +1162,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
         tile_pixel(a.t, tile, q * 32 + 8 * i + (lane >> 2), gp, img, p, valid);
         orow[i] = valid ? a.y + gp * a.ncol + co0 + (lane & 3) * 8 : nullptr;
       }
-      if (!mbar_wait(tfull_bar(acc), aph, abort_flag, 0x21, 512)) break;
+      {
+        int okt = 1;
+        if (lane == 0) okt = mbar_wait(tfull_bar(acc), aph, abort_flag, 0x21) ? 1 : 0;
+        okt = __shfl_sync(0xffffffffu, okt, 0);
+        if (!okt) break;
+      }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * NOUT;
 #pragma unroll
@@ -1179,10 +1185,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
         for (int j = 0; j < 4; ++j) {
           uint4 o;
           const float* bs = bias_s + cc * 32 + j * 8;
-          o.x = pack_bf16x2(__uint_as_float(v[j * 8 + 0]) + bs[0], __uint_as_float(v[j * 8 + 1]) + bs[1]);
-          o.y = pack_bf16x2(__uint_as_float(v[j * 8 + 2]) + bs[2], __uint_as_float(v[j * 8 + 3]) + bs[3]);
-          o.z = pack_bf16x2(__uint_as_float(v[j * 8 + 4]) + bs[4], __uint_as_float(v[j * 8 + 5]) + bs[5]);
-          o.w = pack_bf16x2(__uint_as_float(v[j * 8 + 6]) + bs[6], __uint_as_float(v[j * 8 + 7]) + bs[7]);
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            f[e] = __uint_as_float(v[j * 8 + e]) + bs[e];
+            if (a.relu) f[e] = fmaxf(f[e], 0.f);
+          }
+          o.x = pack_bf16x2(f[0], f[1]);
+          o.y = pack_bf16x2(f[2], f[3]);
+          o.z = pack_bf16x2(f[4], f[5]);
+          o.w = pack_bf16x2(f[6], f[7]);
           sts16(wr_row + ((j ^ wr_x) << 4), o);
         }
         __syncwarp();
@@ -1209,7 +1221,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_gemm_tc_kernel(const GemmA
           bool ok = true;
           for (int tile = blockIdx.x; tile < a.t.tiles && ok; tile += gridDim.x) {
             for (int s = 0; s < a.nsl; ++s) {
-              ok = mbar_wait(empty_bar(st), ph ^ 1, abort_flag, 0x73, 256);
+              ok = mbar_wait(empty_bar(st), ph ^ 1, abort_flag, 0x73);
               if (!ok) break;
               mbar_expect_tx(full_bar(st), WSLICE);
               bulk_g2s(w0 + st * WSLICE, a.wimg + ((size_t)s * a.ncol + co0) * 8, WSLICE, full_bar(st));
@@ -1823,6 +1835,7 @@ static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, con
   a.s.KC = d->K * d->C_in;
   a.s.packed = d->C_in % 64 != 0;
   a.ncol = d->C_out;
+  a.relu = (d->flags & MC_FLAG_RELU) ? 1 : 0;
   GemmPlan p;
   if (!plan_gemm(a.ncol, a.nsl, d->K, p)) return MC_ERR_UNSUPPORTED;
   a.nst = p.nst;
@@ -1949,6 +1962,7 @@ int conv_tc_dgrad_launch(const mc_desc* d, const void* gy, const void* inv, cons
   a.wimg = (const uint4*)ws; a.bias = (const bf16*)bias_out; a.y = (bf16*)gx;
   a.nsl = d->K * (d->C_out / 64);
   a.ncol = d->C_in;
+  a.relu = (bias_out && (d->flags & MC_FLAG_RELU)) ? 1 : 0;  // the transposed layer's forward
   GemmPlan p;
   if (!plan_gemm(a.ncol, a.nsl, d->K, p)) return MC_ERR_UNSUPPORTED;
   a.nst = p.nst;

@@ -283,9 +283,10 @@ bool via_channels_last(const Tensor& input, const OptTensor& iw, mc_desc d_nhwc)
 
 // ---- convolution ---------------------------------------------------------------------------------------
 
+// relu: y = max(0, conv + bias), applied in the kernel's epilogue (MC_FLAG_RELU)
 Tensor conv_forward(const Tensor& input_in, const Tensor& sample_map_in, const OptTensor& iw,
                     const Tensor& weight, const Tensor& bias, int64_t K, int64_t interp,
-                    bool nhwc = false) {
+                    bool nhwc = false, bool relu = false) {
   const Tensor input = aligned16(input_in), sample_map = aligned16(sample_map_in);
   TORCH_CHECK(input.dim() == 4 && weight.dim() == 3, "input must be 4-D, weight 3-D");
   check_conv_args(input, sample_map, weight, bias, weight.size(0), input.size(1), weight.size(0), K);
@@ -294,13 +295,13 @@ Tensor conv_forward(const Tensor& input_in, const Tensor& sample_map_in, const O
   const int64_t Cout = weight.size(0), OH = sample_map.size(0), OW = sample_map.size(1);
   if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH,
                                                       IW, OH, OW, K, 0, interp)))
-    return conv_forward(channels_last(input), sample_map, c10::nullopt, weight, bias, K, interp, true)
-        .contiguous();
+    return conv_forward(channels_last(input), sample_map, c10::nullopt, weight, bias, K, interp, true,
+                        relu).contiguous();
   const int layout = nhwc ? MC_NHWC : layout_of(input);
   check_map(input, sample_map, iw);
   TORCH_CHECK(weight.is_contiguous() && bias.is_contiguous(), "weight and bias must be contiguous");
-  const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, IH, IW, OH, OW, K,
-                              n_interp(iw), interp);
+  mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, IH, IW, OH, OW, K, n_interp(iw),
+                        interp);
   Tensor y = empty_in({B, Cout, OH, OW}, input, layout);
   c10::cuda::CUDAGuard guard(dev);
   if (!iw.has_value()) {
@@ -310,9 +311,11 @@ Tensor conv_forward(const Tensor& input_in, const Tensor& sample_map_in, const O
       check(mc_conv_fwd_rowplan(&d, input.data_ptr(), rp.second.data_ptr(), rp.first.data_ptr(),
                                 weight.data_ptr(), bias.data_ptr(), y.data_ptr(), wsr.p, wsr.n,
                                 cur_stream()));
-      return y;
+      // (these kernels correct single pixels after their epilogue, so the activation follows)
+      return relu ? y.relu_() : y;
     }
   }
+  if (relu) d.flags |= MC_FLAG_RELU;
   Scratch ws = scratch(mc_conv_fwd_workspace_bytes(&d), dev);
   Tensor tab = (ws.n && !iw.has_value()) ? tap_map(d, sample_map) : Tensor();
   if (tab.defined())  // tensor-core path with the map decoded once per map tensor
@@ -327,7 +330,8 @@ Tensor conv_forward(const Tensor& input_in, const Tensor& sample_map_in, const O
 std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sample_map_in,
                                   const OptTensor& iw, const Tensor& input_in, const Tensor& weight,
                                   const Tensor& bias, int64_t K, int64_t interp,
-                                  bool need_input_grad, bool nhwc = false) {
+                                  bool need_input_grad, bool nhwc = false,
+                                  bool need_weight_grad = true) {
   const Tensor input = aligned16(input_in), sample_map = aligned16(sample_map_in);
   TORCH_CHECK(input.dim() == 4 && weight.dim() == 3 && sample_map.dim() >= 4,
               "input must be 4-D, weight 3-D, the map (OH, OW, K, ..)");
@@ -340,7 +344,8 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
   if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH,
                                                       IW, OH, OW, K, 0, interp))) {
     auto g = conv_backward(channels_last(grad_output_in), sample_map, c10::nullopt,
-                           channels_last(input), weight, bias, K, interp, need_input_grad, true);
+                           channels_last(input), weight, bias, K, interp, need_input_grad, true,
+                           need_weight_grad);
     if (g[0].defined()) g[0] = g[0].contiguous();
     return g;
   }
@@ -373,6 +378,14 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
   } else {
     check(mc_conv_dgrad(&d, grad_output.data_ptr(), sample_map.data_ptr(), ptr(iw),
                         weight.data_ptr(), nullptr, gx.data_ptr(), ws.p, ws.n, cur_stream()));
+  }
+  if (!need_weight_grad) return {gx, Tensor(), Tensor()};
+  if (rp.first.defined()) {  // row-invariant map: weight gradient from the same plan
+    Scratch wsr = scratch(mc_conv_wgrad_rowplan_workspace_bytes(&d, rp.second.data_ptr()), dev);
+    check(mc_conv_wgrad_rowplan(&d, grad_output.data_ptr(), input.data_ptr(), rp.second.data_ptr(),
+                                rp.first.data_ptr(), gw.data_ptr(), gb.data_ptr(), wsr.p, wsr.n,
+                                cur_stream()));
+    return {gx, gw.to(weight.scalar_type()), gb.to(bias.scalar_type())};
   }
   Tensor tab = iw.has_value() ? Tensor() : tap_map(d, sample_map);
   int rc = MC_ERR_UNSUPPORTED;
@@ -635,17 +648,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "mapped convolution ops on the sm_100a C-ABI library (reference pybind surface)";
   // MappedConvForward / Backward, include/nn/layers/mapped_convolution_layer.h:64-88, :90-135
   m.def("mapped_conv_forward",
-        [](const Tensor& x, const Tensor& map, const Tensor& w, const Tensor& b, int64_t k, int64_t i) {
-          return conv_forward(x, map, c10::nullopt, w, b, k, i);
-        });
+        [](const Tensor& x, const Tensor& map, const Tensor& w, const Tensor& b, int64_t k, int64_t i,
+           bool relu) { return conv_forward(x, map, c10::nullopt, w, b, k, i, false, relu); },
+        py::arg("input"), py::arg("sample_map"), py::arg("weight"), py::arg("bias"),
+        py::arg("kernel_size"), py::arg("interpolation"), py::arg("relu") = false);
   m.def("mapped_conv_backward",
         [](const Tensor& gy, const Tensor& map, const Tensor& x, const Tensor& w, const Tensor& b,
-           int64_t k, int64_t i, bool need_input_grad) {
-          return conv_backward(gy, map, c10::nullopt, x, w, b, k, i, need_input_grad);
+           int64_t k, int64_t i, bool need_input_grad, bool need_weight_grad) {
+          return conv_backward(gy, map, c10::nullopt, x, w, b, k, i, need_input_grad, false,
+                               need_weight_grad);
         },
         py::arg("grad_output"), py::arg("sample_map"), py::arg("input"), py::arg("weight"),
         py::arg("bias"), py::arg("kernel_size"), py::arg("interpolation"),
-        py::arg("need_input_grad") = true);
+        py::arg("need_input_grad") = true, py::arg("need_weight_grad") = true);
   // include/nn/layers/weighted_mapped_convolution_layer.h:65-93, :95-150
   m.def("weighted_mapped_conv_forward",
         [](const Tensor& x, const Tensor& map, const Tensor& iw, const Tensor& w, const Tensor& b,

@@ -7,6 +7,7 @@ Resample (scatter) <-> Unresample (gather).
 import torch
 from torch.autograd import Function
 
+from ..host import COMPILED as FUSED_RELU  # the compiled extension takes relu=True
 from ..host import impl as ops
 
 
@@ -14,24 +15,36 @@ class MappedConvFn(Function):
     """package/layers/nn/mapped_convolution_layer.py:15-59"""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, sample_map, kernel_size, interp, interp_weights=None):
-        ctx.save_for_backward(x, weight, bias, sample_map, interp_weights)
-        ctx.k, ctx.interp = int(kernel_size), int(interp)
+    def forward(ctx, x, weight, bias, sample_map, kernel_size, interp, interp_weights=None,
+                relu=False):
+        ctx.k, ctx.interp, ctx.relu = int(kernel_size), int(interp), bool(relu)
         if interp_weights is not None:
-            return ops.weighted_mapped_conv_forward(x, sample_map, interp_weights, weight, bias,
-                                                    ctx.k, ctx.interp)
-        return ops.mapped_conv_forward(x, sample_map, weight, bias, ctx.k, ctx.interp)
+            y = ops.weighted_mapped_conv_forward(x, sample_map, interp_weights, weight, bias,
+                                                 ctx.k, ctx.interp)
+            if relu:
+                y = torch.relu_(y)
+        elif relu and FUSED_RELU:
+            # the activation runs in the convolution's epilogue: no separate pass over y
+            y = ops.mapped_conv_forward(x, sample_map, weight, bias, ctx.k, ctx.interp, relu=True)
+        else:
+            y = ops.mapped_conv_forward(x, sample_map, weight, bias, ctx.k, ctx.interp)
+            if relu:
+                y = torch.relu_(y)
+        ctx.save_for_backward(x, weight, bias, sample_map, interp_weights, y if relu else None)
+        return y
 
     @staticmethod
     def backward(ctx, gy):
-        x, weight, bias, sample_map, iw = ctx.saved_tensors
+        x, weight, bias, sample_map, iw, y = ctx.saved_tensors
+        if ctx.relu:  # gradient of the activation, from its own output: y > 0 <=> pre-activation > 0
+            gy = torch.where(y > 0, gy, torch.zeros((), dtype=gy.dtype, device=gy.device))
         if iw is not None:
             gx, gw, gb = ops.weighted_mapped_conv_backward(gy, sample_map, iw, x, weight, bias,
                                                            ctx.k, ctx.interp)
         else:
             gx, gw, gb = ops.mapped_conv_backward(gy, sample_map, x, weight, bias, ctx.k,
                                                   ctx.interp, ctx.needs_input_grad[0])
-        return gx, gw, gb, None, None, None, None
+        return gx, gw, gb, None, None, None, None, None
 
 
 class MappedTransposedConvFn(Function):

@@ -44,13 +44,18 @@ class MappedConvolution(_ConvBase):
     """
 
     def __init__(self, in_channels, out_channels, kernel_size=1, interpolation='bilinear',
-                 bias=True):
+                 bias=True, *, activation=None):
+        """activation (keyword only, not in the reference): None, or 'relu' to get
+        max(0, conv(x) + bias) from the convolution kernel itself instead of a separate
+        element-wise pass; the layer then stands for conv followed by nn.ReLU."""
         super().__init__(in_channels, out_channels, kernel_size, interpolation, bias, False)
+        assert activation in (None, 'relu'), 'activation must be None or "relu"'
+        self.activation = activation
 
     def forward(self, x, sample_map, interp_weights=None):
         check_args(x, sample_map, interp_weights, self.in_channels, self.kernel_size)
         return F.MappedConvFn.apply(x, self.weight, self.bias, sample_map, self.kernel_size,
-                                    self.interp, interp_weights)
+                                    self.interp, interp_weights, self.activation == 'relu')
 
 
 class MappedTransposedConvolution(_ConvBase):

@@ -84,9 +84,56 @@ def build_one(name, ref_root):
     return name, "built"
 
 
+def build_knn(ref_root):
+    """The reference's CUDA-only k-NN module (src/util/cuda/knn_layer.cu + include/util/cuda/knn.cuh,
+    bound by src/util/cpp/knn_layer.cpp), compiled for sm_100a with nvcc.  The reference gives its
+    kernels a (k, N) buffer but indexes it as an (M, N) distance matrix (knn_layer.cu:20-23 against
+    knn.cuh:111-112, :144-187), so it is only ever run with M == k, where every access stays inside
+    the buffers; tests/golden/make_golden_knn.py enforces that."""
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    ext = os.path.join(ref_root, "package", "ext_modules")
+    cu = os.path.join(ext, "src/util/cuda/knn_layer.cu")
+    cpp = os.path.join(ext, "src/util/cpp/knn_layer.cpp")
+    os.makedirs(OUT, exist_ok=True)
+    so = os.path.join(OUT, "_knn.so")
+    if os.path.exists(so) and os.path.getmtime(so) >= os.path.getmtime(cu):
+        return "_knn", "cached"
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    inc = [os.path.join(ext, "include")] + ce.include_paths() + [sysconfig.get_paths()["include"],
+                                                                 os.path.join(os.path.dirname(os.path.dirname(nvcc)), "include")]
+    defs = ["-DTORCH_EXTENSION_NAME=_knn", "-DTORCH_API_INCLUDE_EXTENSION_H",
+            "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+    obj_cu, obj_cpp = so + ".cu.o", so + ".cpp.o"
+    cmd1 = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w", "-Xcompiler",
+            "-fPIC"] + defs + sum((["-isystem", i] for i in inc), []) + ["-c", cu, "-o", obj_cu]
+    cmd2 = ["g++", "-fPIC", "-O2", "-std=c++17", "-w"] + defs + sum((["-isystem", i] for i in inc), []) + \
+           ["-c", cpp, "-o", obj_cpp]
+    libdir = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cudalib = os.path.join(os.path.dirname(os.path.dirname(nvcc)), "lib64")
+    cmd3 = ["g++", "-shared", obj_cu, obj_cpp, "-o", so, "-L" + libdir, "-Wl,-rpath," + libdir, "-lc10",
+            "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-L" + cudalib,
+            "-lcudart"]
+    for cmd in (cmd1, cmd2, cmd3):
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            return "_knn", "FAILED\n" + r.stderr[-3000:]
+    for o in (obj_cu, obj_cpp):
+        os.remove(o)
+    return "_knn", "built"
+
+
+def default_reference_root():
+    """$MC_REFERENCE_ROOT, else a checkout named `reference` beside this repository."""
+    return os.environ.get("MC_REFERENCE_ROOT",
+                          os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("MC_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--ref", default=default_reference_root())
+    ap.add_argument("--knn", action="store_true", help="also build the reference's CUDA k-NN module")
     ap.add_argument("--jobs", type=int, default=min(8, os.cpu_count() or 1))
     ap.add_argument("modules", nargs="*")
     a = ap.parse_args()
@@ -99,6 +146,10 @@ def main():
         for name, status in ex.map(lambda n: build_one(n, a.ref), names):
             print(name, status, flush=True)
             ok &= not status.startswith("FAILED")
+    if a.knn:
+        name, status = build_knn(a.ref)
+        print(name, status, flush=True)
+        ok &= not status.startswith("FAILED")
     return 0 if ok else 1
 
 

@@ -1,6 +1,6 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE's own CPU code.
 
-Needs the reference checkout (default /root/reference) and its CPU extensions built by
+Needs the reference checkout ($MC_REFERENCE_ROOT, or a directory `reference` beside this repository) and its CPU extensions built by
 oracle/build_ref.py.  It is run by hand when the fixtures need refreshing; the tests only read
 the .npz files it writes, never the reference.
 
@@ -251,7 +251,8 @@ def config1():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("MC_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get(
+        "MC_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference")))
     a = ap.parse_args()
     assert ref.available(), "build the reference CPU extensions first: python oracle/build_ref.py"
     kats, n = capture_kats(a.ref)

@@ -515,3 +515,15 @@ def test_non_finite_input_next_to_a_tap_that_reads_nothing(op_binding):
     nan_at = torch.isnan(y.float()).any(1)[0].cpu()
     assert torch.equal(nan_at, outside)
     assert torch.equal(y[0][:, ~outside.cuda()], clean[0][:, ~outside.cuda()])
+
+
+@pytest.mark.parametrize("name", sorted(H.load_cases("knn_ref.npz")))
+def test_knn_equals_the_reference_cuda_kernels(name, op_binding):
+    """mc_knn against outputs of the reference's own CUDA k-NN (include/util/cuda/knn.cuh:42-205)
+    recorded on a B200 - indices and distances bit for bit, exact duplicates among the reference
+    points and zero distances included."""
+    from mappedconvolutions_b200 import ops
+    c = H.load_cases("knn_ref.npz")[name]
+    idx, dist = ops.knn_forward(c["ref"].cuda(), c["query"].cuda(), int(c["k"]))
+    assert torch.equal(idx.cpu(), c["idx"])
+    assert torch.equal(dist.cpu(), c["dist"])

@@ -56,6 +56,22 @@ def cl(t):
     return t.contiguous(memory_format=torch.channels_last)
 
 
+def run_wgrad(d, gy, x, plan):
+    from mappedconvolutions_b200 import _lib
+    L = _lib.lib()
+    plan_h, plan_d = plan
+    nws = L.mc_conv_wgrad_rowplan_workspace_bytes(d, plan_h.ctypes.data)
+    ws = torch.empty(max(nws, 16), dtype=torch.uint8, device=x.device)
+    gw = torch.full((d.C_out, d.C_in, d.K), float("nan"), dtype=torch.float32, device=x.device)
+    gb = torch.full((d.C_out,), float("nan"), dtype=torch.float32, device=x.device)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(L.mc_conv_wgrad_rowplan(d, gy.data_ptr(), x.data_ptr(), plan_h.ctypes.data,
+                                       plan_d.data_ptr(), gw.data_ptr(), gb.data_ptr(), ws.data_ptr(),
+                                       nws, st))
+    assert L.mc_device_status(st, 1) == 0
+    return gw, gb
+
+
 @pytest.mark.parametrize("wrapped,interp,Hh,Ww,B", [(True, 1, 12, 512, 2), (False, 1, 9, 512, 3),
                                                   (True, 2, 7, 1024, 1), (False, 2, 5, 512, 2)])
 def test_rowplan_forward_and_input_gradient(wrapped, interp, Hh, Ww, B):
@@ -71,10 +87,13 @@ def test_rowplan_forward_and_input_gradient(wrapped, interp, Hh, Ww, B):
     w, b = torch.randn(C, C, K, generator=g).to(bf), torch.randn(C, generator=g).to(bf)
     y = run(d, 0, cl(x.cuda()), plan, w.cuda(), b.cuda(), (B, C, Hh, Ww))
     gx = run(d, 1, cl(gy.cuda()), plan, w.cuda(), None, (B, C, Hh, Ww))
+    gw, gb = run_wgrad(d, cl(gy.cuda()), cl(x.cuda()), plan)
     want_y = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, interp)
-    want_gx = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, interp)[0]
+    want = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, interp)
     H.assert_close(y.float(), want_y, 2e-2, "row-plan forward vs oracle")
-    H.assert_close(gx.float(), want_gx, 2e-2, "row-plan input gradient vs oracle")
+    H.assert_close(gx.float(), want[0], 2e-2, "row-plan input gradient vs oracle")
+    H.assert_close(gw, want[1], 2e-2, "row-plan weight gradient vs oracle")
+    H.assert_close(gb, want[2], 2e-2, "row-plan bias gradient vs oracle")
 
 
 def test_rowplan_on_the_gnomonic_map_matches_the_general_kernels():
@@ -92,9 +111,12 @@ def test_rowplan_on_the_gnomonic_map_matches_the_general_kernels():
     w, b = torch.randn(C, C, K, generator=g).to(bf), torch.randn(C, generator=g).to(bf)
     y = run(d, 0, cl(x.cuda()), plan, w.cuda(), b.cuda(), (B, C, Hh, Ww))
     gx = run(d, 1, cl(gy.cuda()), plan, w.cuda(), None, (B, C, Hh, Ww))
+    gw, gb = run_wgrad(d, cl(gy.cuda()), cl(x.cuda()), plan)
     want_y = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, 1)
-    want_gx = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, 1)[0]
+    want = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, 1)
     H.assert_close(y.float(), want_y, 2e-2, "forward vs oracle")
-    H.assert_close(gx.float(), want_gx, 2e-2, "input gradient vs oracle")
+    H.assert_close(gx.float(), want[0], 2e-2, "input gradient vs oracle")
+    H.assert_close(gw, want[1], 2e-2, "weight gradient vs oracle")
+    H.assert_close(gb, want[2], 2e-2, "bias gradient vs oracle")
     y2 = ops.mapped_conv_forward(cl(x.cuda()), m.cuda(), w.cuda(), b.cuda(), K, 1)
     H.assert_close(y.float(), y2.float(), 2e-2, "forward vs the general kernel")

@@ -106,3 +106,72 @@ def test_errors_are_raised_like_in_the_ctypes_twin(ext):
         ext.mapped_avg_pool(x.cuda(), m.double().cuda(), 1, 0)
     with pytest.raises(RuntimeError, match="contiguous"):
         ext.mapped_avg_pool(x.cuda().transpose(2, 3), m.cuda(), 1, 0)
+
+
+def test_fused_relu_equals_conv_then_relu(ext):
+    """activation='relu' runs max(0, .) in the convolution kernel's epilogue (MC_FLAG_RELU).  The
+    result must equal relu(conv(x)) bit for bit - the clamp acts on the same float32 accumulator
+    before the same rounding - and so must the gradients."""
+    from mapped_convolution.nn import MappedConvolution
+    torch.manual_seed(11)
+    for (B, Cin, Cout, Hh, Ww, K, interp, dt, cl) in (
+            (2, 64, 64, 16, 32, 9, 1, torch.bfloat16, True),      # tensor-core kernel
+            (1, 64, 128, 1, 642, 7, 0, torch.bfloat16, True),     # nearest map on a mesh
+            (2, 5, 7, 9, 11, 4, 1, torch.float32, False)):        # generic kernel
+        name = {0: "nearest", 1: "bilinear"}[interp]
+        plain = MappedConvolution(Cin, Cout, K, name).cuda().to(dt)
+        fused = MappedConvolution(Cin, Cout, K, name, activation="relu").cuda().to(dt)
+        fused.load_state_dict(plain.state_dict())
+        x = torch.randn(B, Cin, Hh, Ww, device="cuda").to(dt)
+        if cl:
+            x = x.contiguous(memory_format=torch.channels_last)
+        m = (torch.rand(Hh, Ww, K, 2, device="cuda") * torch.tensor([Ww - 1.0, Hh - 1.0], device="cuda")).contiguous()
+        xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        ya = torch.relu(plain(xa, m))
+        yb = fused(xb, m)
+        assert torch.equal(ya, yb) and (yb >= 0).all() and (yb == 0).any()
+        g = torch.randn_like(ya)
+        ya.backward(g)
+        yb.backward(g)
+        assert torch.equal(xa.grad, xb.grad)
+        assert torch.equal(plain.weight.grad, fused.weight.grad)
+        assert torch.equal(plain.bias.grad, fused.bias.grad)
+
+
+def test_row_plans_through_the_layer_api(ext):
+    """A spherical (gnomonic) map on an equirectangular image is translation invariant along rows:
+    the layer takes the row-plan kernels for forward, input gradient and weight gradient.  Results
+    against the oracle (2e-2) and against the general kernels of the same library (row plans off)."""
+    from mapped_convolution.nn import MappedConvolution
+    from mapped_convolution.util import get_projection_map
+    from oracle import oracle
+    torch.manual_seed(12)
+    Hh, Ww, C, K, B = 32, 512, 64, 9, 2
+    m = get_projection_map((Hh, Ww), (3, 3), "gnomonic").contiguous().cuda()
+    layer = MappedConvolution(C, C, K, "bilinear").cuda().to(torch.bfloat16)
+    x = torch.randn(B, C, Hh, Ww, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    g = torch.randn(B, C, Hh, Ww, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+
+    def run():
+        layer.zero_grad()
+        xi = x.clone().requires_grad_(True)
+        y = layer(xi, m)
+        y.backward(g)
+        return y.detach(), xi.grad, layer.weight.grad.clone(), layer.bias.grad.clone()
+
+    n0 = ext.mapped_conv_forward  # (touch the binding so that a missing symbol fails here)
+    assert n0 is not None
+    fast = run()
+    was = ext.set_row_plans(False)
+    try:
+        slow = run()
+    finally:
+        ext.set_row_plans(was)
+    w, b = layer.weight.detach().float().cpu(), layer.bias.detach().float().cpu()
+    want_y = oracle.mapped_conv_forward(x.float().cpu().contiguous(), m.cpu(), w, b, K, 1)
+    want = oracle.mapped_conv_backward(g.float().cpu().contiguous(), m.cpu(), x.float().cpu().contiguous(), w, b, K, 1)
+    for name, got, ref, other in (("y", fast[0], want_y, slow[0]), ("grad_x", fast[1], want[0], slow[1]),
+                                  ("grad_w", fast[2], want[1], slow[2]), ("grad_b", fast[3], want[2], slow[3])):
+        H.assert_close(got.float(), ref, 2e-2, "row plan " + name + " vs oracle")
+        H.assert_close(other.float(), ref, 2e-2, "general " + name + " vs oracle")
+    assert not torch.equal(fast[0], slow[0])   # two different kernels really ran

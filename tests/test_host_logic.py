@@ -101,7 +101,7 @@ def test_compiled_extension_carries_the_reference_surface():
     public = [n for n, f in inspect.getmembers(ops, inspect.isfunction)
               if not n.startswith("_") and f.__module__ == ops.__name__ and n != "clear_inverse_map_cache"]
     assert len(public) >= 21 and all(hasattr(host.impl, n) for n in public)
-    assert host.impl.abi_version() == 1
+    assert host.impl.abi_version() == 2
 
 
 def _both_bindings():

@@ -133,3 +133,21 @@ def test_oracle_knn_against_independent_searches(D, M, N, k):
     for n in range(N):
         assert set(idx[:, n] - 1) == set(tree_i[n]) == set(brute_i[n]), n
     np.testing.assert_allclose(dist.T, tree_d, rtol=1e-5, atol=1e-6)
+
+
+# ---- k-NN against the reference's own CUDA kernels -----------------------------------------------
+# tests/golden/knn_ref.npz holds outputs of the reference's knn_forward built from its sources for
+# sm_100a and run on a B200 (tests/golden/make_golden_knn.py).  The reference is in bounds only for
+# M == k, so every case has M == k: the whole reference set is returned, sorted - which pins the
+# distance arithmetic (the fma chain over dimensions), the ordering and tie-break by index, the
+# 1-based numbering and the square root.
+KNN_REF = H.load_cases("knn_ref.npz")
+
+
+@pytest.mark.parametrize("name", sorted(KNN_REF))
+def test_oracle_knn_equals_the_reference_kernels(name):
+    c = KNN_REF[name]
+    idx, dist = oracle.knn_forward(c["ref"], c["query"], int(c["k"]))
+    assert torch.equal(idx, c["idx"]), "%s: indices differ at %d places" % (name, (idx != c["idx"]).sum())
+    assert torch.equal(dist, c["dist"]), "%s: distances not bit-identical" % name
+    assert idx.min().item() == 1 and idx.max().item() == int(c["k"])

@@ -43,13 +43,13 @@ def assemble(d, ana, m):
 
 
 HDR = 8   # magic, total, OH, OW, IH, IW, K, interp
-DIR = 16  # ints per direction block
+DIR = 18  # ints per direction block
 
 
 def direction(plan, i):
     f = plan[HDR + DIR * i: HDR + DIR * (i + 1)]
     names = ("rows nwin nslot ncon nskip ngroup max_win max_slot off_row off_win off_slot off_coff "
-             "off_ctap off_cw off_skip off_group").split()
+             "off_ctap off_cw off_skip off_group nwgunit off_wgunit").split()
     return dict(zip(names, (int(v) for v in f)))
 
 
@@ -135,6 +135,12 @@ def test_the_benchmark_map_has_a_plan_and_others_do_not():
     assert plan is not None
     D = direction(plan, 0)
     assert D["rows"] == H and D["max_win"] <= 64 and D["max_slot"] <= 128 and D["nskip"] > 0
+    # weight-gradient units: every window of every row exactly once, at most 8 slot pairs each
+    wg = plan[D["off_wgunit"]: D["off_wgunit"] + 4 * D["nwgunit"]].reshape(-1, 4)
+    win = plan[D["off_win"]: D["off_win"] + 4 * D["nwin"]].reshape(-1, 4)
+    assert wg[:, 2].sum() == D["nwin"] and (wg[1:, 1] == wg[:-1, 1] + wg[:-1, 2]).all()
+    for r, w0, nw, s0 in wg:
+        assert s0 == win[w0, 2] and sum(((win[w0:w0 + nw, 3] & 0xFF) + 1) // 2) <= 8
     # a jittered map is not row invariant; neither is a map whose rows move vertically
     g = torch.Generator().manual_seed(2)
     mj = m + 0.01 * torch.rand(m.shape, generator=g)
