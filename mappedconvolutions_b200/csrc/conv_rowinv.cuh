@@ -220,7 +220,8 @@ static void ri_emit_dir(std::vector<RiCon>& cons, std::vector<RiFix>& fixes, int
   d.off_ctap = put(ctap); d.off_cw = put(cw); d.off_skip = put(skip); d.off_group = put(group);
   // weight-gradient units: consecutive windows of a row, as many as give at most RI_WG_PAIRS pairs
   // of slots (the slots of a window are paired up; an odd one out is paired with itself)
-  std::vector<int> wg;
+  struct WgUnit { int rec[4]; int pairs; };
+  std::vector<WgUnit> units;
   for (int r = 0; r < rows; ++r) {
     int w = row_off[r];
     while (w < row_off[r + 1]) {
@@ -232,11 +233,16 @@ static void ri_emit_dir(std::vector<RiCon>& cons, std::vector<RiFix>& fixes, int
         ++w1;
       }
       if (pairs > RI_WG_PAIRS) ok = false;  // a single window with more than 16 slots
-      const int rec[4] = {r, w, w1 - w, win[4 * w + 2]};
-      wg.insert(wg.end(), rec, rec + 4);
+      units.push_back(WgUnit{{r, w, w1 - w, win[4 * w + 2]}, pairs});
       w = w1;
     }
   }
+  // largest first: the kernel deals the units out to its blocks back and forth in this order, which
+  // evens out the work of the blocks
+  std::stable_sort(units.begin(), units.end(),
+                   [](const WgUnit& p, const WgUnit& q) { return p.pairs > q.pairs; });
+  std::vector<int> wg;
+  for (const WgUnit& u : units) wg.insert(wg.end(), u.rec, u.rec + 4);
   d.nwgunit = (int)wg.size() / 4;
   d.off_wgunit = put(wg);
 }
@@ -409,7 +415,6 @@ struct RowInvArgs {
   int tpu;         // 128-pixel tiles per unit
   int upr;         // units per (row, image): RW / (128 * tpu)
   long units;      // RH * B * upr
-  int dbg;
 };
 
 __device__ __forceinline__ void ri_unit(const RowInvArgs& a, long u, int& r, int& b, int& x0) {
@@ -428,8 +433,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 constexpr int RI_WIN_STAGES = 2;
-static __device__ long long g_ri_prof[16];
-#define RI_T(var) const long long var = clock64()
 
 template <int NOUT>
 struct RiCfg {
@@ -494,11 +497,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
     constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 0, 0);
     uint32_t it = 0, nw = 0, se = 0, pe = 0;
     int ok = 1;
-    long long p_plan = 0, p_temp = 0, p_wf = 0, p_ef = 0, p_iss = 0, p_tot = clock64();
     for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x, ++it) {
       int r, b, x0;
       ri_unit(a, u, r, b, x0);
-      RI_T(t_a);
       const int w0 = __ldg(plan + a.d.off_row + r), w1 = __ldg(plan + a.d.off_row + r + 1);
       __syncwarp();
       for (int i = lane; i < w1 - w0; i += 32)
@@ -512,23 +513,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
       for (int i = lane; i < ns; i += 32) s_shift[i] = __ldg(plan + a.d.off_slot + sfirst + i);
       __syncwarp();
       if (lane == 0) {
-        RI_T(t_b); p_plan += t_b - t_a;
         const uint32_t acc = it & 1, aph = (it >> 1) & 1;
         ok = mbar_wait_spin(tempty(acc), aph ^ 1, abort_flag, 0x81) ? 1 : 0;
         tc_fence_after_sync();
-        RI_T(t_c); p_temp += t_c - t_b;
         const uint32_t tmem_d = tmem_base + acc * (Cfg::TPU * NOUT);
         int si = 0;
         for (int w = 0; w < w1 - w0 && ok; ++w, ++nw) {
           const uint32_t ws = nw % RI_WIN_STAGES, wph = (nw / RI_WIN_STAGES) & 1;
-          RI_T(t_d);
           ok = mbar_wait_spin(wfull(ws), wph, abort_flag, 0x82) ? 1 : 0;
-          RI_T(t_e); p_wf += t_e - t_d;
           const int nsl = s_win[w].w & 0xFF;
           for (int s = 0; s < nsl && ok; ++s, ++si) {
-            RI_T(t_f);
             ok = mbar_wait_spin(efull(se), pe, abort_flag, 0x83) ? 1 : 0;
-            RI_T(t_g); p_ef += t_g - t_f;
             if (!ok) break;
             tc_fence_after_sync();
             const uint64_t bdesc = make_desc_sw128(e0 + se * Cfg::E_BYTES, 16, 1024);
@@ -538,11 +533,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
               const uint64_t adesc = make_desc_sw128(abase + t * (TILE_M * 128), 16, 1024);
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                if (!(a.dbg & 2)) mma_bf16_ss(tmem_d + t * NOUT, adesc + 2 * j, bdesc + 2 * j, idesc, (si | j) != 0);
+                mma_bf16_ss(tmem_d + t * NOUT, adesc + 2 * j, bdesc + 2 * j, idesc, (si | j) != 0);
             }
             mma_commit(eempty(se));
             if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; }
-            p_iss += clock64() - t_g;
           }
           if (ok) mma_commit(wempty(ws));
         }
@@ -553,10 +547,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
     if (lane == 0) {
       mma_commit(drain_bar);
       mbar_wait_spin(drain_bar, 0, abort_flag, 0x84);
-      if (blockIdx.x == 0) {
-        g_ri_prof[0] = clock64() - p_tot; g_ri_prof[1] = p_plan; g_ri_prof[2] = p_temp;
-        g_ri_prof[3] = p_wf; g_ri_prof[4] = p_ef; g_ri_prof[5] = p_iss; g_ri_prof[6] = it;
-      }
     }
     __syncwarp();
   } else if (warp <= N_EPI_WARPS) {
@@ -608,7 +598,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0u;
           }
-          if (a.dbg & 16) continue;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 o;
@@ -648,10 +637,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
         for (int s = s0; s < s1; ++s) {
           ok = mbar_wait_spin(eempty(se), pe ^ 1, abort_flag, 0x86);
           if (!ok) break;
-          if (a.dbg & 8) { mbar_arrive(efull(se)); } else {
           mbar_expect_tx(efull(se), Cfg::E_BYTES);
-          bulk_g2s(e0 + se * Cfg::E_BYTES, a.E + (size_t)((a.dbg & 4) ? 0 : s) * (Cfg::E_BYTES / 16), Cfg::E_BYTES, efull(se));
-          }
+          bulk_g2s(e0 + se * Cfg::E_BYTES, a.E + (size_t)s * (Cfg::E_BYTES / 16), Cfg::E_BYTES, efull(se));
           if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; }
         }
       }
@@ -697,7 +684,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
           bool valid = true;
           int scol = sx;
           if (mode != RI_MODE_WRAP) { valid = sx >= 0 && sx < a.SW; if (!valid) scol = 0; }
-          if (!(a.dbg & 1)) cp_async16(dst + ((lg ^ (j & 7)) << 4), colp + (long)scol * 64, valid ? 16u : 0u);
+          cp_async16(dst + ((lg ^ (j & 7)) << 4), colp + (long)scol * 64, valid ? 16u : 0u);
           dst += JSTEP * 128;
           sx += JSTEP;
           if (mode == RI_MODE_WRAP) { while (sx >= a.SW) sx -= a.SW; }
@@ -844,6 +831,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
   tc_fence_after_sync();
   const uint32_t tmem_base = *misc;
 
+  // The i-th unit of this block: the units are dealt out back and forth (0 .. G-1, G-1 .. 0, ...)
+  // in the planner's order, largest first; -1 after the last one.
+  auto unit_at = [&](uint32_t i) -> long {
+    const long G = gridDim.x;
+    const long u = (long)i * G + ((i & 1) ? G - 1 - (long)blockIdx.x : (long)blockIdx.x);
+    return u < a.units ? u : -1;  // a block without a unit in a round is in the last round
+  };
   // unit u -> (unit record, batch part)
   auto unit_rec = [&](long u, int& part) {
     const int ui = (int)(u / a.bsplit);
@@ -856,7 +850,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
     constexpr uint32_t idesc = make_idesc_bf16(TILE_M, 64, 1, 1);
     uint32_t it = 0, nw = 0, ng = 0;
     int ok = 1;
-    for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x, ++it) {
+    for (long u; ok && (u = unit_at(it)) >= 0; ++it) {
       int part;
       const int4 ur = unit_rec(u, part);
       __syncwarp();
@@ -906,20 +900,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
     if (lane == 0) {
       mma_commit(drain_bar);
       mbar_wait(drain_bar, 0, abort_flag, 0x94);
-      if (blockIdx.x == 0) { g_ri_prof[0] = it; g_ri_prof[1] = nw; g_ri_prof[2] = ng; g_ri_prof[3] = ok; }
     }
     __syncwarp();
   } else if (warp <= N_EPI_WARPS) {
     // ------------------------------------------------------------------ epilogue: accumulators -> gE
     const int q = warp & 3;
     uint32_t it = 0;
-    for (long u = blockIdx.x; u < a.units; u += gridDim.x, ++it) {
+    for (long u; (u = unit_at(it)) >= 0; ++it) {
       int part;
       const int4 ur = unit_rec(u, part);
       int okt = 1;
       if (lane == 0) okt = mbar_wait(accfull, it & 1, abort_flag, 0x95) ? 1 : 0;
       okt = __shfl_sync(0xffffffffu, okt, 0);
-      if (!okt) { if (blockIdx.x == 0 && lane == 0 && q == 0) g_ri_prof[4] = it; break; }
+      if (!okt) break;
       tc_fence_after_sync();
       float* out = a.gE + (size_t)part * a.d.nslot * 4096;
       int pair = 0;
@@ -961,7 +954,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
     const int ptid = ((warp - FIRST_PROD_WARP) % TEAM_WARPS) * 32 + lane;
     constexpr int NPT = TEAM_WARPS * 32, JSTEP = NPT / 8;
     const int lg = ptid & 7, j0 = ptid >> 3;
-    uint32_t nw = 0, ng = 0;
+    uint32_t nw = 0, ng = 0, it = 0;
     bool ok = true;
     auto finish = [&](uint32_t bar) {
       cp_async_commit();
@@ -975,7 +968,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
       if (lane == 0) okw = mbar_wait(bar, parity, abort_flag, code) ? 1 : 0;
       return __shfl_sync(0xffffffffu, okw, 0) != 0;
     };
-    for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x) {
+    for (long u; ok && (u = unit_at(it)) >= 0; ++it) {
       int part;
       const int4 ur = unit_rec(u, part);
       const int b0 = part * bper, b1 = min(a.B, b0 + bper);
@@ -1028,81 +1021,171 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
   }
 }
 
-// gw[co, ci, k] += sum over the slots of a chunk of rows of sum over the slot's contributions with
-// tap k of weight * (sum over batch parts of gE[slot][ci][co]).  Thread = one (ci, co) element;
-// blockIdx.y = chunk of slots.  gw is float32 and zero before the first block adds to it.
-constexpr int WGR_TAPS = 16;
-__global__ void __launch_bounds__(256) rowinv_wgrad_reduce_kernel(const float* __restrict__ gE,
-                                                                  const int* __restrict__ plan, RiDir d,
-                                                                  int bsplit, int K, int Cin,
-                                                                  float* __restrict__ gw) {
-  const int e = blockIdx.x * 256 + threadIdx.x;  // ci * 64 + co
-  const int ci = e >> 6, co = e & 63;
+// Weight gradient, second step.  Three kernels, no atomics, results repeat bit for bit:
+//   rowinv_wgrad_reduce_kernel  P1[y][k][ci][co] = sum over the y-th chunk of slots, over the slot's
+//                               contributions (k, w), of w * (sum over batch parts of gE[slot][ci][co])
+//   rowinv_wgrad_fix_kernel     P2[k][y][ci][co] = the planner's corrections of tap k in the y-th chunk
+//   rowinv_wgrad_final_kernel   gw[co][ci][k] = sum_y P1[y][k] + sum_y P2[k][y]
+// In the first a thread owns four neighbouring co of one ci (one float4 of a slot's 64 x 64 block)
+// and keeps the loads of the next U slots in flight while it works on the current ones.
+constexpr int WGR_PARTS = 2;   // most parts the batch is cut into
+constexpr int WGF_CHUNKS = 128;  // chunks the corrections are cut into
+template <int PARTS, int TAPS, int U>
+__global__ void __launch_bounds__(256, 2) rowinv_wgrad_reduce_kernel(const float4* __restrict__ gE,
+                                                                     const int* __restrict__ plan, RiDir d,
+                                                                     int K, float4* __restrict__ P1) {
+  const int t = blockIdx.x * 256 + threadIdx.x;  // float4 of a slot: ci = t / 16, co = 4 (t % 16)
   const int per = (d.nslot + gridDim.y - 1) / gridDim.y;
   const int s0 = blockIdx.y * per, s1 = min(d.nslot, s0 + per);
-  for (int k0 = 0; k0 < K; k0 += WGR_TAPS) {
-    float acc[WGR_TAPS];
+  const size_t part_stride = (size_t)d.nslot * 1024;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k0 = 0; k0 < K; k0 += TAPS) {
+    float4 acc[TAPS];
 #pragma unroll
-    for (int i = 0; i < WGR_TAPS; ++i) acc[i] = 0.f;
-    for (int s = s0; s < s1; ++s) {
-      float v = 0.f;
-      for (int p = 0; p < bsplit; ++p) v += __ldg(gE + ((size_t)p * d.nslot + s) * 4096 + e);
-      const int c0 = __ldg(plan + d.off_coff + s), c1 = __ldg(plan + d.off_coff + s + 1);
-      for (int c = c0; c < c1; ++c) {
-        const int k = __ldg(plan + d.off_ctap + c) - k0;
-        const float wv = __int_as_float(__ldg(plan + d.off_cw + c)) * v;
+    for (int i = 0; i < TAPS; ++i) acc[i] = zero;
+    float4 cur[U][PARTS], nxt[U][PARTS];
 #pragma unroll
-        for (int i = 0; i < WGR_TAPS; ++i)
-          if (i == k) acc[i] += wv;
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int p = 0; p < PARTS; ++p)
+        cur[u][p] = s0 + u < s1 ? __ldg(gE + p * part_stride + (size_t)(s0 + u) * 1024 + t) : zero;
+    for (int s = s0; s < s1; s += U) {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int p = 0; p < PARTS; ++p)
+          nxt[u][p] = s + U + u < s1 ? __ldg(gE + p * part_stride + (size_t)(s + U + u) * 1024 + t) : zero;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (s + u >= s1) break;
+        float4 v = cur[u][0];
+#pragma unroll
+        for (int p = 1; p < PARTS; ++p) {
+          v.x += cur[u][p].x; v.y += cur[u][p].y; v.z += cur[u][p].z; v.w += cur[u][p].w;
+        }
+        const int c0 = __ldg(plan + d.off_coff + s + u), c1 = __ldg(plan + d.off_coff + s + u + 1);
+        for (int c = c0; c < c1; ++c) {
+          const int k = __ldg(plan + d.off_ctap + c) - k0;
+          const float wv = __int_as_float(__ldg(plan + d.off_cw + c));
+#pragma unroll
+          for (int i = 0; i < TAPS; ++i)
+            if (i == k) {
+              acc[i].x = fmaf(wv, v.x, acc[i].x); acc[i].y = fmaf(wv, v.y, acc[i].y);
+              acc[i].z = fmaf(wv, v.z, acc[i].z); acc[i].w = fmaf(wv, v.w, acc[i].w);
+            }
+        }
       }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int p = 0; p < PARTS; ++p) cur[u][p] = nxt[u][p];
     }
 #pragma unroll
-    for (int i = 0; i < WGR_TAPS; ++i)
-      if (k0 + i < K && acc[i] != 0.f) atomicAdd(gw + ((long)co * Cin + ci) * K + k0 + i, acc[i]);
+    for (int i = 0; i < TAPS; ++i)
+      if (k0 + i < K) P1[((size_t)blockIdx.y * K + k0 + i) * 1024 + t] = acc[i];
   }
 }
 
 // The planner's corrections in the weight gradient:
-// gw[co, ci, k] += sum_b dw gy[b, row, col, co] x[b, srow, scol, ci] for every correction with tap k.
-// blockIdx.x = tap, blockIdx.y = chunk of corrections; thread = co x 4 groups of 16 ci.
+// P2[k][y][ci][co] = sum_b dw gy[b, row, col, co] x[b, srow, scol, ci] over the corrections with tap k
+// in chunk y.  blockIdx.x = tap, blockIdx.y = chunk: the block first lists the corrections of its chunk
+// that belong to its tap (in order), then walks the list; thread = co x 4 groups of 16 ci, eight
+// images in flight.
+constexpr int WGF_LIST = 256;
 __global__ void __launch_bounds__(256) rowinv_wgrad_fix_kernel(const bf16* __restrict__ x,
                                                                const bf16* __restrict__ gy,
                                                                const int* __restrict__ plan, RiDir d,
                                                                int B, int SH, int SW, int RH, int RW,
-                                                               int K, int Cin, float* __restrict__ gw) {
+                                                               float* __restrict__ P2) {
+  __shared__ int s_list[WGF_LIST];
+  __shared__ int s_cnt[9];
   const int k = blockIdx.x;
   const int per = (d.nskip + gridDim.y - 1) / gridDim.y;
   const int e0 = blockIdx.y * per, e1 = min(d.nskip, e0 + per);
   const int co = threadIdx.x & 63, cg = threadIdx.x >> 6;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float acc[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-  bool any = false;
-  for (int e = e0; e < e1; ++e) {
-    const int* ent = plan + d.off_skip + 6 * e;
-    if (__ldg(ent + 4) != k) continue;
-    any = true;
-    const int row = __ldg(ent), col = __ldg(ent + 1), srow = __ldg(ent + 2), scol = __ldg(ent + 3);
-    const float dw = __int_as_float(__ldg(ent + 5));
-    for (int b = 0; b < B; ++b) {
-      const float g = dw * __bfloat162float(gy[(((long)b * RH + row) * RW + col) * 64 + co]);
-      const uint4* xp = reinterpret_cast<const uint4*>(x + (((long)b * SH + srow) * SW + scol) * 64 + cg * 16);
+  for (int base = e0; base < e1; base += WGF_LIST) {
+    // ordered compaction of the entries with this block's tap
+    const int e = base + threadIdx.x;
+    const bool hit = e < e1 && __ldg(plan + d.off_skip + 6 * e + 4) == k;
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) s_cnt[warp + 1] = __popc(m);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s_cnt[0] = 0;
+      for (int w = 0; w < 8; ++w) s_cnt[w + 1] += s_cnt[w];
+    }
+    __syncthreads();
+    if (hit) s_list[s_cnt[warp] + __popc(m & ((1u << lane) - 1))] = e;
+    __syncthreads();
+    const int n = s_cnt[8];
+    for (int i = 0; i < n; ++i) {
+      const int* ent = plan + d.off_skip + 6 * s_list[i];
+      const int row = __ldg(ent), col = __ldg(ent + 1), srow = __ldg(ent + 2), scol = __ldg(ent + 3);
+      const float dw = __int_as_float(__ldg(ent + 5));
+      const bf16* gp = gy + ((long)row * RW + col) * 64 + co;
+      const bf16* xq = x + ((long)srow * SW + scol) * 64 + cg * 16;
+      for (int b0 = 0; b0 < B; b0 += 8) {
+        float g[8];
+        uint4 v[8][2];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint4 v = __ldg(xp + h);
-        const uint32_t p4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          acc[h * 8 + 2 * t] = fmaf(g, __uint_as_float(p4[t] << 16), acc[h * 8 + 2 * t]);
-          acc[h * 8 + 2 * t + 1] = fmaf(g, __uint_as_float(p4[t] & 0xFFFF0000u), acc[h * 8 + 2 * t + 1]);
+        for (int j = 0; j < 8; ++j) {
+          const int b = min(b0 + j, B - 1);
+          g[j] = b0 + j < B ? dw * __bfloat162float(gp[(long)b * RH * RW * 64]) : 0.f;
+          const uint4* xp = reinterpret_cast<const uint4*>(xq + (long)b * SH * SW * 64);
+          v[j][0] = __ldg(xp);
+          v[j][1] = __ldg(xp + 1);
         }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t p4[4] = {v[j][h].x, v[j][h].y, v[j][h].z, v[j][h].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              acc[h * 8 + 2 * q] = fmaf(g[j], __uint_as_float(p4[q] << 16), acc[h * 8 + 2 * q]);
+              acc[h * 8 + 2 * q + 1] = fmaf(g[j], __uint_as_float(p4[q] & 0xFFFF0000u), acc[h * 8 + 2 * q + 1]);
+            }
+          }
       }
     }
+    __syncthreads();
   }
-  if (!any) return;
+  float* out = P2 + ((size_t)k * gridDim.y + blockIdx.y) * 4096;
 #pragma unroll
-  for (int i = 0; i < 16; ++i)
-    atomicAdd(gw + ((long)co * Cin + cg * 16 + i) * K + k, acc[i]);
+  for (int i = 0; i < 16; ++i) out[(cg * 16 + i) * 64 + co] = acc[i];
+}
+
+// gw[co][ci][k] = sum_y P1[y][k][ci][co] + sum_y P2[k][y][ci][co].  blockIdx.x = tap, blockIdx.y = 64
+// elements (one ci); the block's four groups of threads share the terms, eight loads in flight each.
+__global__ void __launch_bounds__(256) rowinv_wgrad_final_kernel(const float* __restrict__ P1, int Y1,
+                                                                 const float* __restrict__ P2, int Y2,
+                                                                 int K, int Cin, float* __restrict__ gw) {
+  __shared__ float s_sum[4][64];
+  const int k = blockIdx.x, e = blockIdx.y * 64 + (threadIdx.x & 63), grp = threadIdx.x >> 6;
+  float acc = 0.f;
+  for (int y0 = grp * 8; y0 < Y1 + Y2; y0 += 32) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int y = y0 + j;
+      v[j] = y < Y1 ? __ldg(P1 + ((size_t)y * K + k) * 4096 + e)
+                    : (y < Y1 + Y2 ? __ldg(P2 + ((size_t)k * Y2 + (y - Y1)) * 4096 + e) : 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += v[j];
+  }
+  s_sum[grp][threadIdx.x & 63] = acc;
+  __syncthreads();
+  if (grp == 0) {
+    const int l = threadIdx.x;
+    const float r = (s_sum[0][l] + s_sum[1][l]) + (s_sum[2][l] + s_sum[3][l]);
+    const int ci = e >> 6, co = e & 63;
+    gw[((long)co * Cin + ci) * K + k] = r;
+  }
 }
 
 static size_t rowinv_e_bytes(const RiDir& d, int NR) { return (size_t)d.nslot * NR * 128; }
@@ -1138,14 +1221,6 @@ int rowinv_analyse_launch(const mc_desc* d, const void* map, void* out, cudaStre
                                                (double*)out), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
-}
-
-extern "C" int mc_debug_ri_prof(long long* out) {
-  unsigned m = 0;
-  cudaMemcpyFromSymbol(&m, tc::g_status_mask, sizeof(m));
-  const int rc = cudaMemcpyFromSymbol(out, tc::g_ri_prof, sizeof(long long) * 16) == cudaSuccess ? 0 : -4;
-  out[15] = m;
-  return rc;
 }
 
 // -> number of int32s of the plan (0: the map does not qualify); copies at most cap ints to out
@@ -1196,7 +1271,6 @@ int rowinv_conv_launch(const mc_desc* d, int dir, const void* src, const void* p
   a.tpu = RiCfg<64>::TPU;
   a.upr = a.RW / (TILE_M * a.tpu);
   a.units = (long)a.RH * a.B * a.upr;
-  a.dbg = getenv("MC_RI_DBG") ? atoi(getenv("MC_RI_DBG")) : 0;
   int rc = rowinv_launch_n<64>(a, st);
   if (rc) return rc;
   if (D.ngroup > 0) {
@@ -1210,12 +1284,32 @@ int rowinv_conv_launch(const mc_desc* d, int dir, const void* src, const void* p
 
 int bias_grad_launch(const mc_desc*, const void*, void*, cudaStream_t);
 
-static int rowinv_bsplit(const mc_desc* d) { return d->B >= 2 ? 2 : 1; }
+// Parts the batch is cut into for the weight gradient: one when the units alone fill the device several
+// times over, two otherwise (more, smaller units; twice the partial sums to add up afterwards).
+static int rowinv_bsplit(const mc_desc* d, const RiDir& D) {
+  return d->B >= 2 && D.nwgunit < 6 * sm_count() ? WGR_PARTS : 1;
+}
+// chunks the slots are cut into for the first reduction
+static int rowinv_wgrad_chunks(const RiDir& D) { return std::max(1, std::min(D.nslot, sm_count())); }
 
+// workspace of the weight gradient: gE [parts][nslot][64][64], P1 [chunks][K][64][64],
+// P2 [K][WGF_CHUNKS][64][64], all float32
 size_t rowinv_wgrad_ws_bytes(const mc_desc* d, const void* plan_host) {
   const RiHeader* h = (const RiHeader*)plan_host;
   if (!rowinv_plan_matches(d, h)) return 0;
-  return (size_t)rowinv_bsplit(d) * h->dir[0].nslot * 4096 * sizeof(float);
+  const RiDir& D = h->dir[0];
+  return ((size_t)rowinv_bsplit(d, D) * D.nslot + (size_t)rowinv_wgrad_chunks(D) * d->K +
+          (size_t)d->K * WGF_CHUNKS) * 4096 * sizeof(float);
+}
+
+template <int PARTS>
+static void rowinv_wgrad_reduce_launch(const float4* gE, const int* plan, const RiDir& D, int K, int Y1,
+                                       float4* P1, cudaStream_t st) {
+  constexpr int U = PARTS == 1 ? 8 : 4;
+  if (K <= 9)
+    rowinv_wgrad_reduce_kernel<PARTS, 9, U><<<dim3(4, Y1), 256, 0, st>>>(gE, plan, D, K, P1), MC_COUNT(1);
+  else
+    rowinv_wgrad_reduce_kernel<PARTS, 16, U><<<dim3(4, Y1), 256, 0, st>>>(gE, plan, D, K, P1), MC_COUNT(1);
 }
 
 // gw (C_out, C_in, K) float32 and gb (C_out) float32 (may be null), fully overwritten.
@@ -1230,25 +1324,29 @@ int rowinv_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const v
   if (!aligned16(gy) || !aligned16(x) || !aligned16(ws) || !aligned16(plan_dev)) return MC_ERR_BAD_ARG;
   if (d->OW % (WG_TILES * TILE_M) != 0) return MC_ERR_UNSUPPORTED;
   const int* plan = (const int*)plan_dev;
-  if (cudaMemsetAsync(gw, 0, (size_t)d->C_out * d->C_in * d->K * sizeof(float), st) != cudaSuccess)
-    return MC_ERR_LAUNCH;
+  const int bsplit = rowinv_bsplit(d, D), Y1 = D.nwgunit > 0 ? rowinv_wgrad_chunks(D) : 0;
+  float* gE = (float*)ws;
+  float* P1 = gE + (size_t)bsplit * D.nslot * 4096;
+  float* P2 = P1 + (size_t)rowinv_wgrad_chunks(D) * d->K * 4096;
   if (D.nwgunit > 0) {
     RowInvWgArgs a;
-    a.x = (const bf16*)x; a.gy = (const bf16*)gy; a.gE = (float*)ws; a.plan = plan; a.d = D;
+    a.x = (const bf16*)x; a.gy = (const bf16*)gy; a.gE = gE; a.plan = plan; a.d = D;
     a.B = d->B; a.SH = d->IH; a.SW = d->IW; a.RH = d->OH; a.RW = d->OW;
-    a.bsplit = rowinv_bsplit(d);
+    a.bsplit = bsplit;
     a.units = (long)D.nwgunit * a.bsplit;
     if (!allow_big_smem(conv_rowinv_wgrad_kernel)) return MC_ERR_LAUNCH;
     const long g = a.units < sm_count() ? a.units : sm_count();
     conv_rowinv_wgrad_kernel<<<(int)g, TC_THREADS, WG_SMEM, st>>>(a), MC_COUNT(1);
     MC_CHECK_LAUNCH();
-    rowinv_wgrad_reduce_kernel<<<dim3(16, 64), 256, 0, st>>>((const float*)ws, plan, D, a.bsplit, d->K,
-                                                             d->C_in, (float*)gw), MC_COUNT(1);
+    if (bsplit == 1) rowinv_wgrad_reduce_launch<1>((const float4*)gE, plan, D, d->K, Y1, (float4*)P1, st);
+    else rowinv_wgrad_reduce_launch<WGR_PARTS>((const float4*)gE, plan, D, d->K, Y1, (float4*)P1, st);
   }
-  if (D.nskip > 0)
-    rowinv_wgrad_fix_kernel<<<dim3(d->K, 32), 256, 0, st>>>((const bf16*)x, (const bf16*)gy, plan, D,
-                                                            d->B, d->IH, d->IW, d->OH, d->OW, d->K,
-                                                            d->C_in, (float*)gw), MC_COUNT(1);
+  const int Y2 = D.nskip > 0 ? WGF_CHUNKS : 0;
+  if (Y2 > 0)
+    rowinv_wgrad_fix_kernel<<<dim3(d->K, Y2), 256, 0, st>>>((const bf16*)x, (const bf16*)gy, plan, D, d->B,
+                                                            d->IH, d->IW, d->OH, d->OW, P2), MC_COUNT(1);
+  rowinv_wgrad_final_kernel<<<dim3(d->K, 64), 256, 0, st>>>(P1, Y1, P2, Y2, d->K, d->C_in, (float*)gw),
+      MC_COUNT(1);
   MC_CHECK_LAUNCH();
   if (gb) return bias_grad_launch(d, gy, gb, st);
   return MC_OK;

@@ -14,7 +14,6 @@ namespace tc {
 // is included by exactly one translation unit (conv_tc.cu), which keeps the build free of
 // relocatable device code.
 static __device__ int g_status = 0;
-static __device__ unsigned g_status_mask = 0;  // bit (code & 31) of every wait that ran out (diagnostic)
 
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -59,9 +58,8 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t par
 // of the device.
 // sleep_ns = 0 (the default): loop on mbarrier.try_wait, which suspends the thread in hardware for a
 // bounded time slice while the phase is pending and wakes it as soon as the phase completes - the
-// right thing for the single threads that hand stages over (measured: a __nanosleep between polls
-// costs ~0.7 us per hand-over, far more than the nominal 32-64 ns).  sleep_ns > 0: back off between
-// polls, for roles where a whole warp waits for something that is far away.
+// right thing for the single threads that hand stages over.  sleep_ns > 0: back off between polls,
+// for roles where a whole warp waits for something that is far away.
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int code, unsigned sleep_ns = 0,
@@ -78,7 +76,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort_flag = 1;
   atomicCAS(&g_status, 0, code);
-  atomicOr(&g_status_mask, 1u << (code & 31));
   return false;
 }
 __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag,

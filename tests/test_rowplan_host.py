@@ -135,12 +135,19 @@ def test_the_benchmark_map_has_a_plan_and_others_do_not():
     assert plan is not None
     D = direction(plan, 0)
     assert D["rows"] == H and D["max_win"] <= 64 and D["max_slot"] <= 128 and D["nskip"] > 0
-    # weight-gradient units: every window of every row exactly once, at most 8 slot pairs each
+    # weight-gradient units: every window of every row exactly once, at most 8 slot pairs each,
+    # largest unit first
     wg = plan[D["off_wgunit"]: D["off_wgunit"] + 4 * D["nwgunit"]].reshape(-1, 4)
     win = plan[D["off_win"]: D["off_win"] + 4 * D["nwin"]].reshape(-1, 4)
-    assert wg[:, 2].sum() == D["nwin"] and (wg[1:, 1] == wg[:-1, 1] + wg[:-1, 2]).all()
+    row_off = plan[D["off_row"]: D["off_row"] + D["rows"] + 1]
+    by_start = wg[np.argsort(wg[:, 1], kind="stable")]
+    assert wg[:, 2].sum() == D["nwin"] and by_start[0, 1] == 0
+    assert (by_start[1:, 1] == by_start[:-1, 1] + by_start[:-1, 2]).all()
+    pairs = []
     for r, w0, nw, s0 in wg:
-        assert s0 == win[w0, 2] and sum(((win[w0:w0 + nw, 3] & 0xFF) + 1) // 2) <= 8
+        assert row_off[r] <= w0 and w0 + nw <= row_off[r + 1] and s0 == win[w0, 2]
+        pairs.append(int(sum(((win[w0:w0 + nw, 3] & 0xFF) + 1) // 2)))
+    assert max(pairs) <= 8 and pairs == sorted(pairs, reverse=True)
     # a jittered map is not row invariant; neither is a map whose rows move vertically
     g = torch.Generator().manual_seed(2)
     mj = m + 0.01 * torch.rand(m.shape, generator=g)
