@@ -818,11 +818,16 @@ def run_profile_case(args):
     gy = bf(B, COUT, H, W).contiguous(memory_format=torch.channels_last)
     w, b = bf(COUT, CIN, K), bf(COUT)
     m = get_projection_map((H, W), (3, 3), "gnomonic").to(dev)
+    # through the compiled binding, as the bench step runs it (row plans for this map);
+    # --general-kernels: the kernels for maps without a row plan
+    from mappedconvolutions_b200.host import impl as host_ops, COMPILED
+    if args.general_kernels and COMPILED:
+        host_ops.set_row_plans(False)
     for _ in range(3):
         if args.profile_case == "fwd":
-            ops.mapped_conv_forward(x, m, w, b, K, 1)
+            host_ops.mapped_conv_forward(x, m, w, b, K, 1)
         else:
-            ops.mapped_conv_backward(gy, m, x, w, b, K, 1)
+            host_ops.mapped_conv_backward(gy, m, x, w, b, K, 1)
     torch.cuda.synchronize()
     print("profile case %s batch %d done" % (args.profile_case, B))
 
@@ -842,6 +847,8 @@ def main():
                     help="run three calls of the config-2 forward / backward at --batch and exit "
                          "(small case for profiler captures)")
     ap.add_argument("--batch", type=int, default=2, help="batch of --profile-case")
+    ap.add_argument("--general-kernels", action="store_true",
+                    help="--profile-case fwd|bwd: the kernels for maps without a row plan")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args)

@@ -444,7 +444,7 @@ struct RiCfg {
   static constexpr int NBAR = 2 * RI_WIN_STAGES + 2 * NE + 5;
   static constexpr size_t SMEM = 1024 + (size_t)RI_WIN_STAGES * WIN_BYTES + (size_t)NE * E_BYTES +
                                  EPI_STAGING_BYTES + NOUT * 4 + NBAR * 8 + 48 +
-                                 (RI_MAX_WIN_PER_ROW * 16 + RI_MAX_SLOT_PER_ROW * 4);
+                                 (RI_MAX_WIN_PER_ROW * 16 + RI_MAX_SLOT_PER_ROW * 4 + 16);
 };
 
 template <int NOUT>
@@ -495,7 +495,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
     // All lanes fetch the row's window and slot records into the warp's strip of shared memory
     // (one round of independent loads); lane 0 then issues from there.
     constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 0, 0);
-    uint32_t it = 0, nw = 0, se = 0, pe = 0;
+    constexpr uint32_t DHI = desc_sw128_hi(1024);
+    const uint32_t blo0 = desc_sw128_lo(e0, 16);
+    uint32_t it = 0, nw = 0, se = 0, pe = 0, blo = blo0;
     int ok = 1;
     for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x, ++it) {
       int r, b, x0;
@@ -510,7 +512,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
         sfirst = s_win[0].z;
         ns = s_win[w1 - w0 - 1].z + (s_win[w1 - w0 - 1].w & 0xFF) - sfirst;
       }
-      for (int i = lane; i < ns; i += 32) s_shift[i] = __ldg(plan + a.d.off_slot + sfirst + i);
+      // a slot's shift as what it adds to the low word of the window's descriptor (bytes >> 4)
+      for (int i = lane; i < ns; i += 32) s_shift[i] = __ldg(plan + a.d.off_slot + sfirst + i) * 8;
       __syncwarp();
       if (lane == 0) {
         const uint32_t acc = it & 1, aph = (it >> 1) & 1;
@@ -518,25 +521,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * (Cfg::TPU * NOUT);
         int si = 0;
+        uint32_t accum = 0;  // the first slot of a unit overwrites the accumulators
         for (int w = 0; w < w1 - w0 && ok; ++w, ++nw) {
           const uint32_t ws = nw % RI_WIN_STAGES, wph = (nw / RI_WIN_STAGES) & 1;
           ok = mbar_wait_spin(wfull(ws), wph, abort_flag, 0x82) ? 1 : 0;
           const int nsl = s_win[w].w & 0xFF;
+          const uint32_t wlo = desc_sw128_lo(win0 + ws * Cfg::WIN_BYTES, 16);
+          uint32_t alo_next = wlo + (uint32_t)s_shift[si];
           for (int s = 0; s < nsl && ok; ++s, ++si) {
+            const uint32_t alo = alo_next;
+            alo_next = wlo + (uint32_t)s_shift[si + 1];  // (one word past the list is readable)
             ok = mbar_wait_spin(efull(se), pe, abort_flag, 0x83) ? 1 : 0;
             if (!ok) break;
             tc_fence_after_sync();
-            const uint64_t bdesc = make_desc_sw128(e0 + se * Cfg::E_BYTES, 16, 1024);
-            const uint32_t abase = win0 + ws * Cfg::WIN_BYTES + (uint32_t)s_shift[si] * 128u;
 #pragma unroll
-            for (int t = 0; t < Cfg::TPU; ++t) {
-              const uint64_t adesc = make_desc_sw128(abase + t * (TILE_M * 128), 16, 1024);
+            for (int t = 0; t < Cfg::TPU; ++t)
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                mma_bf16_ss(tmem_d + t * NOUT, adesc + 2 * j, bdesc + 2 * j, idesc, (si | j) != 0);
-            }
+                mma_bf16_ss_lo(tmem_d + t * NOUT, alo + t * (TILE_M * 128 / 16) + 2 * j, DHI, blo + 2 * j, DHI,
+                               idesc, j ? 1u : accum);
+            accum = 1;
             mma_commit(eempty(se));
-            if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; }
+            blo += Cfg::E_BYTES / 16;
+            if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; blo = blo0; }
           }
           if (ok) mma_commit(wempty(ws));
         }
@@ -720,9 +727,8 @@ __global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
   if (e0 >= e1) return;
   const int row = __ldg(plan + d.off_skip + 6 * e0), col = __ldg(plan + d.off_skip + 6 * e0 + 1);
   __shared__ float xs[FIX_LANES][64];
-  __shared__ float total[64];
+  __shared__ float total[FIX_LANES][64];
   const int n = threadIdx.x, y = threadIdx.y;  // NR == 64 == blockDim.x
-  if (y == 0) total[n] = 0.f;
   float acc = 0.f;
   for (int eb = e0; eb < e1; eb += FIX_LANES) {
     const int e = eb + y;
@@ -754,11 +760,14 @@ __global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
     }
     __syncthreads();
   }
-  atomicAdd(&total[n], acc);
+  total[y][n] = acc;
   __syncthreads();
-  if (y == 0) {
+  if (y == 0) {  // summed in a fixed order: results repeat bit for bit
+    float sum = total[0][n];
+#pragma unroll
+    for (int i = 1; i < FIX_LANES; ++i) sum += total[i][n];
     bf16* rp = res + (((long)b * RH + row) * RW + col) * NR + n;
-    *rp = __float2bfloat16_rn(__bfloat162float(*rp) + total[n]);
+    *rp = __float2bfloat16_rn(__bfloat162float(*rp) + sum);
   }
 }
 
@@ -779,7 +788,7 @@ constexpr uint32_t WG_GY_BYTES = WG_TILES * TILE_M * 128;           // 32 768
 constexpr int WG_NW = 4, WG_NG = 2;                                 // window / gy stages
 constexpr int WG_NBAR = 2 * WG_NW + 2 * WG_NG + 3;
 constexpr size_t WG_SMEM = 1024 + (size_t)WG_NW * WG_WIN_BYTES + (size_t)WG_NG * WG_GY_BYTES +
-                           WG_NBAR * 8 + 64 + (RI_MAX_WIN_PER_ROW * 16 + RI_MAX_SLOT_PER_ROW * 4);
+                           WG_NBAR * 8 + 64 + (RI_MAX_WIN_PER_ROW * 16 + RI_MAX_SLOT_PER_ROW * 4 + 16);
 
 struct RowInvWgArgs {
   const bf16* x;    // (B, SH, SW, 64)
@@ -848,6 +857,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
   if (warp == 0) {
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = make_idesc_bf16(TILE_M, 64, 1, 1);
+    constexpr uint32_t DHI = desc_sw128_hi(1024);
     uint32_t it = 0, nw = 0, ng = 0;
     int ok = 1;
     for (long u; ok && (u = unit_at(it)) >= 0; ++it) {
@@ -857,39 +867,46 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
       for (int i = lane; i < ur.z; i += 32)
         s_win[i] = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + ur.y + i);
       __syncwarp();
-      const int ns = s_win[ur.z - 1].z + (s_win[ur.z - 1].w & 0xFF) - ur.w;
-      for (int i = lane; i < ns; i += 32) s_shift[i] = __ldg(plan + a.d.off_slot + ur.w + i);
+      // per pair of slots the low word of the A descriptor relative to the window's stage: start row of
+      // the first slot (bytes >> 4) and, as leading byte offset, the distance to the second slot
+      for (int w = lane; w < ur.z; w += 32) {
+        const int4 wr = s_win[w];
+        const int nsl = wr.w & 0xFF;
+        for (int s = 0; s < nsl; s += 2) {
+          const int shA = __ldg(plan + a.d.off_slot + wr.z + s);
+          const int shB = s + 1 < nsl ? __ldg(plan + a.d.off_slot + wr.z + s + 1) : shA;
+          s_shift[(wr.z - ur.w) + s] = shA * 8 + (((shB - shA) * 8) << 16);
+        }
+      }
       __syncwarp();
       if (lane == 0) {
         ok = mbar_wait(accempty, (it & 1) ^ 1, abort_flag, 0x91) ? 1 : 0;
         tc_fence_after_sync();
         const int b0 = part * bper, b1 = min(a.B, b0 + bper);
-        bool first = true;
+        uint32_t accum = 0;  // the first chunk of a unit overwrites the accumulators
         for (int b = b0; b < b1 && ok; ++b) {
           for (int ch = 0; ch < nchunk && ok; ++ch, ++ng) {
             const uint32_t gs = ng % WG_NG, gph = (ng / WG_NG) & 1;
             ok = mbar_wait(gfull(gs), gph, abort_flag, 0x92) ? 1 : 0;
-            int si = 0, pair = 0;
+            const uint32_t blo = desc_sw128_lo(gy0 + gs * WG_GY_BYTES, STAGE_BYTES);
+            uint32_t tmem_d = tmem_base;
             for (int w = 0; w < ur.z && ok; ++w, ++nw) {
               const uint32_t ws = nw % WG_NW, wph = (nw / WG_NW) & 1;
+              const int4 wr = s_win[w];
+              const int nsl = wr.w & 0xFF, so = wr.z - ur.w;
+              const uint32_t wlo = desc_sw128_lo(win0 + ws * WG_WIN_BYTES, 0);
               ok = mbar_wait(wfull(ws), wph, abort_flag, 0x93) ? 1 : 0;
               if (!ok) break;
               tc_fence_after_sync();
-              const int nsl = s_win[w].w & 0xFF;
-              for (int s = 0; s < nsl; s += 2, ++pair) {
-                const int shA = s_shift[si + s], shB = s + 1 < nsl ? s_shift[si + s + 1] : shA;
-                const uint32_t abase = win0 + ws * WG_WIN_BYTES + (uint32_t)shA * 128u;
-                const uint64_t adesc = make_desc_sw128(abase, (uint32_t)(shB - shA) * 128u, 1024);
-                const uint64_t bdesc = make_desc_sw128(gy0 + gs * WG_GY_BYTES, STAGE_BYTES, 1024);
+              for (int s = 0; s < nsl; s += 2, tmem_d += 64) {
+                const uint32_t alo = wlo + (uint32_t)s_shift[so + s];
 #pragma unroll
                 for (int kk = 0; kk < WG_TILES * TILE_M / 16; ++kk)  // 16 pixels per MMA: +2048 bytes
-                  mma_bf16_ss(tmem_base + pair * 64, adesc + 128 * kk, bdesc + 128 * kk, idesc,
-                              !(first && kk == 0));
+                  mma_bf16_ss_lo(tmem_d, alo + 128 * kk, DHI, blo + 128 * kk, DHI, idesc, kk ? 1u : accum);
               }
-              si += nsl;
               mma_commit(wempty(ws));
             }
-            first = false;
+            accum = 1;
             if (ok) mma_commit(gempty(gs));
           }
         }

@@ -2107,18 +2107,18 @@ extern "C" int mc_conv_fwd_static_scratch(const mc_desc* d, const void* x, const
 constexpr int SELFTEST_STATUS = 0x7F1;
 __global__ void wait_expiry_selftest_kernel(long long limit_cycles, int* observed) {
   __shared__ uint64_t bar;
-  __shared__ int abort_flag;
+  __shared__ int abort_flag, wait_ok;
   if (threadIdx.x == 0) {
     tc::mbar_init(tc::smem_u32(&bar), 1);
     abort_flag = 0;
     tc::fence_barrier_init();
   }
   __syncthreads();
-  bool ok = true;
-  if (threadIdx.x == 0) ok = tc::mbar_wait(tc::smem_u32(&bar), 0, &abort_flag, SELFTEST_STATUS, 64, limit_cycles);
+  if (threadIdx.x == 0)
+    wait_ok = tc::mbar_wait(tc::smem_u32(&bar), 0, &abort_flag, SELFTEST_STATUS, 64, limit_cycles) ? 1 : 0;
   __syncthreads();
   // the other lanes see the abort flag, as the roles of a real kernel do
-  if (threadIdx.x == 1 && observed) *observed = (abort_flag ? 2 : 0) | (ok ? 1 : 0);
+  if (threadIdx.x == 1 && observed) *observed = (abort_flag ? 2 : 0) | (wait_ok ? 1 : 0);
 }
 
 extern "C" int mc_selftest_wait_expiry(int32_t* observed_dev, void* stream) {

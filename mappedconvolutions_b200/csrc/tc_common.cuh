@@ -152,6 +152,29 @@ __device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t adesc, uin
       : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the descriptors given as 32-bit halves.  Start address and leading byte offset sit in
+// the low word, so an issuing thread that walks through shared memory only adds to one 32-bit
+// register per operand; the high word (stride byte offset, version, swizzle mode) is a constant.
+// Matters because ONE thread issues every MMA of a block: each instruction it spends between two
+// tcgen05.mma shows up directly in the MMA rate (an M128 N64 K16 MMA takes 48 cycles).
+__host__ __device__ constexpr uint32_t desc_sw128_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t desc_sw128_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+__device__ __forceinline__ void mma_bf16_ss_lo(uint32_t tmem_d, uint32_t alo, uint32_t ahi, uint32_t blo,
+                                               uint32_t bhi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      :
+      : "r"(tmem_d), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // The mbarrier gets one arrival when every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
