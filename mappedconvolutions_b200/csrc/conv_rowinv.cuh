@@ -72,7 +72,11 @@ struct RiDir {
 struct RiHeader {
   int magic, total_ints;
   int OH, OW, IH, IW, K, interp;
-  RiDir dir[2];  // 0: forward (result = map grid), 1: adjoint (result = sampled image)
+  RiDir dir[2];   // 0: forward (result = map grid), 1: adjoint (result = sampled image)
+  RiDir pair[2];  // the same two directions planned for PAIRS of adjacent result rows (2p, 2p + 1):
+                  // rows = pairs; a slot is a (source row, shift) either row of the pair reads and has
+                  // two contribution lists, off_coff[2 s] for row 2p and off_coff[2 s + 1] for row
+                  // 2p + 1 (off_coff holds 2 nslot + 1 entries); no corrections, no weight-gradient units
 };
 
 // ---- analysis: is the map row invariant? --------------------------------------------------------------
@@ -247,6 +251,72 @@ static void ri_emit_dir(std::vector<RiCon>& cons, std::vector<RiFix>& fixes, int
   d.off_wgunit = put(wg);
 }
 
+// The plan of one direction for pairs of adjacent result rows.  The forward / input-gradient
+// kernel computes both rows of a pair with one MMA (N = 2 x 64 result channels): the rows share
+// their windows, and a slot only one of them reads gets zero weights for the other.
+static void ri_emit_pairs(std::vector<RiCon> cons, int rows, std::vector<int>& plan, RiDir& d,
+                          bool& ok) {
+  std::stable_sort(cons.begin(), cons.end(), [](const RiCon& a, const RiCon& b) {
+    if ((a.res_row >> 1) != (b.res_row >> 1)) return (a.res_row >> 1) < (b.res_row >> 1);
+    if (a.mode != b.mode) return a.mode < b.mode;
+    if (a.src_row != b.src_row) return a.src_row < b.src_row;
+    if (a.dx != b.dx) return a.dx < b.dx;
+    if (a.res_row != b.res_row) return a.res_row < b.res_row;
+    return a.tap < b.tap;
+  });
+  const int pairs = (rows + 1) / 2;
+  std::vector<int> row_off(pairs + 1, 0), win, slot, coff, ctap, cw;
+  int max_w = 0, max_s = 0;
+  size_t i = 0;
+  for (int p = 0; p < pairs; ++p) {
+    row_off[p] = (int)win.size() / 4;
+    const int slot0 = (int)slot.size();
+    while (i < cons.size() && (cons[i].res_row >> 1) == p) {
+      const RiCon c = cons[i];
+      bool new_win = win.size() / 4 == (size_t)row_off[p];
+      if (!new_win) {
+        const int* w = &win[win.size() - 4];
+        new_win = w[0] != c.src_row || (w[3] >> 16) != c.mode || c.dx - w[1] > RI_SPAN;
+      }
+      if (new_win) {
+        win.push_back(c.src_row); win.push_back(c.dx); win.push_back((int)slot.size());
+        win.push_back(c.mode << 16);
+      }
+      int* w = &win[win.size() - 4];
+      slot.push_back(c.dx - w[1]);
+      w[3] = (w[3] & 0xFFFF0000) | ((c.dx - w[1]) << 8) | (((w[3] & 0xFF) + 1) & 0xFF);
+      for (int sub = 0; sub < 2; ++sub) {
+        coff.push_back((int)ctap.size());
+        while (i < cons.size() && cons[i].res_row == 2 * p + sub && cons[i].mode == c.mode &&
+               cons[i].src_row == c.src_row && cons[i].dx == c.dx) {
+          ctap.push_back(cons[i].tap);
+          int bits;
+          std::memcpy(&bits, &cons[i].w, 4);
+          cw.push_back(bits);
+          ++i;
+        }
+      }
+    }
+    max_w = std::max(max_w, (int)win.size() / 4 - row_off[p]);
+    max_s = std::max(max_s, (int)slot.size() - slot0);
+  }
+  row_off[pairs] = (int)win.size() / 4;
+  coff.push_back((int)ctap.size());
+  if (max_w > RI_MAX_WIN_PER_ROW || max_s > RI_MAX_SLOT_PER_ROW) ok = false;
+  std::memset(&d, 0, sizeof(d));
+  d.rows = pairs; d.nwin = (int)win.size() / 4; d.nslot = (int)slot.size(); d.ncon = (int)ctap.size();
+  d.max_win_per_row = max_w; d.max_slot_per_row = max_s;
+  auto put = [&plan](const std::vector<int>& v) {
+    const int off = (int)plan.size();
+    plan.insert(plan.end(), v.begin(), v.end());
+    while (plan.size() % 4) plan.push_back(0);
+    return off;
+  };
+  d.off_row = put(row_off); d.off_win = put(win); d.off_slot = put(slot); d.off_coff = put(coff);
+  d.off_ctap = put(ctap); d.off_cw = put(cw);
+  d.off_skip = d.off_group = d.off_wgunit = (int)plan.size();
+}
+
 // One decoded map entry on the host: the (up to four) source pixels and weights the general kernels
 // use for it (common.cuh decode_tap; include/core/interpolation.h:125-154, :183-210).
 struct RiCorner {
@@ -355,6 +425,8 @@ static std::vector<int> rowinv_assemble(const mc_desc* d, const double* analysis
   std::vector<int> plan((sizeof(RiHeader) + 3) / 4, 0);
   while (plan.size() % 4) plan.push_back(0);
   bool ok = true;
+  ri_emit_pairs(fwd, OH, plan, h.pair[0], ok);
+  ri_emit_pairs(adj, IH, plan, h.pair[1], ok);
   ri_emit_dir(fwd, ffix, OH, plan, h.dir[0], ok);
   ri_emit_dir(adj, afix, IH, plan, h.dir[1], ok);
   if (!ok) return {};
@@ -433,18 +505,28 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 constexpr int RI_WIN_STAGES = 2;
+// Commands for the MMA thread, one per slot of a unit, written by a helper warp one unit ahead:
+// x = low word of the A descriptor of the slot's first tile (window stage + shift);
+// y = bit 0: first slot of a window - wait for the window stage (bit 1) in phase (bit 2);
+//     bit 3: last slot of a window - hand the stage (bit 1) back afterwards.
+constexpr int RI_CMD_SLOTS = RI_MAX_SLOT_PER_ROW + 2;
+constexpr size_t RI_CMD_BYTES = (size_t)RI_CMD_SLOTS * 8;
 
 template <int NOUT>
 struct RiCfg {
-  static constexpr int TPU = 256 / NOUT;                              // tiles per unit (TMEM: 2 x TPU x NOUT = 512)
+  // NOUT = 128: two adjacent result rows of 64 channels each side by side in the accumulator (the
+  // plan's pair directions); one accumulator set of 4 tiles x 128 columns fills tensor memory, so the
+  // read-out of a unit and the MMAs of the next take turns.  NOUT = 64: one row, two sets of 4 x 64.
+  static constexpr bool PAIR = NOUT == 128;
+  static constexpr int TPU = 4;                                       // 128-pixel tiles per unit
+  static constexpr int NACC = 512 / (TPU * NOUT);                     // accumulator sets in TMEM
   static constexpr uint32_t WIN_ROWS = TPU * TILE_M + RI_SPAN;
   static constexpr uint32_t WIN_BYTES = ((WIN_ROWS * 128 + 1023) / 1024) * 1024;
   static constexpr uint32_t E_BYTES = NOUT * 128;
   static constexpr int NE = NOUT == 64 ? 6 : (NOUT == 128 ? 4 : 2);  // E stages
-  static constexpr int NBAR = 2 * RI_WIN_STAGES + 2 * NE + 5;
+  static constexpr int NBAR = 2 * RI_WIN_STAGES + 2 * NE + 9;
   static constexpr size_t SMEM = 1024 + (size_t)RI_WIN_STAGES * WIN_BYTES + (size_t)NE * E_BYTES +
-                                 EPI_STAGING_BYTES + NOUT * 4 + NBAR * 8 + 48 +
-                                 (RI_MAX_WIN_PER_ROW * 16 + RI_MAX_SLOT_PER_ROW * 4 + 16);
+                                 EPI_STAGING_BYTES + NOUT * 4 + NBAR * 8 + 48 + 2 * RI_CMD_BYTES + 16;
 };
 
 template <int NOUT>
@@ -460,8 +542,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
   uint64_t* bars = (uint64_t*)(bias_s + NOUT);
   uint32_t* misc = (uint32_t*)(bars + Cfg::NBAR);
   volatile int* abort_flag = (volatile int*)(misc + 1);
-  int4* s_win = (int4*)(((uintptr_t)(misc + 4) + 15) & ~(uintptr_t)15);  // the MMA warp's copy of the row's windows
-  int* s_shift = (int*)(s_win + RI_MAX_WIN_PER_ROW);     // and slot shifts
+  uint2* s_cmd = (uint2*)(((uintptr_t)(misc + 4) + 15) & ~(uintptr_t)15);  // two command lists
+  volatile int* s_ns = (volatile int*)(misc + 2);                           // and their lengths
   const uint32_t bar0 = smem_u32(bars);
   auto wfull = [&](int s) { return bar0 + 8u * s; };
   auto wempty = [&](int s) { return bar0 + 8u * (RI_WIN_STAGES + s); };
@@ -470,11 +552,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
   auto tfull = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + i); };
   auto tempty = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 2 + i); };
   const uint32_t drain_bar = bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 4);
+  auto cfull = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 5 + i); };
+  auto cempty = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 7 + i); };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = 512;
   const int* plan = a.plan;
 
   if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) { mbar_init(cfull(i), 1); mbar_init(cempty(i), 1); }
     for (int s = 0; s < RI_WIN_STAGES; ++s) { mbar_init(wfull(s), N_PRODUCER_WARPS / RI_WIN_STAGES); mbar_init(wempty(s), 1); }
     for (int s = 0; s < Cfg::NE; ++s) { mbar_init(efull(s), 1); mbar_init(eempty(s), 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(tfull(i), 1); mbar_init(tempty(i), N_EPI_WARPS); }
@@ -483,7 +568,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
     fence_barrier_init();
   }
   for (int i = threadIdx.x; i < NOUT; i += TC_THREADS)
-    bias_s[i] = a.bias ? __bfloat162float(a.bias[i]) : 0.f;
+    bias_s[i] = a.bias ? __bfloat162float(a.bias[i & 63]) : 0.f;
   if (warp == 0) tmem_alloc(smem_u32(misc), TMEM_COLS);
   tc_fence_before_sync();
   __syncthreads();
@@ -492,64 +577,50 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 
   if (warp == 0) {
     // ------------------------------------------------------------------ MMA issuer
-    // All lanes fetch the row's window and slot records into the warp's strip of shared memory
-    // (one round of independent loads); lane 0 then issues from there.
+    // One thread issues every MMA of the block, so whatever it executes between two MMAs costs MMA
+    // rate.  It therefore only walks a list of commands that a helper warp prepares one unit ahead.
     constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 0, 0);
     constexpr uint32_t DHI = desc_sw128_hi(1024);
-    const uint32_t blo0 = desc_sw128_lo(e0, 16);
-    uint32_t it = 0, nw = 0, se = 0, pe = 0, blo = blo0;
-    int ok = 1;
-    for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x, ++it) {
-      int r, b, x0;
-      ri_unit(a, u, r, b, x0);
-      const int w0 = __ldg(plan + a.d.off_row + r), w1 = __ldg(plan + a.d.off_row + r + 1);
-      __syncwarp();
-      for (int i = lane; i < w1 - w0; i += 32)
-        s_win[i] = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w0 + i);
-      __syncwarp();
-      int ns = 0, sfirst = 0;
-      if (w1 > w0) {
-        sfirst = s_win[0].z;
-        ns = s_win[w1 - w0 - 1].z + (s_win[w1 - w0 - 1].w & 0xFF) - sfirst;
-      }
-      // a slot's shift as what it adds to the low word of the window's descriptor (bytes >> 4)
-      for (int i = lane; i < ns; i += 32) s_shift[i] = __ldg(plan + a.d.off_slot + sfirst + i) * 8;
-      __syncwarp();
-      if (lane == 0) {
-        const uint32_t acc = it & 1, aph = (it >> 1) & 1;
-        ok = mbar_wait_spin(tempty(acc), aph ^ 1, abort_flag, 0x81) ? 1 : 0;
+    if (lane == 0) {
+      const uint32_t blo0 = desc_sw128_lo(e0, 16);
+      uint32_t it = 0, se = 0, pe = 0, blo = blo0;
+      bool ok = true;
+      for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x, ++it) {
+        const uint32_t cb = it & 1, cph = (it >> 1) & 1;
+        ok = mbar_wait_spin(cfull(cb), cph, abort_flag, 0x80);
+        const uint2* cmd = s_cmd + cb * RI_CMD_SLOTS;
+        const int ns = s_ns[cb];
+        const uint32_t acc = Cfg::NACC == 2 ? cb : 0u, aph = Cfg::NACC == 2 ? cph : cb;
+        ok = ok && mbar_wait_spin(tempty(acc), aph ^ 1, abort_flag, 0x81);
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * (Cfg::TPU * NOUT);
-        int si = 0;
         uint32_t accum = 0;  // the first slot of a unit overwrites the accumulators
-        for (int w = 0; w < w1 - w0 && ok; ++w, ++nw) {
-          const uint32_t ws = nw % RI_WIN_STAGES, wph = (nw / RI_WIN_STAGES) & 1;
-          ok = mbar_wait_spin(wfull(ws), wph, abort_flag, 0x82) ? 1 : 0;
-          const int nsl = s_win[w].w & 0xFF;
-          const uint32_t wlo = desc_sw128_lo(win0 + ws * Cfg::WIN_BYTES, 16);
-          uint32_t alo_next = wlo + (uint32_t)s_shift[si];
-          for (int s = 0; s < nsl && ok; ++s, ++si) {
-            const uint32_t alo = alo_next;
-            alo_next = wlo + (uint32_t)s_shift[si + 1];  // (one word past the list is readable)
-            ok = mbar_wait_spin(efull(se), pe, abort_flag, 0x83) ? 1 : 0;
-            if (!ok) break;
-            tc_fence_after_sync();
+        uint2 nxt = cmd[0];
+        for (int i = 0; i < ns && ok; ++i) {
+          const uint2 cur = nxt;
+          nxt = cmd[i + 1];  // (the list has a spare entry)
+          const uint32_t stage = (cur.y >> 1) & 1;
+          if (cur.y & 1) ok = mbar_wait_spin(wfull(stage), (cur.y >> 2) & 1, abort_flag, 0x82);
+          ok = ok && mbar_wait_spin(efull(se), pe, abort_flag, 0x83);
+          if (!ok) break;
+          tc_fence_after_sync();
 #pragma unroll
-            for (int t = 0; t < Cfg::TPU; ++t)
+          for (int t = 0; t < Cfg::TPU; ++t)
 #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                mma_bf16_ss_lo(tmem_d + t * NOUT, alo + t * (TILE_M * 128 / 16) + 2 * j, DHI, blo + 2 * j, DHI,
-                               idesc, j ? 1u : accum);
-            accum = 1;
-            mma_commit(eempty(se));
-            blo += Cfg::E_BYTES / 16;
-            if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; blo = blo0; }
-          }
-          if (ok) mma_commit(wempty(ws));
+            for (int j = 0; j < 4; ++j)
+              mma_bf16_ss_lo(tmem_d + t * NOUT, cur.x + t * (TILE_M * 128 / 16) + 2 * j, DHI, blo + 2 * j, DHI,
+                             idesc, j ? 1u : accum);
+          accum = 1;
+          mma_commit(eempty(se));
+          blo += Cfg::E_BYTES / 16;
+          if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; blo = blo0; }
+          if (cur.y & 8) mma_commit(wempty(stage));
         }
-        if (ok) mma_commit(tfull(acc));
+        if (ok) {
+          mma_commit(tfull(acc));
+          mbar_arrive(cempty(cb));
+        }
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
     }
     if (lane == 0) {
       mma_commit(drain_bar);
@@ -573,7 +644,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
     for (long u = blockIdx.x; u < a.units; u += gridDim.x, ++it) {
       int r, b, x0;
       ri_unit(a, u, r, b, x0);
-      const uint32_t acc = it & 1, aph = (it >> 1) & 1;
+      const uint32_t acc = Cfg::NACC == 2 ? (it & 1) : 0u, aph = Cfg::NACC == 2 ? ((it >> 1) & 1) : (it & 1);
       const bool empty_row = __ldg(plan + a.d.off_row + r) == __ldg(plan + a.d.off_row + r + 1);
       {
         int okt = 1;
@@ -587,8 +658,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
         bf16* orow[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const long gp = ((long)b * a.RH + r) * a.RW + x0 + t * TILE_M + q * 32 + 8 * i + (lane >> 2);
-          orow[i] = a.out + gp * NOUT + (lane & 3) * 8;
+          const long gp = ((long)b * a.RH + (Cfg::PAIR ? 2 * r : r)) * a.RW + x0 + t * TILE_M + q * 32 + 8 * i +
+                          (lane >> 2);
+          orow[i] = a.out + gp * 64 + (lane & 3) * 8;
         }
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * (Cfg::TPU * NOUT) + t * NOUT;
 #pragma unroll
@@ -608,7 +680,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 o;
-            const float* bs = bias_s + cc * 32 + j * 8;
+            const float* bs = bias_s + (cc & 1) * 32 + j * 8;
             o.x = pack_bf16x2(__uint_as_float(v[j * 8 + 0]) + bs[0], __uint_as_float(v[j * 8 + 1]) + bs[1]);
             o.y = pack_bf16x2(__uint_as_float(v[j * 8 + 2]) + bs[2], __uint_as_float(v[j * 8 + 3]) + bs[3]);
             o.z = pack_bf16x2(__uint_as_float(v[j * 8 + 4]) + bs[4], __uint_as_float(v[j * 8 + 5]) + bs[5]);
@@ -622,7 +694,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
                          : "r"(rd_addr[i]));
-            *reinterpret_cast<uint4*>(orow[i] + cc * 32) = o;
+            // (a pair's second row sits 64 accumulator columns and one image row further on)
+            if (!Cfg::PAIR || cc < 2 || 2 * r + 1 < a.RH)
+              *reinterpret_cast<uint4*>(orow[i] + (cc & 1) * 32 + (Cfg::PAIR && cc >= 2 ? (long)a.RW * 64 : 0L)) = o;
           }
           __syncwarp();
         }
@@ -649,6 +723,40 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
           if (++se == (uint32_t)Cfg::NE) { se = 0; pe ^= 1; }
         }
       }
+    }
+  } else if (warp == FIRST_DEC_WARP + 1) {
+    // ------------------------------------------------------------------ command writer
+    // Turns the plan records of the block's next unit into the MMA thread's command list (lane =
+    // window): descriptor words, which window stage a slot reads and when that stage changes hands.
+    uint32_t it = 0, nw = 0;
+    for (long u = blockIdx.x; u < a.units; u += gridDim.x, ++it) {
+      int r, b, x0;
+      ri_unit(a, u, r, b, x0);
+      const uint32_t cb = it & 1, cph = (it >> 1) & 1;
+      const int w0 = __ldg(plan + a.d.off_row + r), w1 = __ldg(plan + a.d.off_row + r + 1);
+      const int sfirst = w1 > w0 ? __ldg(plan + a.d.off_win + 4 * w0 + 2) : 0;
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait(cempty(cb), cph ^ 1, abort_flag, 0x88, 64) ? 1 : 0;
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      if (!okw) break;
+      uint2* cmd = s_cmd + cb * RI_CMD_SLOTS;
+      if (lane == 0 && w1 == w0) s_ns[cb] = 0;
+      for (int w = w0 + lane; w < w1; w += 32) {
+        const int4 wr = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w);
+        const int nsl = wr.w & 0xFF;
+        const uint32_t nwg = nw + (uint32_t)(w - w0);
+        const uint32_t stage = nwg % RI_WIN_STAGES, ph = (nwg / RI_WIN_STAGES) & 1;
+        const uint32_t wlo = desc_sw128_lo(win0 + stage * Cfg::WIN_BYTES, 16);
+        for (int sl = 0; sl < nsl; ++sl) {
+          const uint32_t sh = (uint32_t)__ldg(plan + a.d.off_slot + wr.z + sl);
+          const uint32_t fl = (stage << 1) | (sl == 0 ? (1u | (ph << 2)) : 0u) | (sl == nsl - 1 ? 8u : 0u);
+          cmd[wr.z - sfirst + sl] = make_uint2(wlo + sh * 8u, fl);
+        }
+        if (w == w1 - 1) s_ns[cb] = wr.z + nsl - sfirst;
+      }
+      nw += (uint32_t)(w1 - w0);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(cfull(cb));
     }
   } else if (warp >= FIRST_PROD_WARP) {
     // ------------------------------------------------------------------ window loaders
@@ -1226,7 +1334,7 @@ using namespace tc;
 bool conv_rowinv_shape_ok(const mc_desc* d) {
   return d->dtype == MC_BF16 && d->layout == MC_NHWC && d->P == 0 && (d->interp == 1 || d->interp == 2) &&
          d->C_in == 64 && d->C_out == 64 && d->OW == d->IW && d->OW % TILE_M == 0 &&
-         (d->OW / TILE_M) % RiCfg<64>::TPU == 0 && d->K <= 64 &&
+         (d->OW / TILE_M) % RiCfg<128>::TPU == 0 && d->K <= 64 &&
          (long)d->B * std::max(d->OH, d->IH) * d->OW < (1L << 30);
 }
 
@@ -1260,7 +1368,7 @@ static size_t rowinv_wk_offset(const RiDir& D, int NR) { return (rowinv_e_bytes(
 size_t rowinv_ws_bytes(const mc_desc* d, const void* plan_host, int dir) {
   const RiHeader* h = (const RiHeader*)plan_host;
   if (!rowinv_plan_matches(d, h)) return 0;
-  return rowinv_wk_offset(h->dir[dir], 64) + (size_t)d->K * 64 * 64 * sizeof(bf16);
+  return rowinv_wk_offset(h->pair[dir], 128) + (size_t)d->K * 64 * 64 * sizeof(bf16);
 }
 
 // dir 0: y = conv(x); dir 1: gx = conv^T(gy).  `src` is the tensor that is gathered from.
@@ -1270,25 +1378,28 @@ int rowinv_conv_launch(const mc_desc* d, int dir, const void* src, const void* p
   if (!conv_rowinv_shape_ok(d) || (d->flags & MC_FLAG_RELU)) return MC_ERR_UNSUPPORTED;
   const RiHeader* h = (const RiHeader*)plan_host;
   if (!rowinv_plan_matches(d, h)) return MC_ERR_BAD_ARG;
-  const RiDir& D = h->dir[dir];
+  const RiDir& D = h->dir[dir];    // per row: the corrections
+  const RiDir& P = h->pair[dir];   // per pair of rows: what the main kernel runs on
   if (!ws || ws_bytes < rowinv_ws_bytes(d, plan_host, dir)) return MC_ERR_WORKSPACE;
   if (!aligned16(src) || !aligned16(res) || !aligned16(ws) || !aligned16(plan_dev)) return MC_ERR_BAD_ARG;
   const int* plan = (const int*)plan_dev;
-  bf16* wk = (bf16*)((uint8_t*)ws + rowinv_wk_offset(D, 64));
+  bf16* wk = (bf16*)((uint8_t*)ws + rowinv_wk_offset(P, 128));
   rowinv_wk_kernel<<<grid_for((long)d->K * 64 * 64, 256), 256, 0, st>>>((const bf16*)w, wk, 64, d->K,
                                                                          d->C_in, dir), MC_COUNT(1);
-  if (D.nslot > 0)
-    rowinv_weights_kernel<<<D.nslot, 256, 0, st>>>(wk, plan, D, (uint4*)ws, 64), MC_COUNT(1);
+  // a pair's slot has two lists of contributions, one per row: two consecutive 64 x 64 blocks, which
+  // together are the N = 128 operand of the slot
+  if (P.nslot > 0)
+    rowinv_weights_kernel<<<2 * P.nslot, 256, 0, st>>>(wk, plan, P, (uint4*)ws, 64), MC_COUNT(1);
   RowInvArgs a;
   a.src = (const bf16*)src; a.out = (bf16*)res; a.bias = (const bf16*)bias;
-  a.plan = plan; a.d = D; a.E = (const uint4*)ws;
+  a.plan = plan; a.d = P; a.E = (const uint4*)ws;
   a.B = d->B;
   if (dir == 0) { a.SH = d->IH; a.SW = d->IW; a.RH = d->OH; a.RW = d->OW; }
   else { a.SH = d->OH; a.SW = d->OW; a.RH = d->IH; a.RW = d->IW; }
-  a.tpu = RiCfg<64>::TPU;
+  a.tpu = RiCfg<128>::TPU;
   a.upr = a.RW / (TILE_M * a.tpu);
-  a.units = (long)a.RH * a.B * a.upr;
-  int rc = rowinv_launch_n<64>(a, st);
+  a.units = (long)P.rows * a.B * a.upr;
+  int rc = rowinv_launch_n<128>(a, st);
   if (rc) return rc;
   if (D.ngroup > 0) {
     rowinv_fix_kernel<<<dim3(D.ngroup, d->B), dim3(64, FIX_LANES), 0, st>>>((const bf16*)src, (bf16*)res, wk, plan, D,

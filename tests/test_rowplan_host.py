@@ -53,9 +53,11 @@ def direction(plan, i):
     return dict(zip(names, (int(v) for v in f)))
 
 
-def evaluate(plan, i, src, weight, res_hw, transpose):
-    """float64 evaluation of direction i of the plan.  src (B, C, SH, SW)."""
-    D = direction(plan, i)
+def evaluate(plan, i, src, weight, res_hw, transpose, pairs=False):
+    """float64 evaluation of direction i of the plan.  src (B, C, SH, SW).  pairs: the windows and
+    slots come from the plan for pairs of result rows (directions 2, 3: a slot has one contribution
+    list per row of the pair), the corrections from the per-row plan as always."""
+    D = direction(plan, i + 2 if pairs else i)
     B, C, SH, SW = src.shape
     RH, RW = res_hw
     Wt = weight.double()
@@ -68,21 +70,30 @@ def evaluate(plan, i, src, weight, res_hw, transpose):
     cw = plan[D["off_cw"]: D["off_cw"] + D["ncon"]].view(np.float32)
     xs = torch.arange(RW)
     s64 = src.double()
+    if pairs:
+        coff = plan[D["off_coff"]: D["off_coff"] + 2 * D["nslot"] + 1]
+        assert D["rows"] == (RH + 1) // 2
     for r in range(D["rows"]):
         for w in range(row_off[r], row_off[r + 1]):
             srow, dx0, first, packed = (int(v) for v in win[w])
             nsl, span, mode = packed & 0xFF, (packed >> 8) & 0xFF, packed >> 16
             assert span <= 32 and nsl >= 1
             for s in range(first, first + nsl):
-                E = sum(float(cw[c]) * Wt[:, :, int(ctap[c])] for c in range(coff[s], coff[s + 1]))
-                if transpose:
-                    E = E.t()
                 sx = xs + dx0 + int(shift[s])
                 if mode == 1:
                     ok, sx = torch.ones(RW, dtype=torch.bool), torch.remainder(sx, SW)
                 else:
                     ok, sx = (sx >= 0) & (sx < SW), sx.clamp(0, SW - 1)
-                out[:, :, r, :] += torch.einsum("oc,bcn->bon", E, s64[:, :, srow, :][:, :, sx] * ok)
+                for sub in range(2 if pairs else 1):
+                    v, row = (2 * s + sub, 2 * r + sub) if pairs else (s, r)
+                    if coff[v] == coff[v + 1]:
+                        continue
+                    assert row < RH
+                    E = sum(float(cw[c]) * Wt[:, :, int(ctap[c])] for c in range(coff[v], coff[v + 1]))
+                    if transpose:
+                        E = E.t()
+                    out[:, :, row, :] += torch.einsum("oc,bcn->bon", E, s64[:, :, srow, :][:, :, sx] * ok)
+    D = direction(plan, i)
     skip = plan[D["off_skip"]: D["off_skip"] + 6 * D["nskip"]].reshape(-1, 6)
     for row, col, srow, scol, k, wb in skip:
         w = float(np.array([wb], dtype=np.int32).view(np.float32)[0])
@@ -121,6 +132,11 @@ def test_plan_reproduces_the_mapped_convolution(wrapped, interp):
     # the plan uses ONE position per (row, tap); the map's float32 positions wobble by ~1e-4 px
     assert (got_y - want_y).abs().max().item() <= 2e-3 * want_y.abs().max().item()
     assert (got_gx - want_gx).abs().max().item() <= 2e-3 * want_gx.abs().max().item()
+    # the same through the plan for pairs of rows (what the forward / input-gradient kernels run on)
+    pair_y = evaluate(plan, 0, x, w, (H, W), False, pairs=True)
+    pair_gx = evaluate(plan, 1, gy, w, (H, W), True, pairs=True)
+    assert (pair_y - got_y).abs().max().item() <= 1e-9 * want_y.abs().max().item()
+    assert (pair_gx - got_gx).abs().max().item() <= 1e-9 * want_gx.abs().max().item()
     # corrections exist exactly where the seam matters: bilinear on wrapped positions
     nskip = direction(plan, 0)["nskip"]
     assert (nskip > 0) == (wrapped and interp == 1)
