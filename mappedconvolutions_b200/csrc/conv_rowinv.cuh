@@ -505,6 +505,14 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 constexpr int RI_WIN_STAGES = 2;
+// Warps of the forward / input-gradient kernel: 0 issues the MMAs, 1-4 and 20-23 read the accumulators
+// out (each set two of a unit's four tiles; a warp reaches the 32 TMEM lanes given by its index
+// modulo 4), 5 streams the effective weights, 6 writes the MMA thread's commands, 8-19 copy windows.
+constexpr int RI_LOADER_WARPS = 12;
+constexpr int RI_EPI2_FIRST = FIRST_PROD_WARP + RI_LOADER_WARPS;
+constexpr int RI_EPI_WARPS = 2 * N_EPI_WARPS;
+constexpr size_t RI_STAGING_BYTES = (size_t)RI_EPI_WARPS * 2048;
+static_assert(RI_EPI2_FIRST % 4 == 0 && RI_EPI2_FIRST + N_EPI_WARPS == TC_THREADS / 32, "warp roles");
 // Commands for the MMA thread, one per slot of a unit, written by a helper warp one unit ahead:
 // x = low word of the A descriptor of the slot's first tile (window stage + shift);
 // y = bit 0: first slot of a window - wait for the window stage (bit 1) in phase (bit 2);
@@ -526,7 +534,7 @@ struct RiCfg {
   static constexpr int NE = NOUT == 64 ? 6 : (NOUT == 128 ? 4 : 2);  // E stages
   static constexpr int NBAR = 2 * RI_WIN_STAGES + 2 * NE + 9;
   static constexpr size_t SMEM = 1024 + (size_t)RI_WIN_STAGES * WIN_BYTES + (size_t)NE * E_BYTES +
-                                 EPI_STAGING_BYTES + NOUT * 4 + NBAR * 8 + 48 + 2 * RI_CMD_BYTES + 16;
+                                 RI_STAGING_BYTES + NOUT * 4 + NBAR * 8 + 48 + 2 * RI_CMD_BYTES + 16;
 };
 
 template <int NOUT>
@@ -537,7 +545,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
   const uint32_t win0 = smem_u32(sm);
   const uint32_t e0 = win0 + RI_WIN_STAGES * Cfg::WIN_BYTES;
   const uint32_t stg0 = e0 + Cfg::NE * Cfg::E_BYTES;
-  uint8_t* tail = sm + RI_WIN_STAGES * Cfg::WIN_BYTES + Cfg::NE * Cfg::E_BYTES + EPI_STAGING_BYTES;
+  uint8_t* tail = sm + RI_WIN_STAGES * Cfg::WIN_BYTES + Cfg::NE * Cfg::E_BYTES + RI_STAGING_BYTES;
   float* bias_s = (float*)tail;
   uint64_t* bars = (uint64_t*)(bias_s + NOUT);
   uint32_t* misc = (uint32_t*)(bars + Cfg::NBAR);
@@ -560,9 +568,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) { mbar_init(cfull(i), 1); mbar_init(cempty(i), 1); }
-    for (int s = 0; s < RI_WIN_STAGES; ++s) { mbar_init(wfull(s), N_PRODUCER_WARPS / RI_WIN_STAGES); mbar_init(wempty(s), 1); }
+    for (int s = 0; s < RI_WIN_STAGES; ++s) { mbar_init(wfull(s), RI_LOADER_WARPS / RI_WIN_STAGES); mbar_init(wempty(s), 1); }
     for (int s = 0; s < Cfg::NE; ++s) { mbar_init(efull(s), 1); mbar_init(eempty(s), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(tfull(i), 1); mbar_init(tempty(i), N_EPI_WARPS); }
+    for (int i = 0; i < 2; ++i) { mbar_init(tfull(i), 1); mbar_init(tempty(i), RI_EPI_WARPS); }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -627,12 +635,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
       mbar_wait_spin(drain_bar, 0, abort_flag, 0x84);
     }
     __syncwarp();
-  } else if (warp <= N_EPI_WARPS) {
+  } else if (warp <= N_EPI_WARPS || warp >= RI_EPI2_FIRST) {
     // ------------------------------------------------------------------ epilogue
     // (the same accumulator read-out as conv_gemm_tc_kernel: TMEM -> registers -> + bias -> bf16 ->
     // a 32 x 64-byte block turned around in shared memory -> stores of 8 rows x 64 bytes)
+    // Two sets of four warps: the first reads tiles 0 and 1 of a unit, the second tiles 2 and 3.
     const int q = warp & 3;
-    const uint32_t stg = stg0 + (uint32_t)(warp - 1) * 2048u;
+    const int eset = warp >= RI_EPI2_FIRST ? 1 : 0;
+    const uint32_t stg = stg0 + (uint32_t)(eset ? N_EPI_WARPS + warp - RI_EPI2_FIRST : warp - 1) * 2048u;
     const uint32_t wr_row = stg + lane * 64, wr_x = (lane >> 1) & 3;
     uint32_t rd_addr[4];
 #pragma unroll
@@ -654,7 +664,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
       }
       tc_fence_after_sync();
 #pragma unroll
-      for (int t = 0; t < Cfg::TPU; ++t) {
+      for (int tt = 0; tt < Cfg::TPU / 2; ++tt) {
+        const int t = eset * (Cfg::TPU / 2) + tt;
         bf16* orow[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -668,7 +679,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
           uint32_t v[32];
           tmem_ld_32x32(taddr + cc * 32, v);
           tmem_ld_wait();
-          if (t == Cfg::TPU - 1 && cc == NOUT / 32 - 1) {
+          if (tt == Cfg::TPU / 2 - 1 && cc == NOUT / 32 - 1) {
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty(acc));
@@ -758,13 +769,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
       __syncwarp();
       if (lane == 0) mbar_arrive(cfull(cb));
     }
-  } else if (warp >= FIRST_PROD_WARP) {
+  } else if (warp >= FIRST_PROD_WARP && warp < RI_EPI2_FIRST) {
     // ------------------------------------------------------------------ window loaders
-    // Two teams of eight warps; team t copies the windows t, t + 2, ... of the CTA's window sequence
+    // Two teams of six warps; team t copies the windows t, t + 2, ... of the CTA's window sequence
     // into stage t, so that two windows are in flight at any time: a team sends the arrival for its
     // window once the copies have landed and then waits for its stage to come free again, while the
     // other team's copies are under way.
-    constexpr int TEAM_WARPS = N_PRODUCER_WARPS / RI_WIN_STAGES;
+    constexpr int TEAM_WARPS = RI_LOADER_WARPS / RI_WIN_STAGES;
     const int team = (warp - FIRST_PROD_WARP) / TEAM_WARPS;
     const int ptid = ((warp - FIRST_PROD_WARP) % TEAM_WARPS) * 32 + lane;
     constexpr int NPT = TEAM_WARPS * 32;
@@ -823,62 +834,83 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 }
 
 // ---- fix-up kernel: the planner's corrections for the pixels that deviate from their row's plan --------
-// One block per group of corrections that share a result pixel; thread = result channel.
+// One block per group of corrections that share a result pixel, for every image of the batch;
+// thread = result channel x one of FIX_LANES corrections worked on at the same time.  A thread keeps
+// its row of W_k in registers and uses it for all images (up to FIX_IMGS per pass).
 // forward : y[b, row, col, n]   += sum_e dw_e sum_c W[n, c, k_e]  x[b, srow_e, scol_e, c]
 // adjoint : gx[b, row, col, n]  += sum_e dw_e sum_c W[c, n, k_e] gy[b, srow_e, scol_e, c]
-constexpr int FIX_LANES = 4;  // corrections of a group worked on at the same time
+constexpr int FIX_LANES = 4, FIX_IMGS = 8;
 __global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
     const bf16* __restrict__ src, bf16* __restrict__ res, const bf16* __restrict__ wk,
-    const int* __restrict__ plan, RiDir d, int SH, int SW, int RH, int RW, int NR) {
-  const int g = blockIdx.x, b = blockIdx.y;
+    const int* __restrict__ plan, RiDir d, int B, int SH, int SW, int RH, int RW, int NR) {
+  const int g = blockIdx.x;
   const int e0 = __ldg(plan + d.off_group + g), e1 = __ldg(plan + d.off_group + g + 1);
   if (e0 >= e1) return;
   const int row = __ldg(plan + d.off_skip + 6 * e0), col = __ldg(plan + d.off_skip + 6 * e0 + 1);
-  __shared__ float xs[FIX_LANES][64];
-  __shared__ float total[FIX_LANES][64];
+  __shared__ __align__(16) float xs[FIX_LANES][FIX_IMGS][64];
+  __shared__ float total[FIX_LANES][FIX_IMGS][64];
   const int n = threadIdx.x, y = threadIdx.y;  // NR == 64 == blockDim.x
-  float acc = 0.f;
-  for (int eb = e0; eb < e1; eb += FIX_LANES) {
-    const int e = eb + y;
-    const bool on = e < e1;
-    int k = 0;
-    float we = 0.f;
-    if (on) {
-      const int* ent = plan + d.off_skip + 6 * e;
-      const int srow = __ldg(ent + 2), scol = __ldg(ent + 3);
-      k = __ldg(ent + 4);
-      we = __int_as_float(__ldg(ent + 5));
-      xs[y][n] = __bfloat162float(src[(((long)b * SH + srow) * SW + scol) * 64 + n]);
-    }
-    __syncthreads();
-    if (on) {
-      const uint4* wr = reinterpret_cast<const uint4*>(wk + ((long)k * NR + n) * 64);
-      float part = 0.f;
+  for (int b0 = 0; b0 < B; b0 += FIX_IMGS) {
+    const int nb = min(FIX_IMGS, B - b0);
+    float acc[FIX_IMGS];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const uint4 v = __ldg(wr + q);
-        const uint32_t p4[4] = {v.x, v.y, v.z, v.w};
+    for (int i = 0; i < FIX_IMGS; ++i) acc[i] = 0.f;
+    for (int eb = e0; eb < e1; eb += FIX_LANES) {
+      const int e = eb + y;
+      const bool on = e < e1;
+      int k = 0;
+      float we = 0.f;
+      if (on) {
+        const int* ent = plan + d.off_skip + 6 * e;
+        const int srow = __ldg(ent + 2), scol = __ldg(ent + 3);
+        k = __ldg(ent + 4);
+        we = __int_as_float(__ldg(ent + 5));
+        const bf16* sp = src + (((long)b0 * SH + srow) * SW + scol) * 64 + n;
+        for (int i = 0; i < nb; ++i) xs[y][i][n] = __bfloat162float(sp[(long)i * SH * SW * 64]);
+      }
+      __syncthreads();
+      if (on) {
+        const uint4* wr = reinterpret_cast<const uint4*>(wk + ((long)k * NR + n) * 64);
+        uint4 wv[8];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          part = fmaf(__uint_as_float(p4[t] << 16), xs[y][q * 8 + 2 * t], part);
-          part = fmaf(__uint_as_float(p4[t] & 0xFFFF0000u), xs[y][q * 8 + 2 * t + 1], part);
+        for (int q = 0; q < 8; ++q) wv[q] = __ldg(wr + q);
+        for (int i = 0; i < nb; ++i) {
+          const float4* xv = reinterpret_cast<const float4*>(xs[y][i]);
+          float part = 0.f;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 xa = xv[2 * q], xb = xv[2 * q + 1];
+            part = fmaf(__uint_as_float(wv[q].x << 16), xa.x, part);
+            part = fmaf(__uint_as_float(wv[q].x & 0xFFFF0000u), xa.y, part);
+            part = fmaf(__uint_as_float(wv[q].y << 16), xa.z, part);
+            part = fmaf(__uint_as_float(wv[q].y & 0xFFFF0000u), xa.w, part);
+            part = fmaf(__uint_as_float(wv[q].z << 16), xb.x, part);
+            part = fmaf(__uint_as_float(wv[q].z & 0xFFFF0000u), xb.y, part);
+            part = fmaf(__uint_as_float(wv[q].w << 16), xb.z, part);
+            part = fmaf(__uint_as_float(wv[q].w & 0xFFFF0000u), xb.w, part);
+          }
+#pragma unroll
+          for (int j = 0; j < FIX_IMGS; ++j)
+            if (j == i) acc[j] = fmaf(we, part, acc[j]);
         }
       }
-      acc = fmaf(we, part, acc);
+      __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < FIX_IMGS; ++i) total[y][i][n] = acc[i];
+    __syncthreads();
+    if (y == 0) {  // summed in a fixed order: results repeat bit for bit
+      for (int i = 0; i < nb; ++i) {
+        float sum = total[0][i][n];
+#pragma unroll
+        for (int l = 1; l < FIX_LANES; ++l) sum += total[l][i][n];
+        bf16* rp = res + ((((long)(b0 + i)) * RH + row) * RW + col) * NR + n;
+        *rp = __float2bfloat16_rn(__bfloat162float(*rp) + sum);
+      }
     }
     __syncthreads();
   }
-  total[y][n] = acc;
-  __syncthreads();
-  if (y == 0) {  // summed in a fixed order: results repeat bit for bit
-    float sum = total[0][n];
-#pragma unroll
-    for (int i = 1; i < FIX_LANES; ++i) sum += total[i][n];
-    bf16* rp = res + (((long)b * RH + row) * RW + col) * NR + n;
-    *rp = __float2bfloat16_rn(__bfloat162float(*rp) + sum);
-  }
 }
-
 
 // ---- weight gradient -------------------------------------------------------------------------------
 // Per slot s = (row r, source row sy, shift dx):  gE[s][ci][co] = sum_{b, x} X[b, sy, x + dx, ci] gy[b, r, x, co],
@@ -1402,8 +1434,8 @@ int rowinv_conv_launch(const mc_desc* d, int dir, const void* src, const void* p
   int rc = rowinv_launch_n<128>(a, st);
   if (rc) return rc;
   if (D.ngroup > 0) {
-    rowinv_fix_kernel<<<dim3(D.ngroup, d->B), dim3(64, FIX_LANES), 0, st>>>((const bf16*)src, (bf16*)res, wk, plan, D,
-                                                           a.SH, a.SW, a.RH, a.RW, 64), MC_COUNT(1);
+    rowinv_fix_kernel<<<D.ngroup, dim3(64, FIX_LANES), 0, st>>>((const bf16*)src, (bf16*)res, wk, plan, D, d->B,
+                                                                a.SH, a.SW, a.RH, a.RW, 64), MC_COUNT(1);
     MC_CHECK_LAUNCH();
   }
   return MC_OK;
