@@ -926,9 +926,10 @@ constexpr uint32_t WG_WIN_ROWS = WG_TILES * TILE_M + RI_SPAN;
 constexpr uint32_t WG_WIN_BYTES = ((WG_WIN_ROWS * 128 + 1023) / 1024) * 1024;  // 36 864
 constexpr uint32_t WG_GY_BYTES = WG_TILES * TILE_M * 128;           // 32 768
 constexpr int WG_NW = 4, WG_NG = 2;                                 // window / gy stages
-constexpr int WG_NBAR = 2 * WG_NW + 2 * WG_NG + 3;
+constexpr int WG_NBAR = 2 * WG_NW + 2 * WG_NG + 4;
+constexpr int WG_ISSUERS = 2;  // threads (warps 0 and 5) that issue MMAs, each for every second pair of slots
 constexpr size_t WG_SMEM = 1024 + (size_t)WG_NW * WG_WIN_BYTES + (size_t)WG_NG * WG_GY_BYTES +
-                           WG_NBAR * 8 + 64 + (RI_MAX_WIN_PER_ROW * 16 + RI_MAX_SLOT_PER_ROW * 4 + 16);
+                           WG_NBAR * 8 + 64 + WG_ISSUERS * (RI_MAX_WIN_PER_ROW * 16 + RI_MAX_SLOT_PER_ROW * 4 + 16);
 
 struct RowInvWgArgs {
   const bf16* x;    // (B, SH, SW, 64)
@@ -949,7 +950,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
   uint64_t* bars = (uint64_t*)(sm + WG_NW * WG_WIN_BYTES + WG_NG * WG_GY_BYTES);
   uint32_t* misc = (uint32_t*)(bars + WG_NBAR);
   volatile int* abort_flag = (volatile int*)(misc + 1);
-  int4* s_win = (int4*)(((uintptr_t)(misc + 4) + 15) & ~(uintptr_t)15);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Two threads issue the MMAs (a single one spends more time between two MMAs than the tensor core
+  // takes for one): warp 0 takes the even pairs of slots of a unit, warp FIRST_DEC_WARP the odd ones.
+  // Pairs have accumulators of their own, so the two need no order between them; every hand-over
+  // barrier counts one commit from each.  Each has its copy of the unit's records.
+  const int issuer = warp == 0 ? 0 : 1;
+  int4* s_win = (int4*)(((uintptr_t)(misc + 4) + 15) & ~(uintptr_t)15) +
+                issuer * (RI_MAX_WIN_PER_ROW + (RI_MAX_SLOT_PER_ROW * 4 + 16) / 16);
   int* s_shift = (int*)(s_win + RI_MAX_WIN_PER_ROW);
   const uint32_t bar0 = smem_u32(bars);
   auto wfull = [&](int s) { return bar0 + 8u * s; };
@@ -957,8 +965,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
   auto gfull = [&](int s) { return bar0 + 8u * (2 * WG_NW + s); };
   auto gempty = [&](int s) { return bar0 + 8u * (2 * WG_NW + WG_NG + s); };
   const uint32_t accfull = bar0 + 8u * (2 * WG_NW + 2 * WG_NG);
-  const uint32_t accempty = accfull + 8u, drain_bar = accfull + 16u;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t accempty = accfull + 8u, drain_bar = accfull + 16u + 8u * issuer;
   constexpr uint32_t TMEM_COLS = 512;
   constexpr int TEAMS = 2, TEAM_WARPS = N_PRODUCER_WARPS / TEAMS;
   const int* plan = a.plan;
@@ -966,11 +973,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
   const int bper = (a.B + a.bsplit - 1) / a.bsplit;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < WG_NW; ++s) { mbar_init(wfull(s), TEAM_WARPS); mbar_init(wempty(s), 1); }
-    for (int s = 0; s < WG_NG; ++s) { mbar_init(gfull(s), TEAM_WARPS); mbar_init(gempty(s), 1); }
-    mbar_init(accfull, 1);
+    for (int s = 0; s < WG_NW; ++s) { mbar_init(wfull(s), TEAM_WARPS); mbar_init(wempty(s), WG_ISSUERS); }
+    for (int s = 0; s < WG_NG; ++s) { mbar_init(gfull(s), TEAM_WARPS); mbar_init(gempty(s), WG_ISSUERS); }
+    mbar_init(accfull, WG_ISSUERS);
     mbar_init(accempty, N_EPI_WARPS);
-    mbar_init(drain_bar, 1);
+    mbar_init(accfull + 16u, 1);
+    mbar_init(accfull + 24u, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -994,8 +1002,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
     return __ldg(reinterpret_cast<const int4*>(plan + a.d.off_wgunit) + ui);
   };
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ MMA issuer
+  if (warp == 0 || warp == FIRST_DEC_WARP) {
+    // ------------------------------------------------------------------ MMA issuers
     constexpr uint32_t idesc = make_idesc_bf16(TILE_M, 64, 1, 1);
     constexpr uint32_t DHI = desc_sw128_hi(1024);
     uint32_t it = 0, nw = 0, ng = 0;
@@ -1030,6 +1038,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
             ok = mbar_wait(gfull(gs), gph, abort_flag, 0x92) ? 1 : 0;
             const uint32_t blo = desc_sw128_lo(gy0 + gs * WG_GY_BYTES, STAGE_BYTES);
             uint32_t tmem_d = tmem_base;
+            int mine = issuer;  // 0: the next pair is this thread's
             for (int w = 0; w < ur.z && ok; ++w, ++nw) {
               const uint32_t ws = nw % WG_NW, wph = (nw / WG_NW) & 1;
               const int4 wr = s_win[w];
@@ -1038,7 +1047,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
               ok = mbar_wait(wfull(ws), wph, abort_flag, 0x93) ? 1 : 0;
               if (!ok) break;
               tc_fence_after_sync();
-              for (int s = 0; s < nsl; s += 2, tmem_d += 64) {
+              for (int s = 0; s < nsl; s += 2, tmem_d += 64, mine ^= 1) {
+                if (mine) continue;
                 const uint32_t alo = wlo + (uint32_t)s_shift[so + s];
 #pragma unroll
                 for (int kk = 0; kk < WG_TILES * TILE_M / 16; ++kk)  // 16 pixels per MMA: +2048 bytes

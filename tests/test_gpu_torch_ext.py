@@ -111,7 +111,7 @@ def test_errors_are_raised_like_in_the_ctypes_twin(ext):
 def test_fused_relu_equals_conv_then_relu(ext):
     """activation='relu' runs max(0, .) in the convolution kernel's epilogue (MC_FLAG_RELU).  The
     result must equal relu(conv(x)) bit for bit - the clamp acts on the same float32 accumulator
-    before the same rounding - and so must the gradients."""
+    before the same rounding - and so must the input gradient."""
     from mapped_convolution.nn import MappedConvolution
     torch.manual_seed(11)
     for (B, Cin, Cout, Hh, Ww, K, interp, dt, cl) in (
@@ -134,8 +134,11 @@ def test_fused_relu_equals_conv_then_relu(ext):
         ya.backward(g)
         yb.backward(g)
         assert torch.equal(xa.grad, xb.grad)
-        assert torch.equal(plain.weight.grad, fused.weight.grad)
-        assert torch.equal(plain.bias.grad, fused.bias.grad)
+        # (the general weight-gradient kernels add their blocks' partial sums with atomics: two
+        # runs agree to rounding, not bit for bit)
+        tol = 2e-2 if dt == torch.bfloat16 else 1e-5
+        H.assert_close(fused.weight.grad.float(), plain.weight.grad.float(), tol, "grad_w")
+        H.assert_close(fused.bias.grad.float(), plain.bias.grad.float(), tol, "grad_b")
 
 
 def test_row_plans_through_the_layer_api(ext):
