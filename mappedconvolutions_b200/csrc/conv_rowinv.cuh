@@ -505,10 +505,11 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 constexpr int RI_WIN_STAGES = 2;
-// Warps of the forward / input-gradient kernel: 0 issues the MMAs, 1-4 and 20-23 read the accumulators
+// Warps of the forward / input-gradient kernel: 0 and 7 issue the MMAs, 1-4 and 20-23 read the accumulators
 // out (each set two of a unit's four tiles; a warp reaches the 32 TMEM lanes given by its index
 // modulo 4), 5 streams the effective weights, 6 writes the MMA thread's commands, 8-19 copy windows.
 constexpr int RI_LOADER_WARPS = 12;
+constexpr int RI_ISSUERS = 2, RI_ISSUER2_WARP = FIRST_DEC_WARP + 2;
 constexpr int RI_EPI2_FIRST = FIRST_PROD_WARP + RI_LOADER_WARPS;
 constexpr int RI_EPI_WARPS = 2 * N_EPI_WARPS;
 constexpr size_t RI_STAGING_BYTES = (size_t)RI_EPI_WARPS * 2048;
@@ -532,7 +533,7 @@ struct RiCfg {
   static constexpr uint32_t WIN_BYTES = ((WIN_ROWS * 128 + 1023) / 1024) * 1024;
   static constexpr uint32_t E_BYTES = NOUT * 128;
   static constexpr int NE = NOUT == 64 ? 6 : (NOUT == 128 ? 4 : 2);  // E stages
-  static constexpr int NBAR = 2 * RI_WIN_STAGES + 2 * NE + 9;
+  static constexpr int NBAR = 2 * RI_WIN_STAGES + 2 * NE + 11;
   static constexpr size_t SMEM = 1024 + (size_t)RI_WIN_STAGES * WIN_BYTES + (size_t)NE * E_BYTES +
                                  RI_STAGING_BYTES + NOUT * 4 + NBAR * 8 + 48 + 2 * RI_CMD_BYTES + 16;
 };
@@ -559,7 +560,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
   auto eempty = [&](int s) { return bar0 + 8u * (2 * RI_WIN_STAGES + Cfg::NE + s); };
   auto tfull = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + i); };
   auto tempty = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 2 + i); };
-  const uint32_t drain_bar = bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 4);
+  const uint32_t drain_bar0 = bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 9);
   auto cfull = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 5 + i); };
   auto cempty = [&](int i) { return bar0 + 8u * (2 * RI_WIN_STAGES + 2 * Cfg::NE + 7 + i); };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -567,11 +568,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
   const int* plan = a.plan;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) { mbar_init(cfull(i), 1); mbar_init(cempty(i), 1); }
-    for (int s = 0; s < RI_WIN_STAGES; ++s) { mbar_init(wfull(s), RI_LOADER_WARPS / RI_WIN_STAGES); mbar_init(wempty(s), 1); }
-    for (int s = 0; s < Cfg::NE; ++s) { mbar_init(efull(s), 1); mbar_init(eempty(s), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(tfull(i), 1); mbar_init(tempty(i), RI_EPI_WARPS); }
-    mbar_init(drain_bar, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(cfull(i), 1); mbar_init(cempty(i), RI_ISSUERS); }
+    for (int s = 0; s < RI_WIN_STAGES; ++s) { mbar_init(wfull(s), RI_LOADER_WARPS / RI_WIN_STAGES); mbar_init(wempty(s), RI_ISSUERS); }
+    for (int s = 0; s < Cfg::NE; ++s) { mbar_init(efull(s), 1); mbar_init(eempty(s), RI_ISSUERS); }
+    for (int i = 0; i < 2; ++i) { mbar_init(tfull(i), RI_ISSUERS); mbar_init(tempty(i), RI_EPI_WARPS); }
+    mbar_init(drain_bar0, 1);
+    mbar_init(drain_bar0 + 8u, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -583,11 +585,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
   tc_fence_after_sync();
   const uint32_t tmem_base = *misc;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ MMA issuer
-    // One thread issues every MMA of the block, so whatever it executes between two MMAs costs MMA
-    // rate.  It therefore only walks a list of commands that a helper warp prepares one unit ahead.
+  if (warp == 0 || warp == RI_ISSUER2_WARP) {
+    // ------------------------------------------------------------------ MMA issuers
+    // A thread that issues MMAs spends more time between two of them than the tensor core takes
+    // for one, so two threads issue: warp 0 for tiles 0 and 1 of a unit, warp RI_ISSUER2_WARP for
+    // tiles 2 and 3 (accumulators of their own, so no order is needed between the two; every
+    // hand-over barrier counts one commit from each).  They only walk a list of commands that a
+    // helper warp prepares one unit ahead.
     constexpr uint32_t idesc = make_idesc_bf16(TILE_M, NOUT, 0, 0);
+    const int issuer = warp == 0 ? 0 : 1;
+    const uint32_t drain_bar = drain_bar0 + 8u * issuer;
     constexpr uint32_t DHI = desc_sw128_hi(1024);
     if (lane == 0) {
       const uint32_t blo0 = desc_sw128_lo(e0, 16);
@@ -601,7 +608,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
         const uint32_t acc = Cfg::NACC == 2 ? cb : 0u, aph = Cfg::NACC == 2 ? cph : cb;
         ok = ok && mbar_wait_spin(tempty(acc), aph ^ 1, abort_flag, 0x81);
         tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + acc * (Cfg::TPU * NOUT);
+        const uint32_t tmem_d = tmem_base + acc * (Cfg::TPU * NOUT) + issuer * (Cfg::TPU / 2) * NOUT;
+        const uint32_t aoff = issuer * (Cfg::TPU / 2) * (TILE_M * 128 / 16);
         uint32_t accum = 0;  // the first slot of a unit overwrites the accumulators
         uint2 nxt = cmd[0];
         for (int i = 0; i < ns && ok; ++i) {
@@ -613,11 +621,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
           if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
-          for (int t = 0; t < Cfg::TPU; ++t)
+          for (int t = 0; t < Cfg::TPU / 2; ++t)
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              mma_bf16_ss_lo(tmem_d + t * NOUT, cur.x + t * (TILE_M * 128 / 16) + 2 * j, DHI, blo + 2 * j, DHI,
-                             idesc, j ? 1u : accum);
+              mma_bf16_ss_lo(tmem_d + t * NOUT, cur.x + aoff + t * (TILE_M * 128 / 16) + 2 * j, DHI, blo + 2 * j,
+                             DHI, idesc, j ? 1u : accum);
           accum = 1;
           mma_commit(eempty(se));
           blo += Cfg::E_BYTES / 16;
