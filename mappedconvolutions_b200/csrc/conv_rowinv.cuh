@@ -847,7 +847,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 // its row of W_k in registers and uses it for all images (up to FIX_IMGS per pass).
 // forward : y[b, row, col, n]   += sum_e dw_e sum_c W[n, c, k_e]  x[b, srow_e, scol_e, c]
 // adjoint : gx[b, row, col, n]  += sum_e dw_e sum_c W[c, n, k_e] gy[b, srow_e, scol_e, c]
-constexpr int FIX_LANES = 4, FIX_IMGS = 8;
+constexpr int FIX_LANES = 8, FIX_IMGS = 8;
 __global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
     const bf16* __restrict__ src, bf16* __restrict__ res, const bf16* __restrict__ wk,
     const int* __restrict__ plan, RiDir d, int B, int SH, int SW, int RH, int RW, int NR) {
@@ -856,7 +856,7 @@ __global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
   if (e0 >= e1) return;
   const int row = __ldg(plan + d.off_skip + 6 * e0), col = __ldg(plan + d.off_skip + 6 * e0 + 1);
   __shared__ __align__(16) float xs[FIX_LANES][FIX_IMGS][64];
-  __shared__ float total[FIX_LANES][FIX_IMGS][64];
+  float (*total)[FIX_IMGS][64] = xs;  // (reused for the final sum once the last correction is done)
   const int n = threadIdx.x, y = threadIdx.y;  // NR == 64 == blockDim.x
   for (int b0 = 0; b0 < B; b0 += FIX_IMGS) {
     const int nb = min(FIX_IMGS, B - b0);
@@ -866,40 +866,39 @@ __global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
     for (int eb = e0; eb < e1; eb += FIX_LANES) {
       const int e = eb + y;
       const bool on = e < e1;
-      int k = 0;
       float we = 0.f;
+      uint4 wv[8];  // the thread's row of W_k (bf16 pairs), fetched together with the source pixels
       if (on) {
         const int* ent = plan + d.off_skip + 6 * e;
-        const int srow = __ldg(ent + 2), scol = __ldg(ent + 3);
-        k = __ldg(ent + 4);
+        const int srow = __ldg(ent + 2), scol = __ldg(ent + 3), k = __ldg(ent + 4);
         we = __int_as_float(__ldg(ent + 5));
         const bf16* sp = src + (((long)b0 * SH + srow) * SW + scol) * 64 + n;
+        const uint4* wr = reinterpret_cast<const uint4*>(wk + ((long)k * NR + n) * 64);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) wv[q] = __ldg(wr + q);
         for (int i = 0; i < nb; ++i) xs[y][i][n] = __bfloat162float(sp[(long)i * SH * SW * 64]);
       }
       __syncthreads();
       if (on) {
-        const uint4* wr = reinterpret_cast<const uint4*>(wk + ((long)k * NR + n) * 64);
-        uint4 wv[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) wv[q] = __ldg(wr + q);
         for (int i = 0; i < nb; ++i) {
           const float4* xv = reinterpret_cast<const float4*>(xs[y][i]);
-          float part = 0.f;
+          float p0 = 0.f, p1 = 0.f;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             const float4 xa = xv[2 * q], xb = xv[2 * q + 1];
-            part = fmaf(__uint_as_float(wv[q].x << 16), xa.x, part);
-            part = fmaf(__uint_as_float(wv[q].x & 0xFFFF0000u), xa.y, part);
-            part = fmaf(__uint_as_float(wv[q].y << 16), xa.z, part);
-            part = fmaf(__uint_as_float(wv[q].y & 0xFFFF0000u), xa.w, part);
-            part = fmaf(__uint_as_float(wv[q].z << 16), xb.x, part);
-            part = fmaf(__uint_as_float(wv[q].z & 0xFFFF0000u), xb.y, part);
-            part = fmaf(__uint_as_float(wv[q].w << 16), xb.z, part);
-            part = fmaf(__uint_as_float(wv[q].w & 0xFFFF0000u), xb.w, part);
+            p0 = fmaf(__uint_as_float(wv[q].x << 16), xa.x, p0);
+            p0 = fmaf(__uint_as_float(wv[q].x & 0xFFFF0000u), xa.y, p0);
+            p0 = fmaf(__uint_as_float(wv[q].y << 16), xa.z, p0);
+            p0 = fmaf(__uint_as_float(wv[q].y & 0xFFFF0000u), xa.w, p0);
+            p1 = fmaf(__uint_as_float(wv[q].z << 16), xb.x, p1);
+            p1 = fmaf(__uint_as_float(wv[q].z & 0xFFFF0000u), xb.y, p1);
+            p1 = fmaf(__uint_as_float(wv[q].w << 16), xb.z, p1);
+            p1 = fmaf(__uint_as_float(wv[q].w & 0xFFFF0000u), xb.w, p1);
           }
+          const float part = we * (p0 + p1);
 #pragma unroll
           for (int j = 0; j < FIX_IMGS; ++j)
-            if (j == i) acc[j] = fmaf(we, part, acc[j]);
+            if (j == i) acc[j] += part;
         }
       }
       __syncthreads();
@@ -907,14 +906,12 @@ __global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
 #pragma unroll
     for (int i = 0; i < FIX_IMGS; ++i) total[y][i][n] = acc[i];
     __syncthreads();
-    if (y == 0) {  // summed in a fixed order: results repeat bit for bit
-      for (int i = 0; i < nb; ++i) {
-        float sum = total[0][i][n];
+    if (y < nb) {  // warp pair y adds up image y, in a fixed order: results repeat bit for bit
+      float sum = total[0][y][n];
 #pragma unroll
-        for (int l = 1; l < FIX_LANES; ++l) sum += total[l][i][n];
-        bf16* rp = res + ((((long)(b0 + i)) * RH + row) * RW + col) * NR + n;
-        *rp = __float2bfloat16_rn(__bfloat162float(*rp) + sum);
-      }
+      for (int l = 1; l < FIX_LANES; ++l) sum += total[l][y][n];
+      bf16* rp = res + ((((long)(b0 + y)) * RH + row) * RW + col) * NR + n;
+      *rp = __float2bfloat16_rn(__bfloat162float(*rp) + sum);
     }
     __syncthreads();
   }
