@@ -43,9 +43,11 @@ K = KH * KW
 BATCH = 8  # per GPU
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch at batch 8, scaled from ncu captures of
-# a batch-2 case (every term grows with the batch)
-DRAM_TRAFFIC_BYTES = {"conv_fwd": 2.21e9, "conv_dgrad": 2.25e9, "conv_wgrad": 2.30e9}
+# dram__bytes_read.sum + dram__bytes_write.sum of the family's main kernel per launch at batch 8,
+# scaled from ncu captures of a batch-2 case: the activation terms grow with the batch (x 4), the
+# effective weights (111 MB, forward / input gradient) and the per-slot partial sums (175 MB, weight
+# gradient) do not
+DRAM_TRAFFIC_BYTES = {"conv_fwd": 1.07e9, "conv_dgrad": 1.08e9, "conv_wgrad": 2.29e9}
 
 
 def flops_per_step(batch):

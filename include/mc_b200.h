@@ -182,8 +182,12 @@ int mc_conv_dgrad_inv(const mc_desc* d, const void* gy, const void* inv, const v
  *      It returns the number of int32s the plan needs (call with capacity 0 to size the buffer) or 0
  *      if the map is not row invariant;
  *   3. the caller keeps the host copy and uploads a copy to the device (16-byte aligned).
- * A plan depends only on the map and the image sizes, like the tap table and the inverse map.
- * dir: 0 = forward, 1 = input gradient.  ws holds the effective weights of the call. */
+ * A plan depends only on the map and the image sizes, like the tap table and the inverse map.  It
+ * holds, for each direction, the rows' windows and slots twice: row by row (weight gradient,
+ * corrections) and for pairs of adjacent rows (forward and input gradient compute two result rows
+ * with one N = 128 MMA; the rows of a pair share their windows).
+ * dir: 0 = forward, 1 = input gradient.  ws holds the effective weights of the call (16 KB per slot
+ * of a row pair) and a tap-major copy of w. */
 size_t mc_rowplan_analysis_bytes(const mc_desc* d);
 int mc_rowplan_analyse(const mc_desc* d, const void* map, void* analysis, void* stream);
 int64_t mc_rowplan_assemble(const mc_desc* d, const double* analysis_host, const float* map_host,
@@ -196,7 +200,8 @@ int mc_conv_dgrad_rowplan(const mc_desc* d, const void* gy, const void* plan_hos
                           const void* plan_dev, const void* w, const void* bias_out, void* gx,
                           void* ws, size_t ws_bytes, void* stream);
 /* Weight and bias gradient (float32, fully overwritten; gb may be NULL) from the same plan; ws holds
- * one 64 x 64 float32 partial sum per slot and batch part. */
+ * one 64 x 64 float32 partial sum per slot and batch part and the partial results of the two-step
+ * reduction that follows (no atomics: results repeat bit for bit). */
 size_t mc_conv_wgrad_rowplan_workspace_bytes(const mc_desc* d, const void* plan_host);
 int mc_conv_wgrad_rowplan(const mc_desc* d, const void* gy, const void* x, const void* plan_host,
                           const void* plan_dev, void* gw, void* gb, void* ws, size_t ws_bytes,

@@ -23,6 +23,16 @@
 //   weight gradient  per slot gE = sum over pixels of gy (x) X-window (conv_rowinv_wgrad kernel),
 //                    then gw_k = sum over slots of w * gE
 //
+// Forward and input gradient work on PAIRS of adjacent result rows: the two rows read largely the
+// same source rows, so one window serves both, and their effective weights sit side by side in an
+// N = 128 MMA operand (a slot only one row reads has zeros for the other: 26.5 slots per pair against
+// 2 x 20.8 at 512 x 1024 with a 3 x 3 gnomonic kernel).  Why N = 128: an M128 x N x K16 MMA takes
+// max(48, N / 2) cycles (below N = 96 the 128 B/clk shared-memory fetch of A + B binds), and the ONE
+// thread that issues needs ~45 cycles per instruction plus whatever else it executes - measured with
+// the loops below stripped to bare issue.  So N = 64 MMAs can never run faster than their issuing
+// thread; N = 128 halves the instructions per flop, and two threads (warps 0 and 7, two tiles of a
+// unit each) issue side by side.
+//
 // A row's plan is the NOMINAL behaviour of its taps.  A few pixels deviate from it: a bilinear map
 // whose positions are wrapped into [0, W) has, per tap and row, one pixel whose left corner is
 // column W - 1 and whose right corner (column W) does not exist and reads as zero
@@ -940,6 +950,7 @@ struct RowInvWgArgs {
   const bf16* x;    // (B, SH, SW, 64)
   const bf16* gy;   // (B, RH, RW, 64)
   float* gE;        // [bsplit][nslot][64 ci][64 co]
+  float* gb;        // 64 co, zero before the launch; null: no bias gradient in this launch
   const int* plan;
   RiDir d;
   int B, SH, SW, RH, RW;
@@ -979,7 +990,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < WG_NW; ++s) { mbar_init(wfull(s), TEAM_WARPS); mbar_init(wempty(s), WG_ISSUERS); }
-    for (int s = 0; s < WG_NG; ++s) { mbar_init(gfull(s), TEAM_WARPS); mbar_init(gempty(s), WG_ISSUERS); }
+    for (int s = 0; s < WG_NG; ++s) { mbar_init(gfull(s), TEAM_WARPS); mbar_init(gempty(s), WG_ISSUERS + N_EPI_WARPS); }
     mbar_init(accfull, WG_ISSUERS);
     mbar_init(accempty, N_EPI_WARPS);
     mbar_init(accfull + 16u, 1);
@@ -1076,12 +1087,59 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
     __syncwarp();
   } else if (warp <= N_EPI_WARPS) {
     // ------------------------------------------------------------------ epilogue: accumulators -> gE
+    // While a unit's MMAs run these warps have nothing to read out, so they add up the bias gradient
+    // from the grad_output chunks that pass through shared memory anyway: in the unit that starts a
+    // row (every chunk of a row's grad_output exactly once), thread = 8 channels x 16 pixels of a chunk.
     const int q = warp & 3;
-    uint32_t it = 0;
+    const int bcc = lane & 7, bpg = (warp - 1) * 4 + (lane >> 3);
+    uint32_t it = 0, ng = 0;
     for (long u; (u = unit_at(it)) >= 0; ++it) {
       int part;
       const int4 ur = unit_rec(u, part);
       int okt = 1;
+      {
+        const bool sum_bias = a.gb != nullptr && ur.y == __ldg(plan + a.d.off_row + ur.x);
+        float bs[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bs[i] = 0.f;
+        const int b0 = part * bper, b1 = min(a.B, b0 + bper);
+        for (int c = 0; c < (b1 - b0) * nchunk && okt; ++c, ++ng) {
+          const uint32_t gs = ng % WG_NG, gph = (ng / WG_NG) & 1;
+          if (lane == 0) okt = mbar_wait(gfull(gs), gph, abort_flag, 0x98, 64) ? 1 : 0;
+          okt = __shfl_sync(0xffffffffu, okt, 0);
+          if (!okt) break;
+          if (sum_bias) {
+            const uint32_t base = gy0 + gs * WG_GY_BYTES;
+#pragma unroll 4
+            for (int j = bpg; j < WG_TILES * TILE_M; j += 16) {
+              uint4 v;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                           : "r"(base + j * 128 + ((bcc ^ (j & 7)) << 4)));
+              const uint32_t p4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                bs[2 * t] += __uint_as_float(p4[t] << 16);
+                bs[2 * t + 1] += __uint_as_float(p4[t] & 0xFFFF0000u);
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(gempty(gs));
+        }
+        if (!okt) break;
+        if (sum_bias) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            bs[i] += __shfl_xor_sync(0xffffffffu, bs[i], 8);
+            bs[i] += __shfl_xor_sync(0xffffffffu, bs[i], 16);
+          }
+          if (lane < 8) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) atomicAdd(a.gb + bcc * 8 + i, bs[i]);
+          }
+        }
+      }
       if (lane == 0) okt = mbar_wait(accfull, it & 1, abort_flag, 0x95) ? 1 : 0;
       okt = __shfl_sync(0xffffffffu, okt, 0);
       if (!okt) break;
@@ -1503,9 +1561,18 @@ int rowinv_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const v
   float* gE = (float*)ws;
   float* P1 = gE + (size_t)bsplit * D.nslot * 4096;
   float* P2 = P1 + (size_t)rowinv_wgrad_chunks(D) * d->K * 4096;
+  // the bias gradient comes out of the main kernel when every row of grad_output passes through it
+  // (every row has a unit), otherwise from the stand-alone reduction
+  bool bias_in_kernel = gb != nullptr && D.nwgunit > 0;
+  if (bias_in_kernel) {
+    const int* row_off = (const int*)plan_host + D.off_row;
+    for (int r = 0; r < D.rows && bias_in_kernel; ++r) bias_in_kernel = row_off[r + 1] > row_off[r];
+  }
+  if (bias_in_kernel && cudaMemsetAsync(gb, 0, 64 * sizeof(float), st) != cudaSuccess) return MC_ERR_LAUNCH;
   if (D.nwgunit > 0) {
     RowInvWgArgs a;
     a.x = (const bf16*)x; a.gy = (const bf16*)gy; a.gE = gE; a.plan = plan; a.d = D;
+    a.gb = bias_in_kernel ? (float*)gb : nullptr;
     a.B = d->B; a.SH = d->IH; a.SW = d->IW; a.RH = d->OH; a.RW = d->OW;
     a.bsplit = bsplit;
     a.units = (long)D.nwgunit * a.bsplit;
@@ -1523,7 +1590,7 @@ int rowinv_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const v
   rowinv_wgrad_final_kernel<<<dim3(d->K, 64), 256, 0, st>>>(P1, Y1, P2, Y2, d->K, d->C_in, (float*)gw),
       MC_COUNT(1);
   MC_CHECK_LAUNCH();
-  if (gb) return bias_grad_launch(d, gy, gb, st);
+  if (gb && !bias_in_kernel) return bias_grad_launch(d, gy, gb, st);
   return MC_OK;
 }
 
