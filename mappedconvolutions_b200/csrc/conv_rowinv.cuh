@@ -858,7 +858,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 // forward : y[b, row, col, n]   += sum_e dw_e sum_c W[n, c, k_e]  x[b, srow_e, scol_e, c]
 // adjoint : gx[b, row, col, n]  += sum_e dw_e sum_c W[c, n, k_e] gy[b, srow_e, scol_e, c]
 constexpr int FIX_LANES = 8, FIX_IMGS = 8;
-__global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
+__global__ void __launch_bounds__(64 * FIX_LANES, 2) rowinv_fix_kernel(
     const bf16* __restrict__ src, bf16* __restrict__ res, const bf16* __restrict__ wk,
     const int* __restrict__ plan, RiDir d, int B, int SH, int SW, int RH, int RW, int NR) {
   const int g = blockIdx.x;
@@ -877,38 +877,45 @@ __global__ void __launch_bounds__(64 * FIX_LANES) rowinv_fix_kernel(
       const int e = eb + y;
       const bool on = e < e1;
       float we = 0.f;
-      uint4 wv[8];  // the thread's row of W_k (bf16 pairs), fetched together with the source pixels
+      int k = 0;
       if (on) {
         const int* ent = plan + d.off_skip + 6 * e;
-        const int srow = __ldg(ent + 2), scol = __ldg(ent + 3), k = __ldg(ent + 4);
+        const int srow = __ldg(ent + 2), scol = __ldg(ent + 3);
+        k = __ldg(ent + 4);
         we = __int_as_float(__ldg(ent + 5));
         const bf16* sp = src + (((long)b0 * SH + srow) * SW + scol) * 64 + n;
-        const uint4* wr = reinterpret_cast<const uint4*>(wk + ((long)k * NR + n) * 64);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) wv[q] = __ldg(wr + q);
         for (int i = 0; i < nb; ++i) xs[y][i][n] = __bfloat162float(sp[(long)i * SH * SW * 64]);
       }
       __syncthreads();
       if (on) {
-        for (int i = 0; i < nb; ++i) {
-          const float4* xv = reinterpret_cast<const float4*>(xs[y][i]);
-          float p0 = 0.f, p1 = 0.f;
+        // the thread's row of W_k (bf16 pairs; 72 KB in all, so these loads hit L1 / L2), half a row
+        // at a time to keep the registers of two blocks per SM
+        const uint4* wr = reinterpret_cast<const uint4*>(wk + ((long)k * NR + n) * 64);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const float4 xa = xv[2 * q], xb = xv[2 * q + 1];
-            p0 = fmaf(__uint_as_float(wv[q].x << 16), xa.x, p0);
-            p0 = fmaf(__uint_as_float(wv[q].x & 0xFFFF0000u), xa.y, p0);
-            p0 = fmaf(__uint_as_float(wv[q].y << 16), xa.z, p0);
-            p0 = fmaf(__uint_as_float(wv[q].y & 0xFFFF0000u), xa.w, p0);
-            p1 = fmaf(__uint_as_float(wv[q].z << 16), xb.x, p1);
-            p1 = fmaf(__uint_as_float(wv[q].z & 0xFFFF0000u), xb.y, p1);
-            p1 = fmaf(__uint_as_float(wv[q].w << 16), xb.z, p1);
-            p1 = fmaf(__uint_as_float(wv[q].w & 0xFFFF0000u), xb.w, p1);
+        for (int half = 0; half < 2; ++half) {
+          uint4 wv[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) wv[q] = __ldg(wr + half * 4 + q);
+          for (int i = 0; i < nb; ++i) {
+            const float4* xv = reinterpret_cast<const float4*>(xs[y][i]) + half * 8;
+            float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 xa = xv[2 * q], xb = xv[2 * q + 1];
+              p0 = fmaf(__uint_as_float(wv[q].x << 16), xa.x, p0);
+              p0 = fmaf(__uint_as_float(wv[q].x & 0xFFFF0000u), xa.y, p0);
+              p0 = fmaf(__uint_as_float(wv[q].y << 16), xa.z, p0);
+              p0 = fmaf(__uint_as_float(wv[q].y & 0xFFFF0000u), xa.w, p0);
+              p1 = fmaf(__uint_as_float(wv[q].z << 16), xb.x, p1);
+              p1 = fmaf(__uint_as_float(wv[q].z & 0xFFFF0000u), xb.y, p1);
+              p1 = fmaf(__uint_as_float(wv[q].w << 16), xb.z, p1);
+              p1 = fmaf(__uint_as_float(wv[q].w & 0xFFFF0000u), xb.w, p1);
+            }
+            const float part = we * (p0 + p1);
+#pragma unroll
+            for (int j = 0; j < FIX_IMGS; ++j)
+              if (j == i) acc[j] += part;
           }
-          const float part = we * (p0 + p1);
-#pragma unroll
-          for (int j = 0; j < FIX_IMGS; ++j)
-            if (j == i) acc[j] += part;
         }
       }
       __syncthreads();
