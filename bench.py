@@ -645,7 +645,8 @@ def encoder_record(steps, warmup, min_seconds=0.0):
     nb = hi - lo
     torch.manual_seed(0)
     convs = torch.nn.ModuleList(
-        [mnn.MappedConvolution(ENC_CH[i], ENC_CH[i + 1], 7, "nearest") for i in range(4)]).to(dev).to(torch.bfloat16)
+        [mnn.MappedConvolution(ENC_CH[i], ENC_CH[i + 1], 7, "nearest", activation="relu")
+         for i in range(4)]).to(dev).to(torch.bfloat16)  # (ReLU in the conv kernel's epilogue)
     kmap = {l: ico.vertex_kernel_map(l).to(dev) for l in (7, 6, 5)}
     pmap = {l: ico.pooling_map(l).to(dev) for l in (7, 6)}
     pool = mnn.MappedAvgPool(7, "nearest")
@@ -657,12 +658,12 @@ def encoder_record(steps, warmup, min_seconds=0.0):
     lr = 1e-3
 
     def step(xin):
-        h = torch.relu(convs[0](xin, kmap[7]))
+        h = convs[0](xin, kmap[7])
         h = pool(h, pmap[7])
-        h = torch.relu(convs[1](h, kmap[6]))
+        h = convs[1](h, kmap[6])
         h = pool(h, pmap[6])
-        h = torch.relu(convs[2](h, kmap[5]))
-        h = torch.relu(convs[3](h, kmap[5]))
+        h = convs[2](h, kmap[5])
+        h = convs[3](h, kmap[5])
         loss = h.float().mean()
         loss.backward()
         grads = [p.grad for p in params]

@@ -37,7 +37,7 @@ class MappedConvFn(Function):
     def backward(ctx, gy):
         x, weight, bias, sample_map, iw, y = ctx.saved_tensors
         if ctx.relu:  # gradient of the activation, from its own output: y > 0 <=> pre-activation > 0
-            gy = torch.where(y > 0, gy, torch.zeros((), dtype=gy.dtype, device=gy.device))
+            gy = torch.ops.aten.threshold_backward(gy, y, 0)  # one pass: gy where y > 0, else 0
         if iw is not None:
             gx, gw, gb = ops.weighted_mapped_conv_backward(gy, sample_map, iw, x, weight, bias,
                                                            ctx.k, ctx.interp)
