@@ -664,7 +664,7 @@ def encoder_record(steps, warmup, min_seconds=0.0):
         h = pool(h, pmap[6])
         h = convs[2](h, kmap[5])
         h = convs[3](h, kmap[5])
-        loss = h.float().mean()
+        loss = h.mean(dtype=torch.float32)  # (float32 accumulation straight from the bf16 activation)
         loss.backward()
         grads = [p.grad for p in params]
         if world > 1:
