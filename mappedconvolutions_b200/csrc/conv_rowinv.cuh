@@ -852,83 +852,89 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 }
 
 // ---- fix-up kernel: the planner's corrections for the pixels that deviate from their row's plan --------
-// One block per group of corrections that share a result pixel, for every image of the batch;
-// thread = result channel x one of FIX_LANES corrections worked on at the same time.  A thread keeps
-// its row of W_k in registers and uses it for all images (up to FIX_IMGS per pass).
+// One block per group of corrections that share a result pixel, for every image of the batch:
 // forward : y[b, row, col, n]   += sum_e dw_e sum_c W[n, c, k_e]  x[b, srow_e, scol_e, c]
 // adjoint : gx[b, row, col, n]  += sum_e dw_e sum_c W[c, n, k_e] gy[b, srow_e, scol_e, c]
-constexpr int FIX_LANES = 8, FIX_IMGS = 8;
-__global__ void __launch_bounds__(64 * FIX_LANES, 2) rowinv_fix_kernel(
+// Per correction that is a 64 x 64 by 64 x 8 product (W_k times the source pixel of eight images):
+// 16 warp-level m16n8k16 MMAs (mma.sync - the tensor-core instruction for a product this small; a
+// tcgen05 tile would be 128 rows).  Warp w of the block takes the corrections w, w + 4, ... of the
+// group; the four partial results are added in a fixed order, so results repeat bit for bit.
+constexpr int FIX_WARPS = 4, FIX_IMGS = 8;
+__device__ __forceinline__ void mma_m16n8k16_bf16(float (&d)[4], const uint32_t (&a)[4],
+                                                  const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__global__ void __launch_bounds__(32 * FIX_WARPS) rowinv_fix_kernel(
     const bf16* __restrict__ src, bf16* __restrict__ res, const bf16* __restrict__ wk,
     const int* __restrict__ plan, RiDir d, int B, int SH, int SW, int RH, int RW, int NR) {
-  const int g = blockIdx.x;
-  const int e0 = __ldg(plan + d.off_group + g), e1 = __ldg(plan + d.off_group + g + 1);
+  const int grp = blockIdx.x;
+  const int e0 = __ldg(plan + d.off_group + grp), e1 = __ldg(plan + d.off_group + grp + 1);
   if (e0 >= e1) return;
   const int row = __ldg(plan + d.off_skip + 6 * e0), col = __ldg(plan + d.off_skip + 6 * e0 + 1);
-  __shared__ __align__(16) float xs[FIX_LANES][FIX_IMGS][64];
-  float (*total)[FIX_IMGS][64] = xs;  // (reused for the final sum once the last correction is done)
-  const int n = threadIdx.x, y = threadIdx.y;  // NR == 64 == blockDim.x
+  // fragment coordinates of mma.m16n8k16: g = row of A / column of B and D, t = pair of k / of columns
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  __shared__ float red[FIX_WARPS][4][4][32];  // [warp][m-tile][register][lane]
   for (int b0 = 0; b0 < B; b0 += FIX_IMGS) {
-    const int nb = min(FIX_IMGS, B - b0);
-    float acc[FIX_IMGS];
+    float acc[4][4];
 #pragma unroll
-    for (int i = 0; i < FIX_IMGS; ++i) acc[i] = 0.f;
-    for (int eb = e0; eb < e1; eb += FIX_LANES) {
-      const int e = eb + y;
-      const bool on = e < e1;
-      float we = 0.f;
-      int k = 0;
-      if (on) {
-        const int* ent = plan + d.off_skip + 6 * e;
-        const int srow = __ldg(ent + 2), scol = __ldg(ent + 3);
-        k = __ldg(ent + 4);
-        we = __int_as_float(__ldg(ent + 5));
-        const bf16* sp = src + (((long)b0 * SH + srow) * SW + scol) * 64 + n;
-        for (int i = 0; i < nb; ++i) xs[y][i][n] = __bfloat162float(sp[(long)i * SH * SW * 64]);
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+    for (int e = e0 + warp; e < e1; e += FIX_WARPS) {
+      const int* ent = plan + d.off_skip + 6 * e;
+      const int srow = __ldg(ent + 2), scol = __ldg(ent + 3), k = __ldg(ent + 4);
+      const float dw = __int_as_float(__ldg(ent + 5));
+      // B operand (k = source channel, n = image): image b0 + g, channels 16 ks + 2 t (+ 8), two at a time
+      const bool img = b0 + g < B;
+      const uint32_t* xp = reinterpret_cast<const uint32_t*>(
+          src + ((((long)(img ? b0 + g : 0)) * SH + srow) * SW + scol) * 64);
+      uint32_t bfr[4][2];
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        bfr[ks][0] = img ? __ldg(xp + ks * 8 + t) : 0u;
+        bfr[ks][1] = img ? __ldg(xp + ks * 8 + t + 4) : 0u;
       }
-      __syncthreads();
-      if (on) {
-        // the thread's row of W_k (bf16 pairs; 72 KB in all, so these loads hit L1 / L2), half a row
-        // at a time to keep the registers of two blocks per SM
-        const uint4* wr = reinterpret_cast<const uint4*>(wk + ((long)k * NR + n) * 64);
+      // A operand: W_k[n][c], n = 16 mt + g (+ 8), c = 16 ks + 2 t (+ 8)
+      const uint32_t* wp = reinterpret_cast<const uint32_t*>(wk + (long)k * NR * 64);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint4 wv[4];
+      for (int mt = 0; mt < 4; ++mt) {
+        float tmp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int q = 0; q < 4; ++q) wv[q] = __ldg(wr + half * 4 + q);
-          for (int i = 0; i < nb; ++i) {
-            const float4* xv = reinterpret_cast<const float4*>(xs[y][i]) + half * 8;
-            float p0 = 0.f, p1 = 0.f;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float4 xa = xv[2 * q], xb = xv[2 * q + 1];
-              p0 = fmaf(__uint_as_float(wv[q].x << 16), xa.x, p0);
-              p0 = fmaf(__uint_as_float(wv[q].x & 0xFFFF0000u), xa.y, p0);
-              p0 = fmaf(__uint_as_float(wv[q].y << 16), xa.z, p0);
-              p0 = fmaf(__uint_as_float(wv[q].y & 0xFFFF0000u), xa.w, p0);
-              p1 = fmaf(__uint_as_float(wv[q].z << 16), xb.x, p1);
-              p1 = fmaf(__uint_as_float(wv[q].z & 0xFFFF0000u), xb.y, p1);
-              p1 = fmaf(__uint_as_float(wv[q].w << 16), xb.z, p1);
-              p1 = fmaf(__uint_as_float(wv[q].w & 0xFFFF0000u), xb.w, p1);
-            }
-            const float part = we * (p0 + p1);
-#pragma unroll
-            for (int j = 0; j < FIX_IMGS; ++j)
-              if (j == i) acc[j] += part;
-          }
+        for (int ks = 0; ks < 4; ++ks) {
+          uint32_t afr[4];
+          afr[0] = __ldg(wp + (mt * 16 + g) * 32 + ks * 8 + t);
+          afr[1] = __ldg(wp + (mt * 16 + g + 8) * 32 + ks * 8 + t);
+          afr[2] = __ldg(wp + (mt * 16 + g) * 32 + ks * 8 + t + 4);
+          afr[3] = __ldg(wp + (mt * 16 + g + 8) * 32 + ks * 8 + t + 4);
+          mma_m16n8k16_bf16(tmp, afr, bfr[ks]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][i] = fmaf(dw, tmp[i], acc[mt][i]);
       }
-      __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < FIX_IMGS; ++i) total[y][i][n] = acc[i];
-    __syncthreads();
-    if (y < nb) {  // warp pair y adds up image y, in a fixed order: results repeat bit for bit
-      float sum = total[0][y][n];
+    for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
-      for (int l = 1; l < FIX_LANES; ++l) sum += total[l][y][n];
-      bf16* rp = res + ((((long)(b0 + y)) * RH + row) * RW + col) * NR + n;
-      *rp = __float2bfloat16_rn(__bfloat162float(*rp) + sum);
+      for (int i = 0; i < 4; ++i) red[warp][mt][i][lane] = acc[mt][i];
+    __syncthreads();
+    {
+      // warp w finishes m-tile w: D[n][image], n = 16 w + g (+ 8 for registers 2, 3), image = 2 t (+ 1)
+      const int mt = warp;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float sum = red[0][mt][i][lane];
+#pragma unroll
+        for (int w = 1; w < FIX_WARPS; ++w) sum += red[w][mt][i][lane];
+        const int n = mt * 16 + g + (i >> 1) * 8, b = b0 + 2 * t + (i & 1);
+        if (b < B) {
+          bf16* rp = res + (((long)b * RH + row) * RW + col) * NR + n;
+          *rp = __float2bfloat16_rn(__bfloat162float(*rp) + sum);
+        }
+      }
     }
     __syncthreads();
   }
@@ -1514,7 +1520,7 @@ int rowinv_conv_launch(const mc_desc* d, int dir, const void* src, const void* p
   int rc = rowinv_launch_n<128>(a, st);
   if (rc) return rc;
   if (D.ngroup > 0) {
-    rowinv_fix_kernel<<<D.ngroup, dim3(64, FIX_LANES), 0, st>>>((const bf16*)src, (bf16*)res, wk, plan, D, d->B,
+    rowinv_fix_kernel<<<D.ngroup, 32 * FIX_WARPS, 0, st>>>((const bf16*)src, (bf16*)res, wk, plan, D, d->B,
                                                                 a.SH, a.SW, a.RH, a.RW, 64), MC_COUNT(1);
     MC_CHECK_LAUNCH();
   }
