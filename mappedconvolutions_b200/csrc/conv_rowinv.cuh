@@ -1332,24 +1332,29 @@ __global__ void __launch_bounds__(256, 2) rowinv_wgrad_reduce_kernel(const float
 // The planner's corrections in the weight gradient:
 // P2[k][y][ci][co] = sum_b dw gy[b, row, col, co] x[b, srow, scol, ci] over the corrections with tap k
 // in chunk y.  blockIdx.x = tap, blockIdx.y = chunk: the block first lists the corrections of its chunk
-// that belong to its tap (in order), then walks the list; thread = co x 4 groups of 16 ci, eight
-// images in flight.
-constexpr int WGF_LIST = 256;
-__global__ void __launch_bounds__(256) rowinv_wgrad_fix_kernel(const bf16* __restrict__ x,
+// that belong to its tap (in order), then walks the list.  Per correction that is a 64 x B by B x 64
+// product: warp w holds the 16 co x 64 ci block w of the result and issues 8 m16n8k16 MMAs per 16
+// images (k = image).
+constexpr int WGF_LIST = 128;
+__global__ void __launch_bounds__(128) rowinv_wgrad_fix_kernel(const bf16* __restrict__ x,
                                                                const bf16* __restrict__ gy,
                                                                const int* __restrict__ plan, RiDir d,
                                                                int B, int SH, int SW, int RH, int RW,
                                                                float* __restrict__ P2) {
   __shared__ int s_list[WGF_LIST];
-  __shared__ int s_cnt[9];
+  __shared__ int s_cnt[5];
   const int k = blockIdx.x;
   const int per = (d.nskip + gridDim.y - 1) / gridDim.y;
   const int e0 = blockIdx.y * per, e1 = min(d.nskip, e0 + per);
-  const int co = threadIdx.x & 63, cg = threadIdx.x >> 6;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float acc[16];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const unsigned short* gy16 = reinterpret_cast<const unsigned short*>(gy);
+  const unsigned short* x16 = reinterpret_cast<const unsigned short*>(x);
+  const long gy_img = (long)RH * RW * 64, x_img = (long)SH * SW * 64;
+  float acc[8][4];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
   for (int base = e0; base < e1; base += WGF_LIST) {
     // ordered compaction of the entries with this block's tap
     const int e = base + threadIdx.x;
@@ -1359,47 +1364,55 @@ __global__ void __launch_bounds__(256) rowinv_wgrad_fix_kernel(const bf16* __res
     __syncthreads();
     if (threadIdx.x == 0) {
       s_cnt[0] = 0;
-      for (int w = 0; w < 8; ++w) s_cnt[w + 1] += s_cnt[w];
+      for (int w = 0; w < 4; ++w) s_cnt[w + 1] += s_cnt[w];
     }
     __syncthreads();
     if (hit) s_list[s_cnt[warp] + __popc(m & ((1u << lane) - 1))] = e;
     __syncthreads();
-    const int n = s_cnt[8];
+    const int n = s_cnt[4];
     for (int i = 0; i < n; ++i) {
       const int* ent = plan + d.off_skip + 6 * s_list[i];
       const int row = __ldg(ent), col = __ldg(ent + 1), srow = __ldg(ent + 2), scol = __ldg(ent + 3);
       const float dw = __int_as_float(__ldg(ent + 5));
-      const bf16* gp = gy + ((long)row * RW + col) * 64 + co;
-      const bf16* xq = x + ((long)srow * SW + scol) * 64 + cg * 16;
-      for (int b0 = 0; b0 < B; b0 += 8) {
-        float g[8];
-        uint4 v[8][2];
+      const unsigned short* gp = gy16 + ((long)row * RW + col) * 64 + warp * 16 + g;  // co = 16 w + g (+ 8)
+      const unsigned short* xq = x16 + ((long)srow * SW + scol) * 64 + g;            // ci = 8 nt + g
+      for (int b0 = 0; b0 < B; b0 += 16) {
+        // images b0 + 2 t, + 1 (fragment registers 0, 1) and b0 + 2 t + 8, + 9 (registers 2, 3 / 1)
+        const int ba = b0 + 2 * t;
+        const bool v0 = ba < B, v1 = ba + 1 < B, v2 = ba + 8 < B, v3 = ba + 9 < B;
+        auto pair = [](const unsigned short* p, long s0, bool on0, long s1, bool on1) -> uint32_t {
+          const uint32_t lo = on0 ? (uint32_t)__ldg(p + s0) : 0u, hi = on1 ? (uint32_t)__ldg(p + s1) : 0u;
+          return lo | (hi << 16);
+        };
+        uint32_t afr[4];
+        afr[0] = pair(gp, ba * gy_img, v0, (ba + 1) * gy_img, v1);
+        afr[1] = pair(gp + 8, ba * gy_img, v0, (ba + 1) * gy_img, v1);
+        afr[2] = pair(gp, (ba + 8) * gy_img, v2, (ba + 9) * gy_img, v3);
+        afr[3] = pair(gp + 8, (ba + 8) * gy_img, v2, (ba + 9) * gy_img, v3);
+        uint32_t bfr[8][2];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int b = min(b0 + j, B - 1);
-          g[j] = b0 + j < B ? dw * __bfloat162float(gp[(long)b * RH * RW * 64]) : 0.f;
-          const uint4* xp = reinterpret_cast<const uint4*>(xq + (long)b * SH * SW * 64);
-          v[j][0] = __ldg(xp);
-          v[j][1] = __ldg(xp + 1);
+        for (int nt = 0; nt < 8; ++nt) {
+          bfr[nt][0] = pair(xq + nt * 8, ba * x_img, v0, (ba + 1) * x_img, v1);
+          bfr[nt][1] = pair(xq + nt * 8, (ba + 8) * x_img, v2, (ba + 9) * x_img, v3);
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int nt = 0; nt < 8; ++nt) {
+          float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+          mma_m16n8k16_bf16(tmp, afr, bfr[nt]);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint32_t p4[4] = {v[j][h].x, v[j][h].y, v[j][h].z, v[j][h].w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              acc[h * 8 + 2 * q] = fmaf(g[j], __uint_as_float(p4[q] << 16), acc[h * 8 + 2 * q]);
-              acc[h * 8 + 2 * q + 1] = fmaf(g[j], __uint_as_float(p4[q] & 0xFFFF0000u), acc[h * 8 + 2 * q + 1]);
-            }
-          }
+          for (int j = 0; j < 4; ++j) acc[nt][j] = fmaf(dw, tmp[j], acc[nt][j]);
+        }
       }
     }
     __syncthreads();
   }
+  // D[co][ci]: co = 16 w + g (+ 8 for registers 2, 3), ci = 8 nt + 2 t (+ 1 for registers 1, 3)
   float* out = P2 + ((size_t)k * gridDim.y + blockIdx.y) * 4096;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) out[(cg * 16 + i) * 64 + co] = acc[i];
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      out[(nt * 8 + 2 * t + (j & 1)) * 64 + warp * 16 + g + (j >> 1) * 8] = acc[nt][j];
 }
 
 // gw[co][ci][k] = sum_y P1[y][k][ci][co] + sum_y P2[k][y][ci][co].  blockIdx.x = tap, blockIdx.y = 64
@@ -1598,7 +1611,7 @@ int rowinv_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const v
   }
   const int Y2 = D.nskip > 0 ? WGF_CHUNKS : 0;
   if (Y2 > 0)
-    rowinv_wgrad_fix_kernel<<<dim3(d->K, Y2), 256, 0, st>>>((const bf16*)x, (const bf16*)gy, plan, D, d->B,
+    rowinv_wgrad_fix_kernel<<<dim3(d->K, Y2), 128, 0, st>>>((const bf16*)x, (const bf16*)gy, plan, D, d->B,
                                                             d->IH, d->IW, d->OH, d->OW, P2), MC_COUNT(1);
   rowinv_wgrad_final_kernel<<<dim3(d->K, 64), 256, 0, st>>>(P1, Y1, P2, Y2, d->K, d->C_in, (float*)gw),
       MC_COUNT(1);
