@@ -73,7 +73,8 @@ def run_wgrad(d, gy, x, plan):
 
 
 @pytest.mark.parametrize("wrapped,interp,Hh,Ww,B", [(True, 1, 12, 512, 2), (False, 1, 9, 512, 3),
-                                                  (True, 2, 7, 1024, 1), (False, 2, 5, 512, 2)])
+                                                  (True, 2, 7, 1024, 1), (False, 2, 5, 512, 2),
+                                                  (True, 1, 3, 512, 19)])  # more images than one MMA pass of the corrections takes
 def test_rowplan_forward_and_input_gradient(wrapped, interp, Hh, Ww, B):
     from mappedconvolutions_b200 import _lib
     C, K = 64, 9
