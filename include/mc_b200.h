@@ -17,7 +17,16 @@
  *    map (OH, OW, K, [P,] 2) with (x, y) pairs, weights (OH, OW, K, P); their scalar type is
  *    double when dtype == MC_F64 and float otherwise (also for MC_BF16 activations);
  *  - interp: 0 nearest, 1 bilinear, 2 bispherical (x wraps), any other value = nearest
- *    (include/core/resample.h:45-58).
+ *    (include/core/resample.h:45-58);
+ *  - alignment: the bf16 tensor-core paths (MC_BF16 + MC_NHWC, C_out % 64 == 0, every *_tap, *_inv and
+ *    *_rowplan entry point, mc_conv_fwd_static_scratch) move 16 bytes at a time and return
+ *    MC_ERR_BAD_ARG for a tensor, map, table or workspace pointer that is not 16-byte aligned; the
+ *    generic kernels take any element-aligned pointer;
+ *  - finite inputs: the bf16 tensor-core kernels gather without predicates - a corner or tap that
+ *    contributes nothing still reads a real pixel (pixel 0 of the image for a tap that lies outside
+ *    it completely) and multiplies it by zero.  The reference skips such corners
+ *    (include/core/interpolation.h:125-154); results agree for finite inputs, a NaN or infinity
+ *    in such a pixel reaches the output here.
  */
 #ifndef MC_B200_H_
 #define MC_B200_H_

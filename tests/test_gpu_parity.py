@@ -526,3 +526,23 @@ def test_knn_equals_the_reference_cuda_kernels(name, op_binding):
     idx, dist = ops.knn_forward(c["ref"].cuda(), c["query"].cuda(), int(c["k"]))
     assert torch.equal(idx.cpu(), c["idx"])
     assert torch.equal(dist.cpu(), c["dist"])
+
+
+def test_tensor_core_kernels_on_a_second_device(op_binding):
+    """Shared-memory opt-in, SM count and the static scratch address are properties of a device, not
+    of the process: after a call on device 0 the same process must be able to run the tensor-core
+    kernels on device 1 (plain local kernels, no peer memory)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    from mappedconvolutions_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    Hh, Ww, K = 8, 16, 4
+    x = torch.randn(1, 64, Hh, Ww, generator=g).to(torch.bfloat16)
+    m = torch.rand(Hh, Ww, K, 2, generator=g) * torch.tensor([Ww - 1.0, Hh - 1.0])
+    w, b = torch.randn(64, 64, K, generator=g).to(torch.bfloat16), torch.randn(64, generator=g).to(torch.bfloat16)
+    want = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, 1)
+    for dev in ("cuda:0", "cuda:1", "cuda:0"):
+        with torch.cuda.device(dev):
+            xd = x.to(dev).contiguous(memory_format=torch.channels_last)
+            y = ops.mapped_conv_forward(xd, m.to(dev), w.to(dev), b.to(dev), K, 1)
+            H.assert_close(y.float().cpu(), want, 2e-2, "forward on " + dev)
