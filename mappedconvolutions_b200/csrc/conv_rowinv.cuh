@@ -46,6 +46,8 @@
 // This header is part of conv_tc.cu's translation unit (one device status word, shared helpers).
 #pragma once
 
+#include <cuda.h>  // CUtensorMap (types only: the driver entry point is looked up at run time)
+
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -485,6 +487,48 @@ __global__ void __launch_bounds__(256) rowinv_weights_kernel(const bf16* __restr
   }
 }
 
+// ---- tensor map of the gathered tensor ---------------------------------------------------------------
+// The windows of the forward / input-gradient kernel are fetched by the TMA unit: boxes of RI_BOX
+// consecutive pixels of one image row, 64 channels each, written in the 128-byte swizzle the MMA
+// operand wants.  (B * H, W, 64) view: a box that sticks out of the row's W pixels is filled with
+// zeros there - exactly what a clipped window needs; the one box of a wrapped window that contains
+// the seam is copied by cp.async instead.  Against cp.async for everything this takes the copies
+// off the load/store path that the accumulator read-out's shared-memory traffic shares with them
+// (measured: 50-60 cycles per shared-memory instruction of the read-out while cp.async bursts ran).
+constexpr int RI_BOX = 32;
+static bool ri_make_tensor_map(CUtensorMap* tm, const void* base, long rows, int W) {
+  static std::atomic<void*> fn{nullptr};
+  void* f = fn.load(std::memory_order_acquire);
+  if (!f) {
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !f)
+      return false;
+    fn.store(f, std::memory_order_release);
+  }
+  using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+  const cuuint64_t dims[3] = {64, (cuuint64_t)W, (cuuint64_t)rows};
+  const cuuint64_t strides[2] = {128, (cuuint64_t)W * 128};  // bytes, dimensions 1 and 2
+  const cuuint32_t box[3] = {64, RI_BOX, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return ((Encode)f)(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// One box: pixels [col, col + RI_BOX) of row `row` (col may be negative or reach past the row: zeros).
+// The innermost coordinate (channel) is 0, as the 16-byte rule for it asks.
+__device__ __forceinline__ void tma_load_box(uint32_t dst_smem, const CUtensorMap* tm, int col, int row,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      :
+      : "r"(dst_smem), "l"((uint64_t)tm), "r"(0), "r"(col), "r"(row), "r"(bar)
+      : "memory");
+}
+
 // ---- main kernel: forward / input gradient ---------------------------------------------------------
 struct RowInvArgs {
   const bf16* src;   // (B, SH, SW, 64) channels-last
@@ -549,7 +593,8 @@ struct RiCfg {
 };
 
 template <int NOUT>
-__global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const RowInvArgs a) {
+__global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const RowInvArgs a,
+                                                                       const __grid_constant__ CUtensorMap tmap) {
   using Cfg = RiCfg<NOUT>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -579,7 +624,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) { mbar_init(cfull(i), 1); mbar_init(cempty(i), RI_ISSUERS); }
-    for (int s = 0; s < RI_WIN_STAGES; ++s) { mbar_init(wfull(s), RI_LOADER_WARPS / RI_WIN_STAGES); mbar_init(wempty(s), RI_ISSUERS); }
+    for (int s = 0; s < RI_WIN_STAGES; ++s) { mbar_init(wfull(s), 1); mbar_init(wempty(s), RI_ISSUERS); }
     for (int s = 0; s < Cfg::NE; ++s) { mbar_init(efull(s), 1); mbar_init(eempty(s), RI_ISSUERS); }
     for (int i = 0; i < 2; ++i) { mbar_init(tfull(i), RI_ISSUERS); mbar_init(tempty(i), RI_EPI_WARPS); }
     mbar_init(drain_bar0, 1);
@@ -789,56 +834,65 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_tc_kernel(const Row
     }
   } else if (warp >= FIRST_PROD_WARP && warp < RI_EPI2_FIRST) {
     // ------------------------------------------------------------------ window loaders
-    // Two teams of six warps; team t copies the windows t, t + 2, ... of the CTA's window sequence
-    // into stage t, so that two windows are in flight at any time: a team sends the arrival for its
-    // window once the copies have landed and then waits for its stage to come free again, while the
-    // other team's copies are under way.
-    constexpr int TEAM_WARPS = RI_LOADER_WARPS / RI_WIN_STAGES;
-    const int team = (warp - FIRST_PROD_WARP) / TEAM_WARPS;
-    const int ptid = ((warp - FIRST_PROD_WARP) % TEAM_WARPS) * 32 + lane;
-    constexpr int NPT = TEAM_WARPS * 32;
-    uint32_t nw = 0;   // windows of this CTA so far (both teams count all of them)
-    uint32_t mine = 0; // windows this team has copied
-    bool ok = true;
-    for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x) {
-      int r, b, x0;
-      ri_unit(a, u, r, b, x0);
-      const int w0 = __ldg(plan + a.d.off_row + r), w1 = __ldg(plan + a.d.off_row + r + 1);
-      for (int w = w0; w < w1; ++w, ++nw) {
-        if ((int)(nw % RI_WIN_STAGES) != team) continue;
-        const int4 wr = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w);
-        const uint32_t ws = team, wph = mine & 1;
-        int okw = 1;
-        if (lane == 0) okw = mbar_wait_spin(wempty(ws), wph ^ 1, abort_flag, 0x87) ? 1 : 0;
-        okw = __shfl_sync(0xffffffffu, okw, 0);
-        if (!okw) { ok = false; break; }
-        const int span = (wr.w >> 8) & 0xFF, mode = wr.w >> 16;
-        const bf16* rowp = a.src + ((long)b * a.SH + wr.x) * a.SW * 64;
-        const uint32_t sbase = win0 + ws * Cfg::WIN_BYTES;
-        // thread -> 16-byte chunk lg of rows j0, j0 + NPT / 8, ...; the source column advances with
-        // the row and is wrapped (or clipped) by one compare per step instead of a division
-        const int lg = ptid & 7, j0 = ptid >> 3;
-        constexpr int JSTEP = NPT / 8;
-        int sx = x0 + wr.y + j0;
-        if (mode == RI_MODE_WRAP) { sx %= a.SW; if (sx < 0) sx += a.SW; }
-        const int nrows = Cfg::TPU * TILE_M + span;
-        const bf16* colp = rowp + lg * 8;
-        uint32_t dst = sbase + j0 * 128;
-        for (int j = j0; j < nrows; j += JSTEP) {
-          bool valid = true;
-          int scol = sx;
-          if (mode != RI_MODE_WRAP) { valid = sx >= 0 && sx < a.SW; if (!valid) scol = 0; }
-          cp_async16(dst + ((lg ^ (j & 7)) << 4), colp + (long)scol * 64, valid ? 16u : 0u);
-          dst += JSTEP * 128;
-          sx += JSTEP;
-          if (mode == RI_MODE_WRAP) { while (sx >= a.SW) sx -= a.SW; }
+    // One warp per window stage (warp t copies the windows t, t + 2, ... of the block's window
+    // sequence into stage t: a stage is always filled by the same warp, so a parity wait on its
+    // barrier is unambiguous).  Lane 0 issues one TMA box per RI_BOX pixels; the box of a wrapped
+    // window that contains the seam is copied by the warp with cp.async.  The stage's barrier gets
+    // ONE arrival - after the warp's own copies have landed - which also announces the TMA bytes.
+    const int team = warp - FIRST_PROD_WARP;
+    if (team < RI_WIN_STAGES) {
+      uint32_t nw = 0;   // windows of this block so far (every loader warp counts all of them)
+      uint32_t mine = 0; // windows this warp has copied
+      bool ok = true;
+      for (long u = blockIdx.x; u < a.units && ok; u += gridDim.x) {
+        int r, b, x0;
+        ri_unit(a, u, r, b, x0);
+        const int w0 = __ldg(plan + a.d.off_row + r), w1 = __ldg(plan + a.d.off_row + r + 1);
+        for (int w = w0; w < w1; ++w, ++nw) {
+          if ((int)(nw % RI_WIN_STAGES) != team) continue;
+          const int4 wr = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + w);
+          const uint32_t ws = team, wph = mine & 1;
+          int okw = 1;
+          if (lane == 0) okw = mbar_wait_spin(wempty(ws), wph ^ 1, abort_flag, 0x87) ? 1 : 0;
+          okw = __shfl_sync(0xffffffffu, okw, 0);
+          if (!okw) { ok = false; break; }
+          const int span = (wr.w >> 8) & 0xFF, mode = wr.w >> 16;
+          const int srow = b * a.SH + wr.x;
+          const uint32_t sbase = win0 + ws * Cfg::WIN_BYTES;
+          const int nbox = (Cfg::TPU * TILE_M + span + RI_BOX - 1) / RI_BOX;
+          int c = x0 + wr.y;  // source column of the window's first pixel
+          if (mode == RI_MODE_WRAP) { c %= a.SW; if (c < 0) c += a.SW; }
+          uint32_t tma_bytes = 0;
+          bool seam = false;
+          for (int k = 0; k < nbox; ++k) {
+            if (mode == RI_MODE_WRAP && c + RI_BOX > a.SW) {
+              // the seam: pixel c + lane, wrapped; lane = row of the box, eight 16-byte chunks each
+              int sc = c + lane;
+              if (sc >= a.SW) sc -= a.SW;
+              const bf16* sp = a.src + ((long)srow * a.SW + sc) * 64;
+              const uint32_t dst = sbase + (uint32_t)(k * RI_BOX + lane) * 128u;
+#pragma unroll
+              for (int ch = 0; ch < 8; ++ch) cp_async16(dst + ((ch ^ (lane & 7)) << 4), sp + ch * 8, 16u);
+              seam = true;
+            } else {
+              if (lane == 0) tma_load_box(sbase + (uint32_t)k * (RI_BOX * 128), &tmap, c, srow, wfull(ws));
+              tma_bytes += RI_BOX * 128;
+            }
+            c += RI_BOX;
+            if (mode == RI_MODE_WRAP && c >= a.SW) c -= a.SW;
+          }
+          if (seam) {
+            cp_async_commit();
+            cp_async_wait_all();
+            fence_proxy_async_smem();
+          }
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(wfull(ws)), "r"(tma_bytes)
+                         : "memory");
+          }
+          ++mine;
         }
-        cp_async_commit();
-        cp_async_wait_all();
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(wfull(ws));
-        ++mine;
       }
     }
   }
@@ -1450,9 +1504,12 @@ template <int NOUT>
 static int rowinv_launch_n(const RowInvArgs& a, cudaStream_t st) {
   using Cfg = RiCfg<NOUT>;
   static_assert(Cfg::SMEM <= SMEM_LIMIT, "row-invariant kernel does not fit shared memory");
+  static_assert(Cfg::WIN_BYTES % (RI_BOX * 128) == 0 && (Cfg::TPU * TILE_M + RI_SPAN) % RI_BOX == 0, "window boxes");
   if (!allow_big_smem(conv_rowinv_tc_kernel<NOUT>)) return MC_ERR_LAUNCH;
+  CUtensorMap tmap;
+  if (!ri_make_tensor_map(&tmap, a.src, (long)a.B * a.SH, a.SW)) return MC_ERR_LAUNCH;
   const long g = a.units < sm_count() ? a.units : sm_count();
-  conv_rowinv_tc_kernel<NOUT><<<(int)g, TC_THREADS, Cfg::SMEM, st>>>(a), MC_COUNT(1);
+  conv_rowinv_tc_kernel<NOUT><<<(int)g, TC_THREADS, Cfg::SMEM, st>>>(a, tmap), MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
