@@ -1025,7 +1025,9 @@ struct RowInvWgArgs {
   long units;       // nwgunit * bsplit
 };
 
-__global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const RowInvWgArgs a) {
+__global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const RowInvWgArgs a,
+                                                                         const __grid_constant__ CUtensorMap tmap_x,
+                                                                         const __grid_constant__ CUtensorMap tmap_gy) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t win0 = smem_u32(sm);
@@ -1056,8 +1058,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
   const int bper = (a.B + a.bsplit - 1) / a.bsplit;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < WG_NW; ++s) { mbar_init(wfull(s), TEAM_WARPS); mbar_init(wempty(s), WG_ISSUERS); }
-    for (int s = 0; s < WG_NG; ++s) { mbar_init(gfull(s), TEAM_WARPS); mbar_init(gempty(s), WG_ISSUERS + N_EPI_WARPS); }
+    for (int s = 0; s < WG_NW; ++s) { mbar_init(wfull(s), 1); mbar_init(wempty(s), WG_ISSUERS); }
+    for (int s = 0; s < WG_NG; ++s) { mbar_init(gfull(s), 1); mbar_init(gempty(s), WG_ISSUERS + N_EPI_WARPS); }
     mbar_init(accfull, WG_ISSUERS);
     mbar_init(accempty, N_EPI_WARPS);
     mbar_init(accfull + 16u, 1);
@@ -1242,68 +1244,79 @@ __global__ void __launch_bounds__(TC_THREADS, 1) conv_rowinv_wgrad_kernel(const 
     }
   } else if (warp >= FIRST_PROD_WARP) {
     // ------------------------------------------------------------------ loaders
-    // Items in the order the MMA thread consumes them: per (image, chunk) the gy chunk, then the
-    // unit's windows.  Two teams of eight warps work side by side, so two copies are in flight.  A
-    // ring stage is always filled by the same team (stage index modulo 2): a team waits for its
-    // stages in order, so it can never be more than one phase ahead of the consumer - which is what a
-    // parity wait needs to be unambiguous.
-    const int team = (warp - FIRST_PROD_WARP) / TEAM_WARPS;
-    const int ptid = ((warp - FIRST_PROD_WARP) % TEAM_WARPS) * 32 + lane;
-    constexpr int NPT = TEAM_WARPS * 32, JSTEP = NPT / 8;
-    const int lg = ptid & 7, j0 = ptid >> 3;
-    uint32_t nw = 0, ng = 0, it = 0;
-    bool ok = true;
-    auto finish = [&](uint32_t bar) {
-      cp_async_commit();
-      cp_async_wait_all();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar);
-    };
-    auto wait_empty = [&](uint32_t bar, uint32_t parity, int code) {
-      int okw = 1;
-      if (lane == 0) okw = mbar_wait(bar, parity, abort_flag, code) ? 1 : 0;
-      return __shfl_sync(0xffffffffu, okw, 0) != 0;
-    };
-    for (long u; ok && (u = unit_at(it)) >= 0; ++it) {
-      int part;
-      const int4 ur = unit_rec(u, part);
-      const int b0 = part * bper, b1 = min(a.B, b0 + bper);
-      for (int b = b0; b < b1 && ok; ++b) {
-        for (int ch = 0; ch < nchunk && ok; ++ch) {
-          const int x0 = ch * WG_TILES * TILE_M;
-          if ((int)(ng % TEAMS) == team) {  // the gy chunk
-            const uint32_t gs = ng % WG_NG, gph = (ng / WG_NG) & 1;
-            if (!wait_empty(gempty(gs), gph ^ 1, 0x96)) { ok = false; break; }
-            const bf16* gp = a.gy + (((long)b * a.RH + ur.x) * a.RW + x0) * 64 + lg * 8;
-            const uint32_t dst = gy0 + gs * WG_GY_BYTES;
-            for (int j = j0; j < WG_TILES * TILE_M; j += JSTEP)
-              cp_async16(dst + j * 128 + ((lg ^ (j & 7)) << 4), gp + (long)j * 64, 16u);
-            finish(gfull(gs));
-          }
-          ++ng;
-          for (int w = 0; w < ur.z; ++w, ++nw) {
-            if ((int)(nw % TEAMS) != team) continue;
-            const int4 wr = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + ur.y + w);
-            const uint32_t ws = nw % WG_NW, wph = (nw / WG_NW) & 1;
-            if (!wait_empty(wempty(ws), wph ^ 1, 0x97)) {
-              ok = false; break; }
-            const int span = (wr.w >> 8) & 0xFF, mode = wr.w >> 16;
-            const bf16* colp = a.x + ((long)b * a.SH + wr.x) * a.SW * 64 + lg * 8;
-            int sx = x0 + wr.y + j0;
-            if (mode == RI_MODE_WRAP) { sx %= a.SW; if (sx < 0) sx += a.SW; }
-            const int nrows = WG_TILES * TILE_M + span;
-            uint32_t dst = win0 + ws * WG_WIN_BYTES + j0 * 128;
-            for (int j = j0; j < nrows; j += JSTEP) {
-              bool valid = true;
-              int scol = sx;
-              if (mode != RI_MODE_WRAP) { valid = sx >= 0 && sx < a.SW; if (!valid) scol = 0; }
-              cp_async16(dst + ((lg ^ (j & 7)) << 4), colp + (long)scol * 64, valid ? 16u : 0u);
-              dst += JSTEP * 128;
-              sx += JSTEP;
-              if (mode == RI_MODE_WRAP) { while (sx >= a.SW) sx -= a.SW; }
+    // Items in the order the MMA threads consume them: per (image, chunk) the gy chunk, then the
+    // unit's windows, fetched by the TMA unit in boxes of RI_BOX pixels (the seam box of a wrapped
+    // window by cp.async).  Two warps work side by side, so two items are in flight.  A ring stage is
+    // always filled by the same warp (stage index modulo 2): a warp waits for its stages in order, so
+    // it can never be more than one phase ahead of the consumer - which is what a parity wait needs
+    // to be unambiguous.  A stage's barrier gets one arrival, which also announces the TMA bytes.
+    const int team = warp - FIRST_PROD_WARP;
+    if (team < TEAMS) {
+      uint32_t nw = 0, ng = 0, it = 0;
+      bool ok = true;
+      auto announce = [&](uint32_t bar, uint32_t bytes) {
+        __syncwarp();
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+      };
+      auto wait_empty = [&](uint32_t bar, uint32_t parity, int code) {
+        int okw = 1;
+        if (lane == 0) okw = mbar_wait(bar, parity, abort_flag, code) ? 1 : 0;
+        return __shfl_sync(0xffffffffu, okw, 0) != 0;
+      };
+      for (long u; ok && (u = unit_at(it)) >= 0; ++it) {
+        int part;
+        const int4 ur = unit_rec(u, part);
+        const int b0 = part * bper, b1 = min(a.B, b0 + bper);
+        for (int b = b0; b < b1 && ok; ++b) {
+          for (int ch = 0; ch < nchunk && ok; ++ch) {
+            const int x0 = ch * WG_TILES * TILE_M;
+            if ((int)(ng % TEAMS) == team) {  // the gy chunk
+              const uint32_t gs = ng % WG_NG, gph = (ng / WG_NG) & 1;
+              if (!wait_empty(gempty(gs), gph ^ 1, 0x96)) { ok = false; break; }
+              const uint32_t dst = gy0 + gs * WG_GY_BYTES;
+              if (lane == 0)
+                for (int k = 0; k < WG_TILES * TILE_M / RI_BOX; ++k)
+                  tma_load_box(dst + (uint32_t)k * (RI_BOX * 128), &tmap_gy, x0 + k * RI_BOX, b * a.RH + ur.x, gfull(gs));
+              announce(gfull(gs), WG_GY_BYTES);
             }
-            finish(wfull(ws));
+            ++ng;
+            for (int w = 0; w < ur.z; ++w, ++nw) {
+              if ((int)(nw % TEAMS) != team) continue;
+              const int4 wr = __ldg(reinterpret_cast<const int4*>(plan + a.d.off_win) + ur.y + w);
+              const uint32_t ws = nw % WG_NW, wph = (nw / WG_NW) & 1;
+              if (!wait_empty(wempty(ws), wph ^ 1, 0x97)) { ok = false; break; }
+              const int span = (wr.w >> 8) & 0xFF, mode = wr.w >> 16;
+              const int srow = b * a.SH + wr.x;
+              const uint32_t sbase = win0 + ws * WG_WIN_BYTES;
+              const int nbox = (WG_TILES * TILE_M + span + RI_BOX - 1) / RI_BOX;
+              int c = x0 + wr.y;  // source column of the window's first pixel
+              if (mode == RI_MODE_WRAP) { c %= a.SW; if (c < 0) c += a.SW; }
+              uint32_t tma_bytes = 0;
+              bool seam = false;
+              for (int k = 0; k < nbox; ++k) {
+                if (mode == RI_MODE_WRAP && c + RI_BOX > a.SW) {
+                  int sc = c + lane;  // the seam: lane = row of the box
+                  if (sc >= a.SW) sc -= a.SW;
+                  const bf16* sp = a.x + ((long)srow * a.SW + sc) * 64;
+                  const uint32_t dst = sbase + (uint32_t)(k * RI_BOX + lane) * 128u;
+#pragma unroll
+                  for (int cc = 0; cc < 8; ++cc) cp_async16(dst + ((cc ^ (lane & 7)) << 4), sp + cc * 8, 16u);
+                  seam = true;
+                } else {
+                  if (lane == 0) tma_load_box(sbase + (uint32_t)k * (RI_BOX * 128), &tmap_x, c, srow, wfull(ws));
+                  tma_bytes += RI_BOX * 128;
+                }
+                c += RI_BOX;
+                if (mode == RI_MODE_WRAP && c >= a.SW) c -= a.SW;
+              }
+              if (seam) {
+                cp_async_commit();
+                cp_async_wait_all();
+                fence_proxy_async_smem();
+              }
+              announce(wfull(ws), tma_bytes);
+            }
           }
         }
       }
@@ -1661,7 +1674,11 @@ int rowinv_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const v
     a.units = (long)D.nwgunit * a.bsplit;
     if (!allow_big_smem(conv_rowinv_wgrad_kernel)) return MC_ERR_LAUNCH;
     const long g = a.units < sm_count() ? a.units : sm_count();
-    conv_rowinv_wgrad_kernel<<<(int)g, TC_THREADS, WG_SMEM, st>>>(a), MC_COUNT(1);
+    CUtensorMap tmap_x, tmap_gy;
+    if (!ri_make_tensor_map(&tmap_x, x, (long)d->B * d->IH, d->IW) ||
+        !ri_make_tensor_map(&tmap_gy, gy, (long)d->B * d->OH, d->OW))
+      return MC_ERR_LAUNCH;
+    conv_rowinv_wgrad_kernel<<<(int)g, TC_THREADS, WG_SMEM, st>>>(a, tmap_x, tmap_gy), MC_COUNT(1);
     MC_CHECK_LAUNCH();
     if (bsplit == 1) rowinv_wgrad_reduce_launch<1>((const float4*)gE, plan, D, d->K, Y1, (float4*)P1, st);
     else rowinv_wgrad_reduce_launch<WGR_PARTS>((const float4*)gE, plan, D, d->K, Y1, (float4*)P1, st);
