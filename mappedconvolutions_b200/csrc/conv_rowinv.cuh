@@ -11,7 +11,7 @@
 //
 // No interpolation is left in the data path.  The operand of the GEMM is a plain run of source
 // pixels: a WINDOW of 128 * T + span consecutive pixels of source row sy is copied once into
-// shared memory (cp.async, 128-byte swizzle) and serves every slot of that source row and every
+// shared memory (TMA boxes, 128-byte swizzle) and serves every slot of that source row and every
 // one of the T 128-pixel tiles of the unit - a slot only moves the START ADDRESS of the tcgen05
 // operand by dx rows.  The reference interpolates every tap of every pixel
 // (include/nn/common/mapped_im2col.h:12-42) and multiplies a K-times inflated column buffer
@@ -561,8 +561,9 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 constexpr int RI_WIN_STAGES = 2;
 // Warps of the forward / input-gradient kernel: 0 and 7 issue the MMAs, 1-4 and 20-23 read the accumulators
 // out (each set two of a unit's four tiles; a warp reaches the 32 TMEM lanes given by its index
-// modulo 4), 5 streams the effective weights, 6 writes the MMA thread's commands, 8-19 copy windows.
-constexpr int RI_LOADER_WARPS = 12;
+// modulo 4), 5 streams the effective weights, 6 writes the MMA thread's commands, 8 and 9 fetch
+// windows (one warp per stage; 10-19 have no role).
+constexpr int RI_LOADER_WARPS = 12;  // warps between the two read-out sets
 constexpr int RI_ISSUERS = 2, RI_ISSUER2_WARP = FIRST_DEC_WARP + 2;
 constexpr int RI_EPI2_FIRST = FIRST_PROD_WARP + RI_LOADER_WARPS;
 constexpr int RI_EPI_WARPS = 2 * N_EPI_WARPS;
