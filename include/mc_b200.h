@@ -210,7 +210,8 @@ int mc_conv_dgrad_rowplan(const mc_desc* d, const void* gy, const void* plan_hos
                           void* ws, size_t ws_bytes, void* stream);
 /* Weight and bias gradient (float32, fully overwritten; gb may be NULL) from the same plan; ws holds
  * one 64 x 64 float32 partial sum per slot and batch part and the partial results of the two-step
- * reduction that follows (no atomics: results repeat bit for bit). */
+ * reduction that follows (no atomics: gw repeats bit for bit; gb is summed per row inside the main
+ * kernel and added up with float atomics, so it repeats to rounding only). */
 size_t mc_conv_wgrad_rowplan_workspace_bytes(const mc_desc* d, const void* plan_host);
 int mc_conv_wgrad_rowplan(const mc_desc* d, const void* gy, const void* x, const void* plan_host,
                           const void* plan_dev, void* gw, void* gb, void* ws, size_t ws_bytes,
