@@ -121,3 +121,38 @@ def test_rowplan_on_the_gnomonic_map_matches_the_general_kernels():
     H.assert_close(gb, want[2], 2e-2, "bias gradient vs oracle")
     y2 = ops.mapped_conv_forward(cl(x.cuda()), m.cuda(), w.cuda(), b.cuda(), K, 1)
     H.assert_close(y.float(), y2.float(), 2e-2, "forward vs the general kernel")
+
+
+@pytest.mark.parametrize("dead_row", [None, 3])
+def test_rowplan_with_fewer_map_rows_than_image_rows(dead_row):
+    """A map grid with half as many rows as the sampled image (vertical stride 2) and taps that leave
+    the image at the top and bottom: result rows and source rows differ in count in both directions,
+    some source rows are read by no tap of some row pairs, and an odd number of map rows leaves the
+    last pair with one row.  dead_row: a map row whose taps all lie outside the image (its result is
+    the bias, it has no unit in the weight gradient, and the bias gradient then comes from the
+    stand-alone reduction)."""
+    from mappedconvolutions_b200 import _lib
+    IH, OH, Ww, C, K, B = 14, 7, 512, 64, 9, 2
+    g = torch.Generator().manual_seed(5)
+    kx = torch.tensor([-1., 0., 1.]).repeat(3).view(1, 1, 9) * 1.5 + 0.3 * torch.rand(OH, 1, 9, generator=g)
+    ky = torch.tensor([-1., 0., 1.]).repeat_interleave(3).view(1, 1, 9) * 1.2 + 0.3 * torch.rand(OH, 1, 9, generator=g)
+    x_pos = torch.remainder(torch.arange(Ww).view(1, Ww, 1).float() + kx, Ww).expand(OH, Ww, 9)
+    y_pos = (2.0 * torch.arange(OH).view(OH, 1, 1).float() + ky).expand(OH, Ww, 9).clone()   # rows -1.5 .. 13.5
+    if dead_row is not None:
+        y_pos[dead_row] = -10.0
+    m = torch.stack((x_pos, y_pos), -1).contiguous()
+    d = _lib.McDesc(B, C, C, IH, Ww, OH, Ww, K, 0, 1, _lib.MC_BF16, _lib.MC_NHWC)
+    plan = build_plan(d, m.cuda())
+    assert plan is not None
+    bf = torch.bfloat16
+    x, gy = torch.randn(B, C, IH, Ww, generator=g).to(bf), torch.randn(B, C, OH, Ww, generator=g).to(bf)
+    w, b = torch.randn(C, C, K, generator=g).to(bf), torch.randn(C, generator=g).to(bf)
+    y = run(d, 0, cl(x.cuda()), plan, w.cuda(), b.cuda(), (B, C, OH, Ww))
+    gx = run(d, 1, cl(gy.cuda()), plan, w.cuda(), None, (B, C, IH, Ww))
+    gw, gb = run_wgrad(d, cl(gy.cuda()), cl(x.cuda()), plan)
+    want_y = oracle.mapped_conv_forward(x.float(), m, w.float(), b.float(), K, 1)
+    want = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, 1)
+    H.assert_close(y.float(), want_y, 2e-2, "forward vs oracle")
+    H.assert_close(gx.float(), want[0], 2e-2, "input gradient vs oracle")
+    H.assert_close(gw, want[1], 2e-2, "weight gradient vs oracle")
+    H.assert_close(gb, want[2], 2e-2, "bias gradient vs oracle")
