@@ -140,10 +140,42 @@ def _all_host_threads():
     """torchrun pins OMP_NUM_THREADS=1 for its workers; the CPU legs are meant to use every host
     core this process may run on."""
     import torch
+    if _FULL_AFFINITY is not None:  # (undo the NUMA binding of the end-to-end leg)
+        os.sched_setaffinity(0, _FULL_AFFINITY)
     ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     os.environ["OMP_NUM_THREADS"] = str(ncpu)
     torch.set_num_threads(ncpu)
     return ncpu
+
+
+_FULL_AFFINITY = None  # the CPUs this process could run on before bind_to_gpu_numa_node
+
+
+def bind_to_gpu_numa_node(index):
+    """Runs this process on the CPUs of the NUMA node its GPU hangs off, so that the pinned host
+    buffers of the end-to-end leg (first touch) and the copy threads are local to the GPU's PCIe
+    root.  Best effort: returns the node, or None where the platform does not tell."""
+    try:
+        import torch
+        p = torch.cuda.get_device_properties(index)
+        bdf = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/%s/numa_node" % bdf).read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        global _FULL_AFFINITY
+        full = os.sched_getaffinity(0)
+        cpus &= full
+        if cpus:
+            _FULL_AFFINITY = full
+            os.sched_setaffinity(0, cpus)
+            return node
+    except Exception:
+        pass
+    return None
 
 
 def make_inputs(batch, seed):
@@ -244,6 +276,7 @@ def run_ours(args):
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     L = _lib.lib()
@@ -419,7 +452,8 @@ def run_ours(args):
             "config": {"workload": "config2: spherical mapped conv fwd+bwd, equirect 512x1024, batch 8 "
                                    "per GPU, 64->64 ch, K=9 gnomonic map, bilinear, channels-last",
                        "l2": "inputs (537 MB per activation tensor) are larger than L2",
-                       "parallelism": "batch-sharded dp%d, NCCL allreduce of grad_w/grad_b" % world},
+                       "parallelism": "batch-sharded dp%d, NCCL allreduce of grad_w/grad_b" % world,
+                       "numa_node": numa},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e / e2e_steps},
