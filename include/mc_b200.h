@@ -169,6 +169,15 @@ int mc_conv_dgrad_inv_supported(const mc_desc* d);
 size_t mc_conv_dgrad_inv_workspace_bytes(const mc_desc* d);
 int mc_conv_dgrad_inv(const mc_desc* d, const void* gy, const void* inv, const void* w,
                       const void* bias_out, void* gx, void* ws, size_t ws_bytes, void* stream);
+/* The same input gradient with the contraction done first - for layers with more output than input
+ * channels.  The caller computes z (B, OH * OW, K * C_in) = grad_output, read as a (B * OH * OW, C_out)
+ * matrix (channels-last), times the (C_out, K * C_in) matrix W'[co, k * C_in + ci] = w[co, ci, k] - one
+ * dense GEMM, any GEMM routine - and this call sums the C_in-channel rows of z through the inverse map:
+ * gx[b, q, ci] = sum_k sum_{(p, wt) in list(q, k)} wt * z[b, p, k * C_in + ci].  Every row of z is read
+ * exactly once, where mc_conv_dgrad_inv gathers C_out-channel rows of grad_output.  bf16, MC_NHWC,
+ * C_in / 8 a power of two; z is rounded to bf16 once more than in mc_conv_dgrad_inv.
+ * Replaces cuda::MappedConvBackwardInput, src/nn/cuda/mapped_convolution_layer.cu:75-132. */
+int mc_conv_dgrad_tapsum(const mc_desc* d, const void* z, const void* inv, void* gx, void* stream);
 
 /* Row plans: sample maps that are translation invariant along image rows,
  *     map[r, x, k] = (x + cx[r, k], cy[r, k])      (x possibly wrapped into [0, W)),

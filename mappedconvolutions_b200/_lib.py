@@ -52,6 +52,7 @@ SIGNATURES = {
     "mc_conv_dgrad_inv_supported": (ctypes.c_int, [_dp]),
     "mc_conv_dgrad_inv_workspace_bytes": (_sz, [_dp]),
     "mc_conv_dgrad_inv": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "mc_conv_dgrad_tapsum": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp]),
     "mc_rowplan_analysis_bytes": (_sz, [_dp]),
     "mc_rowplan_analyse": (ctypes.c_int, [_dp, _vp, _vp, _vp]),
     "mc_rowplan_assemble": (ctypes.c_int64, [_dp, _vp, _vp, _vp, ctypes.c_int64]),

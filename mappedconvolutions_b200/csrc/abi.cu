@@ -33,6 +33,7 @@ int conv_tc_wgrad_tab_launch(const mc_desc*, const void*, const void*, const voi
 bool invmap_supported(const mc_desc*);
 size_t invmap_off_bytes(const mc_desc*);
 int scatter_inv_launch(const mc_desc*, const void*, const void*, size_t, void*, int, cudaStream_t);
+int tap_gather_sum_launch(const mc_desc*, const void*, const void*, size_t, void*, cudaStream_t);
 size_t invmap_bytes(const mc_desc*);
 size_t invmap_build_ws(const mc_desc*);
 int invmap_build_launch(const mc_desc*, const void*, void*, void*, size_t, cudaStream_t);
@@ -167,6 +168,11 @@ int mc_pool_avg_bwd_inv(const mc_desc* d, const void* gy, const void* inv, void*
   int rc = scatter_inv_check(d, gy, inv, gx);
   if (rc) return rc;
   return scatter_inv_launch(d, gy, inv, invmap_off_bytes(d), gx, 1, (cudaStream_t)stream);
+}
+int mc_conv_dgrad_tapsum(const mc_desc* d, const void* z, const void* inv, void* gx, void* stream) {
+  if (!d || !z || !inv || !gx) return MC_ERR_BAD_ARG;
+  if (mc_invmap_bytes(d) == 0) return MC_ERR_UNSUPPORTED;
+  return tap_gather_sum_launch(d, z, inv, invmap_off_bytes(d), gx, (cudaStream_t)stream);
 }
 int mc_resample_scatter_inv(const mc_desc* d, const void* x, const void* inv, void* y, void* stream) {
   int rc = scatter_inv_check(d, x, inv, y);

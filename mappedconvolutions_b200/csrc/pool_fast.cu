@@ -545,4 +545,75 @@ int scatter_inv_launch(const mc_desc* d, const void* g, const void* inv, size_t 
   return avg ? launch_inv_gather<bf16, true>(d, a, st) : launch_inv_gather<bf16, false>(d, a, st);
 }
 
+// ---- input gradient of a convolution after the contraction -------------------------------------------
+// gx[b, q, c] = sum over taps k, over the entries (p, w) of the inverse-map list (q, k), of
+//               w * Z[b, p, k * C + c]      with Z[b, p, k * C + c] = sum_co gy[b, p, co] W[co, c, k]
+// Z is the product of grad_output with the weights of every tap - one dense GEMM the caller runs -
+// so what is gathered here are C_in-channel rows, each read exactly once; worth it when the layer
+// has more output than input channels (the gather-in-the-GEMM form of mc_conv_dgrad_inv moves
+// C_out-channel rows).  bf16, channels-last.  Thread = 8 channels of an input pixel; four images in
+// flight per trip.
+__global__ void __launch_bounds__(256) tap_gather_sum_kernel(const bf16* __restrict__ z, bf16* __restrict__ out,
+                                                             const int* __restrict__ off,
+                                                             const int2* __restrict__ ent, int B, int C, int K,
+                                                             long npix, long ngrid, int lpp_log2) {
+  constexpr int UB = 4;
+  const long gthread = blockIdx.x * 256L + threadIdx.x;
+  const long q = gthread >> lpp_log2;
+  const int c0 = (int)(gthread & ((1 << lpp_log2) - 1)) * 8;
+  if (q >= npix) return;
+  const long zrow = (long)K * C, zimg = ngrid * zrow, oimg = npix * C;
+  for (int b = blockIdx.y * UB; b < B; b += UB * gridDim.y) {
+    float acc[UB][8];
+#pragma unroll
+    for (int u = 0; u < UB; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+    int e = __ldg(off + q * K);
+    for (int k = 0; k < K; ++k) {
+      const int end = __ldg(off + q * K + k + 1);
+      for (; e < end; ++e) {
+        const int2 en = __ldg(ent + e);
+        const float w = __int_as_float(en.y);
+        const bf16* zp = z + (long)b * zimg + (long)en.x * zrow + k * C + c0;
+        uint4 r[UB];
+#pragma unroll
+        for (int u = 0; u < UB; ++u)
+          r[u] = b + u < B ? __ldg(reinterpret_cast<const uint4*>(zp + u * zimg)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < UB; ++u) {
+          float v[8];
+          Vec16<bf16>::unpack(r[u], v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[u][j] = fmaf(w, v[j], acc[u][j]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UB; ++u)
+      if (b + u < B)
+        *reinterpret_cast<uint4*>(out + (long)(b + u) * oimg + q * C + c0) = Vec16<bf16>::pack(acc[u]);
+  }
+}
+
+// z (B, ngrid, K * C_in) bf16, gx (B, C_in, IH, IW) channels-last bf16, inv from mc_invmap_build.
+int tap_gather_sum_launch(const mc_desc* d, const void* z, const void* inv, size_t inv_off_bytes, void* gx,
+                          cudaStream_t st) {
+  if (d->P != 0 || d->dtype != MC_BF16 || d->layout != MC_NHWC || d->C_in % 8 != 0) return MC_ERR_UNSUPPORTED;
+  if ((((uintptr_t)z | (uintptr_t)gx | (uintptr_t)inv) & 15)) return MC_ERR_BAD_ARG;
+  const int lanes = d->C_in / 8;
+  int lpp_log2 = 0;
+  while ((1 << lpp_log2) < lanes) ++lpp_log2;
+  if ((1 << lpp_log2) != lanes) return MC_ERR_UNSUPPORTED;  // C_in / 8 a power of two
+  const long npix = (long)d->IH * d->IW;
+  const long xblocks = ((npix << lpp_log2) + 255) / 256;
+  int by = (int)((148L * 8 + xblocks - 1) / xblocks);
+  if (by < 1) by = 1;
+  if (by > (d->B + 3) / 4) by = (d->B + 3) / 4;
+  tap_gather_sum_kernel<<<dim3((unsigned)xblocks, (unsigned)by), 256, 0, st>>>(
+      (const bf16*)z, (bf16*)gx, (const int*)inv, (const int2*)((const uint8_t*)inv + inv_off_bytes), d->B,
+      d->C_in, d->K, npix, (long)d->OH * d->OW, lpp_log2), MC_COUNT(1);
+  return cudaGetLastError() == cudaSuccess ? MC_OK : MC_ERR_LAUNCH;
+}
+
 }  // namespace mc

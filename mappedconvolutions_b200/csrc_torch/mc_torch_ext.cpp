@@ -327,6 +327,15 @@ Tensor conv_forward(const Tensor& input_in, const Tensor& sample_map_in, const O
   return y;
 }
 
+// Input gradient as GEMM + gather-sum (mc_conv_dgrad_tapsum) instead of gather-in-the-GEMM: when the
+// layer has more output than input channels and the product z fits comfortably.
+static bool contract_first(const mc_desc& d) {
+  const int lanes = d.C_in / 8;
+  return d.dtype == MC_BF16 && d.layout == MC_NHWC && d.P == 0 && d.C_out > d.C_in && d.C_in % 8 == 0 &&
+         (lanes & (lanes - 1)) == 0 &&
+         (int64_t)d.B * d.OH * d.OW * d.K * d.C_in * 2 <= ((int64_t)8 << 30);
+}
+
 std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sample_map_in,
                                   const OptTensor& iw, const Tensor& input_in, const Tensor& weight,
                                   const Tensor& bias, int64_t K, int64_t interp,
@@ -368,6 +377,15 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
   }
   Tensor inv = (need_input_grad && mc_conv_dgrad_inv_supported(&d)) ? inverse_map(d, sample_map)
                                                                      : Tensor();
+  if (need_input_grad && inv.defined() && contract_first(d)) {
+    // more output than input channels: contract with the weights first (one dense GEMM), then
+    // gather-sum the narrow rows through the inverse map
+    Tensor g2 = grad_output.permute({0, 2, 3, 1}).reshape({B * OH * OW, Cout});  // a view of channels-last
+    Tensor wr = weight.permute({0, 2, 1}).reshape({Cout, K * Cin});
+    Tensor z = at::matmul(g2, wr);
+    check(mc_conv_dgrad_tapsum(&d, z.data_ptr(), inv.data_ptr(), gx.data_ptr(), cur_stream()));
+    need_input_grad = false;  // done
+  }
   const size_t n_dgrad = inv.defined() ? mc_conv_dgrad_inv_workspace_bytes(&d)
                                        : mc_conv_dgrad_workspace_bytes(&d);
   Scratch ws = scratch(std::max(n_dgrad, mc_conv_wgrad_workspace_bytes(&d)), dev);

@@ -246,6 +246,15 @@ def _conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size, 
     return y
 
 
+def _contract_first(d):
+    """Input gradient as GEMM + gather-sum (mc_conv_dgrad_tapsum) instead of gather-in-the-GEMM: when
+    the layer has more output than input channels and the product z fits comfortably."""
+    lanes = d.C_in // 8
+    return (d.dtype == _lib.MC_BF16 and d.layout == _lib.MC_NHWC and d.P == 0 and d.C_out > d.C_in
+            and d.C_in % 8 == 0 and lanes & (lanes - 1) == 0
+            and d.B * d.OH * d.OW * d.K * d.C_in * 2 <= 8 << 30)
+
+
 def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias, kernel_size,
                    interpolation, need_input_grad=True, _nhwc=False):
     input, sample_map = _a16(input), _a16(sample_map)
@@ -282,6 +291,13 @@ def _conv_backward(grad_output, sample_map, interp_weights, input, weight, bias,
                                 L.mc_conv_wgrad_workspace_bytes(d)), dev)
         if not need_input_grad:
             pass
+        elif inv is not None and _contract_first(d):
+            # more output than input channels: contract with the weights first (one dense GEMM), then
+            # gather-sum the narrow rows through the inverse map
+            g2 = grad_output.permute(0, 2, 3, 1).reshape(B * OH * OW, Cout)   # a view of channels-last
+            wr = weight.permute(0, 2, 1).reshape(Cout, kernel_size * Cin)
+            z = torch.matmul(g2, wr)
+            check(L.mc_conv_dgrad_tapsum(d, z.data_ptr(), inv.data_ptr(), gx.data_ptr(), _stream()))
         elif inv is not None:
             check(L.mc_conv_dgrad_inv(d, grad_output.data_ptr(), inv.data_ptr(), weight.data_ptr(),
                                       None, gx.data_ptr(), wsp, wsn, _stream()))

@@ -546,3 +546,36 @@ def test_tensor_core_kernels_on_a_second_device(op_binding):
             xd = x.to(dev).contiguous(memory_format=torch.channels_last)
             y = ops.mapped_conv_forward(xd, m.to(dev), w.to(dev), b.to(dev), K, 1)
             H.assert_close(y.float().cpu(), want, 2e-2, "forward on " + dev)
+
+
+@pytest.mark.parametrize("interp", [0, 1])
+def test_input_gradient_with_the_contraction_first(interp, op_binding):
+    """Layers with more output than input channels take mc_conv_dgrad_tapsum: grad_output times the
+    weights of every tap as one dense GEMM, then a gather-sum of the narrow rows through the inverse
+    map.  Against the oracle, and against the gather-in-the-GEMM form (mc_conv_dgrad_inv) on the
+    same inverse map."""
+    from mappedconvolutions_b200 import _lib, ops
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(31 + interp)
+    B, Cin, Cout, Hh, Ww, K = 3, 64, 128, 9, 20, 5
+    bf = torch.bfloat16
+    x = torch.randn(B, Cin, Hh, Ww, generator=g).to(bf)
+    gy = torch.randn(B, Cout, Hh, Ww, generator=g).to(bf)
+    w, b = (torch.randn(Cout, Cin, K, generator=g) * 0.2).to(bf), torch.zeros(Cout).to(bf)
+    m = torch.rand(Hh, Ww, K, 2, generator=g) * torch.tensor([Ww + 1.0, Hh + 1.0]) - 1.0   # some taps outside
+    cl = lambda t: t.cuda().contiguous(memory_format=torch.channels_last)
+    gx = ops.mapped_conv_backward(cl(gy), m.cuda(), cl(x), w.cuda(), b.cuda(), K, interp)[0]
+    want = oracle.mapped_conv_backward(gy.float(), m, x.float(), w.float(), b.float(), K, interp)[0]
+    H.assert_close(gx.float(), want, 2e-2, "grad_x, contraction first, vs oracle")
+    import importlib
+    pyops = importlib.import_module("mappedconvolutions_b200.ops")   # (the ctypes twin, for its helpers)
+    d = _lib.McDesc(B, Cin, Cout, Hh, Ww, Hh, Ww, K, 0, interp, _lib.MC_BF16, _lib.MC_NHWC)
+    assert pyops._contract_first(d)
+    inv = pyops._inverse_map(d, m.cuda().contiguous())
+    gx2 = torch.empty_like(gx)
+    nws = L.mc_conv_dgrad_inv_workspace_bytes(d)
+    ws = torch.empty(max(nws, 16), dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(L.mc_conv_dgrad_inv(d, cl(gy).data_ptr(), inv.data_ptr(), w.cuda().data_ptr(), None,
+                                   gx2.data_ptr(), ws.data_ptr(), nws, st))
+    H.assert_close(gx.float(), gx2.float(), 2e-2, "grad_x, contraction first, vs gather in the GEMM")
