@@ -551,39 +551,77 @@ int scatter_inv_launch(const mc_desc* d, const void* g, const void* inv, size_t 
 // Z is the product of grad_output with the weights of every tap - one dense GEMM the caller runs -
 // so what is gathered here are C_in-channel rows, each read exactly once; worth it when the layer
 // has more output than input channels (the gather-in-the-GEMM form of mc_conv_dgrad_inv moves
-// C_out-channel rows).  bf16, channels-last.  Thread = 8 channels of an input pixel; four images in
-// flight per trip.
+// C_out-channel rows).  bf16, channels-last.  Thread = 8 channels of an input pixel; four rows of two
+// images in flight per trip.
 __global__ void __launch_bounds__(256) tap_gather_sum_kernel(const bf16* __restrict__ z, bf16* __restrict__ out,
                                                              const int* __restrict__ off,
                                                              const int2* __restrict__ ent, int B, int C, int K,
                                                              long npix, long ngrid, int lpp_log2) {
-  constexpr int UB = 4;
+  constexpr int UB = 2;
   const long gthread = blockIdx.x * 256L + threadIdx.x;
   const long q = gthread >> lpp_log2;
   const int c0 = (int)(gthread & ((1 << lpp_log2) - 1)) * 8;
   if (q >= npix) return;
   const long zrow = (long)K * C, zimg = ngrid * zrow, oimg = npix * C;
+  // The pixel's entries of all taps (one-ring and 3 x 3 maps: about K of them) are fetched first, so
+  // that the row loads of a trip do not each wait for their list entry; rows beyond NE take the loop.
+  constexpr int NE = 12;
+  const int e0 = __ldg(off + q * K), e1 = __ldg(off + (q + 1) * K);
+  long zo[NE];   // offset of the entry's row inside an image of z (its tap's block, this thread's channels)
+  float zw[NE];
+  {
+    int k = 0, kend = __ldg(off + q * K + 1);
+#pragma unroll
+    for (int i = 0; i < NE; ++i) {
+      const int e = e0 + i;
+      zo[i] = 0; zw[i] = 0.f;
+      if (e < e1) {
+        while (e >= kend) { ++k; kend = __ldg(off + q * K + k + 1); }
+        const int2 en = __ldg(ent + e);
+        zo[i] = (long)en.x * zrow + k * C + c0;
+        zw[i] = __int_as_float(en.y);
+      }
+    }
+  }
   for (int b = blockIdx.y * UB; b < B; b += UB * gridDim.y) {
     float acc[UB][8];
 #pragma unroll
     for (int u = 0; u < UB; ++u)
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
-    int e = __ldg(off + q * K);
-    for (int k = 0; k < K; ++k) {
-      const int end = __ldg(off + q * K + k + 1);
-      for (; e < end; ++e) {
-        const int2 en = __ldg(ent + e);
-        const float w = __int_as_float(en.y);
-        const bf16* zp = z + (long)b * zimg + (long)en.x * zrow + k * C + c0;
-        uint4 r[UB];
+    const bf16* zb = z + (long)b * zimg;
+#pragma unroll
+    for (int i0 = 0; i0 < NE; i0 += 4) {
+      if (e0 + i0 >= e1) break;
+      uint4 r[4][UB];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int u = 0; u < UB; ++u)
-          r[u] = b + u < B ? __ldg(reinterpret_cast<const uint4*>(zp + u * zimg)) : make_uint4(0, 0, 0, 0);
+          r[i][u] = (e0 + i0 + i < e1 && b + u < B) ? __ldg(reinterpret_cast<const uint4*>(zb + zo[i0 + i] + u * zimg))
+                                                   : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int u = 0; u < UB; ++u) {
           float v[8];
-          Vec16<bf16>::unpack(r[u], v);
+          Vec16<bf16>::unpack(r[i][u], v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[u][j] = fmaf(zw[i0 + i], v[j], acc[u][j]);
+        }
+    }
+    if (e1 - e0 > NE) {  // long lists
+      int k = 0, kend = __ldg(off + q * K + 1);
+      for (int e = e0 + NE; e < e1; ++e) {
+        while (e >= kend) { ++k; kend = __ldg(off + q * K + k + 1); }
+        const int2 en = __ldg(ent + e);
+        const float w = __int_as_float(en.y);
+        const bf16* zp = zb + (long)en.x * zrow + k * C + c0;
+#pragma unroll
+        for (int u = 0; u < UB; ++u) {
+          if (b + u >= B) break;
+          float v[8];
+          Vec16<bf16>::unpack(__ldg(reinterpret_cast<const uint4*>(zp + u * zimg)), v);
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[u][j] = fmaf(w, v[j], acc[u][j]);
         }
@@ -609,7 +647,7 @@ int tap_gather_sum_launch(const mc_desc* d, const void* z, const void* inv, size
   const long xblocks = ((npix << lpp_log2) + 255) / 256;
   int by = (int)((148L * 8 + xblocks - 1) / xblocks);
   if (by < 1) by = 1;
-  if (by > (d->B + 3) / 4) by = (d->B + 3) / 4;
+  if (by > (d->B + 1) / 2) by = (d->B + 1) / 2;
   tap_gather_sum_kernel<<<dim3((unsigned)xblocks, (unsigned)by), 256, 0, st>>>(
       (const bf16*)z, (bf16*)gx, (const int*)inv, (const int2*)((const uint8_t*)inv + inv_off_bytes), d->B,
       d->C_in, d->K, npix, (long)d->OH * d->OW, lpp_log2), MC_COUNT(1);
