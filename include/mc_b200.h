@@ -315,6 +315,30 @@ int mc_sphere_locate(const float* samples, int64_t n, int32_t order, const float
                      const int32_t* num_faces, int32_t nearest, int64_t* face_idx,
                      int64_t* vertex_idx, float* weights, void* stream);
 
+/* ---- cube map -> equirectangular image ------------------------------------------------------
+ * cube (C, D, 6 D) of `dtype` (MC_F32 / MC_F64), the six faces side by side in the order
+ * -z, -x, +z, +x, +y, -y; rect (C, rect_h, rect_w), fully written.  interp: 0 nearest, 1 bilinear.
+ * Every pixel of the result looks along its longitude / latitude, finds the face that direction
+ * leaves the cube through and samples the face there.  Replaces Cube2RectLauncher,
+ * include/util/cuda/cube2rect.cuh:66-82 (kernel :15-62) and Cube2RectForward,
+ * src/util/cuda/cube2rect_layer.cu:11-29; same arithmetic, bit-identical results. */
+int mc_cube2rect(int32_t dtype, const void* cube, int32_t channels, int32_t cube_dim, int32_t rect_h,
+                 int32_t rect_w, int32_t interp, void* rect, void* stream);
+
+/* ---- voting resample ------------------------------------------------------------------------
+ * labels (B, C, IH, IW) int64 in [0, num_candidates); map (IH, IW, 2) int64: the (x, y) target
+ * pixel of every source pixel (16-byte aligned; targets outside (OH, OW) are dropped, and so are
+ * labels outside the candidate range).  out (B, C, OH, OW) int64: the label most source pixels
+ * brought to each target pixel - the smallest such label among equals, 0 where nothing landed.
+ * ws: mc_voting_resample_workspace(...) bytes of device scratch (32-bit vote counters).
+ * Replaces ResampleToMap2DVotingLauncher, include/nn/cuda/resample.cuh:166-200, Vote2D,
+ * include/core/interpolation.h:241-257, and VotingResampleToMap (votes + argmax per image),
+ * src/nn/cuda/voting_resample_layer.cu:10-38 / src/nn/cpp/voting_resample_layer.cpp:8-38. */
+size_t mc_voting_resample_workspace(int32_t B, int32_t C, int32_t OH, int32_t OW, int32_t num_candidates);
+int mc_voting_resample(const int64_t* labels, const int64_t* map, int32_t B, int32_t C, int32_t IH,
+                       int32_t IW, int32_t OH, int32_t OW, int32_t num_candidates, void* ws,
+                       size_t ws_bytes, int64_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -81,6 +81,10 @@ SIGNATURES = {
     "mc_sphere_locate": (ctypes.c_int, [_vp, ctypes.c_int64, _i32, ctypes.POINTER(_vp),
                                         ctypes.POINTER(_vp), ctypes.POINTER(_vp),
                                         ctypes.POINTER(_i32), _i32, _vp, _vp, _vp, _vp]),
+    "mc_cube2rect": (ctypes.c_int, [_i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "mc_voting_resample_workspace": (_sz, [_i32, _i32, _i32, _i32, _i32]),
+    "mc_voting_resample": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _sz,
+                                          _vp, _vp]),
 }
 
 

@@ -11,6 +11,7 @@
 //
 // mappedconvolutions_b200/ops.py is the same host logic on ctypes; the tests use it to reach the
 // C ABI without a compiler, and check the two against each other.
+#include <algorithm>
 #include <torch/extension.h>
 
 #include <c10/cuda/CUDAGuard.h>
@@ -659,6 +660,52 @@ std::vector<Tensor> knn_forward(const Tensor& ref, const Tensor& query, int64_t 
   return {idx, dist};
 }
 
+// ---- cube map -> equirectangular image, voting resample -----------------------------------------------
+
+Tensor cube2rect(const Tensor& cubemap_in, int64_t rect_height, int64_t rect_width, int64_t interpolation) {
+  const auto dev = need_cuda({&cubemap_in});
+  TORCH_CHECK(cubemap_in.dim() == 3 && cubemap_in.size(2) == 6 * cubemap_in.size(1),
+              "cubemap must be (channels, cube_dim, 6 * cube_dim)");
+  TORCH_CHECK(cubemap_in.scalar_type() == at::kFloat || cubemap_in.scalar_type() == at::kDouble,
+              "cube2rect works on float32 / float64 images");
+  TORCH_CHECK(interpolation == 0 || interpolation == 1, "interpolation must be 0 (nearest) or 1 (bilinear)");
+  const Tensor cubemap = cubemap_in.contiguous();
+  Tensor rect = at::empty({cubemap.size(0), rect_height, rect_width}, cubemap.options());
+  c10::cuda::CUDAGuard guard(dev);
+  check(mc_cube2rect(cubemap.scalar_type() == at::kDouble ? MC_F64 : MC_F32, cubemap.data_ptr(),
+                     (int32_t)cubemap.size(0), (int32_t)cubemap.size(1), (int32_t)rect_height, (int32_t)rect_width,
+                     (int32_t)interpolation, rect.data_ptr(), cur_stream()));
+  return rect;
+}
+
+Tensor voting_resample_to_map(const Tensor& input_in, const Tensor& map_in, int64_t oh, int64_t ow,
+                              int64_t num_candidates) {
+  const auto dev = need_cuda({&input_in, &map_in});
+  TORCH_CHECK(input_in.scalar_type() == at::kLong && map_in.scalar_type() == at::kLong,
+              "voting resample works on int64 labels and an int64 map");
+  TORCH_CHECK(input_in.dim() == 4 && map_in.dim() == 3 && map_in.size(0) == input_in.size(2) &&
+                  map_in.size(1) == input_in.size(3) && map_in.size(2) == 2,
+              "input must be (B, C, IH, IW) and sample_map (IH, IW, 2)");
+  TORCH_CHECK(num_candidates > 0, "num_candidates must be positive");
+  const Tensor input = input_in.contiguous(), map = map_in.contiguous();
+  const int64_t B = input.size(0), C = input.size(1), IH = input.size(2), IW = input.size(3);
+  Tensor out = at::empty({B, C, oh, ow}, input.options());
+  // (vote counters for a slice of the batch at a time: at most ~1 GiB of scratch)
+  const int64_t per_image =
+      (int64_t)mc_voting_resample_workspace(1, (int32_t)C, (int32_t)oh, (int32_t)ow, (int32_t)num_candidates);
+  const int64_t step = std::max<int64_t>(1, std::min<int64_t>(B, (int64_t(1) << 30) / std::max<int64_t>(1, per_image)));
+  Tensor ws = at::empty({per_image * step}, input.options().dtype(at::kByte));
+  c10::cuda::CUDAGuard guard(dev);
+  for (int64_t b0 = 0; b0 < B; b0 += step) {
+    const int64_t nb = std::min(step, B - b0);
+    check(mc_voting_resample(input.data_ptr<int64_t>() + b0 * C * IH * IW, map.data_ptr<int64_t>(), (int32_t)nb,
+                             (int32_t)C, (int32_t)IH, (int32_t)IW, (int32_t)oh, (int32_t)ow,
+                             (int32_t)num_candidates, ws.data_ptr(), (size_t)(per_image * nb),
+                             out.data_ptr<int64_t>() + b0 * C * oh * ow, cur_stream()));
+  }
+  return out;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -754,6 +801,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         });
   // KNNForward, include/util/layers/knn_layer.h:25-35 -> [idx (B,k,N) int64 1-based, dist]
   m.def("knn_forward", &knn_forward);
+  // Cube2RectForward, include/util/layers/cube2rect_layer.h:14-45
+  m.def("cube2rect", &cube2rect);
+  // VotingResampleToMap, include/nn/layers/voting_resample_layer.h:34-58
+  m.def("voting_resample_to_map", &voting_resample_to_map);
   m.def("clear_plan_cache", &clear_plan_cache);
   // Row plans (the fast path for maps that are translation invariant along image rows) on / off;
   // returns the previous setting.  Off: every map takes the general kernels.

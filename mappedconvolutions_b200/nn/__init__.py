@@ -1,5 +1,5 @@
-from .layers import (MappedAvgPool, MappedAvgUnpool, MappedConvolution, MappedMaxPool,
-                     MappedTransposedConvolution, Resample, Unresample)
+from .layers import (Convolution, MappedAvgPool, MappedAvgUnpool, MappedConvolution, MappedMaxPool,
+                     MappedTransposedConvolution, Resample, TransposedConvolution, Unresample)
 
-__all__ = ["MappedConvolution", "MappedTransposedConvolution", "MappedMaxPool", "MappedAvgPool",
-           "MappedAvgUnpool", "Resample", "Unresample"]
+__all__ = ["Convolution", "TransposedConvolution", "MappedConvolution", "MappedTransposedConvolution",
+           "MappedMaxPool", "MappedAvgPool", "MappedAvgUnpool", "Resample", "Unresample"]

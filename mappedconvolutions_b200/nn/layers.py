@@ -149,3 +149,66 @@ class Unresample(nn.Module):
     def forward(self, x, sample_map, interp_weights=None):
         check_args(x, sample_map, interp_weights, None, None)
         return F.UnresampleFn.apply(x, sample_map, self.interp, interp_weights)
+
+
+def _pair(v):
+    return tuple(v) if isinstance(v, (tuple, list)) else (v, v)
+
+
+class _GridConvBase(nn.Module):
+    """The reference's two ordinary grid convolutions - its own im2col + GEMM code, kept there as
+    a yardstick for the mapped layers (package/layers/nn/convolution_layer.py:34-75,
+    transposed_convolution_layer.py:33-74).  Here they are the same modules (constructor,
+    parameter shapes, initialisation, output sizes) on top of torch's convolutions: a grid
+    convolution is not part of the mapped-convolution path and the library convolution is the
+    right tool for it.
+
+    Initialisation as in the reference: the weight is drawn once per kernel dimension (the last
+    draw, U(-s, s) with s = 1/sqrt(in_channels * kh * kw), stays), then the bias with the same s,
+    so that a seeded construction yields the reference's parameters."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, transposed):
+        super().__init__()
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.kernel_size = _pair(kernel_size)
+        self.padding = _pair(padding)
+        self.stride = _pair(stride)
+        self.dilation = _pair(dilation)
+        first = (in_channels, out_channels) if transposed else (out_channels, in_channels)
+        self.weight = nn.Parameter(torch.empty(*first, *self.kernel_size))
+        self.bias = nn.Parameter(torch.empty(out_channels))
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        n = self.in_channels
+        with torch.no_grad():
+            for k in self.kernel_size:
+                n *= k
+                s = 1.0 / math.sqrt(n)
+                self.weight.uniform_(-s, s)
+            self.bias.uniform_(-s, s)
+
+
+class Convolution(_GridConvBase):
+    """forward(x (B, C_in, H, W)) -> (B, C_out, (H + 2 p - d (k - 1) - 1) / s + 1, ...), the output size of
+    src/nn/cpp/convolution_layer.cpp:17-24.  package/layers/nn/convolution_layer.py:34-75"""
+
+    def __init__(self, in_channels, out_channels, kernel_size=1, stride=1, padding=0, dilation=1):
+        super().__init__(in_channels, out_channels, kernel_size, stride, padding, dilation, False)
+
+    def forward(self, x):
+        return torch.nn.functional.conv2d(x, self.weight, self.bias, self.stride, self.padding, self.dilation)
+
+
+class TransposedConvolution(_GridConvBase):
+    """forward(x (B, C_in, H, W)) -> (B, C_out, s (H - 1) + d (k - 1) + 1 - 2 p, ...), the output size of
+    src/nn/cpp/transposed_convolution_layer.cpp:54-57; weight (C_in, C_out, kh, kw).
+    package/layers/nn/transposed_convolution_layer.py:33-74"""
+
+    def __init__(self, in_channels, out_channels, kernel_size=1, stride=1, padding=0, dilation=1):
+        super().__init__(in_channels, out_channels, kernel_size, stride, padding, dilation, True)
+
+    def forward(self, x):
+        return torch.nn.functional.conv_transpose2d(x, self.weight, self.bias, self.stride, self.padding, 0, 1,
+                                                    self.dilation)

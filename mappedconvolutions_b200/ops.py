@@ -706,3 +706,53 @@ def knn_forward(ref, query, k):
         check(lib().mc_knn(ref.data_ptr(), query.data_ptr(), B, D, M, N, int(k), idx.data_ptr(),
                            dist.data_ptr(), _stream()))
     return [idx, dist]
+
+
+# ------------------------------------------------------------------------------------------
+# cube map -> equirectangular image, voting resample
+# ------------------------------------------------------------------------------------------
+
+def cube2rect(cubemap, rect_height, rect_width, interpolation):
+    """Cube2RectForward, include/util/layers/cube2rect_layer.h:14-45 (src/util/cuda/cube2rect_layer.cu:11-29):
+    cubemap (C, D, 6 D) float32 / float64 with faces -z, -x, +z, +x, +y, -y -> (C, rect_height, rect_width)."""
+    dev = _need_cuda(cubemap)
+    if cubemap.dim() != 3 or cubemap.shape[2] != 6 * cubemap.shape[1]:
+        raise RuntimeError("cubemap must be (channels, cube_dim, 6 * cube_dim)")
+    if cubemap.dtype not in (torch.float32, torch.float64):
+        raise RuntimeError("cube2rect works on float32 / float64 images")
+    if interpolation not in (0, 1):
+        raise RuntimeError("interpolation must be 0 (nearest) or 1 (bilinear)")
+    cubemap = cubemap.contiguous()
+    C, D = cubemap.shape[0], cubemap.shape[1]
+    rect = torch.empty((C, int(rect_height), int(rect_width)), dtype=cubemap.dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().mc_cube2rect(_DT[cubemap.dtype], cubemap.data_ptr(), C, D,
+                                 int(rect_height), int(rect_width), int(interpolation), rect.data_ptr(), _stream()))
+    return rect
+
+
+def voting_resample_to_map(input, sample_map, output_height, output_width, num_candidates):
+    """VotingResampleToMap, include/nn/layers/voting_resample_layer.h:34-58: input (B, C, IH, IW) int64
+    labels, sample_map (IH, IW, 2) int64 target (x, y) of every input pixel -> (B, C, OH, OW) int64, the
+    label most input pixels brought to each output pixel."""
+    dev = _need_cuda(input, sample_map)
+    if input.dtype != torch.int64 or sample_map.dtype != torch.int64:
+        raise RuntimeError("voting resample works on int64 labels and an int64 map")
+    if input.dim() != 4 or tuple(sample_map.shape) != (input.shape[2], input.shape[3], 2):
+        raise RuntimeError("input must be (B, C, IH, IW) and sample_map (IH, IW, 2)")
+    if num_candidates <= 0:
+        raise RuntimeError("num_candidates must be positive")
+    input, sample_map = input.contiguous(), sample_map.contiguous()
+    B, C, IH, IW = input.shape
+    OH, OW, NC = int(output_height), int(output_width), int(num_candidates)
+    out = torch.empty((B, C, OH, OW), dtype=torch.int64, device=dev)
+    # (vote counters for a slice of the batch at a time: at most ~1 GiB of scratch)
+    per_image = lib().mc_voting_resample_workspace(1, C, OH, OW, NC)
+    step = max(1, min(B, (1 << 30) // max(1, per_image)))
+    ws = torch.empty(per_image * step, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        for b0 in range(0, B, step):
+            nb = min(step, B - b0)
+            check(lib().mc_voting_resample(input[b0:].data_ptr(), sample_map.data_ptr(), nb, C, IH, IW, OH, OW, NC,
+                                           ws.data_ptr(), per_image * nb, out[b0:].data_ptr(), _stream()))
+    return out

@@ -149,9 +149,13 @@ def cube_to_3d(depth_cubemap):
 
 
 def cube_to_rect(cubemap, rect_height, rect_width, interpolation="nearest"):
-    """The reference resamples a cube map to an equirectangular image with a dedicated CUDA
-    utility kernel (include/util/cuda/cube2rect.cuh); that utility is not part of this library."""
-    raise NotImplementedError("cube_to_rect is not provided by this library")
+    """cubemap (C, cube_dim, 6 * cube_dim), faces laid out as [-z, -x, +z, +x, +y, -y], resampled
+    to a (C, rect_height, rect_width) equirectangular image on the GPU
+    (spherical_projections.py:199-213; the kernel replaces include/util/cuda/cube2rect.cuh)."""
+    from ..host import impl
+    assert len(cubemap.shape) == 3, "Cubemap must have 3 dimensions"
+    assert interpolation in ("nearest", "bilinear"), "Invalid interpolation option"
+    return impl.cube2rect(cubemap, rect_height, rect_width, 0 if interpolation == "nearest" else 1)
 
 
 def perspective_resampling(fov, width, height, theta):

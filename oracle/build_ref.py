@@ -37,6 +37,7 @@ MODULES = {
     "_sphere": "src/util/cpp/sphere.cpp",
     # not on the hot path; only needed so that the reference's `mapped_convolution.nn` package,
     # which imports every layer module, can be imported when the golden vectors are generated
+    "_voting_resample": "src/nn/cpp/voting_resample_layer.cpp",
     "_convolution": "src/nn/cpp/convolution_layer.cpp",
     "_transposed_convolution": "src/nn/cpp/transposed_convolution_layer.cpp",
 }
@@ -84,26 +85,39 @@ def build_one(name, ref_root):
     return name, "built"
 
 
-def build_knn(ref_root):
-    """The reference's CUDA-only k-NN module (src/util/cuda/knn_layer.cu + include/util/cuda/knn.cuh,
-    bound by src/util/cpp/knn_layer.cpp), compiled for sm_100a with nvcc.  The reference gives its
-    kernels a (k, N) buffer but indexes it as an (M, N) distance matrix (knn_layer.cu:20-23 against
+# CUDA-only utility modules of the reference: name -> (kernel source, binding source)
+CUDA_MODULES = {
+    "_knn": ("src/util/cuda/knn_layer.cu", "src/util/cpp/knn_layer.cpp"),
+    "_cube2rect": ("src/util/cuda/cube2rect_layer.cu", "src/util/cpp/cube2rect_layer.cpp"),
+}
+
+
+def build_cuda_module(ref_root, name):
+    """One of the reference's CUDA-only utility modules, compiled for sm_100a with nvcc from the
+    sources where they lie (kernel source + the .cpp that holds the pybind binding).
+
+    _knn: src/util/cuda/knn_layer.cu + include/util/cuda/knn.cuh.  The reference gives its kernels a
+    (k, N) buffer but indexes it as an (M, N) distance matrix (knn_layer.cu:20-23 against
     knn.cuh:111-112, :144-187), so it is only ever run with M == k, where every access stays inside
-    the buffers; tests/golden/make_golden_knn.py enforces that."""
+    the buffers; tests/golden/make_golden_knn.py enforces that.
+    _cube2rect: src/util/cuda/cube2rect_layer.cu + include/util/cuda/cube2rect.cuh.  Its bilinear
+    branch can read one element past the cube map (the right neighbour of the last face's last
+    pixel, weight zero); tests/golden/make_golden_cube2rect.py hands it a view into a larger zeroed
+    buffer so that this read stays inside an allocation."""
     import sysconfig
     import torch
     from torch.utils import cpp_extension as ce
     ext = os.path.join(ref_root, "package", "ext_modules")
-    cu = os.path.join(ext, "src/util/cuda/knn_layer.cu")
-    cpp = os.path.join(ext, "src/util/cpp/knn_layer.cpp")
+    cu = os.path.join(ext, CUDA_MODULES[name][0])
+    cpp = os.path.join(ext, CUDA_MODULES[name][1])
     os.makedirs(OUT, exist_ok=True)
-    so = os.path.join(OUT, "_knn.so")
+    so = os.path.join(OUT, name + ".so")
     if os.path.exists(so) and os.path.getmtime(so) >= os.path.getmtime(cu):
-        return "_knn", "cached"
+        return name, "cached"
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     inc = [os.path.join(ext, "include")] + ce.include_paths() + [sysconfig.get_paths()["include"],
                                                                  os.path.join(os.path.dirname(os.path.dirname(nvcc)), "include")]
-    defs = ["-DTORCH_EXTENSION_NAME=_knn", "-DTORCH_API_INCLUDE_EXTENSION_H",
+    defs = ["-DTORCH_EXTENSION_NAME=" + name, "-DTORCH_API_INCLUDE_EXTENSION_H",
             "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
     obj_cu, obj_cpp = so + ".cu.o", so + ".cpp.o"
     cmd1 = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w", "-Xcompiler",
@@ -118,10 +132,14 @@ def build_knn(ref_root):
     for cmd in (cmd1, cmd2, cmd3):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
-            return "_knn", "FAILED\n" + r.stderr[-3000:]
+            return name, "FAILED\n" + r.stderr[-3000:]
     for o in (obj_cu, obj_cpp):
         os.remove(o)
-    return "_knn", "built"
+    return name, "built"
+
+
+def build_knn(ref_root):
+    return build_cuda_module(ref_root, "_knn")
 
 
 def default_reference_root():
@@ -134,6 +152,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=default_reference_root())
     ap.add_argument("--knn", action="store_true", help="also build the reference's CUDA k-NN module")
+    ap.add_argument("--cube2rect", action="store_true", help="also build the reference's CUDA cube2rect module")
     ap.add_argument("--jobs", type=int, default=min(8, os.cpu_count() or 1))
     ap.add_argument("modules", nargs="*")
     a = ap.parse_args()
@@ -146,10 +165,11 @@ def main():
         for name, status in ex.map(lambda n: build_one(n, a.ref), names):
             print(name, status, flush=True)
             ok &= not status.startswith("FAILED")
-    if a.knn:
-        name, status = build_knn(a.ref)
-        print(name, status, flush=True)
-        ok &= not status.startswith("FAILED")
+    for flag, cuda_name in ((a.knn, "_knn"), (a.cube2rect, "_cube2rect")):
+        if flag:
+            name, status = build_cuda_module(a.ref, cuda_name)
+            print(name, status, flush=True)
+            ok &= not status.startswith("FAILED")
     return 0 if ok else 1
 
 

@@ -228,3 +228,24 @@ def knn_forward(ref, query, k):
     fn.restype = None
     fn(_p(ref), _p(query), *(ctypes.c_int(int(v)) for v in (B, D, M, N, k)), _p(idx), _p(dist))
     return [idx, dist]
+
+
+# ---- voting resample, cube2rect -----------------------------------------------------------------
+def voting_resample_to_map(input, sample_map, OH, OW, num_candidates):
+    input, sample_map = input.contiguous(), sample_map.contiguous()
+    assert input.dtype == torch.int64 and sample_map.dtype == torch.int64
+    B, C, IH, IW = input.shape
+    out = torch.empty(B, C, OH, OW, dtype=torch.int64)
+    fn = lib().oracle_voting_resample
+    fn.restype = None
+    fn(_p(input), _p(sample_map), *(ctypes.c_int(int(v)) for v in (B, C, IH, IW, OH, OW, num_candidates)),
+       _p(out))
+    return out
+
+
+def cube2rect(cubemap, rect_height, rect_width, interp):
+    cubemap = cubemap.contiguous()
+    C, D = cubemap.shape[0], cubemap.shape[1]
+    rect = torch.empty(C, rect_height, rect_width, dtype=cubemap.dtype)
+    _call("oracle_cube2rect", cubemap, cubemap, C, D, rect_height, rect_width, interp, rect)
+    return rect
