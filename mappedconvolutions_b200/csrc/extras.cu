@@ -162,6 +162,7 @@ extern "C" int mc_cube2rect(int32_t dtype, const void* cube, int32_t channels, i
   else
     cube2rect_kernel<double><<<blocks, threads, 0, st>>>((const double*)cube, channels, cube_dim, rect_h, rect_w,
                                                          interp, (double*)rect);
+  MC_COUNT(1);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
@@ -187,6 +188,7 @@ extern "C" int mc_voting_resample(const int64_t* labels, const int64_t* map, int
   vote_count_kernel<<<vote_grid(n_in, 256), 256, 0, st>>>(labels, map, planes, C, IH, IW, OH, OW, num_candidates,
                                                          (int*)ws);
   vote_pick_kernel<<<vote_grid(n_out, 256), 256, 0, st>>>((const int*)ws, n_out, num_candidates, out);
+  MC_COUNT(2);
   MC_CHECK_LAUNCH();
   return MC_OK;
 }
