@@ -162,6 +162,23 @@ size_t mc_invmap_bytes(const mc_desc* d);
 size_t mc_invmap_build_workspace_bytes(const mc_desc* d);
 int mc_invmap_build(const mc_desc* d, const void* map, void* inv, size_t inv_bytes, void* ws,
                     size_t ws_bytes, void* stream);
+
+/* Plans of WEIGHTED maps (d->P > 0: a tap is the sum over P points of interp_weight x sample,
+ * include/core/resample.h:145-162; e.g. the three barycentric vertices of an icosphere tap).
+ * When P x (corners per point: 1 for nearest, 4 for bilinear / bispherical) <= 4 the points of a tap
+ * fit one tap-table record, and the map "folds": mc_weighted_plan_desc() fills *folded with the same
+ * descriptor with P = 0 and interp = 1 (bilinear), the two builders below write a tap table and an
+ * inverse map from (map, iw) in the layout of that folded descriptor (size the buffers with
+ * mc_tapmap_bytes / mc_invmap_bytes / mc_invmap_build_workspace_bytes of *folded), and the caller
+ * runs mc_conv_fwd_tap, mc_conv_wgrad_tap, mc_conv_dgrad_inv, mc_conv_dgrad_tapsum with *folded:
+ * the bf16 tensor-core path of a weighted layer.  They compute what
+ * WeightedMappedConvForward / Backward compute (src/nn/cuda/weighted_mapped_convolution_layer.cu:16-202).
+ * MC_ERR_UNSUPPORTED: the map does not fold (or MC_F64). */
+int mc_weighted_plan_desc(const mc_desc* d, mc_desc* folded);
+int mc_tapmap_build_weighted(const mc_desc* d, const void* map, const void* iw, void* tapmap,
+                             size_t tapmap_bytes, void* stream);
+int mc_invmap_build_weighted(const mc_desc* d, const void* map, const void* iw, void* inv, size_t inv_bytes,
+                             void* ws, size_t ws_bytes, void* stream);
 /* Same result as mc_conv_dgrad, computed on the tensor cores from a prebuilt inverse map.
  * bf16, MC_NHWC, C_in % 64 == 0, C_out % 64 == 0 (mc_conv_dgrad_inv_supported() tells).
  * Replaces cuda::MappedConvBackwardInput, src/nn/cuda/mapped_convolution_layer.cu:75-132. */

@@ -36,7 +36,9 @@ int scatter_inv_launch(const mc_desc*, const void*, const void*, size_t, void*, 
 int tap_gather_sum_launch(const mc_desc*, const void*, const void*, size_t, void*, cudaStream_t);
 size_t invmap_bytes(const mc_desc*);
 size_t invmap_build_ws(const mc_desc*);
-int invmap_build_launch(const mc_desc*, const void*, void*, void*, size_t, cudaStream_t);
+int invmap_build_launch(const mc_desc*, const void*, const void*, void*, void*, size_t, cudaStream_t);
+bool weighted_fold(const mc_desc*, mc_desc*);
+int tapmap_build_weighted_launch(const mc_desc*, const void*, const void*, void*, cudaStream_t);
 bool conv_tc_wgrad_supported(const mc_desc*);
 size_t conv_tc_wgrad_ws(const mc_desc*);
 int conv_tc_wgrad_launch(const mc_desc*, const void*, const void*, const void*, void*, void*, void*,
@@ -151,7 +153,36 @@ int mc_invmap_build(const mc_desc* d, const void* map, void* inv, size_t inv_byt
   if (!map || !inv) return MC_ERR_BAD_ARG;
   if (!invmap_supported(d)) return MC_ERR_UNSUPPORTED;
   if (inv_bytes < invmap_bytes(d)) return MC_ERR_WORKSPACE;
-  return invmap_build_launch(d, map, inv, ws, ws_bytes, (cudaStream_t)stream);
+  return invmap_build_launch(d, map, nullptr, inv, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+// ---- plans of weighted maps ------------------------------------------------------------------------
+int mc_weighted_plan_desc(const mc_desc* d, mc_desc* folded) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!folded) return MC_ERR_BAD_ARG;
+  if (d->dtype == MC_F64 || !weighted_fold(d, folded)) return MC_ERR_UNSUPPORTED;
+  return MC_OK;
+}
+int mc_tapmap_build_weighted(const mc_desc* d, const void* map, const void* iw, void* tapmap,
+                             size_t tapmap_bytes_, void* stream) {
+  mc_desc f;
+  int rc = mc_weighted_plan_desc(d, &f);
+  if (rc) return rc;
+  if (!map || !iw || !tapmap) return MC_ERR_BAD_ARG;
+  if (mc_tapmap_bytes(&f) == 0) return MC_ERR_UNSUPPORTED;
+  if (tapmap_bytes_ < tapmap_bytes(&f)) return MC_ERR_WORKSPACE;
+  return tapmap_build_weighted_launch(d, map, iw, tapmap, (cudaStream_t)stream);
+}
+int mc_invmap_build_weighted(const mc_desc* d, const void* map, const void* iw, void* inv, size_t inv_bytes,
+                             void* ws, size_t ws_bytes, void* stream) {
+  mc_desc f;
+  int rc = mc_weighted_plan_desc(d, &f);
+  if (rc) return rc;
+  if (!map || !iw || !inv) return MC_ERR_BAD_ARG;
+  if (!invmap_supported(&f)) return MC_ERR_UNSUPPORTED;
+  if (inv_bytes < invmap_bytes(&f)) return MC_ERR_WORKSPACE;
+  return invmap_build_launch(d, map, iw, inv, ws, ws_bytes, (cudaStream_t)stream);
 }
 // adjoint ops (average unpooling, resample scatter) as gathers through the inverse map
 static int scatter_inv_check(const mc_desc* d, const void* a, const void* b, const void* c) {

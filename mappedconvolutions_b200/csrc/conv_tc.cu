@@ -1542,6 +1542,8 @@ __global__ void weight_image_kernel(const bf16* __restrict__ w, uint16_t* __rest
 
 struct InvArgs {
   const float* map;
+  const float* iw;  // weighted maps: (ngrid, K, P) weights of the P points of every tap; else null
+  int P;            // points per tap of a weighted map, 0 for a plain map
   int* cnt;  // pass 1: per-key counts; pass 2: per-key cursors
   const int* off;
   int2* ent;
@@ -1556,17 +1558,22 @@ __global__ void invmap_pass_kernel(InvArgs a) {
        i += (long)gridDim.x * blockDim.x) {
     const long p = i / a.K;
     const int k = (int)(i % a.K);
-    const float2 m = __ldg(reinterpret_cast<const float2*>(a.map) + i);
-    Tap<float> tp;
-    decode_tap<float, float>(m.x, m.y, a.IH, a.IW, a.interp, tp);
-    for (int c = 0; c < tp.n; ++c) {
-      if (tp.off[c] < 0 || tp.w[c] == 0.f) continue;
-      const long key = (long)tp.off[c] * a.K + k;
-      if (PASS == 1) {
-        atomicAdd(a.cnt + key, 1);
-      } else {
-        const int pos = a.off[key] + atomicAdd(a.cnt + key, 1);
-        a.ent[pos] = make_int2((int)p, __float_as_int(tp.w[c]));
+    const int np = a.P > 0 ? a.P : 1;
+    for (int pt = 0; pt < np; ++pt) {
+      const float2 m = __ldg(reinterpret_cast<const float2*>(a.map) + i * np + pt);
+      const float wp = a.P > 0 ? __ldg(a.iw + i * np + pt) : 1.f;
+      Tap<float> tp;
+      decode_tap<float, float>(m.x, m.y, a.IH, a.IW, a.interp, tp);
+      for (int c = 0; c < tp.n; ++c) {
+        const float wc = a.P > 0 ? __fmul_rn(wp, tp.w[c]) : tp.w[c];
+        if (tp.off[c] < 0 || wc == 0.f) continue;
+        const long key = (long)tp.off[c] * a.K + k;
+        if (PASS == 1) {
+          atomicAdd(a.cnt + key, 1);
+        } else {
+          const int pos = a.off[key] + atomicAdd(a.cnt + key, 1);
+          a.ent[pos] = make_int2((int)p, __float_as_int(wc));
+        }
       }
     }
   }
@@ -1606,6 +1613,39 @@ __global__ void tapmap_build_kernel(const float* __restrict__ map, TapEnt* __res
       w[c] = on ? tp.w[c] : 0.f;
     }
     if (out32) out32[i] = off[0];  // nearest: the one source pixel, -1 when the tap reads nothing
+    seal_entry(off, w);
+    uint4* dst = reinterpret_cast<uint4*>(out + i);
+    dst[0] = make_uint4(off[0], off[1], off[2], off[3]);
+    dst[1] = make_uint4(__float_as_uint(w[0]), __float_as_uint(w[1]), __float_as_uint(w[2]),
+                        __float_as_uint(w[3]));
+  }
+}
+
+// Tap table of a WEIGHTED map (include/core/resample.h:145-162: a tap is the sum over P points of
+// weight x sample): the points' source pixels with weight = point weight x interpolation weight,
+// packed into the four corners of a TapEnt.  The launcher guarantees P x (corners per point) <= 4,
+// e.g. the three barycentric vertices of an icosphere tap with nearest sampling.
+__global__ void tapmap_build_weighted_kernel(const float* __restrict__ map, const float* __restrict__ iw,
+                                             int P, TapEnt* __restrict__ out, long n, int SH, int SW,
+                                             int interp) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    int off[4] = {-1, -1, -1, -1};
+    float w[4] = {0.f, 0.f, 0.f, 0.f};
+    int nc = 0;
+    for (int pt = 0; pt < P; ++pt) {
+      const float2 m = __ldg(reinterpret_cast<const float2*>(map) + i * P + pt);
+      const float wp = __ldg(iw + i * P + pt);
+      Tap<float> tp;
+      decode_tap<float, float>(m.x, m.y, SH, SW, interp, tp);
+      for (int c = 0; c < tp.n; ++c) {
+        const float wc = __fmul_rn(wp, tp.w[c]);
+        if (tp.off[c] < 0 || wc == 0.f || nc >= 4) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j == nc) { off[j] = tp.off[c]; w[j] = wc; }
+        ++nc;
+      }
+    }
     seal_entry(off, w);
     uint4* dst = reinterpret_cast<uint4*>(out + i);
     dst[0] = make_uint4(off[0], off[1], off[2], off[3]);
@@ -1814,6 +1854,30 @@ int tapmap_build_launch(const mc_desc* d, const void* map, void* tab, cudaStream
   return MC_OK;
 }
 
+// A weighted map whose taps fit a TapEnt (P points x corners per point <= 4) is "folded": its plans
+// are built from (map, weights) and then used exactly like the plans of a plain bilinear map, under
+// the descriptor this returns in *folded (P = 0, interp = bilinear: four weighted corners per tap).
+bool weighted_fold(const mc_desc* d, mc_desc* folded) {
+  if (d->P <= 0) return false;
+  const int corners = (d->interp == 1 || d->interp == 2) ? 4 : 1;
+  if (d->P * corners > 4) return false;
+  *folded = *d;
+  folded->P = 0;
+  folded->interp = 1;
+  return true;
+}
+
+int tapmap_build_weighted_launch(const mc_desc* d, const void* map, const void* iw, void* tab,
+                                 cudaStream_t st) {
+  if (!aligned16(map) || !aligned16(tab)) return MC_ERR_BAD_ARG;
+  const long n = (long)d->OH * d->OW * d->K;
+  tapmap_build_weighted_kernel<<<grid_for(n, 256), 256, 0, st>>>((const float*)map, (const float*)iw, d->P,
+                                                                 (TapEnt*)tab, n, d->IH, d->IW, d->interp),
+      MC_COUNT(1);
+  MC_CHECK_LAUNCH();
+  return MC_OK;
+}
+
 // map != null: the kernel decodes the map itself; tab != null: prebuilt table (tapmap_build_launch)
 static int fwd_launch_impl(const mc_desc* d, const void* x, const void* map, const void* tab,
                            const void* w, const void* bias, void* y, void* ws, size_t ws_bytes,
@@ -1902,8 +1966,16 @@ size_t invmap_build_ws(const mc_desc* d) {
   return (((nkeys + 1) * sizeof(int) + 255) & ~(size_t)255) + scan_temp_bytes(nkeys + 1);
 }
 
-int invmap_build_launch(const mc_desc* d, const void* map, void* inv, void* ws, size_t ws_bytes,
-                        cudaStream_t st) {
+// iw != null: d_in is a weighted descriptor that folds (weighted_fold); the buffer then has the layout
+// of the folded descriptor, which is the one the consumers are called with.
+int invmap_build_launch(const mc_desc* d_in, const void* map, const void* iw, void* inv, void* ws,
+                        size_t ws_bytes, cudaStream_t st) {
+  mc_desc folded;
+  const mc_desc* d = d_in;
+  if (iw) {
+    if (!weighted_fold(d_in, &folded)) return MC_ERR_UNSUPPORTED;
+    d = &folded;
+  }
   if (!invmap_supported(d)) return MC_ERR_UNSUPPORTED;
   if (!ws || ws_bytes < invmap_build_ws(d)) return MC_ERR_WORKSPACE;
   if (!aligned16(inv) || !aligned16(ws)) return MC_ERR_BAD_ARG;
@@ -1911,11 +1983,13 @@ int invmap_build_launch(const mc_desc* d, const void* map, void* inv, void* ws, 
   const size_t cnt_bytes = ((nkeys + 1) * sizeof(int) + 255) & ~(size_t)255;
   InvArgs a;
   a.map = (const float*)map;
+  a.iw = (const float*)iw;
+  a.P = iw ? d_in->P : 0;
   a.cnt = (int*)ws;
   a.off = (const int*)inv;
   a.ent = (int2*)((uint8_t*)inv + inv_off_bytes(d));
   a.ngrid = (long)d->OH * d->OW;
-  a.K = d->K; a.IH = d->IH; a.IW = d->IW; a.interp = d->interp;
+  a.K = d->K; a.IH = d->IH; a.IW = d->IW; a.interp = d_in->interp;
   if (cudaMemsetAsync(a.cnt, 0, (nkeys + 1) * sizeof(int), st) != cudaSuccess) return MC_ERR_LAUNCH;
   const int grid = grid_for(a.ngrid * a.K, 256);
   invmap_pass_kernel<1><<<grid, 256, 0, st>>>(a), MC_COUNT(1);

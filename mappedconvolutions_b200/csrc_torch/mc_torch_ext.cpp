@@ -152,14 +152,18 @@ struct PlanKey {
   int64_t version;
   std::vector<int64_t> shape;
   int IH, IW, interp, device;
+  const void* iw_data = nullptr;  // plans of weighted maps: the interpolation-weight tensor as well
+  int64_t iw_version = 0;
   bool operator==(const PlanKey& o) const {
     return kind == o.kind && data == o.data && version == o.version && shape == o.shape &&
-           IH == o.IH && IW == o.IW && interp == o.interp && device == o.device;
+           IH == o.IH && IW == o.IW && interp == o.interp && device == o.device &&
+           iw_data == o.iw_data && iw_version == o.iw_version;
   }
 };
 struct PlanEntry {
   PlanKey key;
   c10::weak_intrusive_ptr<c10::TensorImpl> owner;
+  c10::weak_intrusive_ptr<c10::TensorImpl> owner_iw;  // (the map again for plain maps)
   Tensor buf;
   Tensor aux;  // second buffer of the plan (row plans: the host copy)
 };
@@ -179,29 +183,37 @@ std::mutex& plan_mutex() {
 // read the cached buffer from any stream without further ordering.
 // build() returns (device buffer, auxiliary buffer or an undefined tensor)
 template <typename Build>
-std::pair<Tensor, Tensor> cached_plan2(int kind, const mc_desc& d, const Tensor& map, Build build) {
+std::pair<Tensor, Tensor> cached_plan2(int kind, const mc_desc& d, const Tensor& map, Build build,
+                                       const Tensor* iw = nullptr) {
   PlanKey key{kind, map.data_ptr(), (int64_t)map._version(), map.sizes().vec(), d.IH, d.IW, d.interp,
               (int)map.device().index()};
+  const Tensor& second = iw ? *iw : map;
+  if (iw) {
+    key.iw_data = iw->data_ptr();
+    key.iw_version = (int64_t)iw->_version();
+  }
   std::lock_guard<std::mutex> lock(plan_mutex());
   auto& c = plan_cache();
   for (auto it = c.begin(); it != c.end(); ++it) {
     if (it->key == key && !it->owner.expired() &&
-        it->owner.lock().get() == map.unsafeGetTensorImpl()) {
+        it->owner.lock().get() == map.unsafeGetTensorImpl() && !it->owner_iw.expired() &&
+        it->owner_iw.lock().get() == second.unsafeGetTensorImpl()) {
       if (it != c.begin()) c.splice(c.begin(), c, it);
       return {c.front().buf, c.front().aux};
     }
   }
   std::pair<Tensor, Tensor> p = build();
   c10::cuda::getCurrentCUDAStream().synchronize();
-  c.push_front(PlanEntry{key, c10::weak_intrusive_ptr<c10::TensorImpl>(map.getIntrusivePtr()), p.first,
+  c.push_front(PlanEntry{key, c10::weak_intrusive_ptr<c10::TensorImpl>(map.getIntrusivePtr()),
+                         c10::weak_intrusive_ptr<c10::TensorImpl>(second.getIntrusivePtr()), p.first,
                          p.second});
   while (c.size() > PLAN_CACHE_SIZE) c.pop_back();
   return p;
 }
 
 template <typename Build>
-Tensor cached_plan(int kind, const mc_desc& d, const Tensor& map, Build build) {
-  return cached_plan2(kind, d, map, [&]() { return std::make_pair(build(), Tensor()); }).first;
+Tensor cached_plan(int kind, const mc_desc& d, const Tensor& map, Build build, const Tensor* iw = nullptr) {
+  return cached_plan2(kind, d, map, [&]() { return std::make_pair(build(), Tensor()); }, iw).first;
 }
 
 Tensor inverse_map(const mc_desc& d, const Tensor& map) {
@@ -223,6 +235,34 @@ Tensor tap_map(const mc_desc& d, const Tensor& map) {
     check(mc_tapmap_build(&d, map.data_ptr(), tab.data_ptr(), n, cur_stream()));
     return tab;
   });
+}
+
+// Weighted maps whose taps fit a tap-table record (mc_weighted_plan_desc: P points x corners per point
+// <= 4, e.g. barycentric icosphere taps with nearest sampling) get the same two plans, built from
+// (map, interp_weights); the calls that use them run under the folded descriptor *f.
+bool weighted_folds(const mc_desc& d, const OptTensor& iw, mc_desc* f) {
+  return iw.has_value() && iw->scalar_type() == at::kFloat && mc_weighted_plan_desc(&d, f) == MC_OK;
+}
+
+Tensor inverse_map_weighted(const mc_desc& d, const mc_desc& f, const Tensor& map, const Tensor& iw) {
+  return cached_plan(3, d, map, [&]() {
+    const size_t n = mc_invmap_bytes(&f);
+    Tensor inv = at::empty({(int64_t)n}, at::TensorOptions().dtype(at::kByte).device(map.device()));
+    Scratch ws = scratch(mc_invmap_build_workspace_bytes(&f), map.device());
+    check(mc_invmap_build_weighted(&d, map.data_ptr(), iw.data_ptr(), inv.data_ptr(), n, ws.p, ws.n,
+                                   cur_stream()));
+    return inv;
+  }, &iw);
+}
+
+Tensor tap_map_weighted(const mc_desc& d, const mc_desc& f, const Tensor& map, const Tensor& iw) {
+  const size_t n = mc_tapmap_bytes(&f);
+  if (n == 0) return Tensor();
+  return cached_plan(4, d, map, [&]() {
+    Tensor tab = at::empty({(int64_t)n}, at::TensorOptions().dtype(at::kByte).device(map.device()));
+    check(mc_tapmap_build_weighted(&d, map.data_ptr(), iw.data_ptr(), tab.data_ptr(), n, cur_stream()));
+    return tab;
+  }, &iw);
 }
 
 // Row plan of a sample map that is translation invariant along image rows (spherical kernels on
@@ -261,6 +301,15 @@ void clear_plan_cache() {
   plan_cache().clear();
 }
 
+// Kinds of the cached plans, most recently used first (0 inverse map, 1 tap table, 2 row plan,
+// 3 / 4 inverse map / tap table of a weighted map): lets a test see which path a call took.
+std::vector<int64_t> plan_cache_kinds() {
+  std::lock_guard<std::mutex> lock(plan_mutex());
+  std::vector<int64_t> kinds;
+  for (const auto& e : plan_cache()) kinds.push_back(e.key.kind);
+  return kinds;
+}
+
 Tensor channels_last(const Tensor& t) { return t.contiguous(at::MemoryFormat::ChannelsLast); }
 
 // The tensor-core kernels read rows with 16-byte vector loads and bulk copies.  A view into a larger
@@ -276,9 +325,15 @@ Tensor aligned16(const Tensor& t) {
 // contiguous in both layouts at once and counts as NCHW: it is rerouted too, at no cost, and the
 // result comes back in NCHW.  The rerouted call passes nhwc = true.)
 bool via_channels_last(const Tensor& input, const OptTensor& iw, mc_desc d_nhwc) {
-  if (iw.has_value() || input.scalar_type() != at::kBFloat16 || input.dim() != 4) return false;
+  if (input.scalar_type() != at::kBFloat16 || input.dim() != 4) return false;
   if (layout_of(input) != MC_NCHW) return false;
   d_nhwc.layout = MC_NHWC;
+  if (iw.has_value()) {
+    d_nhwc.P = (int32_t)iw->size(-1);
+    mc_desc f;
+    if (!weighted_folds(d_nhwc, iw, &f)) return false;
+    d_nhwc = f;
+  }
   return mc_conv_fwd_workspace_bytes(&d_nhwc) > 0;
 }
 
@@ -296,7 +351,7 @@ Tensor conv_forward(const Tensor& input_in, const Tensor& sample_map_in, const O
   const int64_t Cout = weight.size(0), OH = sample_map.size(0), OW = sample_map.size(1);
   if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH,
                                                       IW, OH, OW, K, 0, interp)))
-    return conv_forward(channels_last(input), sample_map, c10::nullopt, weight, bias, K, interp, true,
+    return conv_forward(channels_last(input), sample_map, iw, weight, bias, K, interp, true,
                         relu).contiguous();
   const int layout = nhwc ? MC_NHWC : layout_of(input);
   check_map(input, sample_map, iw);
@@ -317,6 +372,17 @@ Tensor conv_forward(const Tensor& input_in, const Tensor& sample_map_in, const O
     }
   }
   if (relu) d.flags |= MC_FLAG_RELU;
+  mc_desc f;
+  if (weighted_folds(d, iw, &f) && mc_conv_fwd_workspace_bytes(&f) > 0) {
+    // weighted map on the tensor cores: its points folded into the tap table (f keeps d's flags)
+    Scratch wsf = scratch(mc_conv_fwd_workspace_bytes(&f), dev);
+    Tensor tabw = tap_map_weighted(d, f, sample_map, *iw);
+    if (tabw.defined()) {
+      check(mc_conv_fwd_tap(&f, input.data_ptr(), tabw.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                            y.data_ptr(), wsf.p, wsf.n, cur_stream()));
+      return y;
+    }
+  }
   Scratch ws = scratch(mc_conv_fwd_workspace_bytes(&d), dev);
   Tensor tab = (ws.n && !iw.has_value()) ? tap_map(d, sample_map) : Tensor();
   if (tab.defined())  // tensor-core path with the map decoded once per map tensor
@@ -353,7 +419,7 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
   const int64_t Cout = weight.size(0), OH = sample_map.size(0), OW = sample_map.size(1);
   if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cin, Cout, IH,
                                                       IW, OH, OW, K, 0, interp))) {
-    auto g = conv_backward(channels_last(grad_output_in), sample_map, c10::nullopt,
+    auto g = conv_backward(channels_last(grad_output_in), sample_map, iw,
                            channels_last(input), weight, bias, K, interp, need_input_grad, true,
                            need_weight_grad);
     if (g[0].defined()) g[0] = g[0].contiguous();
@@ -362,8 +428,13 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
   const int layout = nhwc ? MC_NHWC : layout_of(input);
   const Tensor grad_output = aligned16(as_layout(grad_output_in, layout));
   check_map(input, sample_map, iw);
-  const mc_desc d = make_desc(input.scalar_type(), layout, B, Cin, Cout, IH, IW, OH, OW, K,
-                              n_interp(iw), interp);
+  const mc_desc d_map = make_desc(input.scalar_type(), layout, B, Cin, Cout, IH, IW, OH, OW, K,
+                                  n_interp(iw), interp);
+  // A weighted map that folds runs everything below under the folded descriptor, with plans built
+  // from (map, interp_weights); any other weighted map has no plans and takes the plain entry points.
+  mc_desc f;
+  const bool folded = weighted_folds(d_map, iw, &f);
+  const mc_desc d = folded ? f : d_map;
   const auto acc = input.scalar_type() == at::kDouble ? at::kDouble : at::kFloat;
   Tensor gx = need_input_grad ? empty_in(input.sizes(), input, layout) : Tensor();
   Tensor gw = at::empty(weight.sizes(), weight.options().dtype(acc));
@@ -376,8 +447,9 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
                                 weight.data_ptr(), nullptr, gx.data_ptr(), wsr.p, wsr.n, cur_stream()));
     need_input_grad = false;  // done
   }
-  Tensor inv = (need_input_grad && mc_conv_dgrad_inv_supported(&d)) ? inverse_map(d, sample_map)
-                                                                     : Tensor();
+  Tensor inv;
+  if (need_input_grad && (folded || !iw.has_value()) && mc_conv_dgrad_inv_supported(&d))
+    inv = folded ? inverse_map_weighted(d_map, f, sample_map, *iw) : inverse_map(d, sample_map);
   if (need_input_grad && inv.defined() && contract_first(d)) {
     // more output than input channels: contract with the weights first (one dense GEMM), then
     // gather-sum the narrow rows through the inverse map
@@ -388,14 +460,14 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
     need_input_grad = false;  // done
   }
   const size_t n_dgrad = inv.defined() ? mc_conv_dgrad_inv_workspace_bytes(&d)
-                                       : mc_conv_dgrad_workspace_bytes(&d);
-  Scratch ws = scratch(std::max(n_dgrad, mc_conv_wgrad_workspace_bytes(&d)), dev);
+                                       : mc_conv_dgrad_workspace_bytes(&d_map);
+  Scratch ws = scratch(std::max(n_dgrad, mc_conv_wgrad_workspace_bytes(&d_map)), dev);
   if (!need_input_grad) {
   } else if (inv.defined()) {
     check(mc_conv_dgrad_inv(&d, grad_output.data_ptr(), inv.data_ptr(), weight.data_ptr(), nullptr,
                             gx.data_ptr(), ws.p, ws.n, cur_stream()));
   } else {
-    check(mc_conv_dgrad(&d, grad_output.data_ptr(), sample_map.data_ptr(), ptr(iw),
+    check(mc_conv_dgrad(&d_map, grad_output.data_ptr(), sample_map.data_ptr(), ptr(iw),
                         weight.data_ptr(), nullptr, gx.data_ptr(), ws.p, ws.n, cur_stream()));
   }
   if (!need_weight_grad) return {gx, Tensor(), Tensor()};
@@ -406,13 +478,14 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
                                 cur_stream()));
     return {gx, gw.to(weight.scalar_type()), gb.to(bias.scalar_type())};
   }
-  Tensor tab = iw.has_value() ? Tensor() : tap_map(d, sample_map);
+  Tensor tab = folded ? tap_map_weighted(d_map, f, sample_map, *iw)
+                      : (iw.has_value() ? Tensor() : tap_map(d, sample_map));
   int rc = MC_ERR_UNSUPPORTED;
   if (tab.defined())  // weight / bias gradient on the tensor cores from the prebuilt table
     rc = mc_conv_wgrad_tap(&d, grad_output.data_ptr(), input.data_ptr(), tab.data_ptr(),
                            gw.data_ptr(), gb.data_ptr(), cur_stream());
   if (rc == MC_ERR_UNSUPPORTED)  // shapes only the generic kernels take
-    rc = mc_conv_wgrad(&d, grad_output.data_ptr(), input.data_ptr(), sample_map.data_ptr(), ptr(iw),
+    rc = mc_conv_wgrad(&d_map, grad_output.data_ptr(), input.data_ptr(), sample_map.data_ptr(), ptr(iw),
                        gw.data_ptr(), gb.data_ptr(), ws.p, ws.n, cur_stream());
   check(rc);
   return {gx, gw.to(weight.scalar_type()), gb.to(bias.scalar_type())};
@@ -806,6 +879,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // VotingResampleToMap, include/nn/layers/voting_resample_layer.h:34-58
   m.def("voting_resample_to_map", &voting_resample_to_map);
   m.def("clear_plan_cache", &clear_plan_cache);
+  m.def("plan_cache_kinds", &plan_cache_kinds);
   // Row plans (the fast path for maps that are translation invariant along image rows) on / off;
   // returns the previous setting.  Off: every map takes the general kernels.
   m.def("set_row_plans", [](bool on) { const bool was = g_row_plans; g_row_plans = on; return was; });

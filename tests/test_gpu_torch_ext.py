@@ -181,3 +181,63 @@ def test_row_plans_through_the_layer_api(ext):
         H.assert_close(got.float(), ref, 2e-2, "row plan " + name + " vs oracle")
         H.assert_close(other.float(), ref, 2e-2, "general " + name + " vs oracle")
     assert not torch.equal(fast[0], slow[0])   # two different kernels really ran
+
+
+def _weighted_case(P, interp, shape, seed):
+    """bf16 channels-last tensors and a weighted map: P points per tap with positive weights that
+    sum to one (barycentric style); point coordinates include a few outside the image."""
+    B, Cin, Cout, IH, IW, OH, OW, K = shape
+    g = torch.Generator().manual_seed(seed)
+    c = lambda t: _cl(t.to(torch.bfloat16).cuda())
+    x, gy = c(torch.randn(B, Cin, IH, IW, generator=g)), c(torch.randn(B, Cout, OH, OW, generator=g))
+    w = torch.randn(Cout, Cin, K, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(Cout, generator=g).to(torch.bfloat16).cuda()
+    m = torch.rand(OH, OW, K, P, 2, generator=g) * torch.tensor([IW + 1.0, IH + 1.0]) - 1.0
+    if interp == 0:
+        m = m.round()
+    iw = torch.rand(OH, OW, K, P, generator=g) + 0.05
+    iw = iw / iw.sum(-1, keepdim=True)
+    iw[0, 0, 0, 0] = 0.0                                   # a point that contributes nothing
+    return x, gy, w, b, m.float().cuda().contiguous(), iw.float().cuda().contiguous()
+
+
+@pytest.mark.parametrize("name,P,interp,shape,kinds", [
+    ("barycentric 64->128", 3, 0, (2, 64, 128, 1, 642, 1, 642, 7), {3, 4}),
+    ("barycentric 64->64", 3, 0, (3, 64, 64, 1, 300, 1, 300, 7), {3, 4}),
+    ("four points", 4, 0, (1, 128, 64, 12, 20, 16, 32, 5), {3, 4}),
+    ("one bilinear point", 1, 1, (2, 64, 64, 12, 20, 16, 32, 4), {3, 4}),
+    ("first layer 3->64", 3, 0, (2, 3, 64, 1, 642, 1, 642, 7), {4}),
+    ("three bilinear points: does not fold", 3, 1, (1, 64, 64, 12, 20, 16, 32, 3), set()),
+])
+def test_weighted_conv_on_the_tensor_cores(ext, name, P, interp, shape, kinds):
+    """A weighted map whose points fit a tap-table record runs on the tensor-core kernels with plans
+    built from (map, weights); the result is the reference's weighted convolution (oracle, fp32 on
+    the bf16-rounded tensors) within the bf16 tolerance, and equals the generic kernels' within it."""
+    from mappedconvolutions_b200 import ops
+    from oracle import oracle
+    B, Cin, Cout, IH, IW, OH, OW, K = shape
+    x, gy, w, b, m, iw = _weighted_case(P, interp, shape, seed=sum(shape) + P)
+    tol = H.TOL[torch.bfloat16]
+    ext.clear_plan_cache()
+    for _ in range(2):  # the second round runs on cached plans
+        y = ext.weighted_mapped_conv_forward(x, m, iw, w, b, K, interp)
+        g = ext.weighted_mapped_conv_backward(gy, m, iw, x, w, b, K, interp)
+    assert set(ext.plan_cache_kinds()) == kinds, name
+    assert ext.device_status() == 0
+    cpu = lambda t: t.float().cpu().contiguous()
+    y_ref = oracle.weighted_mapped_conv_forward(cpu(x), m.cpu(), iw.cpu(), cpu(w), cpu(b), K, interp)
+    g_ref = oracle.weighted_mapped_conv_backward(cpu(gy), m.cpu(), iw.cpu(), cpu(x), cpu(w), cpu(b), K, interp)
+    H.assert_close(cpu(y), y_ref, tol, name + " forward")
+    for got, want, what in zip(g, g_ref, ("grad_input", "grad_weight", "grad_bias")):
+        H.assert_close(cpu(got), want, tol, name + " " + what)
+    y_gen = ops.weighted_mapped_conv_forward(x, m, iw, w, b, K, interp)
+    H.assert_close(cpu(y), cpu(y_gen), tol, name + " forward vs generic kernels")
+    # the map tensor alone does not identify the plan: other weights, other result
+    iw2 = (iw.flip(-1) if P > 1 else iw * 0.5).contiguous()
+    y2 = ext.weighted_mapped_conv_forward(x, m, iw2, w, b, K, interp)
+    y2_ref = oracle.weighted_mapped_conv_forward(cpu(x), m.cpu(), iw2.cpu(), cpu(w), cpu(b), K, interp)
+    H.assert_close(cpu(y2), y2_ref, tol, name + " forward with other weights")
+    # NCHW activations are rerouted through channels-last and come back in NCHW
+    y_nchw = ext.weighted_mapped_conv_forward(x.contiguous(), m, iw, w, b, K, interp)
+    assert y_nchw.is_contiguous()
+    H.assert_close(cpu(y_nchw), y_ref, tol, name + " forward from NCHW")
