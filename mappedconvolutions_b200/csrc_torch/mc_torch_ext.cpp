@@ -507,7 +507,7 @@ Tensor tconv_forward(const Tensor& input_in, const Tensor& sample_map_in, const 
   // the same layer seen as a convolution: the sampled image carries C_out channels, the grid C_in
   if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cout, Cin, OHt,
                                                       OWt, H, W, K, 0, interp)))
-    return tconv_forward(channels_last(input), sample_map, c10::nullopt, weight, bias, OHt, OWt, K,
+    return tconv_forward(channels_last(input), sample_map, iw, weight, bias, OHt, OWt, K,
                          interp, true).contiguous();
   const int layout = nhwc ? MC_NHWC : layout_of(input);
   check_map(input, sample_map, iw);
@@ -518,11 +518,14 @@ Tensor tconv_forward(const Tensor& input_in, const Tensor& sample_map_in, const 
                                n_interp(iw), interp);
   Tensor y = empty_in({B, Cout, OHt, OWt}, input, layout);
   c10::cuda::CUDAGuard guard(dev);
-  if (!iw.has_value() && mc_conv_dgrad_inv_supported(&ds)) {
+  mc_desc fs;
+  const bool folded = weighted_folds(ds, iw, &fs);  // weighted map with plans (see conv_backward)
+  const mc_desc dsu = folded ? fs : ds;
+  if ((folded || !iw.has_value()) && mc_conv_dgrad_inv_supported(&dsu)) {
     // its input gradient IS this forward pass: the gather-form tensor-core dgrad serves
-    Tensor inv = inverse_map(ds, sample_map);
-    Scratch ws = scratch(mc_conv_dgrad_inv_workspace_bytes(&ds), dev);
-    check(mc_conv_dgrad_inv(&ds, input.data_ptr(), inv.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+    Tensor inv = folded ? inverse_map_weighted(ds, fs, sample_map, *iw) : inverse_map(ds, sample_map);
+    Scratch ws = scratch(mc_conv_dgrad_inv_workspace_bytes(&dsu), dev);
+    check(mc_conv_dgrad_inv(&dsu, input.data_ptr(), inv.data_ptr(), weight.data_ptr(), bias.data_ptr(),
                             y.data_ptr(), ws.p, ws.n, cur_stream()));
     return y;
   }
@@ -550,7 +553,7 @@ std::vector<Tensor> tconv_backward(const Tensor& grad_output_in, const Tensor& s
   const int64_t OHt = grad_output_in.size(2), OWt = grad_output_in.size(3);
   if (!nhwc && via_channels_last(input, iw, make_desc(input.scalar_type(), MC_NHWC, B, Cout, Cin, OHt,
                                                       OWt, H, W, K, 0, interp))) {
-    auto g = tconv_backward(channels_last(grad_output_in), sample_map, c10::nullopt,
+    auto g = tconv_backward(channels_last(grad_output_in), sample_map, iw,
                             channels_last(input), weight, bias, K, interp, true);
     g[0] = g[0].contiguous();
     return g;
@@ -567,18 +570,22 @@ std::vector<Tensor> tconv_backward(const Tensor& grad_output_in, const Tensor& s
   Tensor gw = at::empty(weight.sizes(), weight.options().dtype(acc));
   Tensor gb = at::empty({Cout}, weight.options().dtype(acc));
   c10::cuda::CUDAGuard guard(dev);
-  Tensor tab = iw.has_value() ? Tensor() : tap_map(ds, sample_map);
-  if (tab.defined() && mc_conv_fwd_workspace_bytes(&ds)) {
+  mc_desc fs;
+  const bool folded = weighted_folds(ds, iw, &fs);  // weighted map with plans (see conv_backward)
+  const mc_desc dsu = folded ? fs : ds;
+  Tensor tab = folded ? tap_map_weighted(ds, fs, sample_map, *iw)
+                      : (iw.has_value() ? Tensor() : tap_map(ds, sample_map));
+  if (tab.defined() && mc_conv_fwd_workspace_bytes(&dsu)) {
     // tensor-core path: input gradient = forward of the equivalent convolution applied to
     // grad_output; weight gradient = its weight gradient with the two tensors swapped
-    Scratch ws = scratch(mc_conv_fwd_workspace_bytes(&ds), dev);
-    check(mc_conv_fwd_tap(&ds, grad_output.data_ptr(), tab.data_ptr(), weight.data_ptr(), nullptr,
+    Scratch ws = scratch(std::max(mc_conv_fwd_workspace_bytes(&dsu), mc_conv_wgrad_workspace_bytes(&ds)), dev);
+    check(mc_conv_fwd_tap(&dsu, grad_output.data_ptr(), tab.data_ptr(), weight.data_ptr(), nullptr,
                           gx.data_ptr(), ws.p, ws.n, cur_stream()));
-    int rc = mc_conv_wgrad_tap(&ds, input.data_ptr(), grad_output.data_ptr(), tab.data_ptr(),
+    int rc = mc_conv_wgrad_tap(&dsu, input.data_ptr(), grad_output.data_ptr(), tab.data_ptr(),
                                gw.data_ptr(), nullptr, cur_stream());
     if (rc == MC_ERR_UNSUPPORTED)
       rc = mc_conv_wgrad(&ds, input.data_ptr(), grad_output.data_ptr(), sample_map.data_ptr(),
-                         nullptr, gw.data_ptr(), nullptr, ws.p, ws.n, cur_stream());
+                         ptr(iw), gw.data_ptr(), nullptr, ws.p, ws.n, cur_stream());
     check(rc);
     const mc_desc db = make_desc(input.scalar_type(), layout, B, Cout, Cout, OHt, OWt, OHt, OWt, 1, 0,
                                  interp);

@@ -5,6 +5,7 @@ import pytest
 import torch
 
 import helpers as H
+import helpers as H_mod  # (tests that use H for a height)
 
 pytestmark = pytest.mark.gpu
 
@@ -241,3 +242,39 @@ def test_weighted_conv_on_the_tensor_cores(ext, name, P, interp, shape, kinds):
     y_nchw = ext.weighted_mapped_conv_forward(x.contiguous(), m, iw, w, b, K, interp)
     assert y_nchw.is_contiguous()
     H.assert_close(cpu(y_nchw), y_ref, tol, name + " forward from NCHW")
+
+
+@pytest.mark.parametrize("name,P,interp,shape,kinds", [
+    ("barycentric 64->128", 3, 0, (2, 64, 128, 1, 300, 1, 642, 7), {3, 4}),
+    ("two points 128->64", 2, 0, (1, 128, 64, 12, 20, 16, 32, 5), {3, 4}),
+    ("three bilinear points: does not fold", 3, 1, (1, 64, 64, 12, 20, 16, 32, 3), set()),
+])
+def test_weighted_transposed_conv_on_the_tensor_cores(ext, name, P, interp, shape, kinds):
+    """The transposed layer with a weighted map: x (B, Cin, H, W) lives on the map grid, the map points
+    into the (OH, OW) result; same plans as the weighted convolution, roles swapped."""
+    from oracle import oracle
+    B, Cin, Cout, H, W, OH, OW, K = shape
+    g = torch.Generator().manual_seed(sum(shape) + 7 * P)
+    c = lambda t: _cl(t.to(torch.bfloat16).cuda())
+    x, gy = c(torch.randn(B, Cin, H, W, generator=g)), c(torch.randn(B, Cout, OH, OW, generator=g))
+    w = torch.randn(Cin, Cout, K, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(Cout, generator=g).to(torch.bfloat16).cuda()
+    m = torch.rand(H, W, K, P, 2, generator=g) * torch.tensor([OW + 1.0, OH + 1.0]) - 1.0
+    m = (m.round() if interp == 0 else m).float().cuda().contiguous()
+    iw = torch.rand(H, W, K, P, generator=g) + 0.05
+    iw = (iw / iw.sum(-1, keepdim=True)).float().cuda().contiguous()
+    tol = H_mod.TOL[torch.bfloat16]
+    ext.clear_plan_cache()
+    for _ in range(2):
+        y = ext.weighted_mapped_transposed_conv_forward(x, m, iw, w, b, OH, OW, K, interp)
+        gr = ext.weighted_mapped_transposed_conv_backward(gy, m, iw, x, w, b, K, interp)
+    assert set(ext.plan_cache_kinds()) == kinds, name
+    assert ext.device_status() == 0
+    cpu = lambda t: t.float().cpu().contiguous()
+    y_ref = oracle.weighted_mapped_transposed_conv_forward(cpu(x), m.cpu(), iw.cpu(), cpu(w), cpu(b), OH, OW, K,
+                                                           interp)
+    g_ref = oracle.weighted_mapped_transposed_conv_backward(cpu(gy), m.cpu(), iw.cpu(), cpu(x), cpu(w), cpu(b), K,
+                                                            interp)
+    H_mod.assert_close(cpu(y), y_ref, tol, name + " forward")
+    for got, want, what in zip(gr, g_ref, ("grad_input", "grad_weight", "grad_bias")):
+        H_mod.assert_close(cpu(got), want, tol, name + " " + what)
