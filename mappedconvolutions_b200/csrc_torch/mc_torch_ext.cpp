@@ -668,7 +668,12 @@ Tensor avg_unpool(const Tensor& grad_output, const Tensor& sample_map, const Opt
   Tensor gx = empty_in({d.B, d.C_in, IH, IW}, grad_output, layout);
   c10::cuda::CUDAGuard guard(dev);
   int rc = MC_ERR_UNSUPPORTED;
-  if (!iw.has_value() && mc_invmap_bytes(&d) > 0) {
+  mc_desc f;
+  if (weighted_folds(d, iw, &f) && mc_invmap_bytes(&f) > 0) {
+    // weighted map whose points fit the inverse map's records: the same gather, under the folded descriptor
+    Tensor inv = inverse_map_weighted(d, f, sample_map, *iw);
+    rc = mc_pool_avg_bwd_inv(&f, grad_output.data_ptr(), inv.data_ptr(), gx.data_ptr(), cur_stream());
+  } else if (!iw.has_value() && mc_invmap_bytes(&d) > 0) {
     // gather through the inverse map (built once per map tensor): no atomics
     Tensor inv = inverse_map(d, sample_map);
     rc = mc_pool_avg_bwd_inv(&d, grad_output.data_ptr(), inv.data_ptr(), gx.data_ptr(), cur_stream());
@@ -695,7 +700,11 @@ Tensor resample_to(const Tensor& input, const Tensor& sample_map, const OptTenso
   Tensor y = empty_in({B, C, OH, OW}, input, layout);
   c10::cuda::CUDAGuard guard(dev);
   int rc = MC_ERR_UNSUPPORTED;
-  if (!iw.has_value() && mc_invmap_bytes(&d) > 0) {
+  mc_desc f;
+  if (weighted_folds(d, iw, &f) && mc_invmap_bytes(&f) > 0) {
+    Tensor inv = inverse_map_weighted(d, f, sample_map, *iw);
+    rc = mc_resample_scatter_inv(&f, input.data_ptr(), inv.data_ptr(), y.data_ptr(), cur_stream());
+  } else if (!iw.has_value() && mc_invmap_bytes(&d) > 0) {
     Tensor inv = inverse_map(d, sample_map);
     rc = mc_resample_scatter_inv(&d, input.data_ptr(), inv.data_ptr(), y.data_ptr(), cur_stream());
   }

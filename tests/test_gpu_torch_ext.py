@@ -278,3 +278,38 @@ def test_weighted_transposed_conv_on_the_tensor_cores(ext, name, P, interp, shap
     H_mod.assert_close(cpu(y), y_ref, tol, name + " forward")
     for got, want, what in zip(gr, g_ref, ("grad_input", "grad_weight", "grad_bias")):
         H_mod.assert_close(cpu(got), want, tol, name + " " + what)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("P,interp,folds", [(3, 0, True), (1, 1, True), (3, 1, False)])
+def test_weighted_scatters_through_the_inverse_map(ext, dtype, P, interp, folds):
+    """Weighted average unpooling and weighted resample-to-map: a weighted map whose points fit the
+    inverse map's records is gathered through it (no atomics: the result repeats bit for bit), any
+    other weighted map takes the atomic scatter; both agree with the oracle."""
+    from oracle import oracle
+    B, C, IH, IW, OH, OW, K = 2, 8, 13, 21, 10, 17, 4
+    g = torch.Generator().manual_seed(100 * P + interp)
+    gy = torch.randn(B, C, OH, OW, generator=g).to(dtype).cuda()
+    m = torch.rand(OH, OW, K, P, 2, generator=g) * torch.tensor([IW + 1.0, IH + 1.0]) - 1.0
+    m = (m.round() if interp == 0 else m).float().cuda().contiguous()
+    iw = torch.rand(OH, OW, K, P, generator=g) + 0.05
+    iw = (iw / iw.sum(-1, keepdim=True)).float().cuda().contiguous()
+    tol = H_mod.TOL[dtype]
+    cpu = lambda t: t.float().cpu().contiguous()
+    ext.clear_plan_cache()
+    gx = ext.weighted_mapped_avg_unpool(gy, m, iw, IH, IW, K, interp)
+    assert (3 in ext.plan_cache_kinds()) == folds
+    H_mod.assert_close(cpu(gx), oracle.weighted_mapped_avg_unpool(cpu(gy), m.cpu(), iw.cpu(), IH, IW, K, interp), tol,
+                       "weighted avg unpool")
+    if folds:
+        assert torch.equal(gx, ext.weighted_mapped_avg_unpool(gy, m, iw, IH, IW, K, interp))
+    # resample: one tap per grid pixel
+    m1, iw1 = m[:, :, 0].contiguous(), iw[:, :, 0].contiguous()
+    iw1 = (iw1 / iw1.sum(-1, keepdim=True)).contiguous()
+    ext.clear_plan_cache()
+    y = ext.weighted_resample_to_map(gy, m1, iw1, IH, IW, interp)
+    assert (3 in ext.plan_cache_kinds()) == folds
+    H_mod.assert_close(cpu(y), oracle.weighted_resample_to_map(cpu(gy), m1.cpu(), iw1.cpu(), IH, IW, interp), tol,
+                       "weighted resample to map")
+    if folds:
+        assert torch.equal(y, ext.weighted_resample_to_map(gy, m1, iw1, IH, IW, interp))
