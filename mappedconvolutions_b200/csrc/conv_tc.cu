@@ -2094,6 +2094,8 @@ static int launch_wgrad_n(const GemmArgs& a, const WgradPlan& p, bool pre, cudaS
   return MC_OK;
 }
 
+#include "conv_smallcin.cuh"
+
 static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, const void* map,
                              const void* tab, void* gw, void* gb, cudaStream_t st) {
   if (!aligned16(gy) || !aligned16(x) || !aligned16(map) || !aligned16(tab)) return MC_ERR_BAD_ARG;
@@ -2124,6 +2126,9 @@ static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, co
     return MC_ERR_LAUNCH;
   if (gb && cudaMemsetAsync(gb, 0, (size_t)d->C_out * sizeof(float), st) != cudaSuccess)
     return MC_ERR_LAUNCH;
+  // very few input channels and a nearest map with its compact table: one pass over grad_output
+  if (tab && smallcin_wgrad_shape(d) && tapmap_compact(d, tab))
+    return smallcin_wgrad_launch(d, gy, x, tapmap_compact(d, tab), gw, gb, st);
   return p.nout == 128 ? launch_wgrad_n<128>(a, p, tab != nullptr, st)
                        : launch_wgrad_n<64>(a, p, tab != nullptr, st);
 }

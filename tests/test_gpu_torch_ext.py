@@ -313,3 +313,30 @@ def test_weighted_scatters_through_the_inverse_map(ext, dtype, P, interp, folds)
                        "weighted resample to map")
     if folds:
         assert torch.equal(y, ext.weighted_resample_to_map(gy, m1, iw1, IH, IW, interp))
+
+
+@pytest.mark.parametrize("Cin,K,Cout,B,OHW,IHW", [
+    (3, 7, 64, 5, (1, 333), (1, 333)),      # three n-tiles; images that end inside a 16-pixel step
+    (1, 9, 64, 3, (6, 11), (7, 9)),         # two n-tiles, a 2-D image, taps outside the image
+    (4, 7, 128, 2, (1, 100), (1, 50)),      # four n-tiles, two blocks of output channels
+    (2, 3, 64, 1, (1, 16), (1, 16)),        # one n-tile, one step
+    (3, 10, 64, 4, (1, 70), (1, 90)),       # 31 columns: the widest this kernel takes
+])
+def test_weight_gradient_of_layers_with_very_few_input_channels(ext, Cin, K, Cout, B, OHW, IHW):
+    """Nearest maps, K * C_in + 1 <= 32: the weight / bias gradient runs in one pass over grad_output
+    on warp-level MMAs (conv_wgrad_smallcin_kernel); against the oracle, fp32 on the bf16 tensors."""
+    from oracle import oracle
+    (OH, OW), (IH, IW) = OHW, IHW
+    g = torch.Generator().manual_seed(Cin * 100 + K)
+    c = lambda t: _cl(t.to(torch.bfloat16).cuda())
+    x, gy = c(torch.randn(B, Cin, IH, IW, generator=g)), c(torch.randn(B, Cout, OH, OW, generator=g))
+    w = torch.randn(Cout, Cin, K, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(Cout, generator=g).to(torch.bfloat16).cuda()
+    m = (torch.rand(OH, OW, K, 2, generator=g) * torch.tensor([IW + 1.0, IH + 1.0]) - 1.0).round()
+    m = m.float().cuda().contiguous()
+    gr = ext.mapped_conv_backward(gy, m, x, w, b, K, 0)
+    assert ext.device_status() == 0
+    cpu = lambda t: t.float().cpu().contiguous()
+    want = oracle.mapped_conv_backward(cpu(gy), m.cpu(), cpu(x), cpu(w), cpu(b), K, 0)
+    for got, ref, what in zip(gr, want, ("grad_input", "grad_weight", "grad_bias")):
+        H_mod.assert_close(cpu(got), ref, H_mod.TOL[torch.bfloat16], what)
