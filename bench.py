@@ -691,6 +691,22 @@ def encoder_record(steps, warmup, min_seconds=0.0):
     params = [p for p in convs.parameters()]
     lr = 1e-3
 
+    class MeanLoss(torch.autograd.Function):
+        """loss = h.float().mean().  torch's own backward of mean() expands the scalar into a dense
+        NCHW tensor; next to the channels-last activations of the layers that costs three strided
+        passes per step (the expansion, a mixed-layout ReLU gradient, a copy back to channels-last).
+        This backward writes the constant gradient once, in the activation's own layout."""
+
+        @staticmethod
+        def forward(ctx, h):
+            ctx.save_for_backward(h)
+            return h.mean(dtype=torch.float32)
+
+        @staticmethod
+        def backward(ctx, g):
+            (h,) = ctx.saved_tensors
+            return torch.empty_like(h).copy_((g / h.numel()).to(h.dtype))
+
     def step(xin):
         h = convs[0](xin, kmap[7])
         h = pool(h, pmap[7])
@@ -698,7 +714,7 @@ def encoder_record(steps, warmup, min_seconds=0.0):
         h = pool(h, pmap[6])
         h = convs[2](h, kmap[5])
         h = convs[3](h, kmap[5])
-        loss = h.mean(dtype=torch.float32)  # (float32 accumulation straight from the bf16 activation)
+        loss = MeanLoss.apply(h)  # (float32 accumulation straight from the bf16 activation)
         loss.backward()
         grads = [p.grad for p in params]
         if world > 1:
