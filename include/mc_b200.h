@@ -150,6 +150,13 @@ int mc_conv_fwd_tap(const mc_desc* d, const void* x, const void* tapmap, const v
                     const void* bias, void* y, void* ws, size_t ws_bytes, void* stream);
 int mc_conv_wgrad_tap(const mc_desc* d, const void* gy, const void* x, const void* tapmap, void* gw,
                       void* gb, void* stream);
+/* The same for a layer with a fused ReLU: gy is the gradient behind the activation, y the layer's
+ * output; the kernel uses gy where y > 0 and 0 elsewhere, so the caller needs no masked copy of gy.
+ * Only where the weight gradient is one pass over gy in registers (nearest map, K * C_in + 1 <= 32:
+ * a first layer with a handful of input channels); MC_ERR_UNSUPPORTED otherwise - mask gy and call
+ * mc_conv_wgrad_tap. */
+int mc_conv_wgrad_tap_relu(const mc_desc* d, const void* gy, const void* y, const void* x,
+                           const void* tapmap, void* gw, void* gb, void* stream);
 
 /* Inverse map: for every (input pixel, tap) the list of (grid pixel, weight) pairs whose forward
  * sample reads that input pixel.  It depends only on the sample map and the two image sizes, so

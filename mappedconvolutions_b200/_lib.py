@@ -81,6 +81,7 @@ SIGNATURES = {
     "mc_sphere_locate": (ctypes.c_int, [_vp, ctypes.c_int64, _i32, ctypes.POINTER(_vp),
                                         ctypes.POINTER(_vp), ctypes.POINTER(_vp),
                                         ctypes.POINTER(_i32), _i32, _vp, _vp, _vp, _vp]),
+    "mc_conv_wgrad_tap_relu": (ctypes.c_int, [_dp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mc_weighted_plan_desc": (ctypes.c_int, [_dp, _dp]),
     "mc_tapmap_build_weighted": (ctypes.c_int, [_dp, _vp, _vp, _vp, _sz, _vp]),
     "mc_invmap_build_weighted": (ctypes.c_int, [_dp, _vp, _vp, _vp, _sz, _vp, _sz, _vp]),

@@ -26,6 +26,8 @@ int conv_tc_dgrad_launch(const mc_desc*, const void*, const void*, const void*, 
                          void*, size_t, cudaStream_t);
 size_t tapmap_bytes(const mc_desc*);
 int tapmap_build_launch(const mc_desc*, const void*, void*, cudaStream_t);
+int conv_tc_wgrad_tab_relu_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*, void*,
+                                  cudaStream_t);
 int conv_tc_fwd_tab_launch(const mc_desc*, const void*, const void*, const void*, const void*, void*,
                            void*, size_t, cudaStream_t);
 int conv_tc_wgrad_tab_launch(const mc_desc*, const void*, const void*, const void*, void*, void*,
@@ -134,6 +136,14 @@ int mc_conv_wgrad_tap(const mc_desc* d, const void* gy, const void* x, const voi
   if (!gy || !x || !tapmap || !gw) return MC_ERR_BAD_ARG;
   if (!conv_tc_wgrad_supported(d)) return MC_ERR_UNSUPPORTED;
   return conv_tc_wgrad_tab_launch(d, gy, x, tapmap, gw, gb, (cudaStream_t)stream);
+}
+int mc_conv_wgrad_tap_relu(const mc_desc* d, const void* gy, const void* y, const void* x, const void* tapmap,
+                           void* gw, void* gb, void* stream) {
+  int rc = check_conv_desc_public(d);
+  if (rc) return rc;
+  if (!gy || !y || !x || !tapmap || !gw) return MC_ERR_BAD_ARG;
+  if (!conv_tc_wgrad_supported(d)) return MC_ERR_UNSUPPORTED;
+  return conv_tc_wgrad_tab_relu_launch(d, gy, y, x, tapmap, gw, gb, (cudaStream_t)stream);
 }
 
 // ---- inverse map and the gather-form dgrad ---------------------------------------------------

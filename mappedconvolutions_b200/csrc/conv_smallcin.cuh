@@ -29,6 +29,7 @@ __device__ __forceinline__ void scw_mma(float (&d)[4], const uint32_t (&a)[4], u
 }
 
 struct SmallCinArgs {
+  const bf16* ymask; // MASK kernels: the layer's ReLU output (B, npix, C_out); grad_output counts where it is > 0
   const bf16* gy;    // (B, npix, C_out) channels-last
   const bf16* x;     // (B, spix, C_in) channels-last
   const int* tab32;  // (npix, K): source pixel of every (pixel, tap), -1 = reads nothing
@@ -38,7 +39,10 @@ struct SmallCinArgs {
   int npix, spix, C_in, C_out, K;
 };
 
-template <int NT>  // n-tiles of 8 columns: K * C_in + 1 <= 8 NT
+// MASK: grad_output is the gradient behind a ReLU whose output is ymask - the activation's own
+// gradient (grad_output where ymask > 0, else 0) is applied to the rows as they are loaded, which
+// saves the separate pass that would write the masked tensor.
+template <int NT, bool MASK>  // n-tiles of 8 columns: K * C_in + 1 <= 8 NT
 __global__ void __launch_bounds__(32 * SCW_WARPS, 2) conv_wgrad_smallcin_kernel(const SmallCinArgs a) {
   __shared__ float s_acc[64][8 * NT + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -84,8 +88,9 @@ __global__ void __launch_bounds__(32 * SCW_WARPS, 2) conv_wgrad_smallcin_kernel(
         asm volatile("prefetch.global.L2 [%0];" ::"l"(a.gy + rn * a.C_out + co0 + (lane & 1) * 32));
     }
     const uint4* gyv = reinterpret_cast<const uint4*>(a.gy + (long)r0 * a.C_out + co0) + g;
+    const uint4* ymv = reinterpret_cast<const uint4*>(a.ymask + (long)r0 * a.C_out + co0) + g;
     const int vstride = a.C_out / 8;  // uint4 per row
-    uint4 v[4];
+    uint4 v[4], ym[MASK ? 4 : 1];
     int src[NT][4];
     bool on[4];
     int xrow0[4];
@@ -97,6 +102,7 @@ __global__ void __launch_bounds__(32 * SCW_WARPS, 2) conv_wgrad_smallcin_kernel(
       on[q] = r0 + j < rows;
       const int jc = on[q] ? j : 0;
       v[q] = __ldg(gyv + jc * vstride);
+      if (MASK) ym[q] = __ldg(ymv + jc * vstride);
       int p = p0 + jc, b = b0;
       if (p >= a.npix) { p -= a.npix; ++b; }  // (npix >= 16: at most one image boundary in a step)
       xrow0[q] = b * a.spix;
@@ -114,8 +120,16 @@ __global__ void __launch_bounds__(32 * SCW_WARPS, 2) conv_wgrad_smallcin_kernel(
         bv[nt][q] = !on[q] ? 0u : tap_n[nt] >= 0 ? (src[nt][q] >= 0 ? val : 0u) : (tap_n[nt] == -1 ? 0x3F80u : 0u);
       }
 #pragma unroll
-    for (int q = 0; q < 4; ++q)
+    for (int q = 0; q < 4; ++q) {
       if (!on[q]) v[q] = make_uint4(0u, 0u, 0u, 0u);
+      if (MASK) {  // 0xFFFF per bf16 of the output that is > 0
+        const __nv_bfloat162 z2 = __float2bfloat162_rn(0.f);
+        v[q].x &= __hgt2_mask(*reinterpret_cast<const __nv_bfloat162*>(&ym[q].x), z2);
+        v[q].y &= __hgt2_mask(*reinterpret_cast<const __nv_bfloat162*>(&ym[q].y), z2);
+        v[q].z &= __hgt2_mask(*reinterpret_cast<const __nv_bfloat162*>(&ym[q].z), z2);
+        v[q].w &= __hgt2_mask(*reinterpret_cast<const __nv_bfloat162*>(&ym[q].w), z2);
+      }
+    }
     p0 += adv_p;
     b0 += adv_b;
     if (p0 >= a.npix) { p0 -= a.npix; ++b0; }
@@ -167,9 +181,10 @@ static bool smallcin_wgrad_shape(const mc_desc* d) {
          (long)d->B * d->IH * d->IW * d->C_in < lim;
 }
 
-static int smallcin_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const int* tab32, void* gw,
-                                 void* gb, cudaStream_t st) {
+static int smallcin_wgrad_launch(const mc_desc* d, const void* gy, const void* ymask, const void* x,
+                                 const int* tab32, void* gw, void* gb, cudaStream_t st) {
   SmallCinArgs a;
+  a.ymask = (const bf16*)(ymask ? ymask : gy);
   a.gy = (const bf16*)gy; a.x = (const bf16*)x; a.tab32 = tab32;
   a.gw = (float*)gw; a.gb = (float*)gb;
   a.npix = d->OH * d->OW; a.spix = d->IH * d->IW;
@@ -181,11 +196,21 @@ static int smallcin_wgrad_launch(const mc_desc* d, const void* gy, const void* x
   const long need = (nsteps + SCW_WARPS - 1) / SCW_WARPS;
   if (gx > need) gx = need;
   const dim3 grid((unsigned)gx, (unsigned)(d->C_out / 64));
-  switch (nt) {
-    case 1: conv_wgrad_smallcin_kernel<1><<<grid, 32 * SCW_WARPS, 0, st>>>(a); break;
-    case 2: conv_wgrad_smallcin_kernel<2><<<grid, 32 * SCW_WARPS, 0, st>>>(a); break;
-    case 3: conv_wgrad_smallcin_kernel<3><<<grid, 32 * SCW_WARPS, 0, st>>>(a); break;
-    default: conv_wgrad_smallcin_kernel<4><<<grid, 32 * SCW_WARPS, 0, st>>>(a); break;
+  const int threads = 32 * SCW_WARPS;
+  if (ymask) {
+    switch (nt) {
+      case 1: conv_wgrad_smallcin_kernel<1, true><<<grid, threads, 0, st>>>(a); break;
+      case 2: conv_wgrad_smallcin_kernel<2, true><<<grid, threads, 0, st>>>(a); break;
+      case 3: conv_wgrad_smallcin_kernel<3, true><<<grid, threads, 0, st>>>(a); break;
+      default: conv_wgrad_smallcin_kernel<4, true><<<grid, threads, 0, st>>>(a); break;
+    }
+  } else {
+    switch (nt) {
+      case 1: conv_wgrad_smallcin_kernel<1, false><<<grid, threads, 0, st>>>(a); break;
+      case 2: conv_wgrad_smallcin_kernel<2, false><<<grid, threads, 0, st>>>(a); break;
+      case 3: conv_wgrad_smallcin_kernel<3, false><<<grid, threads, 0, st>>>(a); break;
+      default: conv_wgrad_smallcin_kernel<4, false><<<grid, threads, 0, st>>>(a); break;
+    }
   }
   MC_COUNT(1);
   MC_CHECK_LAUNCH();

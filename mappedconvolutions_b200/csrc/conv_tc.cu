@@ -2096,8 +2096,13 @@ static int launch_wgrad_n(const GemmArgs& a, const WgradPlan& p, bool pre, cudaS
 
 #include "conv_smallcin.cuh"
 
+// ymask != null: grad_output is masked by (ymask > 0) on the way in (only the kernel for very few
+// input channels can do that; MC_ERR_UNSUPPORTED otherwise)
 static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, const void* map,
-                             const void* tab, void* gw, void* gb, cudaStream_t st) {
+                             const void* tab, void* gw, void* gb, cudaStream_t st,
+                             const void* ymask = nullptr) {
+  if (ymask && !(tab && smallcin_wgrad_shape(d) && tapmap_compact(d, tab))) return MC_ERR_UNSUPPORTED;
+  if (!aligned16(ymask)) return MC_ERR_BAD_ARG;
   if (!aligned16(gy) || !aligned16(x) || !aligned16(map) || !aligned16(tab)) return MC_ERR_BAD_ARG;
   if ((long)d->B * d->IH * d->IW >= (1L << 30)) return MC_ERR_TOO_LARGE;
   GemmArgs a = {};
@@ -2128,7 +2133,7 @@ static int wgrad_launch_impl(const mc_desc* d, const void* gy, const void* x, co
     return MC_ERR_LAUNCH;
   // very few input channels and a nearest map with its compact table: one pass over grad_output
   if (tab && smallcin_wgrad_shape(d) && tapmap_compact(d, tab))
-    return smallcin_wgrad_launch(d, gy, x, tapmap_compact(d, tab), gw, gb, st);
+    return smallcin_wgrad_launch(d, gy, ymask, x, tapmap_compact(d, tab), gw, gb, st);
   return p.nout == 128 ? launch_wgrad_n<128>(a, p, tab != nullptr, st)
                        : launch_wgrad_n<64>(a, p, tab != nullptr, st);
 }
@@ -2142,6 +2147,11 @@ int conv_tc_wgrad_launch(const mc_desc* d, const void* gy, const void* x, const 
 int conv_tc_wgrad_tab_launch(const mc_desc* d, const void* gy, const void* x, const void* tab,
                              void* gw, void* gb, cudaStream_t st) {
   return wgrad_launch_impl(d, gy, x, nullptr, tab, gw, gb, st);
+}
+
+int conv_tc_wgrad_tab_relu_launch(const mc_desc* d, const void* gy, const void* y, const void* x,
+                                  const void* tab, void* gw, void* gb, cudaStream_t st) {
+  return wgrad_launch_impl(d, gy, x, nullptr, tab, gw, gb, st, y);
 }
 
 // ---- forward pass with library-owned scratch ---------------------------------------------------

@@ -407,7 +407,22 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
                                   const OptTensor& iw, const Tensor& input_in, const Tensor& weight,
                                   const Tensor& bias, int64_t K, int64_t interp,
                                   bool need_input_grad, bool nhwc = false,
-                                  bool need_weight_grad = true) {
+                                  bool need_weight_grad = true, const OptTensor& relu_output = c10::nullopt) {
+  // relu_output: the layer's output behind a fused ReLU; grad_output is then the gradient behind the
+  // activation.  Where the one kernel that can mask grad_output while it loads it does all the work
+  // (weight gradient only, very few input channels) it is handed over; otherwise it is masked here.
+  if (relu_output.has_value()) {
+    TORCH_CHECK(relu_output->sizes() == grad_output_in.sizes() &&
+                    relu_output->scalar_type() == grad_output_in.scalar_type(),
+                "relu_output must have grad_output's shape and dtype");
+    const bool fusable = !need_input_grad && need_weight_grad && !iw.has_value() &&
+                         input_in.scalar_type() == at::kBFloat16 && input_in.dim() == 4 &&
+                         layout_of(input_in) == MC_NHWC && layout_of(grad_output_in) == MC_NHWC &&
+                         layout_of(*relu_output) == MC_NHWC;
+    if (!fusable)
+      return conv_backward(at::threshold_backward(grad_output_in, *relu_output, 0), sample_map_in, iw, input_in,
+                           weight, bias, K, interp, need_input_grad, nhwc, need_weight_grad);
+  }
   const Tensor input = aligned16(input_in), sample_map = aligned16(sample_map_in);
   TORCH_CHECK(input.dim() == 4 && weight.dim() == 3 && sample_map.dim() >= 4,
               "input must be 4-D, weight 3-D, the map (OH, OW, K, ..)");
@@ -481,6 +496,17 @@ std::vector<Tensor> conv_backward(const Tensor& grad_output_in, const Tensor& sa
   Tensor tab = folded ? tap_map_weighted(d_map, f, sample_map, *iw)
                       : (iw.has_value() ? Tensor() : tap_map(d, sample_map));
   int rc = MC_ERR_UNSUPPORTED;
+  if (relu_output.has_value()) {  // (weight gradient only, see above)
+    const Tensor yr = aligned16(*relu_output);
+    if (tab.defined())
+      rc = mc_conv_wgrad_tap_relu(&d, grad_output.data_ptr(), yr.data_ptr(), input.data_ptr(), tab.data_ptr(),
+                                  gw.data_ptr(), gb.data_ptr(), cur_stream());
+    if (rc == MC_ERR_UNSUPPORTED)  // no kernel masks on the fly for this shape: mask first
+      return conv_backward(at::threshold_backward(grad_output, yr, 0), sample_map, iw, input, weight, bias, K,
+                           interp, false, nhwc, true);
+    check(rc);
+    return {gx, gw.to(weight.scalar_type()), gb.to(bias.scalar_type())};
+  }
   if (tab.defined())  // weight / bias gradient on the tensor cores from the prebuilt table
     rc = mc_conv_wgrad_tap(&d, grad_output.data_ptr(), input.data_ptr(), tab.data_ptr(),
                            gw.data_ptr(), gb.data_ptr(), cur_stream());
@@ -808,13 +834,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("kernel_size"), py::arg("interpolation"), py::arg("relu") = false);
   m.def("mapped_conv_backward",
         [](const Tensor& gy, const Tensor& map, const Tensor& x, const Tensor& w, const Tensor& b,
-           int64_t k, int64_t i, bool need_input_grad, bool need_weight_grad) {
+           int64_t k, int64_t i, bool need_input_grad, bool need_weight_grad,
+           const c10::optional<Tensor>& relu_output) {
           return conv_backward(gy, map, c10::nullopt, x, w, b, k, i, need_input_grad, false,
-                               need_weight_grad);
+                               need_weight_grad, relu_output);
         },
         py::arg("grad_output"), py::arg("sample_map"), py::arg("input"), py::arg("weight"),
         py::arg("bias"), py::arg("kernel_size"), py::arg("interpolation"),
-        py::arg("need_input_grad") = true, py::arg("need_weight_grad") = true);
+        py::arg("need_input_grad") = true, py::arg("need_weight_grad") = true,
+        py::arg("relu_output") = py::none());
   // include/nn/layers/weighted_mapped_convolution_layer.h:65-93, :95-150
   m.def("weighted_mapped_conv_forward",
         [](const Tensor& x, const Tensor& map, const Tensor& iw, const Tensor& w, const Tensor& b,

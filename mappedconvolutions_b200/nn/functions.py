@@ -36,14 +36,17 @@ class MappedConvFn(Function):
     @staticmethod
     def backward(ctx, gy):
         x, weight, bias, sample_map, iw, y = ctx.saved_tensors
-        if ctx.relu:  # gradient of the activation, from its own output: y > 0 <=> pre-activation > 0
-            gy = torch.ops.aten.threshold_backward(gy, y, 0)  # one pass: gy where y > 0, else 0
+        # gradient of the activation, from its own output: y > 0 <=> pre-activation > 0
         if iw is not None:
+            if ctx.relu:
+                gy = torch.ops.aten.threshold_backward(gy, y, 0)  # one pass: gy where y > 0, else 0
             gx, gw, gb = ops.weighted_mapped_conv_backward(gy, sample_map, iw, x, weight, bias,
                                                            ctx.k, ctx.interp)
         else:
+            # (the op masks grad_output itself - inside the weight-gradient kernel where it can)
             gx, gw, gb = ops.mapped_conv_backward(gy, sample_map, x, weight, bias, ctx.k,
-                                                  ctx.interp, ctx.needs_input_grad[0])
+                                                  ctx.interp, need_input_grad=ctx.needs_input_grad[0],
+                                                  relu_output=y if ctx.relu else None)
         return gx, gw, gb, None, None, None, None, None
 
 

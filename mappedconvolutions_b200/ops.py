@@ -325,10 +325,13 @@ def mapped_conv_forward(input, sample_map, weight, bias, kernel_size, interpolat
 
 
 def mapped_conv_backward(grad_output, sample_map, input, weight, bias, kernel_size, interpolation,
-                         need_input_grad=True):
+                         need_input_grad=True, need_weight_grad=True, relu_output=None):
     """MappedConvBackward, include/nn/layers/mapped_convolution_layer.h:90-135.
     Returns [grad_input, grad_weight, grad_bias].  need_input_grad=False (not in the reference's
-    signature) skips the input gradient and returns None in its place."""
+    signature) skips the input gradient and returns None in its place.  relu_output: the layer's
+    output behind a fused ReLU - grad_output is then masked by relu_output > 0 first."""
+    if relu_output is not None:
+        grad_output = torch.ops.aten.threshold_backward(grad_output, relu_output, 0)
     return _conv_backward(grad_output, sample_map, None, input, weight, bias, kernel_size,
                           interpolation, need_input_grad)
 

@@ -340,3 +340,28 @@ def test_weight_gradient_of_layers_with_very_few_input_channels(ext, Cin, K, Cou
     want = oracle.mapped_conv_backward(cpu(gy), m.cpu(), cpu(x), cpu(w), cpu(b), K, 0)
     for got, ref, what in zip(gr, want, ("grad_input", "grad_weight", "grad_bias")):
         H_mod.assert_close(cpu(got), ref, H_mod.TOL[torch.bfloat16], what)
+
+
+def test_relu_gradient_inside_the_first_layer_weight_gradient(ext):
+    """mapped_conv_backward(relu_output=y): grad_output counts where y > 0.  For a first layer (no input
+    gradient, very few input channels) the weight-gradient kernel masks the rows as it loads them;
+    everywhere else the op masks first.  Both must equal masking by hand."""
+    g = torch.Generator().manual_seed(5)
+    c = lambda t: _cl(t.to(torch.bfloat16).cuda())
+    for Cin, Cout, K, n, need_gx in ((3, 64, 7, 1000, False), (3, 64, 7, 1000, True), (64, 64, 7, 300, False)):
+        x, gy = c(torch.randn(3, Cin, 1, n, generator=g)), c(torch.randn(3, Cout, 1, n, generator=g))
+        w = torch.randn(Cout, Cin, K, generator=g).to(torch.bfloat16).cuda()
+        b = torch.randn(Cout, generator=g).to(torch.bfloat16).cuda()
+        m = torch.zeros(1, n, K, 2)
+        m[..., 0] = torch.randint(0, n, (1, n, K), generator=g).float()
+        m = m.cuda()
+        y = ext.mapped_conv_forward(x, m, w, b, K, 0, relu=True)
+        assert 0.2 < (y > 0).float().mean().item() < 0.8
+        got = ext.mapped_conv_backward(gy, m, x, w, b, K, 0, need_input_grad=need_gx, relu_output=y)
+        want = ext.mapped_conv_backward(torch.ops.aten.threshold_backward(gy, y, 0), m, x, w, b, K, 0,
+                                        need_input_grad=need_gx)
+        assert (got[0] is None) == (not need_gx)
+        for a, r, what in zip(got, want, ("grad_input", "grad_weight", "grad_bias")):
+            if a is not None:
+                H_mod.assert_close(a.float(), r.float(), H_mod.TOL[torch.bfloat16], what)
+    assert ext.device_status() == 0
