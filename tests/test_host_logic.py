@@ -162,3 +162,36 @@ def test_bindings_refuse_mismatched_parameters(which):
         o.mapped_max_unpool(g, torch.zeros(2, 4, 5, 6, dtype=torch.int32), m, 8, 8, 3, 0)
     with pytest.raises(RuntimeError, match="idx_mask shape"):
         o.mapped_max_unpool(g, torch.zeros(2, 4, 5, 5, dtype=torch.int64), m, 8, 8, 3, 0)
+
+
+def test_weighted_maps_fold_only_when_a_tap_fits_one_record():
+    """mc_weighted_plan_desc is pure host logic: P points x corners per point (1 nearest, 4 bilinear /
+    bispherical) <= 4 folds into the descriptor of a plain bilinear map; everything else is refused."""
+    import ctypes
+    from mappedconvolutions_b200 import _lib
+    L = _lib.lib()
+    mk = lambda P, interp, dtype=_lib.MC_BF16: _lib.McDesc(2, 64, 128, 1, 300, 1, 300, 7, P, interp, dtype, _lib.MC_NHWC)
+    for P, interp, ok in ((3, 0, True), (4, 0, True), (5, 0, False), (1, 1, True), (1, 2, True), (2, 1, False),
+                          (3, 1, False), (0, 0, False)):
+        d, f = mk(P, interp), _lib.McDesc()
+        rc = L.mc_weighted_plan_desc(ctypes.byref(d), ctypes.byref(f))
+        assert (rc == 0) == ok, (P, interp, rc)
+        if ok:
+            assert (f.P, f.interp, f.C_in, f.C_out, f.K, f.OW) == (0, 1, 64, 128, 7, 300)
+            assert L.mc_tapmap_bytes(ctypes.byref(f)) >= 300 * 7 * 32
+    d, f = mk(3, 0, _lib.MC_F64), _lib.McDesc()
+    assert L.mc_weighted_plan_desc(ctypes.byref(d), ctypes.byref(f)) == -2      # MC_ERR_UNSUPPORTED
+    assert L.mc_weighted_plan_desc(ctypes.byref(mk(3, 0)), None) == -1          # MC_ERR_BAD_ARG
+
+
+def test_utility_entry_points_check_their_arguments_before_touching_the_device():
+    from mappedconvolutions_b200 import _lib
+    L = _lib.lib()
+    assert L.mc_voting_resample_workspace(2, 3, 4, 5, 6) == 2 * 3 * 4 * 5 * 6 * 4
+    assert L.mc_voting_resample_workspace(2, 3, 0, 5, 6) == 0
+    assert L.mc_cube2rect(_lib.MC_F32, None, 3, 8, 16, 32, 0, None, None) == -1
+    assert L.mc_cube2rect(_lib.MC_F32, 16, 3, 8, 16, 32, 2, 16, None) == -1       # unknown interpolation
+    assert L.mc_cube2rect(_lib.MC_BF16, 16, 3, 8, 16, 32, 0, 16, None) == -2      # float32 / float64 only
+    assert L.mc_voting_resample(None, None, 1, 1, 4, 4, 2, 2, 3, None, 0, None, None) == -1
+    assert L.mc_voting_resample(16, 16, 1, 1, 4, 4, 2, 2, 3, None, 0, 16, None) == -3   # MC_ERR_WORKSPACE
+    assert L.mc_voting_resample(16, 24, 1, 1, 4, 4, 2, 2, 3, 16, 1 << 20, 16, None) == -1  # map not 16-byte aligned
