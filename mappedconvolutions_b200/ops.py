@@ -332,8 +332,9 @@ def mapped_conv_backward(grad_output, sample_map, input, weight, bias, kernel_si
     output behind a fused ReLU - grad_output is then masked by relu_output > 0 first."""
     if relu_output is not None:
         grad_output = torch.ops.aten.threshold_backward(grad_output, relu_output, 0)
-    return _conv_backward(grad_output, sample_map, None, input, weight, bias, kernel_size,
-                          interpolation, need_input_grad)
+    g = _conv_backward(grad_output, sample_map, None, input, weight, bias, kernel_size,
+                       interpolation, need_input_grad)
+    return g if need_weight_grad else [g[0], None, None]
 
 
 def weighted_mapped_conv_forward(input, sample_map, interp_weights, weight, bias, kernel_size,
