@@ -398,7 +398,10 @@ Tensor conv_forward(const Tensor& input_in, const Tensor& sample_map_in, const O
 // layer has more output than input channels and the product z fits comfortably.
 static bool contract_first(const mc_desc& d) {
   const int lanes = d.C_in / 8;
-  return d.dtype == MC_BF16 && d.layout == MC_NHWC && d.P == 0 && d.C_out > d.C_in && d.C_in % 8 == 0 &&
+  // (also for square wide layers with a nearest map, where the gather inside the GEMM kernel runs at
+  // half the forward's rate: 256 -> 256 channels 1.30 ms as a gather, 1.0 ms as GEMM + gather-sum)
+  const bool wider = d.C_out > d.C_in || (d.C_out == d.C_in && d.C_in >= 128 && d.interp != 1 && d.interp != 2);
+  return d.dtype == MC_BF16 && d.layout == MC_NHWC && d.P == 0 && wider && d.C_in % 8 == 0 &&
          (lanes & (lanes - 1)) == 0 &&
          (int64_t)d.B * d.OH * d.OW * d.K * d.C_in * 2 <= ((int64_t)8 << 30);
 }

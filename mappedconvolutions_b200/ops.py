@@ -250,7 +250,9 @@ def _contract_first(d):
     """Input gradient as GEMM + gather-sum (mc_conv_dgrad_tapsum) instead of gather-in-the-GEMM: when
     the layer has more output than input channels and the product z fits comfortably."""
     lanes = d.C_in // 8
-    return (d.dtype == _lib.MC_BF16 and d.layout == _lib.MC_NHWC and d.P == 0 and d.C_out > d.C_in
+    # (also square wide layers with a nearest map, where the gather inside the GEMM kernel is slow)
+    wider = d.C_out > d.C_in or (d.C_out == d.C_in and d.C_in >= 128 and d.interp not in (1, 2))
+    return (d.dtype == _lib.MC_BF16 and d.layout == _lib.MC_NHWC and d.P == 0 and wider
             and d.C_in % 8 == 0 and lanes & (lanes - 1) == 0
             and d.B * d.OH * d.OW * d.K * d.C_in * 2 <= 8 << 30)
 
